@@ -1,0 +1,135 @@
+// C ABI of libnanoflow_kernels.so. Every entry point takes raw device pointers and a CUDA stream,
+// launches asynchronously on that stream, allocates nothing, and returns 0 on success or one of
+// the NF_ERR_* codes (common.cuh) when an argument is rejected before any launch.
+// bf16 tensors are passed as void*; int tensors are int32 unless noted.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ------------------------------------------------------------------------------------------------
+// GEMM (gemm.cu)
+// ------------------------------------------------------------------------------------------------
+enum { NFK_EPI_LINEAR = 0, NFK_EPI_SWIGLU = 1 };
+
+typedef struct nfk_gemm_params {
+  const void* A;    // [M,K] bf16, row-major, leading dimension lda
+  const void* B;    // [N,K] bf16, row-major (nn.Linear weight layout); gate weight for SwiGLU
+  const void* B2;   // SwiGLU only: up weight [N,K]
+  void* D;          // [M,N] bf16
+  const void* C;    // optional residual [M,N]: D = A*B^T + bias + beta*C
+  const void* bias; // optional [N] bf16
+  long long lda, ldb, ldd, ldc;
+  float beta;
+  int M, N, K;
+  int epilogue;     // NFK_EPI_*
+  int tile_n;       // 0 = choose; 64 / 128 / 256
+  int num_ctas;     // CTA budget of the persistent grid; 0 = one per SM
+  unsigned int* status;  // optional device word: first non-zero NF_ST_* code wins
+} nfk_gemm_params;
+
+int nfk_gemm_bf16(const nfk_gemm_params* p, cudaStream_t stream);
+
+// ------------------------------------------------------------------------------------------------
+// Elementwise / normalisation / gather kernels (elementwise.cu)
+// ------------------------------------------------------------------------------------------------
+// out[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps) * w[:]
+int nfk_rmsnorm(void* out, const void* x, const void* w, int rows, int cols, float eps,
+                cudaStream_t stream);
+// resid[r,:] += x[r,:]; out[r,:] = rmsnorm(resid[r,:]) (resid updated in place)
+int nfk_add_rmsnorm(void* out, void* resid, const void* x, const void* w, int rows, int cols,
+                    float eps, cudaStream_t stream);
+// Token ids for this iteration, then the embedding rows:
+//   id[t] = feedback_src[t] >= 0 ? prev_tokens[feedback_src[t]] : host_ids[t]
+//   out[t,:] = table[id[t],:]      (ids outside [0,vocab) are clamped and flagged in status)
+// feedback_src / prev_tokens may be null (ids come from host_ids only). ids_out may be null.
+int nfk_embedding(void* out, const void* table, const int* host_ids, const int* feedback_src,
+                  const int* prev_tokens, int* ids_out, int n_tokens, int hidden, int vocab,
+                  unsigned int* status, cudaStream_t stream);
+// out[i,:] = in[rows_idx[i],:]
+int nfk_gather_rows(void* out, const void* in, const int* rows_idx, int n, int cols, long long ld_in,
+                    unsigned int* status, int in_rows, cudaStream_t stream);
+// out = silu(gate) * up, elementwise over n elements (n % 8 == 0)
+int nfk_silu_mul(void* out, const void* gate, const void* up, long long n, cudaStream_t stream);
+// out[r, 0:cols] = in[r, col0 : col0+cols]   (column-block extract / insert with leading dims)
+int nfk_copy_cols(void* out, long long ld_out, const void* in, long long ld_in, int rows, int cols,
+                  cudaStream_t stream);
+// 2-D transpose out[c,r] = in[r,c]
+int nfk_transpose(void* out, const void* in, int rows, int cols, cudaStream_t stream);
+// Greedy sampler: per row arg-max over `cols` logits. idx_out[r] = col_offset + argmax,
+// val_out[r] (optional, fp32) = max. Ties resolve to the lowest index.
+int nfk_argmax(int* idx_out, float* val_out, const void* logits, int rows, int cols,
+               long long ld, int col_offset, cudaStream_t stream);
+// Combine per-shard (val, idx) candidates: cand_val/cand_idx are [shards, rows].
+int nfk_argmax_combine(int* idx_out, const float* cand_val, const int* cand_idx, int shards,
+                       int rows, cudaStream_t stream);
+// Busy-wait for `micros` microseconds (bounded at 1 s); stands in for a collective in ablations.
+int nfk_sleep(int micros, cudaStream_t stream);
+// Device progress counters: add / clear / bounded wait until *flag >= target.
+int nfk_flag_add(unsigned int* flag, unsigned int v, cudaStream_t stream);
+int nfk_flag_clear(unsigned int* flag, cudaStream_t stream);
+int nfk_flag_wait(const unsigned int* flag, unsigned int target, int timeout_us,
+                  unsigned int* status, cudaStream_t stream);
+
+// ------------------------------------------------------------------------------------------------
+// RoPE + paged-KV append (rope_append.cu)
+// ------------------------------------------------------------------------------------------------
+// Paged KV pool of one layer: [num_pages][2 (K,V)][kv_heads][page_size][head_dim] bf16.
+typedef struct nfk_rope_append_params {
+  const void* qkv;       // [T, ld_qkv] bf16: q at q_off, k at k_off, v at v_off (elements)
+  long long ld_qkv;
+  int q_off, k_off, v_off;
+  void* q_out;           // [T, q_heads*head_dim] rotated queries
+  void* kv_pool;         // this layer's pool
+  const float* inv_freq; // [head_dim/2] rotary inverse frequencies (any scaling baked in)
+  const int* positions;  // [T] absolute position of each token in its sequence
+  const int* token_req;  // [T] request index of each token
+  const int* kv_indptr;  // [B+1]
+  const int* kv_indices; // page ids
+  int T, q_heads, kv_heads, head_dim, page_size, num_pages;
+  unsigned int* status;
+} nfk_rope_append_params;
+int nfk_rope_append(const nfk_rope_append_params* p, cudaStream_t stream);
+
+// ------------------------------------------------------------------------------------------------
+// Attention over the paged KV pool (attention.cu)
+// ------------------------------------------------------------------------------------------------
+typedef struct nfk_attn_params {
+  const void* q;           // [T, q_heads*head_dim] bf16 (rotated)
+  void* out;               // [T, q_heads*head_dim] bf16
+  const void* kv_pool;     // layer pool, layout above
+  const int* qo_indptr;    // [B+1] token range of every request in the dense batch
+  const int* kv_indptr;    // [B+1]
+  const int* kv_indices;
+  const int* kv_last_page_len;  // [B]
+  int q_heads, kv_heads, head_dim, page_size, num_pages;
+  float sm_scale;
+  int num_ctas;            // CTA budget (persistent grid); 0 = one per SM
+  // decode: requests [req_begin, req_begin+req_count) each own one query token (qo_indptr[b])
+  int req_begin, req_count;
+  int chunk_pages;         // split-KV chunk length in pages; 0 = no split
+  float* workspace;        // split-KV partials: [req_count*q_heads*max_chunks*(head_dim+2)] fp32
+  int max_chunks;
+  // prefill: work items (req, first token (global index), token count)
+  const int* items;        // [num_items,3]
+  int num_items;
+  unsigned int* status;
+} nfk_attn_params;
+int nfk_attn_decode(const nfk_attn_params* p, cudaStream_t stream);
+int nfk_attn_prefill(const nfk_attn_params* p, cudaStream_t stream);
+
+// ------------------------------------------------------------------------------------------------
+// KV offload (kv_offload.cu): gather / scatter whole pages between the pool and a staging buffer
+// ------------------------------------------------------------------------------------------------
+// page_bytes = 2*kv_heads*page_size*head_dim*2. direction 0: staging[i] = pool[page_ids[i]];
+// direction 1: pool[page_ids[i]] = staging[i].
+int nfk_kv_move_pages(void* pool, void* staging, const int* page_ids, int n_pages,
+                      long long page_bytes, int num_pages, int direction, int num_ctas,
+                      unsigned int* status, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,169 @@
+"""Per-kernel micro-benchmarks: ``python -m nanoflow_b200.ops.microbench [gemm|swiglu|decode|prefill|norm|all]``.
+
+Each case is timed with CUDA events on the launching stream after warm-up, with an L2 flush (a
+write larger than the 126 MB L2) between timed launches, and reported against the measured peaks
+in ``MEASURED_PEAKS.json`` at the repository root (copy bandwidth, cuBLAS bf16 throughput) when that
+file exists. This is the counterpart of the reference's NVBench drivers
+(gemv/src/bench_batch_decode.cu:222-249, gemv/src/bench_batch_prefill.cu:142-151) and of
+``CutlassGEMMWrapper::profile`` (pipeline/include/cutlassGemmWrapperImpl.cuh:378-418).
+"""
+from __future__ import annotations
+
+import json
+import sys
+from pathlib import Path
+
+import torch
+
+from nanoflow_b200 import ops
+
+_FLUSH = None
+
+
+def peaks():
+    f = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if f.exists():
+        d = json.loads(f.read_text())
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def flush_l2():
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _FLUSH.zero_()
+
+
+def time_ms(fn, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2], ts[0]
+
+
+def bench_gemm(shapes=None, swiglu=False, tile_ns=(0,), num_ctas=0):
+    _, tf_peak, how = peaks()
+    shapes = shapes or [
+        # Llama-2-70B TP8 per-GPU shapes (M = dense batch 2048 and nano-batches)
+        (2048, 1280, 8192), (2048, 8192, 1024), (2048, 8192, 3584), (640, 1280, 8192),
+        (1408, 8192, 3584), (4096, 8192, 3584),
+        # TP1 shapes
+        (2048, 10240, 8192), (2048, 8192, 8192), (2048, 8192, 28672), (256, 8192, 8192),
+        # Llama-3-8B TP1
+        (2048, 6144, 4096), (2048, 4096, 4096), (2048, 4096, 14336), (8192, 8192, 8192),
+    ]
+    rows = []
+    for (M, N, K) in shapes:
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
+        w2 = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 if swiglu else None
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        for tn in tile_ns:
+            if swiglu:
+                fn = lambda: ops.gemm_swiglu(a, w, w2, out=out, tile_n=tn, num_ctas=num_ctas)
+                flops = 4.0 * M * N * K
+            else:
+                fn = lambda: ops.gemm(a, w, out=out, tile_n=tn, num_ctas=num_ctas)
+                flops = 2.0 * M * N * K
+            med, best = time_ms(fn)
+            ref_fn = (lambda: torch.matmul(a, w.t(), out=out))
+            rmed, _ = time_ms(ref_fn)
+            rflops = 2.0 * M * N * K
+            rows.append(dict(op="swiglu" if swiglu else "gemm", M=M, N=N, K=K, tile_n=tn,
+                             ms=round(med, 4), tflops=round(flops / med / 1e9, 1),
+                             frac_of_peak=round(flops / med / 1e9 / tf_peak, 3), peak=how,
+                             cublas_ms=round(rmed, 4), cublas_tflops=round(rflops / rmed / 1e9, 1)))
+            print(json.dumps(rows[-1]), flush=True)
+    return rows
+
+
+def _paged(batch, ctx, kv_heads, hd, qo_len=1):
+    page = 16
+    np_ = (ctx + page - 1) // page
+    total = batch * np_
+    pool = torch.randn(total, 2, kv_heads, page, hd, device="cuda", dtype=torch.bfloat16)
+    kv_indptr = torch.arange(0, batch + 1, dtype=torch.int32, device="cuda") * np_
+    kv_indices = torch.randperm(total, device="cuda").int()
+    last = torch.full((batch,), (ctx - 1) % page + 1, dtype=torch.int32, device="cuda")
+    qo = torch.arange(0, batch + 1, dtype=torch.int32, device="cuda") * qo_len
+    return pool, qo, kv_indptr, kv_indices, last
+
+
+def bench_decode():
+    bw_peak, _, how = peaks()
+    for (batch, ctx, kv_heads, group, ctas) in [(683, 1280, 1, 8, 0), (683, 1280, 1, 8, 64), (683, 1280, 1, 8, 32),
+                                                 (256, 1280, 8, 8, 0), (1024, 1280, 8, 4, 0), (64, 4096, 8, 8, 0)]:
+        hd = 128
+        q_heads = kv_heads * group
+        pool, qo, kvp, kvi, last = _paged(batch, ctx, kv_heads, hd)
+        q = torch.randn(batch, q_heads * hd, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        fn = lambda: ops.attn_decode(q, out, pool, qo, kvp, kvi, last, q_heads=q_heads, req_begin=0,
+                                     req_count=batch, num_ctas=ctas)
+        med, best = time_ms(fn)
+        nbytes = batch * ctx * kv_heads * hd * 2 * 2 + 2 * q.numel() * 2
+        print(json.dumps(dict(op="attn_decode", batch=batch, ctx=ctx, kv_heads=kv_heads, group=group,
+                              num_ctas=ctas, ms=round(med, 4), gbs=round(nbytes / med / 1e6, 1),
+                              frac_of_peak=round(nbytes / med / 1e6 / bw_peak, 3), peak=how)), flush=True)
+
+
+def bench_prefill():
+    _, tf_peak, how = peaks()
+    for (batch, ctx, kv_heads, group) in [(2, 1024, 1, 8), (2, 1024, 8, 8), (8, 1024, 8, 4), (1, 4096, 8, 8)]:
+        hd = 128
+        q_heads = kv_heads * group
+        pool, qo, kvp, kvi, last = _paged(batch, ctx, kv_heads, hd, qo_len=ctx)
+        q = torch.randn(batch * ctx, q_heads * hd, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        tq = 128 // group
+        items = torch.tensor([[b, b * ctx + t, min(tq, ctx - t)] for b in range(batch)
+                              for t in range(0, ctx, tq)], dtype=torch.int32, device="cuda")
+        fn = lambda: ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, items, q_heads=q_heads)
+        med, best = time_ms(fn)
+        flops = 4.0 * batch * q_heads * hd * ctx * ctx / 2
+        print(json.dumps(dict(op="attn_prefill", batch=batch, ctx=ctx, kv_heads=kv_heads, group=group,
+                              ms=round(med, 4), tflops=round(flops / med / 1e9, 1),
+                              frac_of_peak=round(flops / med / 1e9 / tf_peak, 3), peak=how)), flush=True)
+
+
+def bench_norm():
+    bw_peak, _, how = peaks()
+    for rows, cols in [(2048, 8192), (16384, 8192), (2048, 4096)]:
+        x = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(cols, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty_like(x)
+        med, _ = time_ms(lambda: ops.rmsnorm(x, w, 1e-5, out=out))
+        nbytes = 2 * x.numel() * 2
+        print(json.dumps(dict(op="rmsnorm", rows=rows, cols=cols, ms=round(med, 4),
+                              gbs=round(nbytes / med / 1e6, 1),
+                              frac_of_peak=round(nbytes / med / 1e6 / bw_peak, 3), peak=how)), flush=True)
+
+
+def main(argv):
+    what = argv[1] if len(argv) > 1 else "all"
+    if what in ("gemm", "all"):
+        bench_gemm()
+    if what in ("swiglu", "all"):
+        bench_gemm(shapes=[(2048, 3584, 8192), (640, 3584, 8192), (2048, 28672, 8192), (2048, 14336, 4096)],
+                   swiglu=True)
+    if what in ("decode", "all"):
+        bench_decode()
+    if what in ("prefill", "all"):
+        bench_prefill()
+    if what in ("norm", "all"):
+        bench_norm()
+
+
+if __name__ == "__main__":
+    main(sys.argv)

@@ -1,0 +1,335 @@
+"""Numerics of every CUDA kernel against the PyTorch fp32 restatement of the same op.
+
+Sweeps follow the reference's kernel tests (gemv/src/test_batch_decode.cu:190-217 batch / head /
+head_dim / sm_blk sweeps; gemv/src/test_batch_prefill.cu:467-554 short and long contexts;
+cutlassGemmWrapperImpl.cuh:333-372 GEMM self-check) with tighter tolerances.
+"""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from nanoflow_b200 import ops
+from nanoflow_b200.ops import reference as ref
+
+
+def _close(got, want, atol, rtol, frac=1.0):
+    got, want = got.float(), want.float()
+    assert not torch.isnan(got).any(), "NaN in kernel output"
+    ok = (got - want).abs() <= atol + rtol * want.abs()
+    assert ok.float().mean().item() >= frac, (
+        f"{(~ok).sum().item()} / {ok.numel()} mismatches, max err {(got - want).abs().max().item()}")
+
+
+@pytest.fixture(autouse=True)
+def _seed():
+    torch.manual_seed(0)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (256, 512, 1024), (77, 264, 200),
+                                   (1, 128, 128), (640, 1280, 8192), (1408, 1024, 1024),
+                                   (300, 8192, 3584)])
+@pytest.mark.parametrize("tile_n", [0, 64, 128, 256])
+def test_gemm_plain(M, N, K, tile_n):
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    st = ops.new_status()
+    out = ops.gemm(a, w, tile_n=tile_n, status=st)
+    ops.check_status(st, "gemm")
+    _close(out, ref.gemm(a, w), atol=2e-2 * math.sqrt(K / 64), rtol=2e-2)
+
+
+@pytest.mark.parametrize("num_ctas", [1, 7, 60, 148])
+def test_gemm_cta_budget_residual_bias(num_ctas):
+    M, N, K = 520, 1032, 328
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    st = ops.new_status()
+    out = ops.gemm(a, w, residual=res, beta=0.125, bias=bias, num_ctas=num_ctas, status=st)
+    ops.check_status(st, "gemm")
+    _close(out, ref.gemm(a, w, res, 0.125, bias), atol=5e-2, rtol=2e-2)
+
+
+def test_gemm_strided_views_and_inplace_residual():
+    M, N, K = 200, 512, 256
+    big_a = torch.randn(M, 2 * K, device="cuda", dtype=torch.bfloat16)
+    a = big_a[:, K:]
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    big_out = torch.randn(M, 2 * N, device="cuda", dtype=torch.bfloat16)
+    want = ref.gemm(a, w, big_out[:, :N], 1.0)
+    ops.gemm(a, w, out=big_out[:, :N], residual=big_out[:, :N], beta=1.0)
+    _close(big_out[:, :N], want, atol=5e-2, rtol=2e-2)
+
+
+def test_gemm_empty_and_bad_args():
+    a = torch.randn(0, 64, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(128, 64, device="cuda", dtype=torch.bfloat16)
+    assert ops.gemm(a, w).shape == (0, 128)
+    with pytest.raises(RuntimeError):
+        ops.gemm(torch.randn(8, 60, device="cuda", dtype=torch.bfloat16),
+                 torch.randn(128, 60, device="cuda", dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("M,F,K", [(128, 128, 64), (300, 3584, 1024), (1408, 1792, 4096), (17, 264, 136)])
+@pytest.mark.parametrize("tile_n", [0, 128])
+def test_gemm_swiglu(M, F, K, tile_n):
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    wg = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    wu = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    st = ops.new_status()
+    out = ops.gemm_swiglu(a, wg, wu, tile_n=tile_n, status=st)
+    ops.check_status(st, "gemm_swiglu")
+    _close(out, ref.gemm_swiglu(a, wg, wu), atol=3e-2 * math.sqrt(K / 64), rtol=3e-2)
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 256), (37, 4096), (640, 8192), (5, 1032)])
+def test_rmsnorm(rows, cols):
+    x = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(cols, device="cuda", dtype=torch.bfloat16)
+    _close(ops.rmsnorm(x, w, 1e-5), ref.rmsnorm(x, w, 1e-5), atol=2e-2, rtol=2e-2)
+    resid = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
+    r0 = resid.clone()
+    out = ops.add_rmsnorm(resid, x, w, 1e-5)
+    newres = (r0.float() + x.float()).bfloat16()
+    _close(resid, newres, atol=1e-2, rtol=1e-2)
+    _close(out, ref.rmsnorm(newres, w, 1e-5), atol=2e-2, rtol=2e-2)
+
+
+def test_embedding_feedback_and_gather():
+    vocab, hidden, n = 1000, 512, 50
+    table = torch.randn(vocab, hidden, device="cuda", dtype=torch.bfloat16)
+    host_ids = torch.randint(0, vocab, (n,), device="cuda", dtype=torch.int32)
+    prev = torch.randint(0, vocab, (20,), device="cuda", dtype=torch.int32)
+    src = torch.full((n,), -1, device="cuda", dtype=torch.int32)
+    src[:15] = torch.randperm(20, device="cuda")[:15].int()
+    ids_out = torch.empty(n, device="cuda", dtype=torch.int32)
+    st = ops.new_status()
+    out = ops.embedding(table, host_ids, feedback_src=src, prev_tokens=prev, ids_out=ids_out, status=st)
+    want_ids = torch.where(src >= 0, prev[src.clamp(min=0).long()], host_ids)
+    assert torch.equal(ids_out, want_ids)
+    assert torch.equal(out, table[want_ids.long()])
+    ops.check_status(st)
+    # out-of-range id is clamped and reported, never dereferenced
+    bad = host_ids.clone(); bad[3] = vocab + 5
+    ops.embedding(table, bad, status=st)
+    with pytest.raises(RuntimeError):
+        ops.check_status(st)
+    idx = torch.tensor([4, 0, 49, 7], device="cuda", dtype=torch.int32)
+    assert torch.equal(ops.gather_rows(out, idx), out[idx.long()])
+
+
+def test_small_elementwise():
+    g = torch.randn(64, 1024, device="cuda", dtype=torch.bfloat16)
+    u = torch.randn(64, 1024, device="cuda", dtype=torch.bfloat16)
+    _close(ops.silu_mul(g, u), ref.silu_mul(g, u), atol=2e-2, rtol=2e-2)
+    assert torch.equal(ops.transpose(g), g.t().contiguous())
+    dst = torch.zeros(64, 256, device="cuda", dtype=torch.bfloat16)
+    ops.copy_cols(dst, g[:, 512:768])
+    assert torch.equal(dst, g[:, 512:768])
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 32000), (37, 128256), (300, 1000), (8, 152064 // 8)])
+def test_argmax(rows, cols):
+    logits = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
+    val = torch.empty(rows, device="cuda", dtype=torch.float32)
+    idx = ops.argmax(logits, col_offset=100, val_out=val)
+    # bf16 ties: the kernel returns the lowest index of the maximum
+    mx = logits.float().max(dim=-1).values
+    first = (logits.float() == mx[:, None]).int().argmax(dim=-1).int()
+    assert torch.equal(idx, first + 100)
+    assert torch.equal(val, mx)
+    # sharded combine
+    shards = 4
+    per = cols // shards // 8 * 8
+    cv = torch.empty(shards, rows, device="cuda", dtype=torch.float32)
+    ci = torch.empty(shards, rows, device="cuda", dtype=torch.int32)
+    for s in range(shards):
+        ops.argmax(logits[:, s * per:(s + 1) * per], col_offset=s * per, idx_out=ci[s], val_out=cv[s])
+    full = ops.argmax(logits[:, :shards * per])
+    assert torch.equal(ops.argmax_combine(cv, ci), full)
+
+
+def test_flags_and_sleep():
+    flag = torch.zeros(1, device="cuda", dtype=torch.int32)
+    st = ops.new_status()
+    ops.flag_add(flag, 3)
+    ops.flag_wait(flag, 3, 1000, st)
+    ops.check_status(st)
+    ops.flag_clear(flag)
+    # a wait nobody satisfies runs out after its limit and reports, leaving the context usable
+    ops.flag_wait(flag, 1, 2000, st)
+    with pytest.raises(RuntimeError):
+        ops.check_status(st)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(); ops.sleep_us(2000); e1.record(); torch.cuda.synchronize()
+    assert 1.5 <= e0.elapsed_time(e1) <= 50
+
+
+def _make_paged(batch_lens, qo_lens, kv_heads, hd, page=16, extra_pages=5, shuffle=True):
+    """Random paged pool + metadata for requests with given kv lengths (after append)."""
+    npages = [(l + page - 1) // page for l in batch_lens]
+    total = sum(npages) + extra_pages
+    perm = torch.randperm(total) if shuffle else torch.arange(total)
+    kv_indptr = [0]
+    for n in npages:
+        kv_indptr.append(kv_indptr[-1] + n)
+    kv_indices = perm[:kv_indptr[-1]].int()
+    last = [(l - 1) % page + 1 for l in batch_lens]
+    qo_indptr = [0]
+    for n in qo_lens:
+        qo_indptr.append(qo_indptr[-1] + n)
+    pool = torch.randn(total, 2, kv_heads, page, hd, device="cuda", dtype=torch.bfloat16)
+    dev = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    return pool, dev(qo_indptr), dev(kv_indptr), kv_indices.cuda(), dev(last)
+
+
+@pytest.mark.parametrize("batch", [1, 7, 37, 61])
+@pytest.mark.parametrize("kv_heads,group,hd", [(8, 8, 128), (1, 8, 128), (4, 4, 128), (2, 1, 128), (2, 2, 64)])
+@pytest.mark.parametrize("num_ctas", [0, 7, 30])
+def test_attn_decode(batch, kv_heads, group, hd, num_ctas):
+    q_heads = kv_heads * group
+    lens = torch.randint(1, 700, (batch,)).tolist()
+    lens[0] = 1
+    if batch > 2:
+        lens[1], lens[2] = 16, 17
+    pool, qo, kvp, kvi, last = _make_paged(lens, [1] * batch, kv_heads, hd)
+    q = torch.randn(batch, q_heads * hd, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros_like(q)
+    st = ops.new_status()
+    ops.attn_decode(q, out, pool, qo, kvp, kvi, last, q_heads=q_heads, req_begin=0, req_count=batch,
+                    num_ctas=num_ctas, status=st)
+    ops.check_status(st, "attn_decode")
+    want = ref.paged_attention(q, pool, qo.cpu(), kvp.cpu(), kvi, last.cpu(), q_heads=q_heads)
+    _close(out, want, atol=1e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("chunk_pages", [4, 9, 64])
+def test_attn_decode_split_kv(chunk_pages):
+    kv_heads, group, hd, batch = 2, 8, 128, 5
+    q_heads = kv_heads * group
+    lens = [2000, 31, 4096, 640, 1]
+    pool, qo, kvp, kvi, last = _make_paged(lens, [1] * batch, kv_heads, hd)
+    q = torch.randn(batch, q_heads * hd, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros_like(q)
+    max_chunks = (256 + chunk_pages - 1) // chunk_pages
+    ws = torch.empty(batch * q_heads * max_chunks * (hd + 2), device="cuda", dtype=torch.float32)
+    st = ops.new_status()
+    ops.attn_decode(q, out, pool, qo, kvp, kvi, last, q_heads=q_heads, req_begin=0, req_count=batch,
+                    chunk_pages=chunk_pages, workspace=ws, max_chunks=max_chunks, status=st)
+    ops.check_status(st, "attn_decode split")
+    want = ref.paged_attention(q, pool, qo.cpu(), kvp.cpu(), kvi, last.cpu(), q_heads=q_heads)
+    _close(out, want, atol=1e-2, rtol=2e-2)
+
+
+def test_attn_decode_request_window():
+    """Decode over a sub-range of requests (one attention group of a nano-batch)."""
+    kv_heads, group, hd, batch = 1, 8, 128, 20
+    q_heads = kv_heads * group
+    lens = torch.randint(1, 300, (batch,)).tolist()
+    pool, qo, kvp, kvi, last = _make_paged(lens, [1] * batch, kv_heads, hd)
+    q = torch.randn(batch, q_heads * hd, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros_like(q)
+    ops.attn_decode(q, out, pool, qo, kvp, kvi, last, q_heads=q_heads, req_begin=5, req_count=9)
+    want = ref.paged_attention(q, pool, qo.cpu(), kvp.cpu(), kvi, last.cpu(), q_heads=q_heads,
+                               requests=range(5, 14))
+    _close(out, want, atol=1e-2, rtol=2e-2)
+
+
+def _prefill_items(qo_indptr, group, reqs=None):
+    tq = 128 // group
+    items = []
+    B = len(qo_indptr) - 1
+    for b in (reqs if reqs is not None else range(B)):
+        t = qo_indptr[b]
+        while t < qo_indptr[b + 1]:
+            n = min(tq, qo_indptr[b + 1] - t)
+            items.append([b, t, n])
+            t += n
+    return torch.tensor(items, dtype=torch.int32, device="cuda").reshape(-1, 3)
+
+
+@pytest.mark.parametrize("kv_heads,group,hd", [(1, 8, 128), (8, 8, 128), (4, 4, 128), (2, 1, 128), (2, 2, 64)])
+@pytest.mark.parametrize("case", ["short", "long", "chunked", "mixed"])
+def test_attn_prefill(kv_heads, group, hd, case):
+    q_heads = kv_heads * group
+    if case == "short":
+        qo_lens, kv_lens = [1, 5, 16, 17, 33], [1, 5, 16, 17, 33]
+    elif case == "long":
+        qo_lens, kv_lens = [1024, 300], [1024, 300]
+    elif case == "chunked":  # later chunks of a prompt: kv_len > qo_len
+        qo_lens, kv_lens = [100, 64, 7], [900, 64 + 512, 2048]
+    else:
+        qo_lens, kv_lens = [1, 1, 1, 200, 3], [77, 1, 300, 200, 130]
+    pool, qo, kvp, kvi, last = _make_paged(kv_lens, qo_lens, kv_heads, hd)
+    T = sum(qo_lens)
+    q = torch.randn(T, q_heads * hd, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros_like(q)
+    items = _prefill_items(qo.tolist(), group)
+    st = ops.new_status()
+    ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, items, q_heads=q_heads, num_ctas=0 if case != "long" else 11,
+                     status=st)
+    ops.check_status(st, "attn_prefill")
+    want = ref.paged_attention(q, pool, qo.cpu(), kvp.cpu(), kvi, last.cpu(), q_heads=q_heads)
+    _close(out, want, atol=1e-2, rtol=2e-2)
+
+
+def test_attn_prefill_split_request_across_items():
+    """A request whose tokens are covered by items of two nano-batches gives the same rows."""
+    kv_heads, group, hd = 1, 8, 128
+    q_heads = 8
+    pool, qo, kvp, kvi, last = _make_paged([500], [500], kv_heads, hd)
+    q = torch.randn(500, q_heads * hd, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros_like(q)
+    it_a = torch.tensor([[0, t, min(16, 203 - t)] for t in range(0, 203, 16)], dtype=torch.int32, device="cuda")
+    it_b = torch.tensor([[0, t, min(16, 500 - t)] for t in range(203, 500, 16)], dtype=torch.int32, device="cuda")
+    ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, it_a, q_heads=q_heads)
+    ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, it_b, q_heads=q_heads)
+    want = ref.paged_attention(q, pool, qo.cpu(), kvp.cpu(), kvi, last.cpu(), q_heads=q_heads)
+    _close(out, want, atol=1e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("q_heads,kv_heads,hd", [(8, 1, 128), (32, 8, 128), (4, 4, 64)])
+def test_rope_append(q_heads, kv_heads, hd):
+    lens = [40, 1, 17, 300]
+    qo_lens = [40, 1, 3, 100]
+    pool, qo, kvp, kvi, last = _make_paged(lens, qo_lens, kv_heads, hd)
+    pool.zero_()
+    T = sum(qo_lens)
+    width = (q_heads + 2 * kv_heads) * hd
+    qkv = torch.randn(T, width, device="cuda", dtype=torch.bfloat16)
+    k_off, v_off, q_off = 0, kv_heads * hd, 2 * kv_heads * hd  # packed K | V | Q
+    positions, token_req = [], []
+    for b, (l, n) in enumerate(zip(lens, qo_lens)):
+        positions += list(range(l - n, l)); token_req += [b] * n
+    positions = torch.tensor(positions, dtype=torch.int32, device="cuda")
+    token_req = torch.tensor(token_req, dtype=torch.int32, device="cuda")
+    scaling = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+               "original_max_position_embeddings": 8192}
+    inv = ref.rope_inv_freq(hd, 500000.0, scaling).cuda()
+    q_out = torch.empty(T, q_heads * hd, device="cuda", dtype=torch.bfloat16)
+    st = ops.new_status()
+    ops.rope_append(qkv, q_out, pool, inv, positions, token_req, kvp, kvi, q_heads=q_heads,
+                    kv_heads=kv_heads, head_dim=hd, q_off=q_off, k_off=k_off, v_off=v_off, status=st)
+    ops.check_status(st, "rope_append")
+    pool_ref = torch.zeros_like(pool)
+    q_ref = ref.rope_append(qkv, pool_ref, inv, positions.cpu(), token_req.cpu(), kvp.cpu(), kvi.cpu(),
+                            q_heads=q_heads, kv_heads=kv_heads, head_dim=hd, q_off=q_off, k_off=k_off,
+                            v_off=v_off)
+    _close(q_out, q_ref, atol=2e-2, rtol=2e-2)
+    _close(pool, pool_ref, atol=2e-2, rtol=2e-2)
+
+
+def test_kv_move_pages_roundtrip():
+    pool = torch.randn(64, 2, 2, 16, 128, device="cuda", dtype=torch.bfloat16)
+    ids = torch.tensor([5, 9, 63, 0, 17], dtype=torch.int32, device="cuda")
+    staging = torch.empty(5, *pool.shape[1:], device="cuda", dtype=torch.bfloat16)
+    ops.kv_move_pages(pool, staging, ids, to_staging=True)
+    assert torch.equal(staging, pool[ids.long()])
+    pool2 = torch.zeros_like(pool)
+    ops.kv_move_pages(pool2, staging, ids, to_staging=False)
+    assert torch.equal(pool2[ids.long()], pool[ids.long()])
+    assert int((pool2 != 0).sum()) == int((pool[ids.long()] != 0).sum())  # nothing else written
