@@ -1,0 +1,352 @@
+"""Model / engine configuration.
+
+One JSON file per (model, dense batch, pipeline type) with four sections, the schema of the
+reference's ``pipeline/config_all/<model>/<batch>.json`` (e.g. llama2-70B/2048.json:1-60):
+
+``model``            the Hugging Face ``config.json`` of the model, verbatim
+``model_configs``    gpu_num, run_layer, allocate_kv_data_batch, frame_page_size, max_batch_size, ...
+``pipeline_configs`` global_batch_size, nanobatch_1_size, kqv1_size, kqv3_size, gemm_op_tag[] (the
+                     reference's CUTLASS tile tags: accepted and ignored) plus the sm_100a tuning
+                     fields of this engine (``nanobatch_sizes``, ``sm_budget``, ``gemm_tile_n``, ...)
+``serve_configs``    model id, actual_gpu_num, weight_path, hf_path, pipeline_type
+
+The reference parses ``model`` + ``model_configs`` into a global struct and derives per-GPU sizes
+(pipeline/include/config.h:90-111, pipeline/src/load_config.cu:11-112); :class:`ModelConfig` is that
+struct, :class:`EngineConfig` holds the rest.
+"""
+from __future__ import annotations
+
+import copy
+import json
+from dataclasses import dataclass, field, asdict
+from pathlib import Path
+from typing import Any, Dict, List, Optional
+
+PIPELINE_TYPES = (
+    "PLLM", "NON_OVERLAP", "NANOBATCH", "PLLM_OFFLOAD", "LOCAL", "NON_OVERLAP_LOCAL",
+    "NANOBATCH_LOCAL", "KQVBIAS", "NONOVERLAP_KQVBIAS", "NANOBATCH_KQVBIAS",
+)
+
+
+@dataclass
+class ModelConfig:
+    """Architecture + derived per-GPU sizes for tensor parallel degree ``tp``."""
+    name: str = "llama"
+    hidden_size: int = 4096
+    intermediate_size: int = 14336
+    num_layers: int = 32
+    num_q_heads: int = 32
+    num_kv_heads: int = 8
+    head_dim: int = 128
+    vocab_size: int = 128256
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    rope_scaling: Optional[Dict[str, Any]] = None
+    qkv_bias: bool = False
+    max_position_embeddings: int = 4096
+    eos_token_id: int = 2
+    bos_token_id: int = 1
+    tp: int = 1                 # tensor-parallel degree the shapes are derived for ("vnranks")
+    run_layers: int = 0         # layers executed (>= num_layers re-uses weights round-robin)
+
+    def __post_init__(self):
+        if self.run_layers <= 0:
+            self.run_layers = self.num_layers
+        if self.num_q_heads % self.tp or self.num_kv_heads % self.tp or self.intermediate_size % self.tp:
+            raise ValueError(f"heads/ffn not divisible by tp={self.tp}")
+        if self.num_q_heads % self.num_kv_heads:
+            raise ValueError("q heads must be a multiple of kv heads")
+
+    # ---- per-GPU sizes -------------------------------------------------------------------------
+    @property
+    def q_heads_local(self) -> int:
+        return self.num_q_heads // self.tp
+
+    @property
+    def kv_heads_local(self) -> int:
+        return self.num_kv_heads // self.tp
+
+    @property
+    def group_size(self) -> int:
+        return self.num_q_heads // self.num_kv_heads
+
+    @property
+    def q_size_local(self) -> int:
+        return self.q_heads_local * self.head_dim
+
+    @property
+    def kv_size_local(self) -> int:
+        return self.kv_heads_local * self.head_dim
+
+    @property
+    def qkv_size_local(self) -> int:
+        """Columns of the packed K|V|Q projection on one GPU (``kqv_n`` in the reference)."""
+        return self.q_size_local + 2 * self.kv_size_local
+
+    @property
+    def ffn_local(self) -> int:
+        return self.intermediate_size // self.tp
+
+    @property
+    def vocab_local(self) -> int:
+        """Rows of the vocab-sharded LM head per GPU, padded to a multiple of 8 columns."""
+        per = (self.vocab_size + self.tp - 1) // self.tp
+        return (per + 7) // 8 * 8
+
+    def kv_bytes_per_token_local(self, dtype_bytes: int = 2) -> int:
+        return 2 * self.kv_heads_local * self.head_dim * dtype_bytes * self.run_layers
+
+    def param_count(self) -> int:
+        h, f = self.hidden_size, self.intermediate_size
+        per_layer = h * (self.num_q_heads + 2 * self.num_kv_heads) * self.head_dim + \
+            self.num_q_heads * self.head_dim * h + 3 * h * f + 2 * h
+        return per_layer * self.num_layers + 2 * self.vocab_size * h + h
+
+    def matmul_flops_per_token(self) -> float:
+        h, f = self.hidden_size, self.intermediate_size
+        per_layer = h * (self.num_q_heads + 2 * self.num_kv_heads) * self.head_dim + \
+            self.num_q_heads * self.head_dim * h + 3 * h * f
+        return 2.0 * per_layer * self.run_layers
+
+    @classmethod
+    def from_hf(cls, hf: Dict[str, Any], *, tp: int = 1, run_layers: int = 0, name: str = "") -> "ModelConfig":
+        heads = hf["num_attention_heads"]
+        arch = (hf.get("architectures") or [""])[0]
+        mtype = hf.get("model_type", "llama")
+        return cls(
+            name=name or mtype,
+            hidden_size=hf["hidden_size"],
+            intermediate_size=hf["intermediate_size"],
+            num_layers=hf["num_hidden_layers"],
+            num_q_heads=heads,
+            num_kv_heads=hf.get("num_key_value_heads", heads),
+            head_dim=hf.get("head_dim") or hf["hidden_size"] // heads,
+            vocab_size=hf["vocab_size"],
+            rms_norm_eps=hf.get("rms_norm_eps", 1e-5),
+            rope_theta=float(hf.get("rope_theta", 10000.0)),
+            rope_scaling=hf.get("rope_scaling"),
+            qkv_bias=bool(hf.get("attention_bias", False)) or mtype == "qwen2" or "Qwen2" in arch,
+            max_position_embeddings=hf.get("max_position_embeddings", 4096),
+            eos_token_id=hf.get("eos_token_id", 2) if not isinstance(hf.get("eos_token_id"), list) else hf["eos_token_id"][0],
+            bos_token_id=hf.get("bos_token_id", 1),
+            tp=tp,
+            run_layers=run_layers,
+        )
+
+
+@dataclass
+class EngineConfig:
+    """Everything that is not architecture: batching, nano-batches, SM budgets, serving options."""
+    global_batch_size: int = 2048          # dense tokens per iteration
+    nanobatch_sizes: List[int] = field(default_factory=list)   # token split of the dense batch
+    attn_groups: int = 4                   # decode-attention groups per dense batch (KQV1..4)
+    page_size: int = 16
+    num_pages: int = 0                     # KV pages per GPU; 0 = derive from free memory
+    max_batch_size: int = 2048             # max concurrent requests in one iteration
+    gpu_mem_fraction: float = 0.92
+    pipeline_type: str = "PLLM"
+    actual_gpu_num: int = 1
+    gpu_num: int = 1
+    # sm_100a tuning fields
+    sm_budget: Dict[str, int] = field(default_factory=lambda: {"gemm": 0, "attn_decode": 0, "attn_prefill": 0, "comm": 16, "offload": 8})
+    gemm_tile_n: Dict[str, int] = field(default_factory=dict)
+    decode_chunk_pages: int = 0            # 0 = choose per iteration
+    use_cuda_graph: bool = False
+    offload: bool = False
+    # serving
+    model_id: str = ""
+    weight_path: str = ""
+    hf_path: str = ""
+    gemm_op_tag: List[str] = field(default_factory=list)   # reference CUTLASS tags: kept, unused
+
+    @property
+    def overlap(self) -> bool:
+        return self.pipeline_type in ("PLLM", "PLLM_OFFLOAD", "LOCAL", "KQVBIAS")
+
+    @property
+    def nanobatch(self) -> bool:
+        return not self.pipeline_type.startswith("NON_OVERLAP") and not self.pipeline_type.startswith("NONOVERLAP")
+
+    def resolved_nanobatches(self) -> List[int]:
+        if not self.nanobatch:
+            return [self.global_batch_size]
+        if self.nanobatch_sizes:
+            sizes = list(self.nanobatch_sizes)
+            if sum(sizes) != self.global_batch_size:
+                raise ValueError("nanobatch_sizes must sum to global_batch_size")
+            return sizes
+        return [self.global_batch_size]
+
+
+@dataclass
+class NanoflowConfig:
+    model: ModelConfig
+    engine: EngineConfig
+    raw: Dict[str, Any] = field(default_factory=dict)
+
+    def to_json(self) -> Dict[str, Any]:
+        return copy.deepcopy(self.raw)
+
+
+def parse_config(raw: Dict[str, Any], *, tp: Optional[int] = None) -> NanoflowConfig:
+    """Build the typed config from the four-section dictionary. Unknown keys are kept in ``raw``."""
+    for sec in ("model", "model_configs", "pipeline_configs", "serve_configs"):
+        if sec not in raw:
+            raise ValueError(f"config is missing section '{sec}'")
+    mc, pc, sc = raw["model_configs"], raw["pipeline_configs"], raw["serve_configs"]
+    gpu_num = int(mc.get("gpu_num", 1))
+    actual = int(sc.get("actual_gpu_num", gpu_num))
+    model = ModelConfig.from_hf(raw["model"], tp=tp or gpu_num, run_layers=int(mc.get("run_layer", 0)),
+                                name=sc.get("model", ""))
+    ptype = sc.get("pipeline_type", "PLLM")
+    if ptype not in PIPELINE_TYPES:
+        raise ValueError(f"unknown pipeline_type '{ptype}' (known: {', '.join(PIPELINE_TYPES)})")
+    gbs = int(pc.get("global_batch_size", mc.get("max_batch_size", 2048)))
+    nano = pc.get("nanobatch_sizes")
+    if nano is None and "nanobatch_1_size" in pc:
+        n1 = int(pc["nanobatch_1_size"])
+        nano = [n1, gbs - n1] if 0 < n1 < gbs else [gbs]
+    page = int(mc.get("frame_page_size", 16))
+    # Explicit "num_pages" wins; else the reference's rule allocate_kv_data_batch * 64 pages
+    # (pipeline/src/vortexData.cu:10-31); 0 leaves the pool size to be derived from free memory.
+    num_pages = int(mc.get("num_pages", 0)) or int(mc.get("allocate_kv_data_batch", 0)) * 64
+    eng = EngineConfig(
+        global_batch_size=gbs,
+        nanobatch_sizes=list(nano or []),
+        attn_groups=int(pc.get("attn_groups", 4)),
+        page_size=page,
+        num_pages=num_pages,
+        max_batch_size=int(mc.get("max_batch_size", 2048)),
+        gpu_mem_fraction=float(mc.get("gpu_mem_fraction", 0.92)),
+        pipeline_type=ptype,
+        actual_gpu_num=actual,
+        gpu_num=gpu_num,
+        decode_chunk_pages=int(pc.get("decode_chunk_pages", 0)),
+        use_cuda_graph=bool(pc.get("use_cuda_graph", False)),
+        offload=ptype == "PLLM_OFFLOAD" or bool(pc.get("offload", False)),
+        model_id=sc.get("model", ""),
+        weight_path=sc.get("weight_path", ""),
+        hf_path=sc.get("hf_path", ""),
+        gemm_op_tag=list(pc.get("gemm_op_tag", [])),
+    )
+    if "sm_budget" in pc:
+        eng.sm_budget.update({k: int(v) for k, v in pc["sm_budget"].items()})
+    if "gemm_tile_n" in pc:
+        eng.gemm_tile_n.update({k: int(v) for k, v in pc["gemm_tile_n"].items()})
+    if eng.nanobatch_sizes and sum(eng.nanobatch_sizes) != gbs:
+        raise ValueError("nano-batch sizes must sum to global_batch_size")
+    return NanoflowConfig(model=model, engine=eng, raw=raw)
+
+
+def load_config(path, *, tp: Optional[int] = None) -> NanoflowConfig:
+    with open(path) as f:
+        raw = json.load(f)
+    return parse_config(raw, tp=tp)
+
+
+# --------------------------------------------------------------------------------------------------
+# Built-in architectures (the models the reference ships configs for, plus the tiny test model)
+# --------------------------------------------------------------------------------------------------
+def _hf(hidden, ffn, layers, heads, kv, vocab, theta, *, mtype="llama", arch="LlamaForCausalLM", eps=1e-5,
+        max_pos=4096, scaling=None, eos=2, bos=1, extra=None):
+    d = {
+        "architectures": [arch], "bos_token_id": bos, "eos_token_id": eos, "hidden_act": "silu",
+        "hidden_size": hidden, "initializer_range": 0.02, "intermediate_size": ffn,
+        "max_position_embeddings": max_pos, "model_type": mtype, "num_attention_heads": heads,
+        "num_hidden_layers": layers, "num_key_value_heads": kv, "rms_norm_eps": eps,
+        "rope_theta": theta, "rope_scaling": scaling, "tie_word_embeddings": False,
+        "torch_dtype": "bfloat16", "vocab_size": vocab,
+    }
+    if extra:
+        d.update(extra)
+    return d
+
+
+_LLAMA31_SCALING = {"factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                    "original_max_position_embeddings": 8192, "rope_type": "llama3"}
+
+MODEL_ARCHS: Dict[str, Dict[str, Any]] = {
+    "tiny": _hf(256, 688, 2, 4, 2, 1024, 10000.0),
+    "llama2-70B": _hf(8192, 28672, 80, 64, 8, 32000, 10000.0),
+    "llama3-70B": _hf(8192, 28672, 80, 64, 8, 128256, 500000.0, max_pos=8192, eos=128001, bos=128000),
+    "llama3.1-70B": _hf(8192, 28672, 80, 64, 8, 128256, 500000.0, max_pos=131072, scaling=_LLAMA31_SCALING,
+                        eos=128001, bos=128000),
+    "llama3-8B": _hf(4096, 14336, 32, 32, 8, 128256, 500000.0, max_pos=8192, eos=128001, bos=128000),
+    "llama3.1-8B": _hf(4096, 14336, 32, 32, 8, 128256, 500000.0, max_pos=131072, scaling=_LLAMA31_SCALING,
+                       eos=128001, bos=128000),
+    "qwen2-72B": _hf(8192, 29568, 80, 64, 8, 152064, 1000000.0, mtype="qwen2", arch="Qwen2ForCausalLM",
+                     eps=1e-6, max_pos=32768, eos=151643, bos=151643),
+    "deepseek-67B": _hf(8192, 22016, 95, 64, 8, 102400, 10000.0, eps=1e-6, eos=100001, bos=100000),
+    # Mixtral appears in the reference only as a JSON (no MoE code exists there); the dense
+    # attention shapes are kept so the config parses, experts are not modelled.
+    "mixtral-8-7B": _hf(4096, 14336, 32, 32, 8, 32000, 1000000.0, mtype="mixtral", arch="MixtralForCausalLM",
+                        max_pos=32768, extra={"num_local_experts": 8, "num_experts_per_tok": 2}),
+}
+
+MODEL_IDS = {
+    "llama2-70B": "meta-llama/Llama-2-70b-chat-hf", "llama3-70B": "meta-llama/Meta-Llama-3-70B-Instruct",
+    "llama3.1-70B": "meta-llama/Meta-Llama-3.1-70B-Instruct", "llama3-8B": "meta-llama/Meta-Llama-3-8B-Instruct",
+    "llama3.1-8B": "meta-llama/Meta-Llama-3.1-8B-Instruct", "qwen2-72B": "Qwen/Qwen2-72B-Instruct",
+    "deepseek-67B": "deepseek-ai/deepseek-llm-67b-chat", "mixtral-8-7B": "mistralai/Mixtral-8x7B-Instruct-v0.1",
+    "tiny": "nanoflow/tiny-llama-test",
+}
+
+
+def default_nanobatches(gbs: int, pipeline_type: str) -> List[int]:
+    if pipeline_type.startswith("NON_OVERLAP") or pipeline_type.startswith("NONOVERLAP"):
+        return [gbs]
+    # Two nano-batches in the reference's 5:11 proportion (640 / 1408 of 2048), rounded to whole
+    # 128-row GEMM tiles so neither nano-batch ends in a ragged tile.
+    n1 = max(128, int(round(gbs * 640 / 2048 / 128)) * 128)
+    return [n1, gbs - n1] if gbs > n1 else [gbs]
+
+
+def make_config(model: str, *, gpu_num: int = 1, global_batch_size: int = 2048,
+                pipeline_type: Optional[str] = None, run_layer: int = 0, actual_gpu_num: Optional[int] = None,
+                num_pages: int = 0, weight_path: str = "", **pipeline_overrides) -> Dict[str, Any]:
+    """Generate the four-section dictionary for a built-in architecture."""
+    if model not in MODEL_ARCHS:
+        raise KeyError(f"unknown model '{model}' (known: {', '.join(MODEL_ARCHS)})")
+    hf = copy.deepcopy(MODEL_ARCHS[model])
+    if pipeline_type is None:
+        if hf["model_type"] == "qwen2":
+            pipeline_type = "KQVBIAS"
+        else:
+            pipeline_type = "PLLM" if gpu_num > 1 else "LOCAL"
+    nano = default_nanobatches(global_batch_size, pipeline_type)
+    raw = {
+        "model": hf,
+        "model_configs": {
+            "gpu_num": gpu_num, "run_layer": run_layer or hf["num_hidden_layers"],
+            "allocate_kv_data_batch": 0, "frame_page_size": 16, "max_batch_size": global_batch_size,
+            "gpu_mem_fraction": 0.92,
+        },
+        "pipeline_configs": {
+            "gemm_op_tag": [], "global_batch_size": global_batch_size,
+            "nanobatch_1_size": nano[0], "nanobatch_sizes": nano,
+            "kqv1_size": 0, "kqv3_size": 0, "attn_groups": 4,
+            "sm_budget": {"gemm": 0, "attn_decode": 0, "attn_prefill": 0, "comm": 16, "offload": 8},
+            "decode_chunk_pages": 0,
+        },
+        "serve_configs": {
+            "model": MODEL_IDS.get(model, model), "actual_gpu_num": actual_gpu_num or gpu_num,
+            "weight_path": weight_path or f"./nanoflow_weight_{model}/", "hf_path": "",
+            "pipeline_type": pipeline_type,
+        },
+    }
+    if num_pages:
+        raw["model_configs"]["num_pages"] = num_pages
+    raw["pipeline_configs"].update(pipeline_overrides)
+    return raw
+
+
+def builtin_config(model: str, **kw) -> NanoflowConfig:
+    tp = kw.pop("tp", None)
+    return parse_config(make_config(model, **kw), tp=tp)
+
+
+CONFIG_DIR = Path(__file__).resolve().parent / "configs"
+
+
+def shipped_config_path(model: str, variant: str = "2048") -> Path:
+    return CONFIG_DIR / model / f"{variant}.json"

@@ -130,6 +130,48 @@ int nfk_kv_move_pages(void* pool, void* staging, const int* page_ids, int n_page
                       long long page_bytes, int num_pages, int direction, int num_ctas,
                       unsigned int* status, cudaStream_t stream);
 
+// ------------------------------------------------------------------------------------------------
+// Uniform launch ABI (abi.cu): every op is also reachable as  int fn(const <params>*, cudaStream_t)
+// so that a generic executor can replay a list of (function pointer, parameter block) pairs.
+// ------------------------------------------------------------------------------------------------
+typedef struct nfk_norm_params {
+  void* out; const void* x; const void* w; void* resid;   // resid != NULL: resid += x, out = norm(resid)
+  int rows, cols; float eps;
+} nfk_norm_params;
+typedef struct nfk_embedding_params {
+  void* out; const void* table; const int* host_ids; const int* feedback_src; const int* prev_tokens;
+  int* ids_out; int n_tokens, hidden, vocab; unsigned int* status;
+} nfk_embedding_params;
+typedef struct nfk_gather_params {
+  void* out; const void* in; const int* rows_idx; int n, cols; long long ld_in; int in_rows;
+  unsigned int* status;
+} nfk_gather_params;
+typedef struct nfk_argmax_params {
+  int* idx_out; float* val_out; const void* logits; int rows, cols; long long ld; int col_offset;
+} nfk_argmax_params;
+typedef struct nfk_argmax_combine_params {
+  int* idx_out; const float* cand_val; const int* cand_idx; int shards, rows;
+} nfk_argmax_combine_params;
+typedef struct nfk_copy_cols_params {
+  void* out; long long ld_out; const void* in; long long ld_in; int rows, cols;
+} nfk_copy_cols_params;
+typedef struct nfk_memcpy_params {   // plain async copy (any direction); elem_bytes * count bytes
+  void* dst; const void* src; long long elem_bytes; int count;
+} nfk_memcpy_params;
+typedef struct nfk_kv_move_params {
+  void* pool; void* staging; const int* page_ids; int n_pages; long long page_bytes; int num_pages;
+  int direction; int num_ctas; unsigned int* status;
+} nfk_kv_move_params;
+
+int nfk_norm_p(const nfk_norm_params* p, cudaStream_t s);
+int nfk_embedding_p(const nfk_embedding_params* p, cudaStream_t s);
+int nfk_gather_p(const nfk_gather_params* p, cudaStream_t s);
+int nfk_argmax_p(const nfk_argmax_params* p, cudaStream_t s);
+int nfk_argmax_combine_p(const nfk_argmax_combine_params* p, cudaStream_t s);
+int nfk_copy_cols_p(const nfk_copy_cols_params* p, cudaStream_t s);
+int nfk_memcpy_p(const nfk_memcpy_params* p, cudaStream_t s);
+int nfk_kv_move_p(const nfk_kv_move_params* p, cudaStream_t s);
+
 #ifdef __cplusplus
 }
 #endif

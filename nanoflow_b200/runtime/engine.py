@@ -1,0 +1,269 @@
+"""Per-GPU engine: owns the weights, the paged KV pool, the static activation buffers, the
+per-iteration metadata block and the op graph; runs iterations asynchronously.
+
+API (names follow the reference's ``pllm_python`` surface, pipeline/src/pybind.cu:189-283, and its
+worker loop, pipeline/src/computeBound.cu:115-193):
+
+``update(plan)``        stage the batch metadata of the next iteration in pinned host memory
+``run_async()``         H2D the metadata, launch the whole iteration, D2H the sampled tokens; returns
+                        immediately
+``run_async_wait()``    block until the oldest launched iteration is done; returns its sampled tokens
+``run(plan)``           the three above in sequence
+``getPipelineOutput()`` tokens of the last waited iteration
+
+Input token ids of decode requests never visit the host: the embedding op reads them from the
+previous iteration's ``sampled`` array on the device through ``feedback_src`` indices
+(computeBound.cu:122-150 does this merge on the host in the reference).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..config import EngineConfig, ModelConfig, NanoflowConfig
+from ..models.llama import RankWeights
+from ..ops import reference as ref
+from ..serving.scheduler import BatchPlan
+from .graph import OpGraph, PyExecutor
+from .pipeline import Buffers, CollectiveHooks, IoSpec, build_graph
+
+RING = 3                       # host staging slots (iterations in flight + one being formed)
+DECODE_MAX_CHUNKS = 16
+DECODE_SPLIT_ROWS = 8192       # workspace rows (request x q head) reserved for split-KV decode
+
+
+class MetaLayout:
+    """Offsets (int32 words) of every per-iteration array inside one contiguous metadata block."""
+
+    def __init__(self, T: int, B: int, nano_sizes: List[int], num_pages: int):
+        self.T, self.B = T, B
+        off = 0
+        self.off: Dict[str, int] = {}
+        self.size: Dict[str, int] = {}
+
+        def put(name, n):
+            nonlocal off
+            self.off[name], self.size[name] = off, n
+            off += (n + 3) // 4 * 4        # keep every array 16-byte aligned
+
+        for name in ("host_ids", "feedback_src", "positions", "token_req"):
+            put(name, T)
+        put("qo_indptr", B + 1)
+        put("kv_indptr", B + 1)
+        put("kv_last_page_len", B)
+        put("sample_rows", B)
+        self.item_caps = [s + 2 for s in nano_sizes]
+        for k, cap in enumerate(self.item_caps):
+            put(f"items{k}", cap * 3)
+        self.fixed_words = off
+        put("kv_indices", num_pages + B)
+        self.total_words = off
+
+
+class Engine:
+    def __init__(self, cfg: NanoflowConfig, weights: RankWeights, *, device: Optional[torch.device] = None,
+                 collectives: Optional[CollectiveHooks] = None, num_pages: Optional[int] = None,
+                 executor: str = "auto"):
+        if not torch.cuda.is_available():
+            raise RuntimeError("Engine needs a CUDA device (use runtime.cpu_backend.CpuEngine on CPU)")
+        ops.lib()   # fail loudly if the kernel library is missing
+        self.cfg, self.model, self.eng = cfg, cfg.model, cfg.engine
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.w = weights
+        self.coll = collectives or CollectiveHooks()
+        m, e = self.model, self.eng
+        if e.page_size != 16:
+            raise ValueError("the attention kernels are built for 16-token pages")
+        T, B = e.global_batch_size, e.max_batch_size
+        self.nano_sizes = e.resolved_nanobatches()
+        dev, bf = self.device, torch.bfloat16
+
+        def alloc(*shape, dtype=bf):
+            return self.coll.alloc(shape, dtype) if hasattr(self.coll, "alloc") else \
+                torch.zeros(*shape, dtype=dtype, device=dev)
+
+        plain = lambda *shape, dtype=bf: torch.zeros(*shape, dtype=dtype, device=dev)
+        # activations (x buffers take part in collectives under TP -> symmetric allocation)
+        x = [alloc(T, m.hidden_size), alloc(T, m.hidden_size) if weights.tp > 1 else None]
+        if x[1] is None:
+            x[1] = x[0]
+        self.num_pages = int(num_pages or e.num_pages or self._derive_num_pages(T, B))
+        layout = MetaLayout(T, B, self.nano_sizes, self.num_pages)
+        self.layout = layout
+        self.meta_dev = torch.zeros(layout.total_words, dtype=torch.int32, device=dev)
+        self.meta_host = [torch.zeros(layout.total_words, dtype=torch.int32).pin_memory() for _ in range(RING)]
+        self.meta_np = [t.numpy() for t in self.meta_host]
+        view = lambda name: self.meta_dev[layout.off[name]:layout.off[name] + layout.size[name]]
+        meta = {n: view(n) for n in ("host_ids", "feedback_src", "positions", "token_req", "qo_indptr",
+                                     "kv_indptr", "kv_last_page_len", "sample_rows", "kv_indices")}
+        nano_items = [view(f"items{k}").view(-1, 3) for k in range(len(self.nano_sizes))]
+        kv_pool = [torch.zeros(self.num_pages, 2, m.kv_heads_local, e.page_size, m.head_dim, dtype=bf, device=dev)
+                   for _ in range(m.run_layers)]
+        self.bufs = Buffers(
+            x=x, h=plain(T, m.hidden_size), qkv=plain(T, m.qkv_size_local), q_rot=plain(T, m.q_size_local),
+            attn_out=plain(T, m.q_size_local), act=plain(T, m.ffn_local),
+            sample_h=plain(B, m.hidden_size), sample_hn=plain(B, m.hidden_size),
+            logits=plain(B, weights.lm_head.shape[0]),
+            cand_val=alloc(weights.tp, B, dtype=torch.float32), cand_idx=alloc(weights.tp, B, dtype=torch.int32),
+            sampled=plain(B, dtype=torch.int32), kv_pool=kv_pool,
+            inv_freq=ref.rope_inv_freq(m.head_dim, m.rope_theta, m.rope_scaling).to(dev),
+            status=torch.zeros(1, dtype=torch.int32, device=dev),
+            decode_ws=torch.empty(DECODE_SPLIT_ROWS * DECODE_MAX_CHUNKS * (m.head_dim + 2), dtype=torch.float32,
+                                  device=dev),
+            meta=meta, nano_items=nano_items)
+        io = IoSpec(self.meta_dev, layout.fixed_words, layout.off["kv_indices"])
+        self.graph: OpGraph = build_graph(m, e, weights, self.bufs, self.coll, io)
+        self.tokens_host = [torch.zeros(B, dtype=torch.int32).pin_memory() for _ in range(RING)]
+        self.tokens_np = [t.numpy() for t in self.tokens_host]
+        self.stream = torch.cuda.Stream(device=dev)
+        self.done_events = [torch.cuda.Event() for _ in range(RING)]
+        self._staged: Optional[dict] = None
+        self._inflight: List[dict] = []
+        self._iter = 0
+        self._last_tokens = np.zeros(0, dtype=np.int32)
+        self.h2d_bytes_last = 0
+        self.d2h_bytes_last = 0
+        self.launches_per_iteration = len(self.graph.ops)
+        self.executor_kind = executor
+        self._make_executor(executor)
+
+    # ---- sizing -----------------------------------------------------------------------------------
+    def _derive_num_pages(self, T: int, B: int) -> int:
+        m, e = self.model, self.eng
+        free, total = torch.cuda.mem_get_info(self.device)
+        act = 2 * T * (3 * m.hidden_size + m.qkv_size_local + 2 * m.q_size_local + m.ffn_local)
+        act += 2 * B * (2 * m.hidden_size + self.w.lm_head.shape[0]) + (256 << 20)
+        budget = free - (total * (1.0 - e.gpu_mem_fraction)) - act
+        page_bytes = 2 * m.kv_heads_local * e.page_size * m.head_dim * 2 * m.run_layers
+        n = int(budget // page_bytes)
+        if n < 64:
+            raise RuntimeError(f"not enough GPU memory for a KV pool ({free >> 20} MiB free)")
+        return n
+
+    def _make_executor(self, kind: str) -> None:
+        self.native = None
+        single = not self.eng.overlap
+        if kind in ("auto", "native"):
+            try:
+                from .native import NativeExecutor
+                self.native = NativeExecutor(self.graph, self.stream, single_stream=single,
+                                             device=self.device.index or 0)
+            except ImportError:
+                if kind == "native":
+                    raise
+        self.py_exec = None if self.native is not None else PyExecutor(self.graph, single_stream=single)
+
+    # ---- per-iteration ----------------------------------------------------------------------------
+    def update(self, plan: BatchPlan) -> None:
+        """Write the plan's arrays into the next pinned staging slot and compute the symbol table."""
+        lay = self.layout
+        if plan.num_tokens > lay.T or plan.num_requests > lay.B:
+            raise ValueError("plan exceeds the configured dense batch / request capacity")
+        slot = self._iter % RING
+        buf = self.meta_np[slot]
+
+        def put(name, arr):
+            o = lay.off[name]
+            if arr.size > lay.size[name]:
+                raise ValueError(f"{name}: {arr.size} entries exceed capacity {lay.size[name]}")
+            buf[o:o + arr.size] = arr
+
+        put("host_ids", plan.host_ids); put("feedback_src", plan.feedback_src)
+        put("positions", plan.positions); put("token_req", plan.token_req)
+        put("qo_indptr", plan.qo_indptr); put("kv_indptr", plan.kv_indptr)
+        put("kv_last_page_len", plan.kv_last_page_len); put("sample_rows", plan.sample_rows)
+        put("kv_indices", plan.kv_indices)
+        sym: Dict[str, int] = {"T": plan.num_tokens, "n_sample": int(plan.sample_rows.size)}
+        if len(plan.nano) != len(self.nano_sizes):
+            raise ValueError("plan was cut for a different nano-batch configuration")
+        for k, nb in enumerate(plan.nano):
+            put(f"items{k}", nb.items.reshape(-1))
+            sym[f"nb{k}_T"], sym[f"nb{k}_items"] = nb.token_count, int(nb.items.shape[0])
+            sym[f"nb{k}_dec_begin"], sym[f"nb{k}_dec_count"] = nb.dec_begin, nb.dec_count
+        cp, mc = self._decode_split(plan)
+        sym["decode_chunk_pages"], sym["decode_max_chunks"] = cp, mc
+        self._staged = dict(slot=slot, sym=sym, n_sample=int(plan.sample_rows.size),
+                            kv_words=int(plan.kv_indices.size), plan=plan)
+
+    def _decode_split(self, plan: BatchPlan):
+        if self.eng.decode_chunk_pages > 0:
+            cp = self.eng.decode_chunk_pages
+        else:
+            items = plan.num_decode * self.model.kv_heads_local
+            target = 2 * 148 * 2
+            if items == 0 or items >= target or plan.max_kv_pages <= 16:
+                return 0, 1
+            want = min(DECODE_MAX_CHUNKS, math.ceil(target / items))
+            cp = max(8, math.ceil(plan.max_kv_pages / want))
+        mc = max(1, math.ceil(plan.max_kv_pages / cp))
+        if mc > DECODE_MAX_CHUNKS or plan.num_decode * self.model.q_heads_local > DECODE_SPLIT_ROWS:
+            return 0, 1
+        return cp, mc
+
+    def run_async(self, timed: bool = False) -> None:
+        st = self._staged
+        if st is None:
+            raise RuntimeError("run_async without update")
+        if len(self._inflight) >= RING - 1:
+            raise RuntimeError("too many iterations in flight; call run_async_wait first")
+        lay, slot = self.layout, st["slot"]
+        sym = st["sym"]
+        # The graph starts with the metadata H2D copies (on the iteration's first stream, ordered
+        # after the previous iteration) and ends with the D2H copy of the sampled tokens.
+        sym["meta_src"] = self.meta_host[slot].data_ptr()
+        sym["kv_src"] = self.meta_host[slot].data_ptr() + 4 * lay.off["kv_indices"]
+        sym["kv_words"] = st["kv_words"]
+        sym["tokens_dst"] = self.tokens_host[slot].data_ptr()
+        if self.native is not None:
+            st["ticket"] = self.native.submit(sym, timed)
+        else:
+            with torch.cuda.stream(self.stream):
+                self.py_exec.timing = timed
+                self.py_exec.run(sym, main_stream=self.stream)
+                self.done_events[slot].record(self.stream)
+        self.h2d_bytes_last = 4 * (lay.fixed_words + st["kv_words"])
+        self.d2h_bytes_last = 4 * st["n_sample"]
+        self._inflight.append(st)
+        self._staged = None
+        self._iter += 1
+
+    def run_async_wait(self) -> np.ndarray:
+        if not self._inflight:
+            raise RuntimeError("nothing in flight")
+        st = self._inflight.pop(0)
+        if self.native is not None:
+            self.native.wait(st["ticket"])
+        else:
+            self.done_events[st["slot"]].synchronize()
+        self._last_tokens = self.tokens_np[st["slot"]][:st["n_sample"]].copy()
+        return self._last_tokens
+
+    def timeline(self):
+        """(op name, stream class, start_us, end_us) of the last iteration run with ``timed=True``."""
+        return self.native.timeline() if self.native is not None else list(self.py_exec.timeline)
+
+    def run(self, plan: BatchPlan) -> np.ndarray:
+        self.update(plan)
+        self.run_async()
+        return self.run_async_wait()
+
+    def getPipelineOutput(self) -> np.ndarray:
+        return self._last_tokens
+
+    @property
+    def in_flight(self) -> int:
+        return len(self._inflight)
+
+    def check_status(self) -> None:
+        ops.check_status(self.bufs.status, "engine iteration")
+
+    def finalize(self) -> None:
+        torch.cuda.synchronize(self.device)
+        self._inflight.clear()
+        if self.native is not None:
+            self.native.close()

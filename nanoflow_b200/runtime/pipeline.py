@@ -1,0 +1,265 @@
+"""Builds the per-iteration op graph of a Llama-family decoder from the config.
+
+One graph covers the whole iteration: token-id feedback + embedding, ``run_layers`` decoder layers
+over every nano-batch, and the sampling epilogue (gather last-token rows, final norm, vocab-sharded
+LM head, arg-max, cross-rank combine). Nano-batches own fixed row ranges of the activation buffers;
+their token counts are symbols, so the graph is built once.
+
+Pipeline variants (the reference's ``PipelineType``s, pipeline/include/pipeline.h:53-468,
+selected by ``serve_configs.pipeline_type``):
+
+* ``NON_OVERLAP*``   one nano-batch, every op on one stream.
+* ``NANOBATCH*``     nano-batches, still one stream (isolates the cost of splitting the batch).
+* ``PLLM / LOCAL / KQVBIAS / PLLM_OFFLOAD``  nano-batches, ops spread over the gemm / attn / net /
+  other / copy streams with event dependencies, issue order software-pipelined so that the
+  attention of one nano-batch runs next to the GEMMs of the other (reference schedule:
+  pipeline/src/pipeline.cu:628-733 for TP, pipeline/src/pipeline_local.cu:353-431 for one GPU), and
+  CTA budgets taken from ``pipeline_configs.sm_budget``.
+
+Tensor parallel layout per layer: QKV (K|V|Q packed, N-split) -> RoPE/append -> attention (head
+parallel) -> O (K-split, residual folded in with beta = 1/tp) -> all-reduce -> RMSNorm -> gate/up
+(N-split, SwiGLU epilogue) -> down (K-split, beta = 1/tp) -> all-reduce. The residual stream
+alternates between two buffers so that a GEMM never overwrites the residual it is reading while
+peers still need the old one.
+"""
+from __future__ import annotations
+
+from ctypes import c_void_p
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Optional
+
+import torch
+
+from ..config import EngineConfig, ModelConfig
+from ..models.llama import RankWeights
+from .graph import (ArgmaxCombineParams, ArgmaxParams, AttnParams, EmbeddingParams, GatherParams, GemmParams,
+                    KvMoveParams, MemcpyParams, NormParams, OpGraph, RopeAppendParams)
+
+
+def _ptr(t: Optional[torch.Tensor], row: int = 0) -> c_void_p:
+    if t is None:
+        return c_void_p(0)
+    return c_void_p(t.data_ptr() + row * t.stride(0) * t.element_size())
+
+
+@dataclass
+class Buffers:
+    """Device tensors an iteration reads and writes (allocated once by the engine)."""
+    x: List[torch.Tensor]            # residual stream, two buffers [T, hidden]
+    h: torch.Tensor                  # normed activations [T, hidden]
+    qkv: torch.Tensor                # [T, qkv_local]
+    q_rot: torch.Tensor              # [T, q_local]
+    attn_out: torch.Tensor           # [T, q_local]
+    act: torch.Tensor                # [T, ffn_local]
+    sample_h: torch.Tensor           # [B, hidden]
+    sample_hn: torch.Tensor          # [B, hidden]
+    logits: torch.Tensor             # [B, vocab_local]
+    cand_val: torch.Tensor           # [tp, B] fp32 (symmetric under TP)
+    cand_idx: torch.Tensor           # [tp, B] int32
+    sampled: torch.Tensor            # [B] int32 tokens of the last iteration (device feedback source)
+    kv_pool: List[torch.Tensor]      # per layer [pages, 2, kv_heads_local, page, head_dim]
+    inv_freq: torch.Tensor           # [head_dim/2] fp32
+    status: torch.Tensor             # [1] int32
+    decode_ws: Optional[torch.Tensor]  # split-KV workspace (fp32)
+    meta: Dict[str, torch.Tensor]    # int32 views into the metadata block (see engine.MetaLayout)
+    nano_items: List[torch.Tensor]   # per nano-batch [cap,3] int32 views
+
+
+class CollectiveHooks:
+    """Adds the tensor-parallel collectives to the graph. The TP1 default adds nothing."""
+    tp = 1
+
+    def all_reduce(self, g: OpGraph, name: str, buf: torch.Tensor, row0: int, rows_sym: str, cols: int,
+                   deps, layer: int, nano: int, stream: str = "net") -> Optional[int]:
+        return None
+
+    def all_gather_candidates(self, g: OpGraph, bufs: Buffers, rows_sym: str, deps) -> Optional[int]:
+        return None
+
+
+@dataclass
+class IoSpec:
+    """Where the iteration's host<->device copies go: the metadata block and the sampled tokens."""
+    meta_dev: torch.Tensor      # int32 block on the device
+    fixed_words: int            # words [0, fixed_words) are copied every iteration
+    kv_off_words: int           # start of the kv_indices array (a prefix of it is copied)
+
+
+def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buffers,
+                coll: Optional[CollectiveHooks] = None, io: Optional[IoSpec] = None) -> OpGraph:
+    coll = coll or CollectiveHooks()
+    tp = w.tp
+    g = OpGraph()
+    overlap = eng.overlap
+    sizes = eng.resolved_nanobatches()
+    starts = [sum(sizes[:k]) for k in range(len(sizes))]
+    nn = len(sizes)
+    hd, hidden = model.head_dim, model.hidden_size
+    st = bufs.status
+    budget = eng.sm_budget if overlap else {}
+    S = (lambda cls: cls) if overlap else (lambda cls: "gemm")   # stream chooser
+
+    T_all = g.symbol("T")
+    n_sample = g.symbol("n_sample")
+    nb_T = [g.symbol(f"nb{k}_T") for k in range(nn)]
+    nb_dec0 = [g.symbol(f"nb{k}_dec_begin") for k in range(nn)]
+    nb_decn = [g.symbol(f"nb{k}_dec_count") for k in range(nn)]
+    nb_items = [g.symbol(f"nb{k}_items") for k in range(nn)]
+    chunk_pages = g.symbol("decode_chunk_pages")
+    max_chunks = g.symbol("decode_max_chunks")
+
+    m = bufs.meta
+    # ---- prologue: ids (device feedback) + embedding into residual buffer 0 ------------------------
+    ep = EmbeddingParams(out=_ptr(bufs.x[0]), table=_ptr(w.embed), host_ids=_ptr(m["host_ids"]),
+                         feedback_src=_ptr(m["feedback_src"]), prev_tokens=_ptr(bufs.sampled),
+                         ids_out=c_void_p(0), n_tokens=0, hidden=hidden, vocab=model.vocab_size, status=_ptr(st))
+    pre = []
+    if io is not None:
+        # pinned host -> device metadata copies; the source slot rotates, so the pointers are symbols
+        c1 = MemcpyParams(dst=_ptr(io.meta_dev), src=c_void_p(0), elem_bytes=4, count=io.fixed_words)
+        pre.append(g.add("meta_h2d", c1, S("other"), dyn=[("src", g.symbol("meta_src"))]))
+        c2 = MemcpyParams(dst=c_void_p(io.meta_dev.data_ptr() + 4 * io.kv_off_words), src=c_void_p(0),
+                          elem_bytes=4, count=0)
+        pre.append(g.add("kv_indices_h2d", c2, S("other"),
+                         dyn=[("src", g.symbol("kv_src")), ("count", g.symbol("kv_words"))]))
+    emb = g.add("embedding", ep, S("other"), deps=pre, dyn=[("n_tokens", T_all)])
+
+    last_x_writer: List[Optional[int]] = [emb] * nn     # op that last wrote nano-batch k's residual rows
+    prev_attn: List[Optional[int]] = [None] * nn
+    cur = 0                                             # which residual buffer holds x
+
+    def gemm(name, a, wt, out, k, *, residual=None, beta=1.0, bias=None, swiglu_up=None, deps=(), layer=-1,
+             tile_key=None):
+        p = GemmParams()
+        r0 = starts[k]
+        p.A, p.B, p.D = _ptr(a, r0), _ptr(wt), _ptr(out, r0)
+        p.B2 = _ptr(swiglu_up)
+        p.C, p.bias = _ptr(residual, r0) if residual is not None else c_void_p(0), _ptr(bias)
+        p.lda, p.ldb, p.ldd = a.stride(0), wt.stride(0), out.stride(0)
+        p.ldc = residual.stride(0) if residual is not None else 0
+        p.beta, p.M, p.N, p.K = beta, 0, wt.shape[0], wt.shape[1]
+        p.epilogue = 1 if swiglu_up is not None else 0
+        p.tile_n = eng.gemm_tile_n.get(tile_key or name.split(".")[-1], 0)
+        p.num_ctas = budget.get("gemm", 0)
+        p.status = _ptr(st)
+        return g.add(name, p, "gemm", deps=deps, dyn=[("M", nb_T[k])], layer=layer, nano=k)
+
+    def norm(name, x, wt, out, k, deps, layer, resid=None):
+        r0 = starts[k]
+        p = NormParams(out=_ptr(out, r0), x=_ptr(x, r0), w=_ptr(wt), resid=c_void_p(0), rows=0, cols=hidden,
+                       eps=model.rms_norm_eps)
+        return g.add(name, p, S("other"), deps=deps, dyn=[("rows", nb_T[k])], layer=layer, nano=k)
+
+    def attn_front(l, k, lw, pool):
+        """norm -> QKV -> RoPE/append -> attention for nano-batch k of layer l."""
+        xin = bufs.x[cur]
+        n1 = norm(f"L{l}.nb{k}.ln_attn", xin, lw.ln_attn, bufs.h, k, [last_x_writer[k]], l)
+        q = gemm(f"L{l}.nb{k}.qkv", bufs.h, lw.wqkv, bufs.qkv, k, bias=lw.bqkv, deps=[n1], layer=l, tile_key="qkv")
+        r0 = starts[k]
+        rp = RopeAppendParams()
+        rp.qkv, rp.ld_qkv = _ptr(bufs.qkv, r0), bufs.qkv.stride(0)
+        rp.k_off, rp.v_off, rp.q_off = 0, model.kv_size_local, 2 * model.kv_size_local
+        rp.q_out, rp.kv_pool, rp.inv_freq = _ptr(bufs.q_rot, r0), _ptr(pool), _ptr(bufs.inv_freq)
+        rp.positions = c_void_p(m["positions"].data_ptr() + 4 * r0)
+        rp.token_req = c_void_p(m["token_req"].data_ptr() + 4 * r0)
+        rp.kv_indptr, rp.kv_indices = _ptr(m["kv_indptr"]), _ptr(m["kv_indices"])
+        rp.T, rp.q_heads, rp.kv_heads, rp.head_dim = 0, model.q_heads_local, model.kv_heads_local, hd
+        rp.page_size, rp.num_pages, rp.status = eng.page_size, pool.shape[0], _ptr(st)
+        ro = g.add(f"L{l}.nb{k}.rope_append", rp, "gemm" if overlap else S("other"), deps=[q],
+                   dyn=[("T", nb_T[k])], layer=l, nano=k)
+
+        def attn_params():
+            ap = AttnParams()
+            ap.q, ap.out, ap.kv_pool = _ptr(bufs.q_rot), _ptr(bufs.attn_out), _ptr(pool)
+            ap.qo_indptr, ap.kv_indptr = _ptr(m["qo_indptr"]), _ptr(m["kv_indptr"])
+            ap.kv_indices, ap.kv_last_page_len = _ptr(m["kv_indices"]), _ptr(m["kv_last_page_len"])
+            ap.q_heads, ap.kv_heads, ap.head_dim = model.q_heads_local, model.kv_heads_local, hd
+            ap.page_size, ap.num_pages, ap.sm_scale = eng.page_size, pool.shape[0], hd ** -0.5
+            ap.status = _ptr(st)
+            return ap
+
+        # A prompt chunk that straddles the previous nano-batch reads keys that nano-batch appended.
+        straddle = [rope_of[(l, k - 1)]] if k > 0 else []
+        dp = attn_params()
+        dp.num_ctas = budget.get("attn_decode", 0)
+        dp.workspace = _ptr(bufs.decode_ws)
+        dec = g.add(f"L{l}.nb{k}.attn_decode", dp, S("attn"), deps=[ro], kernel="nfk_attn_decode",
+                    dyn=[("req_begin", nb_dec0[k]), ("req_count", nb_decn[k]), ("chunk_pages", chunk_pages),
+                         ("max_chunks", max_chunks)], layer=l, nano=k)
+        pp = attn_params()
+        pp.num_ctas = budget.get("attn_prefill", 0)
+        pp.items = _ptr(bufs.nano_items[k])
+        pre = g.add(f"L{l}.nb{k}.attn_prefill", pp, S("attn"), deps=[ro] + straddle, kernel="nfk_attn_prefill",
+                    dyn=[("num_items", nb_items[k])], layer=l, nano=k)
+        rope_of[(l, k)] = ro
+        return dec, pre
+
+    def attn_back(l, k, lw, dec, pre):
+        """O projection (+residual) -> all-reduce -> norm -> gate/up SwiGLU -> down (+residual) -> all-reduce."""
+        xin, xout = bufs.x[cur], bufs.x[1 - cur] if tp > 1 else bufs.x[cur]
+        beta = 1.0 / tp
+        o = gemm(f"L{l}.nb{k}.o", bufs.attn_out, lw.wo, xout, k, residual=xin, beta=beta, deps=[dec, pre],
+                 layer=l, tile_key="o")
+        ar1 = coll.all_reduce(g, f"L{l}.nb{k}.ar_o", xout, starts[k], nb_T[k], hidden, [o], l, k)
+        n2 = norm(f"L{l}.nb{k}.ln_ffn", xout, lw.ln_ffn, bufs.h, k, [ar1 if ar1 is not None else o], l)
+        gu = gemm(f"L{l}.nb{k}.gate_up", bufs.h, lw.wg, bufs.act, k, swiglu_up=lw.wu, deps=[n2], layer=l,
+                  tile_key="gate_up")
+        # down writes back into the first buffer: after both projections the residual is where it started
+        d = gemm(f"L{l}.nb{k}.down", bufs.act, lw.wd, xin, k, residual=xout, beta=beta, deps=[gu], layer=l,
+                 tile_key="down")
+        ar2 = coll.all_reduce(g, f"L{l}.nb{k}.ar_d", xin, starts[k], nb_T[k], hidden, [d], l, k)
+        last_x_writer[k] = ar2 if ar2 is not None else d
+
+    rope_of: Dict = {}
+    for l in range(model.run_layers):
+        lw = w.layers[l % model.num_layers]
+        pool = bufs.kv_pool[l]
+        fronts = []
+        if overlap and nn > 1:
+            # software pipeline: all attention front-ends first, then the FFN halves, so that the
+            # attention of nano-batch k+1 runs beside the O/FFN GEMMs of nano-batch k
+            for k in range(nn):
+                fronts.append(attn_front(l, k, lw, pool))
+            for k in range(nn):
+                attn_back(l, k, lw, *fronts[k])
+        else:
+            for k in range(nn):
+                dec, pre = attn_front(l, k, lw, pool)
+                attn_back(l, k, lw, dec, pre)
+
+    # ---- epilogue: sample --------------------------------------------------------------------------
+    gp = GatherParams(out=_ptr(bufs.sample_h), inp=_ptr(bufs.x[cur]), rows_idx=_ptr(m["sample_rows"]), n=0,
+                      cols=hidden, ld_in=bufs.x[cur].stride(0), in_rows=bufs.x[cur].shape[0], status=_ptr(st))
+    ga = g.add("gather_last", gp, S("other"), deps=[d for d in last_x_writer if d is not None],
+               dyn=[("n", n_sample)])
+    fp = NormParams(out=_ptr(bufs.sample_hn), x=_ptr(bufs.sample_h), w=_ptr(w.norm), resid=c_void_p(0), rows=0,
+                    cols=hidden, eps=model.rms_norm_eps)
+    fn = g.add("final_norm", fp, S("other"), deps=[ga], dyn=[("rows", n_sample)])
+    lp = GemmParams()
+    lp.A, lp.B, lp.D = _ptr(bufs.sample_hn), _ptr(w.lm_head), _ptr(bufs.logits)
+    lp.B2, lp.C, lp.bias = c_void_p(0), c_void_p(0), c_void_p(0)
+    lp.lda, lp.ldb, lp.ldd, lp.ldc = bufs.sample_hn.stride(0), w.lm_head.stride(0), bufs.logits.stride(0), 0
+    lp.beta, lp.M, lp.N, lp.K = 0.0, 0, w.lm_head.shape[0], hidden
+    lp.epilogue, lp.tile_n, lp.num_ctas, lp.status = 0, eng.gemm_tile_n.get("lm_head", 0), 0, _ptr(st)
+    lm = g.add("lm_head", lp, "gemm", deps=[fn], dyn=[("M", n_sample)])
+    vl = w.lm_head.shape[0]
+    valid = max(0, min(vl, model.vocab_size - w.rank * vl))
+    Bcap = bufs.sampled.shape[0]
+    if tp == 1:
+        ap = ArgmaxParams(idx_out=_ptr(bufs.sampled), val_out=c_void_p(0), logits=_ptr(bufs.logits), rows=0,
+                          cols=valid, ld=bufs.logits.stride(0), col_offset=0)
+        last = g.add("argmax", ap, S("other") if overlap else "gemm", deps=[lm], dyn=[("rows", n_sample)])
+    else:
+        ap = ArgmaxParams(idx_out=_ptr(bufs.cand_idx, w.rank), val_out=_ptr(bufs.cand_val, w.rank),
+                          logits=_ptr(bufs.logits), rows=0, cols=valid, ld=bufs.logits.stride(0),
+                          col_offset=w.rank * vl)
+        am = g.add("argmax_local", ap, S("other") if overlap else "gemm", deps=[lm], dyn=[("rows", n_sample)])
+        agc = coll.all_gather_candidates(g, bufs, n_sample, [am])
+        cp = ArgmaxCombineParams(idx_out=_ptr(bufs.sampled), cand_val=_ptr(bufs.cand_val),
+                                 cand_idx=_ptr(bufs.cand_idx), shards=tp, rows=Bcap)
+        last = g.add("argmax_combine", cp, S("net"), deps=[agc if agc is not None else am])
+    if io is not None:
+        c3 = MemcpyParams(dst=c_void_p(0), src=_ptr(bufs.sampled), elem_bytes=4, count=0)
+        g.add("tokens_d2h", c3, g.ops[last].stream, deps=[last],
+              dyn=[("dst", g.symbol("tokens_dst")), ("count", n_sample)])
+    return g
