@@ -1,0 +1,312 @@
+// Tensor-parallel collectives over a symmetric heap: every rank maps every peer's heap (CUDA IPC),
+// so a buffer lives at the same byte offset on all GPUs and kernels reach peers with plain
+// loads / stores over NVLink 5 through the NVSwitch (uniform bandwidth to every peer, hence direct
+// one-step algorithms, no rings).
+//
+//   nfk_allreduce   in-place sum of a bf16 [rows, cols] buffer. Row i is owned by rank i % nranks:
+//                   the owner pulls the row from all ranks with 16-byte loads, adds in fp32 in rank
+//                   order (deterministic, identical on all ranks) and pushes the result to every
+//                   rank. Optionally the owner also applies RMSNorm to the reduced row and pushes
+//                   the normed row into a second symmetric buffer (all-reduce + norm fused, so the
+//                   norm is computed once per row instead of once per rank).
+//   nfk_allgather   every rank pushes its shard of a symmetric buffer to all peers.
+//   nfk_comm_barrier  cross-rank barrier.
+//
+// Synchronisation: per-op flag words in the symmetric heap, written by peers with st.release.sys
+// and polled with ld.acquire.sys. Flags carry the caller's epoch (monotonic, e.g. the iteration
+// number), so they are never reset. Every poll is bounded (~2 s); on expiry the kernel records
+// NF_ST_TIMEOUT_PEER_FLAG in the status word, stops waiting and returns, so a dead peer shows up
+// as an error on the host instead of a hung GPU.
+//
+// Counterparts in the reference: pipeline/src/comm.cu:58-114 (all-gather), :169-282 (reduce-scatter,
+// fp16 adds), :284-323 (all-reduce = RS + AG in one kernel), :325-360 (all-reduce + RMSNorm),
+// :475-485 (syncDevices); wrappers pipeline/include/netWrapper.cuh:141-402.
+#include "common.cuh"
+#include "kernels.h"
+#include <string.h>
+
+namespace nf {
+namespace {
+
+constexpr int kCommThreads = 256;
+constexpr long long kPollLimitNs = 2000000000ll;
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_sys_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_sys_v4(void* p, const uint4& v) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// Bounded wait until *flag has reached `epoch` (wrap-safe). Returns false on timeout.
+__device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int epoch) {
+  uint64_t t0 = 0;
+  for (unsigned int it = 0;; ++it) {
+    if (static_cast<int>(ld_acquire_sys(flag) - epoch) >= 0) return true;
+    if ((it & 63u) == 63u) {
+      uint64_t now;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      if (static_cast<long long>(now - t0) > kPollLimitNs) return false;
+      __nanosleep(100);
+    }
+  }
+}
+
+struct FlagBlock {          // one per collective op instance, at the same heap offset on all ranks
+  unsigned int ready[8];    // ready[src]: rank src's input is complete
+  unsigned int done[8];     // done[src]: rank src has finished pushing into this rank
+  unsigned int cta_counter;
+  unsigned int pad[15];
+};
+
+__device__ __forceinline__ FlagBlock* flags_of(const nfk_comm_ctx& c, int r, long long off) {
+  return reinterpret_cast<FlagBlock*>(reinterpret_cast<char*>(c.heap[r]) + off);
+}
+
+// Entry handshake: tell every rank that this rank's input is complete, wait for everyone's.
+__device__ __forceinline__ void comm_enter(const nfk_comm_ctx& c, long long flag_off, unsigned int epoch,
+                                           unsigned int* status) {
+  if (blockIdx.x == 0 && threadIdx.x < c.nranks)
+    st_release_sys(&flags_of(c, threadIdx.x, flag_off)->ready[c.rank], epoch);
+  if (threadIdx.x < c.nranks) {
+    if (!wait_flag(&flags_of(c, c.rank, flag_off)->ready[threadIdx.x], epoch))
+      report_status(status, NF_ST_TIMEOUT_PEER_FLAG);
+  }
+  __syncthreads();
+}
+
+// Exit handshake: the last CTA of this rank tells every rank that its pushes have landed, then
+// waits until every rank has said so, so the buffer is complete when the kernel ends.
+__device__ __forceinline__ void comm_exit(const nfk_comm_ctx& c, long long flag_off, unsigned int epoch,
+                                          unsigned int* status) {
+  __shared__ int is_last;
+  __threadfence_system();
+  __syncthreads();
+  FlagBlock* mine = flags_of(c, c.rank, flag_off);
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(&mine->cta_counter, 1u);
+    is_last = (prev == gridDim.x - 1);
+    if (is_last) mine->cta_counter = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence_system();
+  if (threadIdx.x < c.nranks) {
+    st_release_sys(&flags_of(c, threadIdx.x, flag_off)->done[c.rank], epoch);
+    if (!wait_flag(&mine->done[threadIdx.x], epoch)) report_status(status, NF_ST_TIMEOUT_PEER_FLAG);
+  }
+}
+
+__device__ __forceinline__ float block_sum_comm(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < (kCommThreads >> 5)) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+constexpr int kMaxVecPerThread = 8;  // cols <= 8 * 8 * 256 = 16384
+
+template <bool NORM>
+__global__ void __launch_bounds__(kCommThreads)
+allreduce_kernel(nfk_allreduce_params p) {
+  __shared__ float red[32];
+  const nfk_comm_ctx& c = p.ctx;
+  comm_enter(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status);
+
+  const int nvec = p.cols >> 3;
+  const long long row_bytes = p.ld * 2;
+  const uint4* wv = NORM ? reinterpret_cast<const uint4*>(p.norm_w) : nullptr;
+  for (int row = c.rank + c.nranks * blockIdx.x; row < p.rows; row += c.nranks * gridDim.x) {
+    float acc[kMaxVecPerThread][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxVecPerThread; ++i) {
+      const int v = threadIdx.x + i * kCommThreads;
+      if (v < nvec) {
+        uint4 in[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (r < c.nranks)
+            in[r] = ld_sys_v4(reinterpret_cast<const char*>(c.heap[r]) + p.buf_off + row * row_bytes + v * 16);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          if (r < c.nranks) {
+            const uint32_t w4[4] = {in[r].x, in[r].y, in[r].z, in[r].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = unpack_bf16x2(w4[j]);
+              acc[i][2 * j] += f.x;
+              acc[i][2 * j + 1] += f.y;
+            }
+          }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(acc[i][0], acc[i][1]);
+        o.y = pack_bf16x2(acc[i][2], acc[i][3]);
+        o.z = pack_bf16x2(acc[i][4], acc[i][5]);
+        o.w = pack_bf16x2(acc[i][6], acc[i][7]);
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (r < c.nranks)
+            st_sys_v4(reinterpret_cast<char*>(c.heap[r]) + p.buf_off + row * row_bytes + v * 16, o);
+        if (NORM) {
+          // normalise what was stored (bf16-rounded), as the standalone norm kernel would read it
+          const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = unpack_bf16x2(ow[j]);
+            acc[i][2 * j] = f.x;
+            acc[i][2 * j + 1] = f.y;
+            ss += f.x * f.x + f.y * f.y;
+          }
+        }
+      }
+    }
+    if (NORM) {
+      const float tot = block_sum_comm(ss, red);
+      const float inv = rsqrtf(tot / static_cast<float>(p.cols) + p.eps);
+#pragma unroll
+      for (int i = 0; i < kMaxVecPerThread; ++i) {
+        const int v = threadIdx.x + i * kCommThreads;
+        if (v < nvec) {
+          const uint4 ww = wv[v];
+          const uint32_t w4[4] = {ww.x, ww.y, ww.z, ww.w};
+          uint32_t ov[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 g = unpack_bf16x2(w4[j]);
+            ov[j] = pack_bf16x2(acc[i][2 * j] * inv * g.x, acc[i][2 * j + 1] * inv * g.y);
+          }
+          const uint4 o = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+#pragma unroll
+          for (int r = 0; r < 8; ++r)
+            if (r < c.nranks)
+              st_sys_v4(reinterpret_cast<char*>(c.heap[r]) + p.norm_out_off +
+                            row * static_cast<long long>(p.norm_ld) * 2 + v * 16, o);
+        }
+      }
+    }
+  }
+  comm_exit(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status);
+}
+
+__global__ void __launch_bounds__(kCommThreads)
+allgather_kernel(nfk_allgather_params p) {
+  const nfk_comm_ctx& c = p.ctx;
+  if (p.handshake_in) comm_enter(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status);
+  const long long nvec = p.shard_bytes >> 4;
+  const char* src = reinterpret_cast<const char*>(c.heap[c.rank]) + p.buf_off + c.rank * p.shard_stride;
+  for (long long v = blockIdx.x * static_cast<long long>(kCommThreads) + threadIdx.x; v < nvec;
+       v += static_cast<long long>(gridDim.x) * kCommThreads) {
+    const uint4 val = *reinterpret_cast<const uint4*>(src + v * 16);
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      if (r < c.nranks && r != c.rank)
+        st_sys_v4(reinterpret_cast<char*>(c.heap[r]) + p.buf_off + c.rank * p.shard_stride + v * 16, val);
+  }
+  comm_exit(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status);
+}
+
+__global__ void comm_barrier_kernel(nfk_comm_ctx c, long long flag_off, int epoch, unsigned int* status) {
+  if (threadIdx.x < c.nranks) {
+    st_release_sys(&flags_of(c, threadIdx.x, flag_off)->ready[c.rank], static_cast<unsigned int>(epoch));
+    if (!wait_flag(&flags_of(c, c.rank, flag_off)->ready[threadIdx.x], static_cast<unsigned int>(epoch)))
+      report_status(status, NF_ST_TIMEOUT_PEER_FLAG);
+  }
+}
+
+bool ctx_ok(const nfk_comm_ctx& c) {
+  if (c.nranks < 1 || c.nranks > 8 || c.rank < 0 || c.rank >= c.nranks) return false;
+  for (int r = 0; r < c.nranks; ++r)
+    if (c.heap[r] == nullptr) return false;
+  return true;
+}
+
+}  // namespace
+}  // namespace nf
+
+extern "C" int nfk_allreduce(const nfk_allreduce_params* p, cudaStream_t stream) {
+  using namespace nf;
+  if (!p || !ctx_ok(p->ctx)) return NF_ERR_BAD_ARG;
+  if (p->cols <= 0 || p->cols % 8 != 0 || p->cols > kMaxVecPerThread * 8 * kCommThreads || p->ld % 8 != 0 ||
+      p->rows < 0 || p->buf_off % 16 != 0 || p->flag_off % 16 != 0)
+    return NF_ERR_BAD_ARG;
+  if (p->norm_w != nullptr && (p->norm_out_off % 16 != 0 || p->norm_ld % 8 != 0)) return NF_ERR_BAD_ARG;
+  // Even an empty buffer takes part in the handshakes so that all ranks stay in step.
+  const int owned = (p->rows + p->ctx.nranks - 1) / p->ctx.nranks;
+  int ctas = p->num_ctas > 0 ? p->num_ctas : 32;
+  if (ctas > owned) ctas = owned > 0 ? owned : 1;
+  if (p->norm_w != nullptr)
+    allreduce_kernel<true><<<ctas, kCommThreads, 0, stream>>>(*p);
+  else
+    allreduce_kernel<false><<<ctas, kCommThreads, 0, stream>>>(*p);
+  return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
+}
+
+extern "C" int nfk_allgather(const nfk_allgather_params* p, cudaStream_t stream) {
+  using namespace nf;
+  if (!p || !ctx_ok(p->ctx)) return NF_ERR_BAD_ARG;
+  if (p->shard_bytes < 0 || p->shard_bytes % 16 != 0 || p->shard_stride % 16 != 0 || p->buf_off % 16 != 0 ||
+      p->flag_off % 16 != 0 || p->shard_stride < p->shard_bytes)
+    return NF_ERR_BAD_ARG;
+  long long ctas = p->num_ctas > 0 ? p->num_ctas : 16;
+  const long long need = ((p->shard_bytes >> 4) + kCommThreads - 1) / kCommThreads;
+  if (ctas > need) ctas = need > 0 ? need : 1;
+  allgather_kernel<<<static_cast<int>(ctas), kCommThreads, 0, stream>>>(*p);
+  return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
+}
+
+extern "C" int nfk_comm_barrier(const nfk_comm_barrier_params* p, cudaStream_t stream) {
+  using namespace nf;
+  if (!p || !ctx_ok(p->ctx) || p->flag_off % 16 != 0) return NF_ERR_BAD_ARG;
+  comm_barrier_kernel<<<1, 32, 0, stream>>>(p->ctx, p->flag_off, p->epoch, p->status);
+  return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
+}
+
+// ---- symmetric heap plumbing (host) -----------------------------------------------------------------
+extern "C" int nfk_symm_alloc(void** out, long long bytes) {
+  using namespace nf;
+  if (!out || bytes <= 0) return NF_ERR_BAD_ARG;
+  if (cudaMalloc(out, static_cast<size_t>(bytes)) != cudaSuccess) return NF_ERR_CUDA;
+  if (cudaMemset(*out, 0, static_cast<size_t>(bytes)) != cudaSuccess) return NF_ERR_CUDA;
+  return cudaDeviceSynchronize() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
+}
+extern "C" int nfk_symm_free(void* p) { return cudaFree(p) == cudaSuccess ? nf::NF_OK : nf::NF_ERR_CUDA; }
+extern "C" int nfk_ipc_get_handle(void* ptr, unsigned char* out64) {
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, ptr) != cudaSuccess) return nf::NF_ERR_CUDA;
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(out64, &h, 64);
+  return nf::NF_OK;
+}
+extern "C" int nfk_ipc_open_handle(const unsigned char* in64, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, in64, 64);
+  return cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess ? nf::NF_OK
+                                                                                    : nf::NF_ERR_CUDA;
+}
+extern "C" int nfk_ipc_close_handle(void* p) {
+  return cudaIpcCloseMemHandle(p) == cudaSuccess ? nf::NF_OK : nf::NF_ERR_CUDA;
+}

@@ -131,6 +131,54 @@ int nfk_kv_move_pages(void* pool, void* staging, const int* page_ids, int n_page
                       unsigned int* status, cudaStream_t stream);
 
 // ------------------------------------------------------------------------------------------------
+// Tensor-parallel collectives on a symmetric heap (collectives.cu)
+// ------------------------------------------------------------------------------------------------
+typedef struct nfk_comm_ctx {
+  void* heap[8];       // base of every rank's symmetric heap as mapped into this process
+  int rank, nranks;
+} nfk_comm_ctx;
+
+typedef struct nfk_allreduce_params {
+  nfk_comm_ctx ctx;
+  long long buf_off;      // byte offset of the bf16 [rows, ld] buffer inside the heap (summed in place)
+  long long flag_off;     // byte offset of this op's 128-byte flag block
+  int rows, cols;
+  long long ld;           // elements
+  int epoch;              // monotonic per call on this flag block (e.g. iteration number)
+  int num_ctas;
+  const void* norm_w;     // optional: RMSNorm weight [cols]; normed rows go to norm_out on all ranks
+  long long norm_out_off; // byte offset of the bf16 [rows, norm_ld] output inside the heap
+  long long norm_ld;
+  float eps;
+  unsigned int* status;
+} nfk_allreduce_params;
+int nfk_allreduce(const nfk_allreduce_params* p, cudaStream_t stream);
+
+typedef struct nfk_allgather_params {
+  nfk_comm_ctx ctx;
+  long long buf_off;       // symmetric buffer holding nranks shards, shard r at buf_off + r*shard_stride
+  long long shard_bytes, shard_stride, flag_off;
+  int epoch, num_ctas, handshake_in;
+  unsigned int* status;
+} nfk_allgather_params;
+int nfk_allgather(const nfk_allgather_params* p, cudaStream_t stream);
+
+typedef struct nfk_comm_barrier_params {
+  nfk_comm_ctx ctx;
+  long long flag_off;
+  int epoch;
+  unsigned int* status;
+} nfk_comm_barrier_params;
+int nfk_comm_barrier(const nfk_comm_barrier_params* p, cudaStream_t stream);
+
+// Symmetric heap plumbing: allocate (zero-filled), export / open CUDA IPC handles (64 bytes).
+int nfk_symm_alloc(void** out, long long bytes);
+int nfk_symm_free(void* p);
+int nfk_ipc_get_handle(void* ptr, unsigned char* out64);
+int nfk_ipc_open_handle(const unsigned char* in64, void** out);
+int nfk_ipc_close_handle(void* p);
+
+// ------------------------------------------------------------------------------------------------
 // Uniform launch ABI (abi.cu): every op is also reachable as  int fn(const <params>*, cudaStream_t)
 // so that a generic executor can replay a list of (function pointer, parameter block) pairs.
 // ------------------------------------------------------------------------------------------------

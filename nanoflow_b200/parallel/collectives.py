@@ -1,0 +1,167 @@
+"""Tensor-parallel collective ops for the op graph and for direct use.
+
+:class:`TpCollectives` owns the symmetric heap of this rank, hands out symmetric tensors to the
+engine (residual buffers, normed activations, arg-max candidates) and appends all-reduce /
+all-gather ops to the graph. Every op instance gets its own 128-byte flag block; the epoch that
+the flags carry is the iteration counter symbol ``epoch``, so nothing is ever reset.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import Structure, byref, c_float, c_int, c_longlong, c_void_p
+from typing import Optional, Sequence
+
+import torch
+
+from .. import ops as _ops
+from ..runtime.graph import KERNEL_OF, OpGraph
+from ..runtime.pipeline import Buffers, CollectiveHooks
+from .symm import SymmetricHeap
+
+
+class CommCtx(Structure):
+    _fields_ = [("heap", c_void_p * 8), ("rank", c_int), ("nranks", c_int)]
+
+
+class AllReduceParams(Structure):
+    _fields_ = [("ctx", CommCtx), ("buf_off", c_longlong), ("flag_off", c_longlong), ("rows", c_int),
+                ("cols", c_int), ("ld", c_longlong), ("epoch", c_int), ("num_ctas", c_int),
+                ("norm_w", c_void_p), ("norm_out_off", c_longlong), ("norm_ld", c_longlong), ("eps", c_float),
+                ("status", c_void_p)]
+
+
+class AllGatherParams(Structure):
+    _fields_ = [("ctx", CommCtx), ("buf_off", c_longlong), ("shard_bytes", c_longlong),
+                ("shard_stride", c_longlong), ("flag_off", c_longlong), ("epoch", c_int), ("num_ctas", c_int),
+                ("handshake_in", c_int), ("status", c_void_p)]
+
+
+class BarrierParams(Structure):
+    _fields_ = [("ctx", CommCtx), ("flag_off", c_longlong), ("epoch", c_int), ("status", c_void_p)]
+
+
+KERNEL_OF[AllReduceParams] = "nfk_allreduce"
+KERNEL_OF[AllGatherParams] = "nfk_allgather"
+KERNEL_OF[BarrierParams] = "nfk_comm_barrier"
+
+FLAG_BYTES = 128
+
+
+class TpCollectives(CollectiveHooks):
+    def __init__(self, rank: int, world: int, device: torch.device, heap_bytes: int = 1 << 30,
+                 num_ctas: int = 16, fuse_norm: bool = True):
+        if world > 8:
+            raise ValueError("at most 8 ranks (one NVSwitch domain)")
+        self.rank, self.tp, self.device = rank, world, device
+        self.heap = SymmetricHeap(rank, world, device, heap_bytes)
+        self.num_ctas = num_ctas
+        self.fuse_norm = fuse_norm
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._epoch = 0
+        self._adhoc_flags = self.heap.alloc_bytes(FLAG_BYTES)
+
+    # ---- plumbing ---------------------------------------------------------------------------------
+    def ctx(self) -> CommCtx:
+        c = CommCtx()
+        for r in range(self.tp):
+            c.heap[r] = self.heap.peer_base[r]
+        c.rank, c.nranks = self.rank, self.tp
+        return c
+
+    def alloc(self, shape, dtype) -> torch.Tensor:
+        return self.heap.alloc(shape, dtype)
+
+    def new_flags(self) -> int:
+        return self.heap.alloc_bytes(FLAG_BYTES)
+
+    # ---- graph hooks --------------------------------------------------------------------------------
+    def all_reduce(self, g: OpGraph, name: str, buf: torch.Tensor, row0: int, rows_sym: str, cols: int,
+                   deps, layer: int, nano: int, stream: str = "net", norm_w: Optional[torch.Tensor] = None,
+                   norm_out: Optional[torch.Tensor] = None, eps: float = 1e-5, status=None, num_ctas: int = 0):
+        p = AllReduceParams()
+        p.ctx = self.ctx()
+        esz = buf.element_size()
+        p.buf_off = self.heap.offset_of(buf) + row0 * buf.stride(0) * esz
+        p.flag_off = self.new_flags()
+        p.rows, p.cols, p.ld = 0, cols, buf.stride(0)
+        p.epoch, p.num_ctas = 0, num_ctas or self.num_ctas
+        fused = self.fuse_norm and norm_w is not None and norm_out is not None
+        if fused:
+            p.norm_w = norm_w.data_ptr()
+            p.norm_out_off = self.heap.offset_of(norm_out) + row0 * norm_out.stride(0) * esz
+            p.norm_ld, p.eps = norm_out.stride(0), eps
+        p.status = (status if status is not None else self.status).data_ptr()
+        idx = g.add(name, p, stream, deps=deps, dyn=[("rows", rows_sym), ("epoch", g.symbol("epoch"))],
+                    layer=layer, nano=nano)
+        return idx, fused
+
+    def all_gather_candidates(self, g: OpGraph, bufs: Buffers, rows_sym: str, deps):
+        """cand_val / cand_idx are [tp, B] symmetric arrays; every rank pushes its row to all peers."""
+        last = None
+        for t, nm in ((bufs.cand_val, "val"), (bufs.cand_idx, "idx")):
+            p = AllGatherParams()
+            p.ctx = self.ctx()
+            p.buf_off = self.heap.offset_of(t)
+            p.shard_stride = t.stride(0) * t.element_size()
+            p.shard_bytes = p.shard_stride
+            p.flag_off = self.new_flags()
+            p.epoch, p.num_ctas, p.handshake_in = 0, 2, 1
+            p.status = self.status.data_ptr()
+            last = g.add(f"ag_cand_{nm}", p, "net", deps=list(deps) + ([last] if last is not None else []),
+                         dyn=[("epoch", g.symbol("epoch"))])
+        return last
+
+    # ---- direct (eager) calls, used by tests and micro-benchmarks --------------------------------------
+    def _next_epoch(self) -> int:
+        self._epoch += 1
+        return self._epoch
+
+    def all_reduce_(self, buf: torch.Tensor, *, norm_w=None, norm_out=None, eps: float = 1e-5,
+                    num_ctas: int = 0, flag_off: Optional[int] = None, epoch: Optional[int] = None):
+        """In-place sum of a symmetric bf16 [rows, cols] tensor over all ranks (launches on the
+        current stream). All ranks must call it the same number of times with the same flag block."""
+        p = AllReduceParams()
+        p.ctx = self.ctx()
+        p.buf_off = self.heap.offset_of(buf)
+        p.flag_off = self._adhoc_flags if flag_off is None else flag_off
+        p.rows, p.cols, p.ld = buf.shape[0], buf.shape[1], buf.stride(0)
+        p.epoch = self._next_epoch() if epoch is None else epoch
+        p.num_ctas = num_ctas or self.num_ctas
+        if norm_w is not None:
+            p.norm_w = norm_w.data_ptr()
+            p.norm_out_off = self.heap.offset_of(norm_out)
+            p.norm_ld, p.eps = norm_out.stride(0), eps
+        p.status = self.status.data_ptr()
+        rc = _ops.lib().nfk_allreduce(byref(p), c_void_p(torch.cuda.current_stream().cuda_stream))
+        if rc != 0:
+            raise RuntimeError(f"nfk_allreduce: {_ops.ERRORS.get(rc, rc)}")
+        return buf
+
+    def all_gather_(self, buf: torch.Tensor, *, num_ctas: int = 0):
+        """buf is a symmetric [world, ...] tensor whose row ``rank`` holds this rank's shard."""
+        p = AllGatherParams()
+        p.ctx = self.ctx()
+        p.buf_off = self.heap.offset_of(buf)
+        p.shard_stride = buf.stride(0) * buf.element_size()
+        p.shard_bytes = p.shard_stride
+        p.flag_off = self._adhoc_flags
+        p.epoch, p.num_ctas, p.handshake_in = self._next_epoch(), num_ctas or self.num_ctas, 1
+        p.status = self.status.data_ptr()
+        rc = _ops.lib().nfk_allgather(byref(p), c_void_p(torch.cuda.current_stream().cuda_stream))
+        if rc != 0:
+            raise RuntimeError(f"nfk_allgather: {_ops.ERRORS.get(rc, rc)}")
+        return buf
+
+    def barrier_(self):
+        p = BarrierParams()
+        p.ctx, p.flag_off, p.epoch = self.ctx(), self._adhoc_flags, self._next_epoch()
+        p.status = self.status.data_ptr()
+        rc = _ops.lib().nfk_comm_barrier(byref(p), c_void_p(torch.cuda.current_stream().cuda_stream))
+        if rc != 0:
+            raise RuntimeError(f"nfk_comm_barrier: {_ops.ERRORS.get(rc, rc)}")
+
+    def check_status(self):
+        _ops.check_status(self.status, "collective")
+
+    def close(self):
+        self.heap.close()

@@ -105,7 +105,7 @@ class Engine:
         kv_pool = [torch.zeros(self.num_pages, 2, m.kv_heads_local, e.page_size, m.head_dim, dtype=bf, device=dev)
                    for _ in range(m.run_layers)]
         self.bufs = Buffers(
-            x=x, h=plain(T, m.hidden_size), qkv=plain(T, m.qkv_size_local), q_rot=plain(T, m.q_size_local),
+            x=x, h=alloc(T, m.hidden_size) if weights.tp > 1 else plain(T, m.hidden_size), qkv=plain(T, m.qkv_size_local), q_rot=plain(T, m.q_size_local),
             attn_out=plain(T, m.q_size_local), act=plain(T, m.ffn_local),
             sample_h=plain(B, m.hidden_size), sample_hn=plain(B, m.hidden_size),
             logits=plain(B, weights.lm_head.shape[0]),
@@ -219,6 +219,7 @@ class Engine:
         sym["kv_src"] = self.meta_host[slot].data_ptr() + 4 * lay.off["kv_indices"]
         sym["kv_words"] = st["kv_words"]
         sym["tokens_dst"] = self.tokens_host[slot].data_ptr()
+        sym["epoch"] = self._iter + 1      # collective flag epoch: same on every rank, never reset
         if self.native is not None:
             st["ticket"] = self.native.submit(sym, timed)
         else:

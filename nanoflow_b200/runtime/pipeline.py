@@ -70,8 +70,10 @@ class CollectiveHooks:
     tp = 1
 
     def all_reduce(self, g: OpGraph, name: str, buf: torch.Tensor, row0: int, rows_sym: str, cols: int,
-                   deps, layer: int, nano: int, stream: str = "net") -> Optional[int]:
-        return None
+                   deps, layer: int, nano: int, stream: str = "net", norm_w=None, norm_out=None,
+                   eps: float = 1e-5, status=None, num_ctas: int = 0):
+        """Returns (op index or None, whether the RMSNorm was fused into the collective)."""
+        return None, False
 
     def all_gather_candidates(self, g: OpGraph, bufs: Buffers, rows_sym: str, deps) -> Optional[int]:
         return None
@@ -153,7 +155,11 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
     def attn_front(l, k, lw, pool):
         """norm -> QKV -> RoPE/append -> attention for nano-batch k of layer l."""
         xin = bufs.x[cur]
-        n1 = norm(f"L{l}.nb{k}.ln_attn", xin, lw.ln_attn, bufs.h, k, [last_x_writer[k]], l)
+        if h_normed[k] is not None:
+            n1 = h_normed[k]          # the previous all-reduce already wrote the normed rows into h
+            h_normed[k] = None
+        else:
+            n1 = norm(f"L{l}.nb{k}.ln_attn", xin, lw.ln_attn, bufs.h, k, [last_x_writer[k]], l)
         q = gemm(f"L{l}.nb{k}.qkv", bufs.h, lw.wqkv, bufs.qkv, k, bias=lw.bqkv, deps=[n1], layer=l, tile_key="qkv")
         r0 = starts[k]
         rp = RopeAppendParams()
@@ -200,17 +206,28 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         beta = 1.0 / tp
         o = gemm(f"L{l}.nb{k}.o", bufs.attn_out, lw.wo, xout, k, residual=xin, beta=beta, deps=[dec, pre],
                  layer=l, tile_key="o")
-        ar1 = coll.all_reduce(g, f"L{l}.nb{k}.ar_o", xout, starts[k], nb_T[k], hidden, [o], l, k)
-        n2 = norm(f"L{l}.nb{k}.ln_ffn", xout, lw.ln_ffn, bufs.h, k, [ar1 if ar1 is not None else o], l)
+        comm_ctas = budget.get("comm", 0)
+        ar1, fused1 = coll.all_reduce(g, f"L{l}.nb{k}.ar_o", xout, starts[k], nb_T[k], hidden, [o], l, k,
+                                      stream=S("net"), norm_w=lw.ln_ffn, norm_out=bufs.h, eps=model.rms_norm_eps,
+                                      status=st, num_ctas=comm_ctas)
+        if fused1:
+            n2 = ar1
+        else:
+            n2 = norm(f"L{l}.nb{k}.ln_ffn", xout, lw.ln_ffn, bufs.h, k, [ar1 if ar1 is not None else o], l)
         gu = gemm(f"L{l}.nb{k}.gate_up", bufs.h, lw.wg, bufs.act, k, swiglu_up=lw.wu, deps=[n2], layer=l,
                   tile_key="gate_up")
         # down writes back into the first buffer: after both projections the residual is where it started
         d = gemm(f"L{l}.nb{k}.down", bufs.act, lw.wd, xin, k, residual=xout, beta=beta, deps=[gu], layer=l,
                  tile_key="down")
-        ar2 = coll.all_reduce(g, f"L{l}.nb{k}.ar_d", xin, starts[k], nb_T[k], hidden, [d], l, k)
+        nxt = w.layers[(l + 1) % model.num_layers].ln_attn if l + 1 < model.run_layers else None
+        ar2, fused2 = coll.all_reduce(g, f"L{l}.nb{k}.ar_d", xin, starts[k], nb_T[k], hidden, [d], l, k,
+                                      stream=S("net"), norm_w=nxt, norm_out=bufs.h if nxt is not None else None,
+                                      eps=model.rms_norm_eps, status=st, num_ctas=comm_ctas)
         last_x_writer[k] = ar2 if ar2 is not None else d
+        h_normed[k] = ar2 if fused2 else None
 
     rope_of: Dict = {}
+    h_normed: List[Optional[int]] = [None] * nn     # op that already wrote normed rows of nano-batch k into h
     for l in range(model.run_layers):
         lw = w.layers[l % model.num_layers]
         pool = bufs.kv_pool[l]

@@ -1,0 +1,171 @@
+"""Multi-GPU test worker, one process per GPU:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port 29511 tests/mp_worker.py {collectives|engine|timeout}
+
+Prints ``MP_WORKER_OK <case>`` from rank 0 on success; any rank's assertion failure exits non-zero.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from nanoflow_b200.ops import reference as ref  # noqa: E402
+from nanoflow_b200.parallel.collectives import TpCollectives  # noqa: E402
+
+
+def case_collectives(rank, world, dev):
+    coll = TpCollectives(rank, world, dev, heap_bytes=256 << 20)
+    # exact integer pattern (the reference's comm_test.cu:15 uses (i*rank)%101, exact in fp16; here
+    # values < 101 * world stay exact in bf16 only when small, so use (i*(rank+1)) % 13)
+    for rows, cols in [(64, 1024), (37, 8192), (1, 256), (0, 512), (300, 4096)]:
+        buf = coll.alloc((max(rows, 1), cols), torch.bfloat16)[:rows]
+        idx = torch.arange(rows * cols, device=dev).reshape(rows, cols)
+        buf.copy_(((idx * (rank + 1)) % 13).to(torch.bfloat16))
+        want = sum(((idx * (r + 1)) % 13).float() for r in range(world))
+        torch.cuda.synchronize(); dist.barrier()
+        coll.all_reduce_(buf)
+        torch.cuda.synchronize()
+        coll.check_status()
+        assert torch.equal(buf.float(), want), f"all-reduce mismatch {rows}x{cols} on rank {rank}"
+    # random data + fused RMSNorm against the fp32 restatement
+    rows, cols = 203, 8192
+    g = torch.Generator(device="cpu").manual_seed(7)
+    parts = [torch.randn(rows, cols, generator=g).bfloat16() for _ in range(world)]
+    wnorm = (1 + 0.1 * torch.randn(cols, generator=g)).bfloat16().to(dev)
+    buf = coll.alloc((rows, cols), torch.bfloat16)
+    out = coll.alloc((rows, cols), torch.bfloat16)
+    buf.copy_(parts[rank].to(dev))
+    torch.cuda.synchronize(); dist.barrier()
+    coll.all_reduce_(buf, norm_w=wnorm, norm_out=out, eps=1e-5)
+    torch.cuda.synchronize()
+    coll.check_status()
+    total = sum(p.float() for p in parts).to(dev)
+    assert torch.allclose(buf.float(), total, atol=3e-2, rtol=1e-2)
+    want_n = ref.rmsnorm(buf, wnorm, 1e-5)
+    assert torch.allclose(out.float(), want_n, atol=3e-2, rtol=2e-2)
+    # every rank holds bit-identical results (deterministic reduction order)
+    gathered = [torch.empty_like(buf) for _ in range(world)]
+    dist.all_gather(gathered, buf.contiguous())
+    assert all(torch.equal(gathered[0], t) for t in gathered)
+    # all-gather + barrier
+    ag = coll.alloc((world, 4096), torch.int32)
+    ag.zero_(); ag[rank] = torch.arange(4096, device=dev, dtype=torch.int32) + 1000 * rank
+    torch.cuda.synchronize(); dist.barrier()
+    coll.all_gather_(ag)
+    coll.barrier_()
+    torch.cuda.synchronize()
+    coll.check_status()
+    want = torch.stack([torch.arange(4096, dtype=torch.int32) + 1000 * r for r in range(world)]).to(dev)
+    assert torch.equal(ag, want)
+    # bandwidth (device-timed, max over ranks)
+    rows, cols = 2048, 8192
+    buf = coll.alloc((rows, cols), torch.bfloat16)
+    for ctas in (8, 16, 32, 64):
+        for _ in range(3):
+            coll.all_reduce_(buf, num_ctas=ctas)
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            coll.all_reduce_(buf, num_ctas=ctas)
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / 10], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            nbytes = rows * cols * 2
+            busbw = 2 * (world - 1) / world * nbytes / (t.item() * 1e-3) / 1e9
+            print(f"allreduce {rows}x{cols} bf16 ctas={ctas}: {t.item()*1e3:.1f} us, bus bw {busbw:.0f} GB/s", flush=True)
+    coll.check_status()
+    coll.close()
+
+
+def case_engine(rank, world, dev):
+    from nanoflow_b200.config import builtin_config
+    from nanoflow_b200.models import ReferenceLlama, random_full_weights, shard_weights
+    from nanoflow_b200.runtime.engine import Engine
+    from nanoflow_b200.serving import DistKVPool, RequestManager, Scheduler
+    from nanoflow_b200.serving.loop import ServingLoop
+
+    for ptype, nano in (("NON_OVERLAP", None), ("PLLM", [16, 32])):
+        gbs = 48
+        cfg = builtin_config("tiny", gpu_num=world, global_batch_size=gbs, pipeline_type=ptype, nanobatch_sizes=nano)
+        cfg.engine.max_batch_size = gbs
+        fw = random_full_weights(cfg.model, seed=0, std=0.05)
+        for lay in fw.layers:
+            for k, v in vars(lay).items():
+                if v is not None:
+                    setattr(lay, k, v.bfloat16().float())
+        fw.embed, fw.norm, fw.lm_head = fw.embed.bfloat16().float(), fw.norm.bfloat16().float(), fw.lm_head.bfloat16().float()
+        oracle = ReferenceLlama(builtin_config("tiny").model, fw)
+        rng = np.random.default_rng(0)
+        prompts = [rng.integers(0, 1024, size=32, dtype=np.int32) for _ in range(4)]
+        rm = RequestManager(vocab_size=1024)
+        for p in prompts:
+            rm.add_request(32, 16, 0.0, prompt=p)
+        rm.finalize_stats()
+        pool = DistKVPool(2, 2, 64, 64, 16, world)
+        sch = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=gbs,
+                        nanobatch_sizes=cfg.engine.resolved_nanobatches(), average_prefill_length=32,
+                        average_decode_length=16, group_size=2)
+        coll = TpCollectives(rank, world, dev, heap_bytes=64 << 20)
+        eng = Engine(cfg, shard_weights(fw, cfg.model, rank, world, device=dev), device=dev, collectives=coll,
+                     num_pages=64)
+        st = ServingLoop(eng, sch, rm, est_cycle_time=1.0).run()
+        eng.check_status(); coll.check_status()
+        eng.finalize()
+        assert len(st.retired) == 4
+        outs = {r.req_idx: r.output for r in st.retired}
+        # all ranks agree on every sampled token
+        flat = torch.tensor([t for i in sorted(outs) for t in outs[i]], device=dev)
+        gathered = [torch.empty_like(flat) for _ in range(world)]
+        dist.all_gather(gathered, flat)
+        assert all(torch.equal(gathered[0], t) for t in gathered), "ranks disagree on sampled tokens"
+        for i, out in outs.items():
+            seq = torch.tensor(prompts[i].tolist() + out[:-1])
+            logits, _ = oracle.forward(seq)
+            steps = logits[31:]
+            gap = steps.max(dim=-1).values - steps[torch.arange(16), torch.tensor(out)]
+            assert gap.max().item() < 0.05 * steps.abs().max().item(), f"{ptype}: token far from oracle arg-max"
+        coll.close()
+        dist.barrier()
+
+
+def case_timeout(rank, world, dev):
+    """A collective whose peers never arrive ends by itself with a status code; the context stays usable.
+    Rank 0 alone calls the all-reduce (nobody else signals), then everyone proves the GPU still works."""
+    coll = TpCollectives(rank, world, dev, heap_bytes=16 << 20)
+    buf = coll.alloc((8, 256), torch.bfloat16)
+    spare = coll.new_flags()
+    torch.cuda.synchronize(); dist.barrier()
+    if rank == 0:
+        coll.all_reduce_(buf, flag_off=spare, epoch=1)
+        torch.cuda.synchronize()
+        try:
+            coll.check_status()
+            raise AssertionError("expected a peer-flag timeout")
+        except RuntimeError as e:
+            assert "0x500" in str(e)
+    dist.barrier()
+    x = torch.ones(4, device=dev)
+    dist.all_reduce(x)
+    assert x[0].item() == world
+    coll.close()
+
+
+if __name__ == "__main__":
+    case = sys.argv[1]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    {"collectives": case_collectives, "engine": case_engine, "timeout": case_timeout}[case](rank, world, dev)
+    dist.barrier()
+    if rank == 0:
+        print(f"MP_WORKER_OK {case}", flush=True)
+    dist.destroy_process_group()

@@ -61,10 +61,8 @@ def _run(pipeline_type, nano, executor, gbs=48):
 @pytest.mark.parametrize("pipeline_type,nano", [("NON_OVERLAP_LOCAL", None), ("NANOBATCH_LOCAL", [16, 32]),
                                                 ("LOCAL", [16, 32])])
 def test_engine_matches_oracle_py_executor(pipeline_type, nano):
-    exact = _run(pipeline_type, nano, "python")
-    assert exact >= 3
+    _run(pipeline_type, nano, "python")   # asserts greedy consistency with the oracle
 
 
 def test_engine_matches_oracle_native_executor():
-    exact = _run("LOCAL", [16, 32], "native")
-    assert exact >= 3
+    _run("LOCAL", [16, 32], "native")

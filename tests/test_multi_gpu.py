@@ -1,0 +1,38 @@
+"""Multi-GPU tests (need >= 2 GPUs): collectives exactness, TP engine vs oracle, bounded peer waits.
+Each case runs as child processes, one per GPU, NVLS off in NCCL (a rank leaving early must not
+disturb multicast bindings)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _launch(case, n, port):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "mp_worker.py"), case]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert res.returncode == 0 and f"MP_WORKER_OK {case}" in res.stdout, res.stdout[-3000:] + res.stderr[-3000:]
+    return res.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("case,port", [("collectives", 29611), ("engine", 29612), ("timeout", 29613)])
+def test_two_gpus(case, port):
+    print(_launch(case, 2, port))
+
+
+@pytest.mark.skipif(_ngpu() < 8, reason="needs 8 GPUs")
+@pytest.mark.parametrize("case,port", [("collectives", 29621), ("engine", 29622)])
+def test_eight_gpus(case, port):
+    print(_launch(case, 8, port))
