@@ -106,6 +106,8 @@ def main():
     ap.add_argument("--pipeline", default="", help="override pipeline_type")
     ap.add_argument("--skip-cycles", type=int, default=1600)
     ap.add_argument("--executor", default="auto")
+    ap.add_argument("--timeline", default="", help="after the timed regions, time every op of one iteration "
+                    "with CUDA events and write the aggregate + Chrome trace to this file")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -236,6 +238,20 @@ def main():
     tokens_e2e = loop.stats.tokens_processed - tok1
     clocks = sampler.stop(tw0, time.perf_counter())
     eng.check_status()
+
+    if args.timeline:
+        from nanoflow_b200.utils import timeline as tl
+        loop._release()
+        plan = sch.schedule()
+        eng.update(plan)
+        eng.run_async(timed=True)
+        toks = eng.run_async_wait()
+        sch.process_outputs(plan, toks)
+        ev = eng.timeline()
+        if rank == 0:
+            tl.dump(ev, args.timeline, pid=rank)
+            agg = tl.aggregate(ev)
+            print("timeline:", json.dumps({k: v for k, v in list(agg.items())[:14]}), file=sys.stderr)
 
     if world > 1:
         t = torch.tensor([dev_ms, e2e_s * 1e3], device=dev, dtype=torch.float64)

@@ -150,8 +150,46 @@ def bench_norm():
                               frac_of_peak=round(nbytes / med / 1e6 / bw_peak, 3), peak=how)), flush=True)
 
 
+def small_case(which: str):
+    """A few launches of one kernel on inputs larger than L2 (for a profiler capture)."""
+    if which == "gemm":
+        M, N, K = 4096, 8192, 8192
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        for _ in range(4):
+            ops.gemm(a, w, out=out)
+    elif which == "swiglu":
+        M, N, K = 4096, 7168, 8192
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
+        w2 = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        for _ in range(4):
+            ops.gemm_swiglu(a, w, w2, out=out)
+    elif which == "decode":
+        pool, qo, kvp, kvi, last = _paged(512, 1280, 8, 128)
+        q = torch.randn(512, 64 * 128, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        for _ in range(4):
+            ops.attn_decode(q, out, pool, qo, kvp, kvi, last, q_heads=64, req_begin=0, req_count=512)
+    elif which == "prefill":
+        pool, qo, kvp, kvi, last = _paged(4, 1024, 8, 128, qo_len=1024)
+        q = torch.randn(4096, 64 * 128, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        items = torch.tensor([[b, b * 1024 + t, 16] for b in range(4) for t in range(0, 1024, 16)],
+                             dtype=torch.int32, device="cuda")
+        for _ in range(4):
+            ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, items, q_heads=64)
+    torch.cuda.synchronize()
+    print("small case done:", which)
+
+
 def main(argv):
     what = argv[1] if len(argv) > 1 else "all"
+    if what.startswith("small_"):
+        small_case(what[len("small_"):])
+        return
     if what in ("gemm", "all"):
         bench_gemm()
     if what in ("swiglu", "all"):

@@ -117,14 +117,15 @@ class TpCollectives(CollectiveHooks):
         return self._epoch
 
     def all_reduce_(self, buf: torch.Tensor, *, norm_w=None, norm_out=None, eps: float = 1e-5,
-                    num_ctas: int = 0, flag_off: Optional[int] = None, epoch: Optional[int] = None):
+                    num_ctas: int = 0, flag_off: Optional[int] = None, epoch: Optional[int] = None,
+                    rows: Optional[int] = None):
         """In-place sum of a symmetric bf16 [rows, cols] tensor over all ranks (launches on the
         current stream). All ranks must call it the same number of times with the same flag block."""
         p = AllReduceParams()
         p.ctx = self.ctx()
         p.buf_off = self.heap.offset_of(buf)
         p.flag_off = self._adhoc_flags if flag_off is None else flag_off
-        p.rows, p.cols, p.ld = buf.shape[0], buf.shape[1], buf.stride(0)
+        p.rows, p.cols, p.ld = (buf.shape[0] if rows is None else rows), buf.shape[1], buf.stride(0)
         p.epoch = self._next_epoch() if epoch is None else epoch
         p.num_ctas = num_ctas or self.num_ctas
         if norm_w is not None:

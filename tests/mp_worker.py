@@ -23,12 +23,13 @@ def case_collectives(rank, world, dev):
     # exact integer pattern (the reference's comm_test.cu:15 uses (i*rank)%101, exact in fp16; here
     # values < 101 * world stay exact in bf16 only when small, so use (i*(rank+1)) % 13)
     for rows, cols in [(64, 1024), (37, 8192), (1, 256), (0, 512), (300, 4096)]:
-        buf = coll.alloc((max(rows, 1), cols), torch.bfloat16)[:rows]
+        full = coll.alloc((max(rows, 1), cols), torch.bfloat16)
+        buf = full[:rows]
         idx = torch.arange(rows * cols, device=dev).reshape(rows, cols)
         buf.copy_(((idx * (rank + 1)) % 13).to(torch.bfloat16))
         want = sum(((idx * (r + 1)) % 13).float() for r in range(world))
         torch.cuda.synchronize(); dist.barrier()
-        coll.all_reduce_(buf)
+        coll.all_reduce_(full, rows=rows)      # rows == 0 still takes part in the handshakes
         torch.cuda.synchronize()
         coll.check_status()
         assert torch.equal(buf.float(), want), f"all-reduce mismatch {rows}x{cols} on rank {rank}"
@@ -164,7 +165,12 @@ if __name__ == "__main__":
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    {"collectives": case_collectives, "engine": case_engine, "timeout": case_timeout}[case](rank, world, dev)
+    try:
+        {"collectives": case_collectives, "engine": case_engine, "timeout": case_timeout}[case](rank, world, dev)
+    except BaseException:
+        import traceback
+        print(f"MP_WORKER_FAIL rank {rank}\n" + traceback.format_exc(), flush=True)
+        raise
     dist.barrier()
     if rank == 0:
         print(f"MP_WORKER_OK {case}", flush=True)
