@@ -4,6 +4,10 @@
 //   D[M,N] = A[M,K] * B[N,K]^T (+ bias[N]) (+ beta * C[M,N])            (linear epilogue)
 //   D[M,F] = silu(A * Bg[F,K]^T) .* (A * Bu[F,K]^T)                      (SwiGLU epilogue)
 //
+// Work units are whole output tiles, or with split-K (tile, k range) pairs whose fp32 partial tiles
+// a second pass adds up. For small M one CTA can cover several M tiles with the same weight tile,
+// so each weight byte is fetched into shared memory once. A cost model picks the shape.
+//
 // Roles inside one 192-thread CTA: warp 0 lane 0 = TMA producer, warp 1 = TMEM owner and (lane 0)
 // MMA issuer, warps 2..5 = epilogue (TMEM -> registers -> global). Two TMEM accumulators are
 // ping-ponged so the epilogue of tile i overlaps the main loop of tile i+1.
@@ -54,24 +58,37 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kGemmThreads = 192;
+constexpr int kSmemBudget = 227 * 1024 - 2048;
 
-template <int BN>
+// BN = tile width in weight rows; MT = number of 128-row M tiles one CTA covers with the same B
+// tile (MT > 1 is the small-M, weight-streaming shape: every weight byte enters shared memory once).
+template <int BN, int MT>
 struct Cfg {
-  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int A_TILE_BYTES = BM * BK * 2;
+  static constexpr int A_BYTES = MT * A_TILE_BYTES;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
-  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int STAGES_RAW = kSmemBudget / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int ACC_COLS = MT * BN;                       // fp32 columns of one accumulator set
+  static constexpr int ACC_BUFS = ACC_COLS <= 256 ? 2 : 1;       // ping-pong when TMEM has room
+  static constexpr int TMEM_NEED = ACC_COLS * ACC_BUFS;
+  static constexpr int TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128
+                                   : TMEM_NEED <= 256 ? 256 : 512;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static_assert(STAGES >= 2, "tile does not fit shared memory");
+  static_assert(TMEM_NEED <= 512, "accumulators exceed TMEM");
 };
 
 struct DevParams {
   __nv_bfloat16* D;
   const __nv_bfloat16* C;
   const __nv_bfloat16* bias;
+  float* partial;   // split-K: fp32 [split_k][M][N] partial sums (second pass reduces them)
   long long ldd, ldc;
   float beta;
-  int M, N, K;  // N = number of output columns
+  int M, N, K;      // N = number of output columns
+  int split_k;
   unsigned int* status;
 };
 
@@ -99,12 +116,38 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
   }
 }
 
-template <int BN, int EPI>
+// ---- work distribution -----------------------------------------------------------------------------
+// The output is cut into tiles (m group x n block; m groups vary fastest so CTAs that run together
+// share B panels in L2) and, with split-K, each tile's k-blocks into split_k equal ranges. A work
+// unit is (tile, k range); CTA c takes units c, c+G, ... A k range that is only part of K is written
+// as an fp32 partial tile and a second pass adds the partials and applies the epilogue.
+struct Segment {
+  int tile, ks, kb0, kb1;
+};
+struct Walk {
+  int cur, units, tiles, num_kb, kb_per, step;
+  __device__ __forceinline__ Walk(int cta, int G, int tiles_, int num_kb_, int split_k)
+      : cur(cta), units(tiles_ * split_k), tiles(tiles_), num_kb(num_kb_),
+        kb_per((num_kb_ + split_k - 1) / split_k), step(G) {}
+  __device__ __forceinline__ bool next(Segment& s) {
+    if (cur >= units) return false;
+    s.tile = cur % tiles;
+    s.ks = cur / tiles;
+    s.kb0 = min(num_kb, s.ks * kb_per);
+    s.kb1 = min(num_kb, s.kb0 + kb_per);
+    cur += step;
+    return true;
+  }
+};
+
+template <int BN, int MT, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                     const __grid_constant__ CUtensorMap tmB1, DevParams p) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, MT>;
   constexpr int STAGES = C::STAGES;
+  constexpr int ACC_BUFS = C::ACC_BUFS;
+  constexpr int ACC_COLS = C::ACC_COLS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -115,16 +158,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint64_t* tmem_empty = bars + 2 * STAGES + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
+  
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   // Output tile width: the SwiGLU epilogue folds a gate half and an up half of BN/2 columns each.
   constexpr int OUT_BN = (EPI == 1) ? BN / 2 : BN;
-  const int m_blocks = (p.M + BM - 1) / BM;
+  const int m_tiles = (p.M + BM - 1) / BM;
+  const int m_groups = (m_tiles + MT - 1) / MT;
   const int n_blocks = (p.N + OUT_BN - 1) / OUT_BN;
-  const int num_tiles = m_blocks * n_blocks;
   const int num_kb = (p.K + BK - 1) / BK;
+  const int tiles = m_groups * n_blocks;
+  const int sk = p.split_k;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -154,10 +199,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------- TMA producer ----------------
     uint32_t it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m_blk = tile % m_blocks;
-      const int n_blk = tile / m_blocks;
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+    Walk walk(blockIdx.x, gridDim.x, tiles, num_kb, sk);
+    Segment sg;
+    while (ok && walk.next(sg)) {
+      const int m_grp = sg.tile % m_groups, n_blk = sg.tile / m_groups;
+      const int mt_valid = min(MT, m_tiles - m_grp * MT);
+      for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
         if (!wait_or_abort(&empty_bar[s], ph ^ 1, abort_flag)) {
@@ -168,14 +215,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         uint8_t* sa = smem + s * C::STAGE_BYTES;
         uint8_t* sb = sa + C::A_BYTES;
-        mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
-        tma_load_2d(sa, &tmA, &full_bar[s], kb * BK, m_blk * BM);
+        mbar_expect_tx(&full_bar[s], mt_valid * C::A_TILE_BYTES + C::B_BYTES);
         if (EPI == 1) {
           tma_load_2d(sb, &tmB0, &full_bar[s], kb * BK, n_blk * OUT_BN);
           tma_load_2d(sb + C::B_BYTES / 2, &tmB1, &full_bar[s], kb * BK, n_blk * OUT_BN);
         } else {
           tma_load_2d(sb, &tmB0, &full_bar[s], kb * BK, n_blk * BN);
         }
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+          if (mt < mt_valid)
+            tma_load_2d(sa + mt * C::A_TILE_BYTES, &tmA, &full_bar[s], kb * BK, (m_grp * MT + mt) * BM);
       }
     }
     if (!ok) {
@@ -203,17 +253,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
     uint32_t it = 0, tcount = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
-      const uint32_t acc = tcount & 1;
-      const uint32_t acc_ph = (tcount >> 1) & 1;
+    Walk walk(blockIdx.x, gridDim.x, tiles, num_kb, sk);
+    Segment sg;
+    while (ok && walk.next(sg)) {
+      const int m_grp = sg.tile % m_groups;
+      const int mt_valid = min(MT, m_tiles - m_grp * MT);
+      const uint32_t acc = (ACC_BUFS == 2) ? (tcount & 1) : 0;
+      const uint32_t acc_ph = (ACC_BUFS == 2) ? ((tcount >> 1) & 1) : (tcount & 1);
       if (!wait_or_abort(&tmem_empty[acc], acc_ph ^ 1, abort_flag)) {
         report_status(p.status, NF_ST_TIMEOUT_TMEM_EMPTY);
         *abort_flag = 1;
         break;
       }
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + acc * BN;
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+      const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+      for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
         if (!wait_or_abort(&full_bar[s], ph, abort_flag)) {
@@ -226,24 +280,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
         const uint32_t b_addr = a_addr + C::A_BYTES;
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          const uint64_t da = umma_desc_k_sw128(a_addr + k * UMMA_K * 2);
-          const uint64_t db = umma_desc_k_sw128(b_addr + k * UMMA_K * 2);
-          umma_bf16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+        for (int mt = 0; mt < MT; ++mt) {
+          if (mt < mt_valid) {
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t da = umma_desc_k_sw128(a_addr + mt * C::A_TILE_BYTES + k * UMMA_K * 2);
+              const uint64_t db = umma_desc_k_sw128(b_addr + k * UMMA_K * 2);
+              umma_bf16_ss(d_tmem + mt * BN, da, db, idesc, (kb != sg.kb0 || k != 0) ? 1u : 0u);
+            }
+          }
         }
         umma_commit(&empty_bar[s]);  // stage is free once these MMAs have read it
       }
       if (ok) umma_commit(&tmem_full[acc]);
+      ++tcount;
     }
   } else if (warp >= 2) {
-    // ---------------- epilogue ----------------
+    // ---------------- epilogue (4 warps, 128 threads) ----------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t tcount = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
-      const int m_blk = tile % m_blocks;
-      const int n_blk = tile / m_blocks;
-      const uint32_t acc = tcount & 1;
-      const uint32_t acc_ph = (tcount >> 1) & 1;
+    Walk walk(blockIdx.x, gridDim.x, tiles, num_kb, sk);
+    Segment sg;
+    while (walk.next(sg)) {
+      const int m_grp = sg.tile % m_groups, n_blk = sg.tile / m_groups;
+      const int mt_valid = min(MT, m_tiles - m_grp * MT);
+      const uint32_t acc = (ACC_BUFS == 2) ? (tcount & 1) : 0;
+      const uint32_t acc_ph = (ACC_BUFS == 2) ? ((tcount >> 1) & 1) : (tcount & 1);
+      ++tcount;
       if (!wait_or_abort(&tmem_full[acc], acc_ph, abort_flag)) {
         if (lane == 0) report_status(p.status, NF_ST_TIMEOUT_TMEM_FULL);
         *abort_flag = 1;
@@ -251,67 +314,89 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       __syncwarp();
       tc_fence_after();
-      const int row = m_blk * BM + q * 32 + lane;
-      const bool row_ok = row < p.M;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      __nv_bfloat16* drow = p.D + static_cast<long long>(row) * p.ldd;
-      const __nv_bfloat16* crow =
-          (EPI == 0 && p.C != nullptr) ? p.C + static_cast<long long>(row) * p.ldc : nullptr;
+      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * ACC_COLS;
+      // a k range that received no k-blocks contributes zeros (its accumulator was never written)
+      const bool empty_range = sg.kb0 >= sg.kb1;
+      {
 #pragma unroll 1
-      for (int c = 0; c < OUT_BN / 32; ++c) {
-        uint32_t r[32];
-        float v[32];
-        tmem_ld_32x32b_x32(t_row + c * 32, r);
-        if (EPI == 1) {
-          uint32_t u[32];
-          tmem_ld_32x32b_x32(t_row + BN / 2 + c * 32, u);
-          tmem_ld_wait();
+        for (int mt = 0; mt < mt_valid; ++mt) {
+          const int row = (m_grp * MT + mt) * BM + q * 32 + lane;
+          const bool row_ok = row < p.M;
+          __nv_bfloat16* drow = p.D + static_cast<long long>(row) * p.ldd;
+          const __nv_bfloat16* crow =
+              (EPI == 0 && p.C != nullptr) ? p.C + static_cast<long long>(row) * p.ldc : nullptr;
+#pragma unroll 1
+          for (int c = 0; c < OUT_BN / 32; ++c) {
+            uint32_t r[32];
+            float v[32];
+            tmem_ld_32x32b_x32(t_lane + mt * BN + c * 32, r);
+            if (EPI == 1) {
+              uint32_t uu[32];
+              tmem_ld_32x32b_x32(t_lane + mt * BN + BN / 2 + c * 32, uu);
+              tmem_ld_wait();
+              float gsum[32], usum[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float g = __uint_as_float(r[j]);
-            const float up = __uint_as_float(u[j]);
-            v[j] = g / (1.0f + __expf(-g)) * up;
-          }
-        } else {
-          tmem_ld_wait();
+              for (int j = 0; j < 32; ++j) {
+                gsum[j] = __uint_as_float(r[j]);
+                usum[j] = __uint_as_float(uu[j]);
+              }
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        }
-        const int col0 = n_blk * OUT_BN + c * 32;
-        if (row_ok && col0 < p.N) {
+              for (int j = 0; j < 32; ++j) v[j] = gsum[j] / (1.0f + __expf(-gsum[j])) * usum[j];
+            } else {
+              tmem_ld_wait();
 #pragma unroll
-          for (int g8 = 0; g8 < 4; ++g8) {
-            const int col = col0 + g8 * 8;
-            if (col < p.N) {  // N is a multiple of 8
-              float* vv = v + g8 * 8;
-              if (EPI == 0) {
-                if (p.bias != nullptr) {
-                  const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
-                  const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+              for (int j = 0; j < 32; ++j) v[j] = empty_range ? 0.f : __uint_as_float(r[j]);
+            }
+            const int col0 = n_blk * OUT_BN + c * 32;
+            if (EPI == 0 && p.partial != nullptr) {
+              if (row_ok && col0 < p.N) {
+                float* prow = p.partial + (static_cast<long long>(sg.ks) * p.M + row) * p.N;
 #pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    const float2 f = unpack_bf16x2(bw[j]);
-                    vv[2 * j] += f.x;
-                    vv[2 * j + 1] += f.y;
-                  }
-                }
-                if (crow != nullptr) {
-                  const uint4 cv = *reinterpret_cast<const uint4*>(crow + col);
-                  const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    const float2 f = unpack_bf16x2(cw[j]);
-                    vv[2 * j] += p.beta * f.x;
-                    vv[2 * j + 1] += p.beta * f.y;
-                  }
+                for (int g4 = 0; g4 < 8; ++g4) {
+                  const int col = col0 + g4 * 4;
+                  if (col < p.N)
+                    *reinterpret_cast<float4*>(prow + col) =
+                        make_float4(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2], v[g4 * 4 + 3]);
                 }
               }
-              uint4 o;
-              o.x = pack_bf16x2(vv[0], vv[1]);
-              o.y = pack_bf16x2(vv[2], vv[3]);
-              o.z = pack_bf16x2(vv[4], vv[5]);
-              o.w = pack_bf16x2(vv[6], vv[7]);
-              *reinterpret_cast<uint4*>(drow + col) = o;
+              continue;
+            }
+            if (row_ok && col0 < p.N) {
+#pragma unroll
+              for (int g8 = 0; g8 < 4; ++g8) {
+                const int col = col0 + g8 * 8;
+                if (col < p.N) {  // N is a multiple of 8
+                  float* vv = v + g8 * 8;
+                  if (EPI == 0) {
+                    if (p.bias != nullptr) {
+                      const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+                      const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                      for (int j = 0; j < 4; ++j) {
+                        const float2 f = unpack_bf16x2(bw[j]);
+                        vv[2 * j] += f.x;
+                        vv[2 * j + 1] += f.y;
+                      }
+                    }
+                    if (crow != nullptr) {
+                      const uint4 cv = *reinterpret_cast<const uint4*>(crow + col);
+                      const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+                      for (int j = 0; j < 4; ++j) {
+                        const float2 f = unpack_bf16x2(cw[j]);
+                        vv[2 * j] += p.beta * f.x;
+                        vv[2 * j + 1] += p.beta * f.y;
+                      }
+                    }
+                  }
+                  uint4 o;
+                  o.x = pack_bf16x2(vv[0], vv[1]);
+                  o.y = pack_bf16x2(vv[2], vv[3]);
+                  o.z = pack_bf16x2(vv[4], vv[5]);
+                  o.w = pack_bf16x2(vv[6], vv[7]);
+                  *reinterpret_cast<uint4*>(drow + col) = o;
+                }
+              }
             }
           }
         }
@@ -341,9 +426,53 @@ int sm_count() {
   return n;
 }
 
-template <int BN, int EPI>
-int launch(const nfk_gemm_params& g, cudaStream_t stream) {
-  using C = Cfg<BN>;
+// Split-K second pass: D = sum_s partial[s] (+ bias) (+ beta * C), fp32 -> bf16.
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(DevParams p) {
+  const long long total = static_cast<long long>(p.M) * (p.N >> 3);
+  const long long slab = static_cast<long long>(p.M) * p.N;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += 256ll * gridDim.x) {
+    const int row = static_cast<int>(i / (p.N >> 3));
+    const int col = static_cast<int>(i % (p.N >> 3)) * 8;
+    float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = 0; s < p.split_k; ++s) {
+      const float4* src = reinterpret_cast<const float4*>(p.partial + s * slab + static_cast<long long>(row) * p.N + col);
+      const float4 a = src[0], b = src[1];
+      v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+      v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+    }
+    if (p.bias != nullptr) {
+      const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+      const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(bw[j]);
+        v[2 * j] += f.x;
+        v[2 * j + 1] += f.y;
+      }
+    }
+    if (p.C != nullptr) {
+      const uint4 cv = *reinterpret_cast<const uint4*>(p.C + static_cast<long long>(row) * p.ldc + col);
+      const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(cw[j]);
+        v[2 * j] += p.beta * f.x;
+        v[2 * j + 1] += p.beta * f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(v[0], v[1]);
+    o.y = pack_bf16x2(v[2], v[3]);
+    o.z = pack_bf16x2(v[4], v[5]);
+    o.w = pack_bf16x2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(p.D + static_cast<long long>(row) * p.ldd + col) = o;
+  }
+}
+
+template <int BN, int MT, int EPI>
+int launch(const nfk_gemm_params& g, int split_k, cudaStream_t stream) {
+  using C = Cfg<BN, MT>;
   constexpr int OUT_BN = (EPI == 1) ? BN / 2 : BN;
   CUtensorMap tmA, tmB0, tmB1;
   int rc = make_tmap_bf16_2d(&tmA, g.A, g.M, g.K, g.lda, BM, BK);
@@ -358,30 +487,91 @@ int launch(const nfk_gemm_params& g, cudaStream_t stream) {
   }
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>,
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, MT, EPI>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                              C::SMEM_BYTES) != cudaSuccess)
       return NF_ERR_CUDA;
     attr_set = true;
   }
-  const int m_blocks = (g.M + BM - 1) / BM;
+  const int m_tiles = (g.M + BM - 1) / BM;
+  const int m_groups = (m_tiles + MT - 1) / MT;
   const int n_blocks = (g.N + OUT_BN - 1) / OUT_BN;
-  const int tiles = m_blocks * n_blocks;
+  const int units = m_groups * n_blocks * split_k;
   int ctas = g.num_ctas > 0 ? g.num_ctas : sm_count();
-  if (ctas > tiles) ctas = tiles;
+  if (ctas > units) ctas = units;
   DevParams p;
   p.D = reinterpret_cast<__nv_bfloat16*>(g.D);
   p.C = reinterpret_cast<const __nv_bfloat16*>(g.C);
   p.bias = reinterpret_cast<const __nv_bfloat16*>(g.bias);
+  p.partial = split_k > 1 ? reinterpret_cast<float*>(g.workspace) : nullptr;
   p.ldd = g.ldd;
   p.ldc = g.ldc;
   p.beta = g.beta;
   p.M = g.M;
   p.N = g.N;
   p.K = g.K;
+  p.split_k = split_k;
   p.status = g.status;
-  gemm_tcgen05_kernel<BN, EPI><<<ctas, kGemmThreads, C::SMEM_BYTES, stream>>>(tmA, tmB0, tmB1, p);
-  return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
+  gemm_tcgen05_kernel<BN, MT, EPI><<<ctas, kGemmThreads, C::SMEM_BYTES, stream>>>(tmA, tmB0, tmB1, p);
+  if (cudaGetLastError() != cudaSuccess) return NF_ERR_CUDA;
+  if (split_k > 1) {
+    const long long total = static_cast<long long>(g.M) * (g.N >> 3);
+    long long blocks = (total + 255) / 256;
+    if (blocks > 4ll * sm_count()) blocks = 4ll * sm_count();
+    splitk_reduce_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(p);
+    if (cudaGetLastError() != cudaSuccess) return NF_ERR_CUDA;
+  }
+  return NF_OK;
+}
+
+// Tile-shape choice when the caller leaves it open: a small cost model over the candidate shapes.
+// A unit (tile x k range) costs its k-blocks times the per-k-block time of the tile shape (the
+// larger of tensor time and shared-memory fill time) plus a fixed prologue/epilogue; the GEMM costs
+// waves x unit cost, plus the reduce pass when K is split. MT > 1 shapes let one CTA cover several
+// M tiles with one weight tile (each weight byte enters shared memory once), which wins when M is
+// small and the GEMM is bound by streaming the weight.
+struct Shape {
+  int bn, mt, split_k;
+};
+Shape choose_shape(const nfk_gemm_params& g, bool swiglu) {
+  const int ctas = g.num_ctas > 0 ? g.num_ctas : sm_count();
+  const int m_tiles = (g.M + BM - 1) / BM;
+  const int num_kb = (g.K + BK - 1) / BK;
+  static const int cand_lin[][2] = {{256, 1}, {128, 1}, {64, 1}, {256, 2}, {128, 2}, {128, 4}};
+  static const int cand_sw[][2] = {{256, 1}, {128, 1}, {256, 2}, {128, 2}, {128, 4}};
+  const int ncand = swiglu ? 5 : 6;
+  Shape best{256, 1, 1};
+  double best_cost = 1e30;
+  for (int i = 0; i < ncand; ++i) {
+    const int bn = swiglu ? cand_sw[i][0] : cand_lin[i][0];
+    const int mt = swiglu ? cand_sw[i][1] : cand_lin[i][1];
+    if (mt > 1 && m_tiles < mt && !(mt == 2 && m_tiles == 2)) {
+      if (m_tiles <= mt / 2) continue;             // most of the M tiles would be empty
+    }
+    const int out_bn = swiglu ? bn / 2 : bn;
+    const int m_groups = (m_tiles + mt - 1) / mt;
+    const int n_blocks = (g.N + out_bn - 1) / out_bn;
+    const int tiles = m_groups * n_blocks;
+    const int mt_eff = m_tiles < mt ? m_tiles : mt;
+    // per k-block: tensor time (us) at ~11 TFLOP/s per SM, smem fill at ~110 GB/s per SM
+    const double t_mma = 2.0 * BM * mt_eff * bn * BK / 11.0e6;
+    const double t_fill = (mt_eff * 16384.0 + bn * 128.0) / 110.0e3;
+    const double t_kb = t_mma > t_fill ? t_mma : t_fill;
+    const int max_sk = (swiglu || g.workspace == nullptr) ? 1 : 8;
+    for (int sk = 1; sk <= max_sk; ++sk) {
+      if (sk > 1 && (num_kb / sk < 8 || static_cast<long long>(sk) * g.M * g.N * 4 > g.workspace_bytes)) break;
+      const int units = tiles * sk;
+      const int waves = (units + ctas - 1) / ctas;
+      const int kb_per = (num_kb + sk - 1) / sk;
+      double cost = waves * (kb_per * t_kb + 2.5 + 0.004 * mt_eff * bn);
+      if (sk > 1) cost += 3.0 + (sk + 1.0) * g.M * static_cast<double>(g.N) * 4.0 / 4.0e6;  // partial write + reduce
+      if (cost < best_cost) {
+        best_cost = cost;
+        best = Shape{bn, mt, sk};
+      }
+    }
+  }
+  return best;
 }
 
 }  // namespace
@@ -398,27 +588,43 @@ extern "C" int nfk_gemm_bf16(const nfk_gemm_params* g, cudaStream_t stream) {
   if ((reinterpret_cast<uintptr_t>(g->D) & 15) != 0) return NF_ERR_BAD_ARG;
   if (g->C != nullptr && ((reinterpret_cast<uintptr_t>(g->C) & 15) != 0 || g->ldc % 8 != 0))
     return NF_ERR_BAD_ARG;
-  if (g->epilogue == NFK_EPI_SWIGLU) {
-    if (g->B2 == nullptr) return NF_ERR_BAD_ARG;
-    switch (g->tile_n) {
-      case 0:
-      case 256: return launch<256, 1>(*g, stream);
-      case 128: return launch<128, 1>(*g, stream);
+  if (g->workspace != nullptr && (reinterpret_cast<uintptr_t>(g->workspace) & 15) != 0) return NF_ERR_BAD_ARG;
+  const bool swiglu = g->epilogue == NFK_EPI_SWIGLU;
+  if (swiglu && g->B2 == nullptr) return NF_ERR_BAD_ARG;
+
+  Shape s = choose_shape(*g, swiglu);
+  if (g->tile_n != 0 || g->tile_m != 0) {
+    // pinned tile shape: fill in the other dimension with its default, split only on request
+    s.bn = g->tile_n != 0 ? g->tile_n : 256;
+    s.mt = g->tile_m != 0 ? g->tile_m : 1;
+    s.split_k = 1;
+  }
+  if (g->split_k != 0) s.split_k = g->split_k;
+  if (s.split_k < 1 || s.split_k > 16) return NF_ERR_BAD_ARG;
+  if (s.split_k > 1) {
+    if (swiglu || g->workspace == nullptr ||
+        static_cast<long long>(s.split_k) * g->M * g->N * 4 > g->workspace_bytes)
+      return NF_ERR_BAD_ARG;
+  }
+  const int key = s.bn * 10 + s.mt;
+  if (swiglu) {
+    switch (key) {
+      case 2561: return launch<256, 1, 1>(*g, 1, stream);
+      case 1281: return launch<128, 1, 1>(*g, 1, stream);
+      case 2562: return launch<256, 2, 1>(*g, 1, stream);
+      case 1282: return launch<128, 2, 1>(*g, 1, stream);
+      case 1284: return launch<128, 4, 1>(*g, 1, stream);
       default: return NF_ERR_UNSUPPORTED;
     }
   }
-  int bn = g->tile_n;
-  if (bn == 0) {
-    // Pick the widest tile that still gives every SM of the budget a tile.
-    const int ctas = g->num_ctas > 0 ? g->num_ctas : sm_count();
-    const int m_blocks = (g->M + BM - 1) / BM;
-    bn = 256;
-    while (bn > 64 && m_blocks * ((g->N + bn - 1) / bn) < ctas) bn >>= 1;
-  }
-  switch (bn) {
-    case 256: return launch<256, 0>(*g, stream);
-    case 128: return launch<128, 0>(*g, stream);
-    case 64: return launch<64, 0>(*g, stream);
+  switch (key) {
+    case 2561: return launch<256, 1, 0>(*g, s.split_k, stream);
+    case 1281: return launch<128, 1, 0>(*g, s.split_k, stream);
+    case 641: return launch<64, 1, 0>(*g, s.split_k, stream);
+    case 2562: return launch<256, 2, 0>(*g, s.split_k, stream);
+    case 1282: return launch<128, 2, 0>(*g, s.split_k, stream);
+    case 1284: return launch<128, 4, 0>(*g, s.split_k, stream);
+    case 644: return launch<64, 4, 0>(*g, s.split_k, stream);
     default: return NF_ERR_UNSUPPORTED;
   }
 }

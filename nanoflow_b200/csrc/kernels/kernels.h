@@ -29,6 +29,10 @@ typedef struct nfk_gemm_params {
   int tile_n;       // 0 = choose; 64 / 128 / 256
   int num_ctas;     // CTA budget of the persistent grid; 0 = one per SM
   unsigned int* status;  // optional device word: first non-zero NF_ST_* code wins
+  int tile_m;       // 0 = choose; number of 128-row M tiles one CTA covers: 1 / 2 / 4
+  int split_k;      // 0 = choose; > 1 needs `workspace` (fp32 partials, split_k*M*N*4 bytes)
+  void* workspace;
+  long long workspace_bytes;
 } nfk_gemm_params;
 
 int nfk_gemm_bf16(const nfk_gemm_params* p, cudaStream_t stream);

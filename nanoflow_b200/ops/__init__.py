@@ -35,7 +35,8 @@ class GemmParams(Structure):
                 ("lda", c_longlong), ("ldb", c_longlong), ("ldd", c_longlong), ("ldc", c_longlong),
                 ("beta", c_float), ("M", c_int), ("N", c_int), ("K", c_int),
                 ("epilogue", c_int), ("tile_n", c_int), ("num_ctas", c_int),
-                ("status", c_void_p)]
+                ("status", c_void_p), ("tile_m", c_int), ("split_k", c_int), ("workspace", c_void_p),
+                ("workspace_bytes", c_longlong)]
 
 
 class RopeAppendParams(Structure):
@@ -114,8 +115,12 @@ def check_status(status: torch.Tensor, what: str = "kernel") -> None:
 def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, beta: float = 1.0,
          bias: Optional[torch.Tensor] = None, tile_n: int = 0, num_ctas: int = 0,
-         status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[M,N] = a[M,K] @ w[N,K]^T (+ bias) (+ beta * residual). Rows may be strided."""
+         status: Optional[torch.Tensor] = None, tile_m: int = 0, split_k: int = 0,
+         workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M,N] = a[M,K] @ w[N,K]^T (+ bias) (+ beta * residual). Rows may be strided.
+
+    ``tile_n`` / ``tile_m`` / ``split_k`` pin the kernel shape (0 = let the launcher's cost model
+    choose); split-K needs ``workspace`` (any dtype, >= split_k*M*N*4 bytes)."""
     _bf16(a, "a"); _bf16(w, "w")
     M, K = a.shape
     N, K2 = w.shape
@@ -142,13 +147,17 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     p.beta, p.M, p.N, p.K = beta, M, N, K
     p.epilogue, p.tile_n, p.num_ctas = 0, tile_n, num_ctas
     p.status = _p(status)
+    p.tile_m, p.split_k = tile_m, split_k
+    p.workspace = _p(workspace)
+    p.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     _check(lib().nfk_gemm_bf16(byref(p), _stream()), "nfk_gemm_bf16")
     return out
 
 
 def gemm_swiglu(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, *,
                 out: Optional[torch.Tensor] = None, tile_n: int = 0, num_ctas: int = 0,
-                status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                status: Optional[torch.Tensor] = None, tile_m: int = 0, split_k: int = 0,
+                workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[M,F] = silu(a @ w_gate^T) * (a @ w_up^T), gate and up products fused in one kernel."""
     _bf16(a, "a"); _bf16(w_gate, "w_gate"); _bf16(w_up, "w_up")
     M, K = a.shape
@@ -166,6 +175,9 @@ def gemm_swiglu(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, *,
     p.beta, p.M, p.N, p.K = 0.0, M, F, K
     p.epilogue, p.tile_n, p.num_ctas = 1, tile_n, num_ctas
     p.status = _p(status)
+    p.tile_m, p.split_k = tile_m, split_k
+    p.workspace = _p(workspace)
+    p.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     _check(lib().nfk_gemm_bf16(byref(p), _stream()), "nfk_gemm_bf16(swiglu)")
     return out
 

@@ -69,12 +69,13 @@ def bench_gemm(shapes=None, swiglu=False, tile_ns=(0,), num_ctas=0):
         w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
         w2 = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 if swiglu else None
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ws = torch.zeros(160 << 20, dtype=torch.uint8, device="cuda")
         for tn in tile_ns:
             if swiglu:
-                fn = lambda: ops.gemm_swiglu(a, w, w2, out=out, tile_n=tn, num_ctas=num_ctas)
+                fn = lambda: ops.gemm_swiglu(a, w, w2, out=out, tile_n=tn, num_ctas=num_ctas, workspace=ws)
                 flops = 4.0 * M * N * K
             else:
-                fn = lambda: ops.gemm(a, w, out=out, tile_n=tn, num_ctas=num_ctas)
+                fn = lambda: ops.gemm(a, w, out=out, tile_n=tn, num_ctas=num_ctas, workspace=ws)
                 flops = 2.0 * M * N * K
             med, best = time_ms(fn)
             ref_fn = (lambda: torch.matmul(a, w.t(), out=out))
@@ -189,6 +190,37 @@ def main(argv):
     what = argv[1] if len(argv) > 1 else "all"
     if what.startswith("small_"):
         small_case(what[len("small_"):])
+        return
+    if what == "smallm":
+        ws = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
+        bw_peak = peaks()[0]
+        for (M, N, K) in [(256, 10240, 8192), (256, 8192, 8192), (256, 8192, 28672), (128, 8192, 28672),
+                          (512, 8192, 28672), (256, 1280, 8192), (256, 8192, 3584), (85, 32000, 8192)]:
+            a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+            w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
+            out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            for (tm, tn, sk) in [(0, 0, 0), (2, 256, 1), (2, 256, 2), (2, 256, 4), (2, 128, 2), (2, 128, 4),
+                                 (1, 256, 4), (1, 128, 1), (1, 128, 2), (1, 64, 1)]:
+                try:
+                    med, _ = time_ms(lambda: ops.gemm(a, w, out=out, tile_m=tm, tile_n=tn, split_k=sk, workspace=ws))
+                except RuntimeError:
+                    continue
+                gbs = (N * K * 2 + M * K * 2 + M * N * 2) / med / 1e6
+                print(json.dumps(dict(op="gemm_smallm", M=M, N=N, K=K, tile_m=tm, tile_n=tn, split_k=sk,
+                                      ms=round(med, 4), gbs=round(gbs, 1), frac_of_bw=round(gbs / bw_peak, 3))), flush=True)
+            med, _ = time_ms(lambda: torch.matmul(a, w.t(), out=out))
+            print(json.dumps(dict(op="cublas", M=M, N=N, K=K, ms=round(med, 4),
+                                  gbs=round((N * K * 2 + M * K * 2 + M * N * 2) / med / 1e6, 1))), flush=True)
+        for (M, F, K) in [(256, 28672, 8192), (256, 3584, 8192)]:
+            a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+            w = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.02
+            w2 = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.02
+            out = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
+            for (tm, tn) in [(0, 0), (2, 256), (2, 128), (1, 256), (1, 128)]:
+                med, _ = time_ms(lambda: ops.gemm_swiglu(a, w, w2, out=out, tile_m=tm, tile_n=tn, workspace=ws))
+                gbs = (2 * F * K * 2) / med / 1e6
+                print(json.dumps(dict(op="swiglu_smallm", M=M, F=F, K=K, tile_m=tm, tile_n=tn, ms=round(med, 4),
+                                      gbs=round(gbs, 1), frac_of_bw=round(gbs / bw_peak, 3))), flush=True)
         return
     if what in ("gemm", "all"):
         bench_gemm()

@@ -34,6 +34,7 @@ from .pipeline import Buffers, CollectiveHooks, IoSpec, build_graph
 
 RING = 3                       # host staging slots (iterations in flight + one being formed)
 DECODE_MAX_CHUNKS = 16
+GEMM_WS_BYTES = 160 << 20      # stream-K scratch: tile counters + two fp32 partial tiles per CTA
 DECODE_SPLIT_ROWS = 8192       # workspace rows (request x q head) reserved for split-KV decode
 
 
@@ -115,7 +116,8 @@ class Engine:
             status=torch.zeros(1, dtype=torch.int32, device=dev),
             decode_ws=torch.empty(DECODE_SPLIT_ROWS * DECODE_MAX_CHUNKS * (m.head_dim + 2), dtype=torch.float32,
                                   device=dev),
-            meta=meta, nano_items=nano_items)
+            meta=meta, nano_items=nano_items,
+            gemm_ws=torch.zeros(GEMM_WS_BYTES // 4, dtype=torch.float32, device=dev))
         io = IoSpec(self.meta_dev, layout.fixed_words, layout.off["kv_indices"])
         self.graph: OpGraph = build_graph(m, e, weights, self.bufs, self.coll, io)
         self.tokens_host = [torch.zeros(B, dtype=torch.int32).pin_memory() for _ in range(RING)]

@@ -61,6 +61,7 @@ class Buffers:
     inv_freq: torch.Tensor           # [head_dim/2] fp32
     status: torch.Tensor             # [1] int32
     decode_ws: Optional[torch.Tensor]  # split-KV workspace (fp32)
+    gemm_ws: Optional[torch.Tensor] = None   # split-K partial sums (fp32); all GEMMs share one stream
     meta: Dict[str, torch.Tensor]    # int32 views into the metadata block (see engine.MetaLayout)
     nano_items: List[torch.Tensor]   # per nano-batch [cap,3] int32 views
 
@@ -144,6 +145,9 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         p.tile_n = eng.gemm_tile_n.get(tile_key or name.split(".")[-1], 0)
         p.num_ctas = budget.get("gemm", 0)
         p.status = _ptr(st)
+        if bufs.gemm_ws is not None:
+            p.workspace = _ptr(bufs.gemm_ws)
+            p.workspace_bytes = bufs.gemm_ws.numel() * bufs.gemm_ws.element_size()
         return g.add(name, p, "gemm", deps=deps, dyn=[("M", nb_T[k])], layer=layer, nano=k)
 
     def norm(name, x, wt, out, k, deps, layer, resid=None):
@@ -258,6 +262,9 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
     lp.lda, lp.ldb, lp.ldd, lp.ldc = bufs.sample_hn.stride(0), w.lm_head.stride(0), bufs.logits.stride(0), 0
     lp.beta, lp.M, lp.N, lp.K = 0.0, 0, w.lm_head.shape[0], hidden
     lp.epilogue, lp.tile_n, lp.num_ctas, lp.status = 0, eng.gemm_tile_n.get("lm_head", 0), 0, _ptr(st)
+    if bufs.gemm_ws is not None:
+        lp.workspace = _ptr(bufs.gemm_ws)
+        lp.workspace_bytes = bufs.gemm_ws.numel() * bufs.gemm_ws.element_size()
     lm = g.add("lm_head", lp, "gemm", deps=[fn], dyn=[("M", n_sample)])
     vl = w.lm_head.shape[0]
     valid = max(0, min(vl, model.vocab_size - w.rank * vl))

@@ -41,6 +41,55 @@ def test_gemm_plain(M, N, K, tile_n):
     _close(out, ref.gemm(a, w), atol=2e-2 * math.sqrt(K / 64), rtol=2e-2)
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 8192, 8192), (85, 1024, 3584), (300, 2048, 4096), (512, 4096, 1024),
+                                   (129, 10240, 2048)])
+@pytest.mark.parametrize("tile_m,tile_n,split_k", [(0, 0, 0), (2, 256, 1), (2, 256, 4), (4, 128, 3), (1, 256, 2),
+                                                   (4, 64, 1), (2, 128, 8), (1, 128, 5), (1, 64, 2)])
+def test_gemm_small_m_weight_streaming(M, N, K, tile_m, tile_n, split_k):
+    """Multi-M-tile CTAs (weights fetched once) and split-K with fp32 partials + reduce pass."""
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    ws = torch.zeros(64 << 20, device="cuda", dtype=torch.float32)
+    st = ops.new_status()
+    want = ref.gemm(a, w, res, 0.5, bias)
+    out = ops.gemm(a, w, residual=res, beta=0.5, bias=bias, tile_m=tile_m, tile_n=tile_n,
+                   split_k=split_k, workspace=ws, status=st)
+    ops.check_status(st, "gemm")
+    _close(out, want, atol=3e-2 * math.sqrt(K / 64), rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 1280, 2048), (640, 1280, 1024), (1408, 8192, 512), (1000, 3000, 1000)])
+@pytest.mark.parametrize("num_ctas", [0, 100, 37])
+def test_gemm_split_k_large(M, N, K, num_ctas):
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    ws = torch.zeros(64 << 20, device="cuda", dtype=torch.float32)
+    st = ops.new_status()
+    out = ops.gemm(a, w, residual=res, beta=1.0, split_k=3, workspace=ws, num_ctas=num_ctas, status=st)
+    ops.check_status(st, "gemm")
+    _close(out, ref.gemm(a, w, res, 1.0), atol=3e-2 * math.sqrt(K / 64), rtol=2e-2)
+    out0 = ops.gemm(a, w, residual=res, beta=1.0, workspace=ws, num_ctas=num_ctas)   # chooser
+    _close(out0, ref.gemm(a, w, res, 1.0), atol=3e-2 * math.sqrt(K / 64), rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,F,K,tile_m,tile_n", [(256, 3584, 1024, 2, 256), (200, 1792, 2048, 2, 128),
+                                                 (500, 1024, 1024, 4, 128), (256, 28672 // 8, 8192, 0, 0)])
+def test_gemm_swiglu_small_m(M, F, K, tile_m, tile_n):
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    wg = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    wu = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    ws = torch.zeros(80 << 20, device="cuda", dtype=torch.float32)
+    st = ops.new_status()
+    want = ref.gemm_swiglu(a, wg, wu)
+    out = ops.gemm_swiglu(a, wg, wu, tile_m=tile_m, tile_n=tile_n, status=st)
+    ops.check_status(st, "gemm_swiglu")
+    _close(out, want, atol=3e-2 * math.sqrt(K / 64), rtol=3e-2)
+
+
+
 @pytest.mark.parametrize("num_ctas", [1, 7, 60, 148])
 def test_gemm_cta_budget_residual_bias(num_ctas):
     M, N, K = 520, 1032, 328
