@@ -61,9 +61,9 @@ class Buffers:
     inv_freq: torch.Tensor           # [head_dim/2] fp32
     status: torch.Tensor             # [1] int32
     decode_ws: Optional[torch.Tensor]  # split-KV workspace (fp32)
-    gemm_ws: Optional[torch.Tensor] = None   # split-K partial sums (fp32); all GEMMs share one stream
     meta: Dict[str, torch.Tensor]    # int32 views into the metadata block (see engine.MetaLayout)
     nano_items: List[torch.Tensor]   # per nano-batch [cap,3] int32 views
+    gemm_ws: Optional[torch.Tensor] = None   # split-K partial sums (fp32); all GEMMs share one stream
 
 
 class CollectiveHooks:
