@@ -43,8 +43,7 @@ __device__ __forceinline__ uint4 ld_sys_v4(const void* p) {
   uint4 v;
   asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
+               : "l"(p));
   return v;
 }
 __device__ __forceinline__ void st_sys_v4(void* p, const uint4& v) {
@@ -124,11 +123,16 @@ __device__ __forceinline__ float block_sum_comm(float v, float* red) {
   return t;
 }
 
-constexpr int kMaxVecPerThread = 8;  // cols <= 8 * 8 * 256 = 16384
+constexpr int kVecPerRow = 4;        // 16-byte vectors per thread per row: cols <= 4 * 8 * 256 = 8192
+constexpr int kMaxCols = kVecPerRow * 8 * kCommThreads;
 
-template <bool NORM>
+// Loads over NVLink have microseconds of latency, so the kernel first issues every load of a batch
+// of rows (RP rows x 4 vectors x NR ranks = 32 outstanding 16-byte loads per thread), then reduces
+// and pushes. With 256 threads per CTA a few tens of CTAs keep the links busy.
+template <int NR, bool NORM>
 __global__ void __launch_bounds__(kCommThreads)
 allreduce_kernel(nfk_allreduce_params p) {
+  constexpr int RP = NR <= 2 ? 4 : (NR <= 4 ? 2 : 1);   // rows per batch
   __shared__ float red[32];
   const nfk_comm_ctx& c = p.ctx;
   comm_enter(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status);
@@ -136,80 +140,100 @@ allreduce_kernel(nfk_allreduce_params p) {
   const int nvec = p.cols >> 3;
   const long long row_bytes = p.ld * 2;
   const uint4* wv = NORM ? reinterpret_cast<const uint4*>(p.norm_w) : nullptr;
-  for (int row = c.rank + c.nranks * blockIdx.x; row < p.rows; row += c.nranks * gridDim.x) {
-    float acc[kMaxVecPerThread][8];
-    float ss = 0.f;
+  const int owned = (p.rows - c.rank + NR - 1) / NR;     // rows rank, rank+NR, ... (may be <= 0)
+  for (int base = blockIdx.x * RP; base < owned; base += gridDim.x * RP) {
+    uint4 in[RP][kVecPerRow][NR];
 #pragma unroll
-    for (int i = 0; i < kMaxVecPerThread; ++i) {
-      const int v = threadIdx.x + i * kCommThreads;
-      if (v < nvec) {
-        uint4 in[8];
+    for (int j = 0; j < RP; ++j) {
+      const long long row = c.rank + static_cast<long long>(NR) * (base + j);
 #pragma unroll
-        for (int r = 0; r < 8; ++r)
-          if (r < c.nranks)
-            in[r] = ld_sys_v4(reinterpret_cast<const char*>(c.heap[r]) + p.buf_off + row * row_bytes + v * 16);
+      for (int i = 0; i < kVecPerRow; ++i) {
+        const int v = threadIdx.x + i * kCommThreads;
+        if (base + j < owned && v < nvec) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          if (r < c.nranks) {
-            const uint32_t w4[4] = {in[r].x, in[r].y, in[r].z, in[r].w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = unpack_bf16x2(w4[j]);
-              acc[i][2 * j] += f.x;
-              acc[i][2 * j + 1] += f.y;
-            }
-          }
-        }
-        uint4 o;
-        o.x = pack_bf16x2(acc[i][0], acc[i][1]);
-        o.y = pack_bf16x2(acc[i][2], acc[i][3]);
-        o.z = pack_bf16x2(acc[i][4], acc[i][5]);
-        o.w = pack_bf16x2(acc[i][6], acc[i][7]);
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-          if (r < c.nranks)
-            st_sys_v4(reinterpret_cast<char*>(c.heap[r]) + p.buf_off + row * row_bytes + v * 16, o);
-        if (NORM) {
-          // normalise what was stored (bf16-rounded), as the standalone norm kernel would read it
-          const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = unpack_bf16x2(ow[j]);
-            acc[i][2 * j] = f.x;
-            acc[i][2 * j + 1] = f.y;
-            ss += f.x * f.x + f.y * f.y;
-          }
+          for (int r = 0; r < NR; ++r)
+            in[j][i][r] = ld_sys_v4(reinterpret_cast<const char*>(c.heap[r]) + p.buf_off + row * row_bytes + v * 16);
         }
       }
     }
-    if (NORM) {
-      const float tot = block_sum_comm(ss, red);
-      const float inv = rsqrtf(tot / static_cast<float>(p.cols) + p.eps);
 #pragma unroll
-      for (int i = 0; i < kMaxVecPerThread; ++i) {
+    for (int j = 0; j < RP; ++j) {
+      if (base + j >= owned) break;            // uniform across the CTA
+      const long long row = c.rank + static_cast<long long>(NR) * (base + j);
+      float acc[kVecPerRow][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < kVecPerRow; ++i) {
         const int v = threadIdx.x + i * kCommThreads;
         if (v < nvec) {
-          const uint4 ww = wv[v];
-          const uint32_t w4[4] = {ww.x, ww.y, ww.z, ww.w};
-          uint32_t ov[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 g = unpack_bf16x2(w4[j]);
-            ov[j] = pack_bf16x2(acc[i][2 * j] * inv * g.x, acc[i][2 * j + 1] * inv * g.y);
+          for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+#pragma unroll
+          for (int r = 0; r < NR; ++r) {
+            const uint32_t w4[4] = {in[j][i][r].x, in[j][i][r].y, in[j][i][r].z, in[j][i][r].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = unpack_bf16x2(w4[e]);
+              acc[i][2 * e] += f.x;
+              acc[i][2 * e + 1] += f.y;
+            }
           }
-          const uint4 o = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+          uint4 o;
+          o.x = pack_bf16x2(acc[i][0], acc[i][1]);
+          o.y = pack_bf16x2(acc[i][2], acc[i][3]);
+          o.z = pack_bf16x2(acc[i][4], acc[i][5]);
+          o.w = pack_bf16x2(acc[i][6], acc[i][7]);
 #pragma unroll
-          for (int r = 0; r < 8; ++r)
-            if (r < c.nranks)
+          for (int r = 0; r < NR; ++r)
+            st_sys_v4(reinterpret_cast<char*>(c.heap[r]) + p.buf_off + row * row_bytes + v * 16, o);
+          if (NORM) {
+            // normalise what was stored (bf16-rounded), as the standalone norm kernel would read it
+            const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = unpack_bf16x2(ow[e]);
+              acc[i][2 * e] = f.x;
+              acc[i][2 * e + 1] = f.y;
+              ss += f.x * f.x + f.y * f.y;
+            }
+          }
+        }
+      }
+      if (NORM) {
+        const float tot = block_sum_comm(ss, red);
+        const float inv = rsqrtf(tot / static_cast<float>(p.cols) + p.eps);
+#pragma unroll
+        for (int i = 0; i < kVecPerRow; ++i) {
+          const int v = threadIdx.x + i * kCommThreads;
+          if (v < nvec) {
+            const uint4 ww = wv[v];
+            const uint32_t w4[4] = {ww.x, ww.y, ww.z, ww.w};
+            uint32_t ov[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 g = unpack_bf16x2(w4[e]);
+              ov[e] = pack_bf16x2(acc[i][2 * e] * inv * g.x, acc[i][2 * e + 1] * inv * g.y);
+            }
+            const uint4 o = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+#pragma unroll
+            for (int r = 0; r < NR; ++r)
               st_sys_v4(reinterpret_cast<char*>(c.heap[r]) + p.norm_out_off +
                             row * static_cast<long long>(p.norm_ld) * 2 + v * 16, o);
+          }
         }
       }
     }
   }
   comm_exit(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status);
+}
+
+template <int NR>
+int launch_allreduce(const nfk_allreduce_params* p, int ctas, cudaStream_t stream) {
+  if (p->norm_w != nullptr)
+    allreduce_kernel<NR, true><<<ctas, kCommThreads, 0, stream>>>(*p);
+  else
+    allreduce_kernel<NR, false><<<ctas, kCommThreads, 0, stream>>>(*p);
+  return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
 }
 
 __global__ void __launch_bounds__(kCommThreads)
@@ -250,19 +274,24 @@ bool ctx_ok(const nfk_comm_ctx& c) {
 extern "C" int nfk_allreduce(const nfk_allreduce_params* p, cudaStream_t stream) {
   using namespace nf;
   if (!p || !ctx_ok(p->ctx)) return NF_ERR_BAD_ARG;
-  if (p->cols <= 0 || p->cols % 8 != 0 || p->cols > kMaxVecPerThread * 8 * kCommThreads || p->ld % 8 != 0 ||
-      p->rows < 0 || p->buf_off % 16 != 0 || p->flag_off % 16 != 0)
+  if (p->cols <= 0 || p->cols % 8 != 0 || p->cols > kMaxCols || p->ld % 8 != 0 || p->rows < 0 ||
+      p->buf_off % 16 != 0 || p->flag_off % 16 != 0)
     return NF_ERR_BAD_ARG;
   if (p->norm_w != nullptr && (p->norm_out_off % 16 != 0 || p->norm_ld % 8 != 0)) return NF_ERR_BAD_ARG;
   // Even an empty buffer takes part in the handshakes so that all ranks stay in step.
-  const int owned = (p->rows + p->ctx.nranks - 1) / p->ctx.nranks;
+  const int nr = p->ctx.nranks;
+  const int rp = nr <= 2 ? 4 : (nr <= 4 ? 2 : 1);
+  const int owned = (p->rows + nr - 1) / nr;
+  const int batches = (owned + rp - 1) / rp;
   int ctas = p->num_ctas > 0 ? p->num_ctas : 32;
-  if (ctas > owned) ctas = owned > 0 ? owned : 1;
-  if (p->norm_w != nullptr)
-    allreduce_kernel<true><<<ctas, kCommThreads, 0, stream>>>(*p);
-  else
-    allreduce_kernel<false><<<ctas, kCommThreads, 0, stream>>>(*p);
-  return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
+  if (ctas > batches) ctas = batches > 0 ? batches : 1;
+  switch (nr) {
+    case 1: return launch_allreduce<1>(p, ctas, stream);
+    case 2: return launch_allreduce<2>(p, ctas, stream);
+    case 4: return launch_allreduce<4>(p, ctas, stream);
+    case 8: return launch_allreduce<8>(p, ctas, stream);
+    default: return NF_ERR_UNSUPPORTED;
+  }
 }
 
 extern "C" int nfk_allgather(const nfk_allgather_params* p, cudaStream_t stream) {

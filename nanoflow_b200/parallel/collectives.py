@@ -49,7 +49,7 @@ FLAG_BYTES = 128
 
 class TpCollectives(CollectiveHooks):
     def __init__(self, rank: int, world: int, device: torch.device, heap_bytes: int = 1 << 30,
-                 num_ctas: int = 16, fuse_norm: bool = True):
+                 num_ctas: int = 64, fuse_norm: bool = True):
         if world > 8:
             raise ValueError("at most 8 ranks (one NVSwitch domain)")
         self.rank, self.tp, self.device = rank, world, device

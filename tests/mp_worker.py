@@ -66,7 +66,7 @@ def case_collectives(rank, world, dev):
     # bandwidth (device-timed, max over ranks)
     rows, cols = 2048, 8192
     buf = coll.alloc((rows, cols), torch.bfloat16)
-    for ctas in (8, 16, 32, 64):
+    for ctas in (8, 16, 32, 64, 128):
         for _ in range(3):
             coll.all_reduce_(buf, num_ctas=ctas)
         torch.cuda.synchronize(); dist.barrier()
