@@ -104,6 +104,9 @@ def main():
     ap.add_argument("--global-batch", type=int, default=0, help="dense tokens per iteration (0 = choose)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the result invalid)")
     ap.add_argument("--pipeline", default="", help="override pipeline_type")
+    ap.add_argument("--nano", default="", help="comma-separated nano-batch sizes (must sum to the dense batch); "
+                    "default: two halves for the overlapped pipelines")
+    ap.add_argument("--comm-ctas", type=int, default=0)
     ap.add_argument("--skip-cycles", type=int, default=1600)
     ap.add_argument("--executor", default="auto")
     ap.add_argument("--timeline", default="", help="after the timed regions, time every op of one iteration "
@@ -164,8 +167,17 @@ def main():
         max_decode = tok_cap / (avg_ctx * 1.12)
         gbs = int(max_decode * (args.input_len + args.output_len) / args.output_len)
         gbs = max(256, min(8192, gbs // 128 * 128))
-    ptype = args.pipeline or ("NON_OVERLAP" if tp > 1 else "NON_OVERLAP_LOCAL")
-    cfg = builtin_config(args.model, gpu_num=tp, global_batch_size=gbs, pipeline_type=ptype)
+    ptype = args.pipeline or ("PLLM" if tp > 1 else "NON_OVERLAP_LOCAL")
+    nano = None
+    if args.nano:
+        nano = [int(x) for x in args.nano.split(",")]
+    elif not ptype.startswith("NON"):
+        half = max(128, (gbs // 2) // 128 * 128)
+        nano = [half, gbs - half]
+    cfg = builtin_config(args.model, gpu_num=tp, global_batch_size=gbs, pipeline_type=ptype,
+                         **({"nanobatch_sizes": nano} if nano else {}))
+    if args.comm_ctas:
+        cfg.engine.sm_budget["comm"] = args.comm_ctas
     if args.layers:
         cfg.model.num_layers = args.layers
         cfg.model.run_layers = args.layers
@@ -274,6 +286,7 @@ def main():
             "config": {"model": args.model, "global_batch": gbs, "seq_len": args.input_len + args.output_len,
                        "input_len": args.input_len, "output_len": args.output_len,
                        "parallelism": f"tp{world}", "pipeline_type": ptype, "layers": model.run_layers,
+                       "nanobatches": cfg.engine.resolved_nanobatches(),
                        "kv_pages": eng.num_pages, "tokens_per_step": round(tokens_dev / args.steps, 1),
                        "l2": "inputs larger than L2 (weights per GPU >> 126 MB); no flush",
                        "steady_state": f"{args.skip_cycles} scheduler-only cycles before warm-up",

@@ -100,7 +100,16 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
     hd, hidden = model.head_dim, model.hidden_size
     st = bufs.status
     budget = eng.sm_budget if overlap else {}
-    S = (lambda cls: cls) if overlap else (lambda cls: "gemm")   # stream chooser
+    # Stream chooser. Collectives always get the net stream in overlap mode: their CTAs need no
+    # shared memory and co-reside with GEMM CTAs. Attention CTAs cannot share an SM with a GEMM CTA
+    # (shared memory), so under tensor parallelism they stay in line with the GEMMs; on one GPU
+    # (LOCAL pipelines) they get their own stream and fill SMs as GEMM CTAs retire.
+    if not overlap:
+        S = lambda cls: "gemm"
+    elif tp > 1:
+        S = lambda cls: "net" if cls == "net" else "gemm"
+    else:
+        S = lambda cls: cls
 
     T_all = g.symbol("T")
     n_sample = g.symbol("n_sample")
@@ -204,24 +213,27 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         rope_of[(l, k)] = ro
         return dec, pre
 
-    def attn_back(l, k, lw, dec, pre):
-        """O projection (+residual) -> all-reduce -> norm -> gate/up SwiGLU -> down (+residual) -> all-reduce."""
+    comm_ctas = budget.get("comm", 0)
+
+    def o_proj(l, k, lw, dec, pre):
+        """O projection (+ residual / tp) -> all-reduce (+ fused FFN norm). Returns the op the FFN waits for."""
         xin, xout = bufs.x[cur], bufs.x[1 - cur] if tp > 1 else bufs.x[cur]
-        beta = 1.0 / tp
-        o = gemm(f"L{l}.nb{k}.o", bufs.attn_out, lw.wo, xout, k, residual=xin, beta=beta, deps=[dec, pre],
+        o = gemm(f"L{l}.nb{k}.o", bufs.attn_out, lw.wo, xout, k, residual=xin, beta=1.0 / tp, deps=[dec, pre],
                  layer=l, tile_key="o")
-        comm_ctas = budget.get("comm", 0)
         ar1, fused1 = coll.all_reduce(g, f"L{l}.nb{k}.ar_o", xout, starts[k], nb_T[k], hidden, [o], l, k,
                                       stream=S("net"), norm_w=lw.ln_ffn, norm_out=bufs.h, eps=model.rms_norm_eps,
                                       status=st, num_ctas=comm_ctas)
         if fused1:
-            n2 = ar1
-        else:
-            n2 = norm(f"L{l}.nb{k}.ln_ffn", xout, lw.ln_ffn, bufs.h, k, [ar1 if ar1 is not None else o], l)
+            return ar1
+        return norm(f"L{l}.nb{k}.ln_ffn", xout, lw.ln_ffn, bufs.h, k, [ar1 if ar1 is not None else o], l)
+
+    def ffn(l, k, lw, n2):
+        """gate/up SwiGLU -> down (+ residual / tp) -> all-reduce (+ fused next-layer attention norm)."""
+        xin, xout = bufs.x[cur], bufs.x[1 - cur] if tp > 1 else bufs.x[cur]
         gu = gemm(f"L{l}.nb{k}.gate_up", bufs.h, lw.wg, bufs.act, k, swiglu_up=lw.wu, deps=[n2], layer=l,
                   tile_key="gate_up")
         # down writes back into the first buffer: after both projections the residual is where it started
-        d = gemm(f"L{l}.nb{k}.down", bufs.act, lw.wd, xin, k, residual=xout, beta=beta, deps=[gu], layer=l,
+        d = gemm(f"L{l}.nb{k}.down", bufs.act, lw.wd, xin, k, residual=xout, beta=1.0 / tp, deps=[gu], layer=l,
                  tile_key="down")
         nxt = w.layers[(l + 1) % model.num_layers].ln_attn if l + 1 < model.run_layers else None
         ar2, fused2 = coll.all_reduce(g, f"L{l}.nb{k}.ar_d", xin, starts[k], nb_T[k], hidden, [d], l, k,
@@ -235,18 +247,22 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
     for l in range(model.run_layers):
         lw = w.layers[l % model.num_layers]
         pool = bufs.kv_pool[l]
-        fronts = []
         if overlap and nn > 1:
-            # software pipeline: all attention front-ends first, then the FFN halves, so that the
-            # attention of nano-batch k+1 runs beside the O/FFN GEMMs of nano-batch k
+            # Issue order per layer: (front_k, o_k) for every nano-batch, then ffn_k for every
+            # nano-batch. The all-reduce after o_k then runs (on the net stream, its CTAs sharing SMs
+            # with the GEMM CTAs) beside the attention front-end of nano-batch k+1, the one after
+            # ffn_k beside ffn_{k+1} or the next layer's front-end: no GEMM waits on a collective
+            # that started right before it.
+            n2s = []
             for k in range(nn):
-                fronts.append(attn_front(l, k, lw, pool))
+                dec, pre = attn_front(l, k, lw, pool)
+                n2s.append(o_proj(l, k, lw, dec, pre))
             for k in range(nn):
-                attn_back(l, k, lw, *fronts[k])
+                ffn(l, k, lw, n2s[k])
         else:
             for k in range(nn):
                 dec, pre = attn_front(l, k, lw, pool)
-                attn_back(l, k, lw, dec, pre)
+                ffn(l, k, lw, o_proj(l, k, lw, dec, pre))
 
     # ---- epilogue: sample --------------------------------------------------------------------------
     gp = GatherParams(out=_ptr(bufs.sample_h), inp=_ptr(bufs.x[cur]), rows_idx=_ptr(m["sample_rows"]), n=0,
