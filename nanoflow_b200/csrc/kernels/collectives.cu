@@ -3,12 +3,14 @@
 // loads / stores over NVLink 5 through the NVSwitch (uniform bandwidth to every peer, hence direct
 // one-step algorithms, no rings).
 //
-//   nfk_allreduce   in-place sum of a bf16 [rows, cols] buffer. Row i is owned by rank i % nranks:
+//   nfk_allreduce   sum of a bf16 [rows, cols] buffer over ranks. Row i is owned by rank i % nranks:
 //                   the owner pulls the row from all ranks with 16-byte loads, adds in fp32 in rank
-//                   order (deterministic, identical on all ranks) and pushes the result to every
-//                   rank. Optionally the owner also applies RMSNorm to the reduced row and pushes
-//                   the normed row into a second symmetric buffer (all-reduce + norm fused, so the
-//                   norm is computed once per row instead of once per rank).
+//                   order (deterministic), optionally adds its local residual row, and then any of:
+//                   writes the sum to a local buffer (the residual stream stays sharded by owner),
+//                   pushes the sum back into the buffer on every rank (classic in-place all-reduce),
+//                   applies RMSNorm and pushes the normed row into a second symmetric buffer on every
+//                   rank (reduce-scatter + norm + all-gather in one pass: the norm is computed once
+//                   per row instead of once per rank and the pre-norm sum never crosses NVLink).
 //   nfk_allgather   every rank pushes its shard of a symmetric buffer to all peers.
 //   nfk_comm_barrier  cross-rank barrier.
 //
@@ -123,103 +125,129 @@ __device__ __forceinline__ float block_sum_comm(float v, float* red) {
   return t;
 }
 
-constexpr int kVecPerRow = 4;        // 16-byte vectors per thread per row: cols <= 4 * 8 * 256 = 8192
-constexpr int kMaxCols = kVecPerRow * 8 * kCommThreads;
+constexpr int kArThreads = 128;
+constexpr int kArVec = 8;                                  // 16-byte vectors per thread per row
+constexpr int kMaxCols = kArVec * 8 * kArThreads;          // 8192 columns
 
-// Loads over NVLink have microseconds of latency, so the kernel first issues every load of a batch
-// of rows (RP rows x 4 vectors x NR ranks = 32 outstanding 16-byte loads per thread), then reduces
-// and pushes. With 256 threads per CTA a few tens of CTAs keep the links busy.
+__device__ __forceinline__ float block_sum_ar(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < (kArThreads >> 5)) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+// Small CTAs (128 threads, <= 168 registers, no dynamic shared memory) so that they fit on an SM
+// next to a resident GEMM CTA: the collective then runs beside the GEMMs of another nano-batch
+// instead of waiting for SMs. Loads over NVLink have microseconds of latency, so each thread keeps
+// 16 independent 16-byte loads in flight (CH vectors x NR ranks) before it reduces and pushes.
 template <int NR, bool NORM>
-__global__ void __launch_bounds__(kCommThreads)
+__global__ void __launch_bounds__(kArThreads, 3)
 allreduce_kernel(nfk_allreduce_params p) {
-  constexpr int RP = NR <= 2 ? 4 : (NR <= 4 ? 2 : 1);   // rows per batch
-  __shared__ float red[32];
+  constexpr int CH = NR >= 8 ? 2 : (NR >= 4 ? 4 : 8);     // vectors per chunk
+  __shared__ float red[8];
   const nfk_comm_ctx& c = p.ctx;
   comm_enter(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status);
 
   const int nvec = p.cols >> 3;
   const long long row_bytes = p.ld * 2;
   const uint4* wv = NORM ? reinterpret_cast<const uint4*>(p.norm_w) : nullptr;
-  const int owned = (p.rows - c.rank + NR - 1) / NR;     // rows rank, rank+NR, ... (may be <= 0)
-  for (int base = blockIdx.x * RP; base < owned; base += gridDim.x * RP) {
-    uint4 in[RP][kVecPerRow][NR];
+  const char* resid = reinterpret_cast<const char*>(p.resid);
+  char* sum_out = reinterpret_cast<char*>(p.sum_out);
+  const int owned = (p.rows - c.rank + NR - 1) / NR;       // rows rank, rank+NR, ... (may be <= 0)
+  for (int k = blockIdx.x; k < owned; k += gridDim.x) {
+    const long long row = c.rank + static_cast<long long>(NR) * k;
+    uint4 packed[kArVec];
+    float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < RP; ++j) {
-      const long long row = c.rank + static_cast<long long>(NR) * (base + j);
+    for (int i0 = 0; i0 < kArVec; i0 += CH) {
+      uint4 in[CH][NR];
+      uint4 rs[CH];
 #pragma unroll
-      for (int i = 0; i < kVecPerRow; ++i) {
-        const int v = threadIdx.x + i * kCommThreads;
-        if (base + j < owned && v < nvec) {
-#pragma unroll
-          for (int r = 0; r < NR; ++r)
-            in[j][i][r] = ld_sys_v4(reinterpret_cast<const char*>(c.heap[r]) + p.buf_off + row * row_bytes + v * 16);
-        }
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < RP; ++j) {
-      if (base + j >= owned) break;            // uniform across the CTA
-      const long long row = c.rank + static_cast<long long>(NR) * (base + j);
-      float acc[kVecPerRow][8];
-      float ss = 0.f;
-#pragma unroll
-      for (int i = 0; i < kVecPerRow; ++i) {
-        const int v = threadIdx.x + i * kCommThreads;
+      for (int i = 0; i < CH; ++i) {
+        const int v = threadIdx.x + (i0 + i) * kArThreads;
         if (v < nvec) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+          for (int r = 0; r < NR; ++r)
+            in[i][r] = ld_sys_v4(reinterpret_cast<const char*>(c.heap[r]) + p.buf_off + row * row_bytes + v * 16);
+          if (resid != nullptr) rs[i] = *reinterpret_cast<const uint4*>(resid + row * p.resid_ld * 2 + v * 16);
+        }
+      }
 #pragma unroll
-          for (int r = 0; r < NR; ++r) {
-            const uint32_t w4[4] = {in[j][i][r].x, in[j][i][r].y, in[j][i][r].z, in[j][i][r].w};
+      for (int i = 0; i < CH; ++i) {
+        const int v = threadIdx.x + (i0 + i) * kArThreads;
+        if (v < nvec) {
+          float acc[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+          if (resid != nullptr) {
+            const uint32_t w4[4] = {rs[i].x, rs[i].y, rs[i].z, rs[i].w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const float2 f = unpack_bf16x2(w4[e]);
-              acc[i][2 * e] += f.x;
-              acc[i][2 * e + 1] += f.y;
+              acc[2 * e] = f.x;
+              acc[2 * e + 1] = f.y;
+            }
+          }
+#pragma unroll
+          for (int r = 0; r < NR; ++r) {
+            const uint32_t w4[4] = {in[i][r].x, in[i][r].y, in[i][r].z, in[i][r].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = unpack_bf16x2(w4[e]);
+              acc[2 * e] += f.x;
+              acc[2 * e + 1] += f.y;
             }
           }
           uint4 o;
-          o.x = pack_bf16x2(acc[i][0], acc[i][1]);
-          o.y = pack_bf16x2(acc[i][2], acc[i][3]);
-          o.z = pack_bf16x2(acc[i][4], acc[i][5]);
-          o.w = pack_bf16x2(acc[i][6], acc[i][7]);
+          o.x = pack_bf16x2(acc[0], acc[1]);
+          o.y = pack_bf16x2(acc[2], acc[3]);
+          o.z = pack_bf16x2(acc[4], acc[5]);
+          o.w = pack_bf16x2(acc[6], acc[7]);
+          packed[i0 + i] = o;
+          if (sum_out != nullptr) *reinterpret_cast<uint4*>(sum_out + row * p.sum_ld * 2 + v * 16) = o;
+          if (p.push_sum) {
 #pragma unroll
-          for (int r = 0; r < NR; ++r)
-            st_sys_v4(reinterpret_cast<char*>(c.heap[r]) + p.buf_off + row * row_bytes + v * 16, o);
+            for (int r = 0; r < NR; ++r)
+              st_sys_v4(reinterpret_cast<char*>(c.heap[r]) + p.buf_off + row * row_bytes + v * 16, o);
+          }
           if (NORM) {
             // normalise what was stored (bf16-rounded), as the standalone norm kernel would read it
             const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const float2 f = unpack_bf16x2(ow[e]);
-              acc[i][2 * e] = f.x;
-              acc[i][2 * e + 1] = f.y;
               ss += f.x * f.x + f.y * f.y;
             }
           }
         }
       }
-      if (NORM) {
-        const float tot = block_sum_comm(ss, red);
-        const float inv = rsqrtf(tot / static_cast<float>(p.cols) + p.eps);
+    }
+    if (NORM) {
+      const float tot = block_sum_ar(ss, red);
+      const float inv = rsqrtf(tot / static_cast<float>(p.cols) + p.eps);
 #pragma unroll
-        for (int i = 0; i < kVecPerRow; ++i) {
-          const int v = threadIdx.x + i * kCommThreads;
-          if (v < nvec) {
-            const uint4 ww = wv[v];
-            const uint32_t w4[4] = {ww.x, ww.y, ww.z, ww.w};
-            uint32_t ov[4];
+      for (int i = 0; i < kArVec; ++i) {
+        const int v = threadIdx.x + i * kArThreads;
+        if (v < nvec) {
+          const uint4 ww = wv[v];
+          const uint32_t w4[4] = {ww.x, ww.y, ww.z, ww.w};
+          const uint32_t x4[4] = {packed[i].x, packed[i].y, packed[i].z, packed[i].w};
+          uint32_t ov[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 g = unpack_bf16x2(w4[e]);
-              ov[e] = pack_bf16x2(acc[i][2 * e] * inv * g.x, acc[i][2 * e + 1] * inv * g.y);
-            }
-            const uint4 o = make_uint4(ov[0], ov[1], ov[2], ov[3]);
-#pragma unroll
-            for (int r = 0; r < NR; ++r)
-              st_sys_v4(reinterpret_cast<char*>(c.heap[r]) + p.norm_out_off +
-                            row * static_cast<long long>(p.norm_ld) * 2 + v * 16, o);
+          for (int e = 0; e < 4; ++e) {
+            const float2 g = unpack_bf16x2(w4[e]);
+            const float2 f = unpack_bf16x2(x4[e]);
+            ov[e] = pack_bf16x2(f.x * inv * g.x, f.y * inv * g.y);
           }
+          const uint4 o = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+#pragma unroll
+          for (int r = 0; r < NR; ++r)
+            st_sys_v4(reinterpret_cast<char*>(c.heap[r]) + p.norm_out_off +
+                          row * static_cast<long long>(p.norm_ld) * 2 + v * 16, o);
         }
       }
     }
@@ -230,9 +258,9 @@ allreduce_kernel(nfk_allreduce_params p) {
 template <int NR>
 int launch_allreduce(const nfk_allreduce_params* p, int ctas, cudaStream_t stream) {
   if (p->norm_w != nullptr)
-    allreduce_kernel<NR, true><<<ctas, kCommThreads, 0, stream>>>(*p);
+    allreduce_kernel<NR, true><<<ctas, kArThreads, 0, stream>>>(*p);
   else
-    allreduce_kernel<NR, false><<<ctas, kCommThreads, 0, stream>>>(*p);
+    allreduce_kernel<NR, false><<<ctas, kArThreads, 0, stream>>>(*p);
   return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
 }
 
@@ -278,13 +306,15 @@ extern "C" int nfk_allreduce(const nfk_allreduce_params* p, cudaStream_t stream)
       p->buf_off % 16 != 0 || p->flag_off % 16 != 0)
     return NF_ERR_BAD_ARG;
   if (p->norm_w != nullptr && (p->norm_out_off % 16 != 0 || p->norm_ld % 8 != 0)) return NF_ERR_BAD_ARG;
+  if (p->resid != nullptr && ((reinterpret_cast<uintptr_t>(p->resid) & 15) || p->resid_ld % 8 != 0))
+    return NF_ERR_BAD_ARG;
+  if (p->sum_out != nullptr && ((reinterpret_cast<uintptr_t>(p->sum_out) & 15) || p->sum_ld % 8 != 0))
+    return NF_ERR_BAD_ARG;
   // Even an empty buffer takes part in the handshakes so that all ranks stay in step.
   const int nr = p->ctx.nranks;
-  const int rp = nr <= 2 ? 4 : (nr <= 4 ? 2 : 1);
   const int owned = (p->rows + nr - 1) / nr;
-  const int batches = (owned + rp - 1) / rp;
-  int ctas = p->num_ctas > 0 ? p->num_ctas : 32;
-  if (ctas > batches) ctas = batches > 0 ? batches : 1;
+  int ctas = p->num_ctas > 0 ? p->num_ctas : 148;
+  if (ctas > owned) ctas = owned > 0 ? owned : 1;
   switch (nr) {
     case 1: return launch_allreduce<1>(p, ctas, stream);
     case 2: return launch_allreduce<2>(p, ctas, stream);

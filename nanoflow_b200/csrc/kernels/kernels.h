@@ -155,6 +155,11 @@ typedef struct nfk_allreduce_params {
   long long norm_ld;
   float eps;
   unsigned int* status;
+  int push_sum;           // 1: write the sum back into the buffer on every rank (in-place all-reduce)
+  const void* resid;      // optional local bf16 [rows, resid_ld]: owned rows are added to the sum
+  long long resid_ld;
+  void* sum_out;          // optional local bf16 [rows, sum_ld]: owned rows of the sum are stored here
+  long long sum_ld;
 } nfk_allreduce_params;
 int nfk_allreduce(const nfk_allreduce_params* p, cudaStream_t stream);
 

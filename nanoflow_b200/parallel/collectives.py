@@ -27,7 +27,8 @@ class AllReduceParams(Structure):
     _fields_ = [("ctx", CommCtx), ("buf_off", c_longlong), ("flag_off", c_longlong), ("rows", c_int),
                 ("cols", c_int), ("ld", c_longlong), ("epoch", c_int), ("num_ctas", c_int),
                 ("norm_w", c_void_p), ("norm_out_off", c_longlong), ("norm_ld", c_longlong), ("eps", c_float),
-                ("status", c_void_p)]
+                ("status", c_void_p), ("push_sum", c_int), ("resid", c_void_p), ("resid_ld", c_longlong),
+                ("sum_out", c_void_p), ("sum_ld", c_longlong)]
 
 
 class AllGatherParams(Structure):
@@ -49,7 +50,7 @@ FLAG_BYTES = 128
 
 class TpCollectives(CollectiveHooks):
     def __init__(self, rank: int, world: int, device: torch.device, heap_bytes: int = 1 << 30,
-                 num_ctas: int = 64, fuse_norm: bool = True):
+                 num_ctas: int = 148, fuse_norm: bool = True):
         if world > 8:
             raise ValueError("at most 8 ranks (one NVSwitch domain)")
         self.rank, self.tp, self.device = rank, world, device
@@ -77,7 +78,14 @@ class TpCollectives(CollectiveHooks):
     # ---- graph hooks --------------------------------------------------------------------------------
     def all_reduce(self, g: OpGraph, name: str, buf: torch.Tensor, row0: int, rows_sym: str, cols: int,
                    deps, layer: int, nano: int, stream: str = "net", norm_w: Optional[torch.Tensor] = None,
-                   norm_out: Optional[torch.Tensor] = None, eps: float = 1e-5, status=None, num_ctas: int = 0):
+                   norm_out: Optional[torch.Tensor] = None, eps: float = 1e-5, status=None, num_ctas: int = 0,
+                   resid: Optional[torch.Tensor] = None, sum_out: Optional[torch.Tensor] = None,
+                   push_sum: bool = True):
+        """Append a reduction of ``buf`` rows [row0, row0+rows) over all ranks.
+
+        ``resid`` / ``sum_out`` are local tensors (rows owned by this rank are read / written);
+        ``push_sum`` writes the sum back into ``buf`` on every rank; ``norm_w`` + ``norm_out`` push
+        the RMS-normed sum into the symmetric ``norm_out`` on every rank."""
         p = AllReduceParams()
         p.ctx = self.ctx()
         esz = buf.element_size()
@@ -85,11 +93,16 @@ class TpCollectives(CollectiveHooks):
         p.flag_off = self.new_flags()
         p.rows, p.cols, p.ld = 0, cols, buf.stride(0)
         p.epoch, p.num_ctas = 0, num_ctas or self.num_ctas
-        fused = self.fuse_norm and norm_w is not None and norm_out is not None
+        fused = norm_w is not None and norm_out is not None
         if fused:
             p.norm_w = norm_w.data_ptr()
             p.norm_out_off = self.heap.offset_of(norm_out) + row0 * norm_out.stride(0) * esz
             p.norm_ld, p.eps = norm_out.stride(0), eps
+        p.push_sum = 1 if push_sum else 0
+        if resid is not None:
+            p.resid, p.resid_ld = resid.data_ptr() + row0 * resid.stride(0) * esz, resid.stride(0)
+        if sum_out is not None:
+            p.sum_out, p.sum_ld = sum_out.data_ptr() + row0 * sum_out.stride(0) * esz, sum_out.stride(0)
         p.status = (status if status is not None else self.status).data_ptr()
         idx = g.add(name, p, stream, deps=deps, dyn=[("rows", rows_sym), ("epoch", g.symbol("epoch"))],
                     layer=layer, nano=nano)
@@ -118,7 +131,8 @@ class TpCollectives(CollectiveHooks):
 
     def all_reduce_(self, buf: torch.Tensor, *, norm_w=None, norm_out=None, eps: float = 1e-5,
                     num_ctas: int = 0, flag_off: Optional[int] = None, epoch: Optional[int] = None,
-                    rows: Optional[int] = None):
+                    rows: Optional[int] = None, resid: Optional[torch.Tensor] = None,
+                    sum_out: Optional[torch.Tensor] = None, push_sum: bool = True):
         """In-place sum of a symmetric bf16 [rows, cols] tensor over all ranks (launches on the
         current stream). All ranks must call it the same number of times with the same flag block."""
         p = AllReduceParams()
@@ -132,6 +146,11 @@ class TpCollectives(CollectiveHooks):
             p.norm_w = norm_w.data_ptr()
             p.norm_out_off = self.heap.offset_of(norm_out)
             p.norm_ld, p.eps = norm_out.stride(0), eps
+        p.push_sum = 1 if push_sum else 0
+        if resid is not None:
+            p.resid, p.resid_ld = resid.data_ptr(), resid.stride(0)
+        if sum_out is not None:
+            p.sum_out, p.sum_ld = sum_out.data_ptr(), sum_out.stride(0)
         p.status = self.status.data_ptr()
         rc = _ops.lib().nfk_allreduce(byref(p), c_void_p(torch.cuda.current_stream().cuda_stream))
         if rc != 0:

@@ -89,10 +89,10 @@ class Engine:
                 torch.zeros(*shape, dtype=dtype, device=dev)
 
         plain = lambda *shape, dtype=bf: torch.zeros(*shape, dtype=dtype, device=dev)
-        # activations (x buffers take part in collectives under TP -> symmetric allocation)
-        x = [alloc(T, m.hidden_size), alloc(T, m.hidden_size) if weights.tp > 1 else None]
-        if x[1] is None:
-            x[1] = x[0]
+        # x[0]: residual stream (local). x[1]: under TP the symmetric buffer the K-split GEMMs write
+        # their partial products into (peers pull from it); on one GPU it aliases x[0].
+        x0 = plain(T, m.hidden_size)
+        x = [x0, alloc(T, m.hidden_size) if weights.tp > 1 else x0]
         self.num_pages = int(num_pages or e.num_pages or self._derive_num_pages(T, B))
         layout = MetaLayout(T, B, self.nano_sizes, self.num_pages)
         self.layout = layout

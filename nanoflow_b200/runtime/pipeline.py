@@ -17,10 +17,10 @@ selected by ``serve_configs.pipeline_type``):
   CTA budgets taken from ``pipeline_configs.sm_budget``.
 
 Tensor parallel layout per layer: QKV (K|V|Q packed, N-split) -> RoPE/append -> attention (head
-parallel) -> O (K-split, residual folded in with beta = 1/tp) -> all-reduce -> RMSNorm -> gate/up
-(N-split, SwiGLU epilogue) -> down (K-split, beta = 1/tp) -> all-reduce. The residual stream
-alternates between two buffers so that a GEMM never overwrites the residual it is reading while
-peers still need the old one.
+parallel) -> O (K-split partial products) -> reduce-scatter + residual + RMSNorm + all-gather in one
+collective -> gate/up (N-split, SwiGLU epilogue) -> down (K-split) -> the same collective with the
+next layer's attention norm. The residual stream stays sharded by row owner between layers; only
+normed activations cross NVLink on the gather side.
 """
 from __future__ import annotations
 
@@ -72,7 +72,8 @@ class CollectiveHooks:
 
     def all_reduce(self, g: OpGraph, name: str, buf: torch.Tensor, row0: int, rows_sym: str, cols: int,
                    deps, layer: int, nano: int, stream: str = "net", norm_w=None, norm_out=None,
-                   eps: float = 1e-5, status=None, num_ctas: int = 0):
+                   eps: float = 1e-5, status=None, num_ctas: int = 0, resid=None, sum_out=None,
+                   push_sum: bool = True):
         """Returns (op index or None, whether the RMSNorm was fused into the collective)."""
         return None, False
 
@@ -215,31 +216,45 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
 
     comm_ctas = budget.get("comm", 0)
 
+    # Residual stream under tensor parallelism: x is a local buffer in which a rank keeps only the
+    # rows it owns (row i belongs to rank i % tp) up to date; the K-split GEMMs write their partial
+    # products into the symmetric buffer `part`; the collective pulls a row's partials from all
+    # ranks, adds the owner's residual row, stores the new residual row locally and pushes only the
+    # RMS-normed row to every rank (the next GEMM's input). After the last layer the sums are pushed
+    # to every rank instead, so `part` then holds the full final hidden state for sampling.
+    x_res = bufs.x[0]
+    part = bufs.x[1]
+
     def o_proj(l, k, lw, dec, pre):
-        """O projection (+ residual / tp) -> all-reduce (+ fused FFN norm). Returns the op the FFN waits for."""
-        xin, xout = bufs.x[cur], bufs.x[1 - cur] if tp > 1 else bufs.x[cur]
-        o = gemm(f"L{l}.nb{k}.o", bufs.attn_out, lw.wo, xout, k, residual=xin, beta=1.0 / tp, deps=[dec, pre],
-                 layer=l, tile_key="o")
-        ar1, fused1 = coll.all_reduce(g, f"L{l}.nb{k}.ar_o", xout, starts[k], nb_T[k], hidden, [o], l, k,
-                                      stream=S("net"), norm_w=lw.ln_ffn, norm_out=bufs.h, eps=model.rms_norm_eps,
-                                      status=st, num_ctas=comm_ctas)
-        if fused1:
-            return ar1
-        return norm(f"L{l}.nb{k}.ln_ffn", xout, lw.ln_ffn, bufs.h, k, [ar1 if ar1 is not None else o], l)
+        """O projection -> reduce (+ residual, + fused FFN norm). Returns the op the FFN waits for."""
+        if tp == 1:
+            o = gemm(f"L{l}.nb{k}.o", bufs.attn_out, lw.wo, x_res, k, residual=x_res, beta=1.0, deps=[dec, pre],
+                     layer=l, tile_key="o")
+            return norm(f"L{l}.nb{k}.ln_ffn", x_res, lw.ln_ffn, bufs.h, k, [o], l)
+        o = gemm(f"L{l}.nb{k}.o", bufs.attn_out, lw.wo, part, k, deps=[dec, pre, last_x_writer[k]], layer=l,
+                 tile_key="o")
+        ar1, _ = coll.all_reduce(g, f"L{l}.nb{k}.ar_o", part, starts[k], nb_T[k], hidden, [o], l, k,
+                                 stream=S("net"), norm_w=lw.ln_ffn, norm_out=bufs.h, eps=model.rms_norm_eps,
+                                 status=st, num_ctas=comm_ctas, resid=x_res, sum_out=x_res, push_sum=False)
+        return ar1
 
     def ffn(l, k, lw, n2):
-        """gate/up SwiGLU -> down (+ residual / tp) -> all-reduce (+ fused next-layer attention norm)."""
-        xin, xout = bufs.x[cur], bufs.x[1 - cur] if tp > 1 else bufs.x[cur]
+        """gate/up SwiGLU -> down -> reduce (+ residual, + fused next-layer attention norm)."""
         gu = gemm(f"L{l}.nb{k}.gate_up", bufs.h, lw.wg, bufs.act, k, swiglu_up=lw.wu, deps=[n2], layer=l,
                   tile_key="gate_up")
-        # down writes back into the first buffer: after both projections the residual is where it started
-        d = gemm(f"L{l}.nb{k}.down", bufs.act, lw.wd, xin, k, residual=xout, beta=1.0 / tp, deps=[gu], layer=l,
-                 tile_key="down")
-        nxt = w.layers[(l + 1) % model.num_layers].ln_attn if l + 1 < model.run_layers else None
-        ar2, fused2 = coll.all_reduce(g, f"L{l}.nb{k}.ar_d", xin, starts[k], nb_T[k], hidden, [d], l, k,
-                                      stream=S("net"), norm_w=nxt, norm_out=bufs.h if nxt is not None else None,
-                                      eps=model.rms_norm_eps, status=st, num_ctas=comm_ctas)
-        last_x_writer[k] = ar2 if ar2 is not None else d
+        if tp == 1:
+            d = gemm(f"L{l}.nb{k}.down", bufs.act, lw.wd, x_res, k, residual=x_res, beta=1.0, deps=[gu], layer=l,
+                     tile_key="down")
+            last_x_writer[k] = d
+            return
+        d = gemm(f"L{l}.nb{k}.down", bufs.act, lw.wd, part, k, deps=[gu], layer=l, tile_key="down")
+        last = l + 1 >= model.run_layers
+        nxt = None if last else w.layers[(l + 1) % model.num_layers].ln_attn
+        ar2, fused2 = coll.all_reduce(g, f"L{l}.nb{k}.ar_d", part, starts[k], nb_T[k], hidden, [d], l, k,
+                                      stream=S("net"), norm_w=nxt, norm_out=None if last else bufs.h,
+                                      eps=model.rms_norm_eps, status=st, num_ctas=comm_ctas, resid=x_res,
+                                      sum_out=x_res, push_sum=last)
+        last_x_writer[k] = ar2
         h_normed[k] = ar2 if fused2 else None
 
     rope_of: Dict = {}
@@ -265,8 +280,9 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
                 ffn(l, k, lw, o_proj(l, k, lw, dec, pre))
 
     # ---- epilogue: sample --------------------------------------------------------------------------
-    gp = GatherParams(out=_ptr(bufs.sample_h), inp=_ptr(bufs.x[cur]), rows_idx=_ptr(m["sample_rows"]), n=0,
-                      cols=hidden, ld_in=bufs.x[cur].stride(0), in_rows=bufs.x[cur].shape[0], status=_ptr(st))
+    final_x = bufs.x[0] if tp == 1 else bufs.x[1]
+    gp = GatherParams(out=_ptr(bufs.sample_h), inp=_ptr(final_x), rows_idx=_ptr(m["sample_rows"]), n=0,
+                      cols=hidden, ld_in=final_x.stride(0), in_rows=final_x.shape[0], status=_ptr(st))
     ga = g.add("gather_last", gp, S("other"), deps=[d for d in last_x_writer if d is not None],
                dyn=[("n", n_sample)])
     fp = NormParams(out=_ptr(bufs.sample_hn), x=_ptr(bufs.sample_h), w=_ptr(w.norm), resid=c_void_p(0), rows=0,

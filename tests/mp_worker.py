@@ -49,6 +49,23 @@ def case_collectives(rank, world, dev):
     assert torch.allclose(buf.float(), total, atol=3e-2, rtol=1e-2)
     want_n = ref.rmsnorm(buf, wnorm, 1e-5)
     assert torch.allclose(out.float(), want_n, atol=3e-2, rtol=2e-2)
+    # sharded-residual form: owners add their residual rows, keep the sum locally, push only the norm
+    buf.copy_(parts[rank].to(dev))
+    resid = torch.randn(rows, cols, generator=g).bfloat16().to(dev)      # same on every rank
+    x_loc = resid.clone()
+    out.zero_()
+    torch.cuda.synchronize(); dist.barrier()
+    coll.all_reduce_(buf, norm_w=wnorm, norm_out=out, eps=1e-5, resid=x_loc, sum_out=x_loc, push_sum=False)
+    torch.cuda.synchronize()
+    coll.check_status()
+    mine = torch.arange(rank, rows, world, device=dev)
+    want_x = (total + resid.float())
+    assert torch.allclose(x_loc[mine].float(), want_x[mine], atol=4e-2, rtol=1e-2)
+    others = torch.tensor([i for i in range(rows) if i % world != rank], device=dev)
+    assert torch.equal(x_loc[others], resid[others])                      # rows of other owners untouched
+    assert torch.equal(buf, parts[rank].to(dev))                          # partials not overwritten
+    assert torch.allclose(out.float(), ref.rmsnorm(want_x.bfloat16(), wnorm, 1e-5), atol=4e-2, rtol=3e-2)
+    buf.copy_(total.bfloat16())
     # every rank holds bit-identical results (deterministic reduction order)
     gathered = [torch.empty_like(buf) for _ in range(world)]
     dist.all_gather(gathered, buf.contiguous())
