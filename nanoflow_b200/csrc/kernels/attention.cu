@@ -21,6 +21,7 @@
 // (gemv/include/attention/decode.cuh:827-872) and the wrappers in pipeline/include/gemvWrapper.cuh:140-237, :322-374.
 #include "common.cuh"
 #include "kernels.h"
+#include "attn_decode_static.h"
 
 namespace nf {
 namespace {
@@ -576,6 +577,55 @@ extern "C" int nfk_attn_decode(const nfk_attn_params* p, cudaStream_t stream) {
   if (p->chunk_pages < 0 || (p->chunk_pages > 0 && (p->max_chunks < 1 || p->workspace == nullptr)))
     return NF_ERR_BAD_ARG;
   return p->head_dim == 128 ? launch_decode<128>(p, stream) : launch_decode<64>(p, stream);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Split-KV decode without any allocation: the per-chunk partial results live in a fixed array that
+// is part of the library image instead of a caller-provided workspace.
+// ------------------------------------------------------------------------------------------------
+static __device__ __align__(256) float g_decode_static_scratch[NFK_ATTN_DECODE_STATIC_SCRATCH_FLOATS];
+
+namespace nf {
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch array on the current device. In host code the array's name is only
+// a handle for the runtime, never an address a kernel could use; the address has to be asked for,
+// once per device, with that device current.
+int static_scratch_for_current_device(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return NF_ERR_CUDA;
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_decode_static_scratch) != cudaSuccess || ptr == nullptr)
+      return NF_ERR_CUDA;
+    g_static_scratch_ptr[dev] = static_cast<float*>(ptr);
+  }
+  *out = g_static_scratch_ptr[dev];
+  return NF_OK;
+}
+}  // namespace
+}  // namespace nf
+
+extern "C" int nfk_attn_decode_static(const nfk_attn_params* p, cudaStream_t stream) {
+  using namespace nf;
+  const int rc = check_common(p);
+  if (rc != NF_OK) return rc;
+  if (p->req_count == 0) return NF_OK;
+  if (p->req_count < 0 || p->req_begin < 0 || p->chunk_pages < 0) return NF_ERR_BAD_ARG;
+  nfk_attn_params q = *p;
+  q.workspace = nullptr;
+  if (q.chunk_pages > 0) {
+    if (q.max_chunks < 1) return NF_ERR_BAD_ARG;
+    const long long need = static_cast<long long>(q.req_count) * q.q_heads * q.max_chunks * (q.head_dim + 2);
+    if (need > NFK_ATTN_DECODE_STATIC_SCRATCH_FLOATS) return NF_ERR_BAD_ARG;   // beyond the fixed scratch
+    float* scratch = nullptr;
+    const int rs = static_scratch_for_current_device(&scratch);
+    if (rs != NF_OK) return rs;
+    q.workspace = scratch;
+  }
+  return q.head_dim == 128 ? launch_decode<128>(&q, stream) : launch_decode<64>(&q, stream);
 }
 
 extern "C" int nfk_attn_prefill(const nfk_attn_params* p, cudaStream_t stream) {
