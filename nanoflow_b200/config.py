@@ -350,3 +350,49 @@ CONFIG_DIR = Path(__file__).resolve().parent / "configs"
 
 def shipped_config_path(model: str, variant: str = "2048") -> Path:
     return CONFIG_DIR / model / f"{variant}.json"
+
+
+# --------------------------------------------------------------------------------------------------
+# Shipped per-model configs: the variants the reference ships under pipeline/config_all/<model>/
+# (768 / 1024 / 2048 dense batch, non-overlap, nanobatch-only, pllm-offload) plus a B200-sized one.
+# --------------------------------------------------------------------------------------------------
+def shipped_variants(model: str) -> Dict[str, Dict[str, Any]]:
+    hf = MODEL_ARCHS[model]
+    small = hf["hidden_size"] <= 4096
+    gpus = 1 if small else 8
+    local = "_LOCAL" if gpus == 1 else ""
+    bias = hf["model_type"] == "qwen2"
+    full = "KQVBIAS" if bias else ("LOCAL" if gpus == 1 else "PLLM")
+    non = "NONOVERLAP_KQVBIAS" if bias else f"NON_OVERLAP{local}"
+    nano = "NANOBATCH_KQVBIAS" if bias else f"NANOBATCH{local}"
+    out = {}
+    for gbs in (768, 1024, 2048):
+        out[str(gbs)] = make_config(model, gpu_num=gpus, global_batch_size=gbs, pipeline_type=full)
+    out["non-overlap"] = make_config(model, gpu_num=gpus, global_batch_size=2048, pipeline_type=non)
+    out["nanobatch-only"] = make_config(model, gpu_num=gpus, global_batch_size=2048, pipeline_type=nano)
+    if gpus > 1 and not bias:
+        out["pllm-offload"] = make_config(model, gpu_num=gpus, global_batch_size=2048, pipeline_type="PLLM_OFFLOAD")
+    # 180 GB of HBM3e per GPU holds a far larger KV pool than the 80 GB parts the 2048 batch was sized for
+    big = 4096 if small else 8192
+    out[f"b200-{big}"] = make_config(model, gpu_num=gpus, global_batch_size=big, pipeline_type=full,
+                                     nanobatch_sizes=[big // 2, big // 2])
+    return out
+
+
+def write_shipped_configs(root: Optional[Path] = None) -> List[Path]:
+    root = root or CONFIG_DIR
+    written = []
+    for model in MODEL_ARCHS:
+        if model == "tiny":
+            continue
+        for name, raw in shipped_variants(model).items():
+            path = root / model / f"{name}.json"
+            path.parent.mkdir(parents=True, exist_ok=True)
+            path.write_text(json.dumps(raw, indent=2) + "\n")
+            written.append(path)
+    return written
+
+
+if __name__ == "__main__":
+    for p in write_shipped_configs():
+        print(p)

@@ -1,0 +1,122 @@
+"""Serving / offline-throughput entry point.
+
+    python -m nanoflow_b200.serve -t trace.csv -c nanoflow_b200/configs/llama3-8B/2048.json -r 200 \
+        --empty_weight True -o out/run1
+
+Flags follow the reference's ``serve_8B.py`` (pipeline/utils/serve_8B.py:584-596): ``-t`` trace CSV,
+``-c`` config JSON, ``-r`` run cycles, ``-s`` skip cycles (scheduler-only warm-up to the steady batch
+mix), ``--est_cycle_time`` (simulated seconds per cycle while skipping / in simulated-time mode),
+``--empty_weight`` (random-init weights instead of converted checkpoints), ``-o`` output prefix,
+``--allocate_page_num`` (KV pages per GPU; 0 = size from free memory). For tensor parallel runs launch
+one process per GPU with ``python -m torch.distributed.run --nproc-per-node N -m nanoflow_b200.serve ...``.
+Outputs: ``<prefix>.stat / .stat.csv / .req_time / .req_tokens / .schedule`` (see serving/stats.py).
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import time
+
+
+def _bool(s: str) -> bool:
+    return str(s).lower() in ("1", "true", "yes", "y")
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("-t", "--trace_path", type=str, required=True, help="request trace CSV")
+    ap.add_argument("-r", "--run_cycles", type=int, default=20)
+    ap.add_argument("-c", "--config_path", type=str, required=True, help="four-section config JSON")
+    ap.add_argument("-s", "--skip_cycles", type=int, default=0)
+    ap.add_argument("--est_cycle_time", type=float, default=0.175)
+    ap.add_argument("-o", "--output_prefix", type=str, default="")
+    ap.add_argument("--allocate_page_num", type=int, default=0)
+    ap.add_argument("--empty_weight", type=_bool, default=False)
+    ap.add_argument("--online", type=_bool, default=False, help="release requests by wall clock (arrival times)")
+    ap.add_argument("--random_ids", type=_bool, default=True, help="synthetic prompts use uniform-random token ids")
+    ap.add_argument("--stop_on_eos", type=_bool, default=False)
+    ap.add_argument("--backend", choices=["gpu", "cpu"], default="gpu")
+    ap.add_argument("--until_empty", type=_bool, default=False, help="ignore -r and run until the trace is served")
+    return ap
+
+
+def main(argv=None) -> int:
+    args = build_parser().parse_args(argv)
+    import torch
+
+    from .config import load_config
+    from .models import random_full_weights, random_rank_weights, shard_weights
+    from .models.weights import load_rank_weights
+    from .serving import DistKVPool, RequestManager, Scheduler
+    from .serving.loop import ServingLoop
+    from .serving.stats import summarize, write_outputs
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    cfg = load_config(args.config_path, tp=world if world > 1 else None)
+    model, eng_cfg = cfg.model, cfg.engine
+    if world > 1 and world != model.tp:
+        raise SystemExit(f"config is for tp={model.tp} but WORLD_SIZE={world}")
+
+    rm = RequestManager(args.trace_path, vocab_size=model.vocab_size, random_ids=args.random_ids)
+    rm.read_request(eng_cfg.model_id if False else None)
+
+    coll = None
+    if args.backend == "gpu":
+        from .runtime.engine import Engine
+
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        if world > 1:
+            import torch.distributed as dist
+            from .parallel.collectives import TpCollectives
+
+            dist.init_process_group("nccl", device_id=dev)
+            coll = TpCollectives(rank, world, dev)
+        if args.empty_weight or not eng_cfg.weight_path or not os.path.isdir(eng_cfg.weight_path):
+            weights = random_rank_weights(model, rank, max(1, world), dev)
+        else:
+            weights = load_rank_weights(eng_cfg.weight_path, model, rank, max(1, world), device=dev)
+        engine = Engine(cfg, weights, device=dev, collectives=coll, num_pages=args.allocate_page_num or None)
+        num_pages = engine.num_pages
+    else:
+        from .runtime.cpu_backend import CpuEngine
+
+        tp = model.tp
+        fw = random_full_weights(model, seed=0)
+        num_pages = args.allocate_page_num or 4096
+        engine = CpuEngine(cfg, [shard_weights(fw, model, r, tp, dtype=torch.float32) for r in range(tp)],
+                           num_pages=num_pages)
+
+    pool = DistKVPool(model.run_layers, model.num_kv_heads, model.head_dim, num_pages, eng_cfg.page_size, model.tp)
+    sch = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=eng_cfg.global_batch_size,
+                    nanobatch_sizes=eng_cfg.resolved_nanobatches(), max_batch_size=eng_cfg.max_batch_size,
+                    average_prefill_length=rm.average_prefill_length, average_decode_length=rm.average_decode_length,
+                    group_size=model.group_size, eos_token_id=model.eos_token_id, stop_on_eos=args.stop_on_eos)
+    sch.keep_schedule_log = bool(args.output_prefix)
+    loop = ServingLoop(engine, sch, rm, simulated_time=not args.online, est_cycle_time=args.est_cycle_time)
+    if args.skip_cycles:
+        loop.skip_cycles(args.skip_cycles)
+    rm.start_processing()
+    t0 = time.perf_counter()
+    loop.run(max_cycles=None if args.until_empty else args.run_cycles, until_empty=True)
+    wall = time.perf_counter() - t0
+    engine.check_status()
+    st = loop.stats
+    summary = summarize(st.retired, wall, st.cycles, model.tp, rm.average_prefill_length, rm.average_decode_length)
+    if rank == 0:
+        print(f"cycles {st.cycles}  retired {summary.retired}  tokens/s {summary.token_per_second:.1f} "
+              f"(per GPU {summary.token_per_second_per_gpu:.1f})  cycle {summary.cycle_time * 1e3:.2f} ms")
+        if args.output_prefix:
+            os.makedirs(os.path.dirname(os.path.abspath(args.output_prefix)) or ".", exist_ok=True)
+            write_outputs(args.output_prefix, summary, st.retired, sch.schedule_log)
+    engine.finalize()
+    if world > 1:
+        torch.distributed.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -111,15 +111,17 @@ class RequestManager:
         else:
             self.start_idx = -1
 
-    def release_request(self, stamp_wall_clock: bool = True) -> None:
+    def release_request(self) -> None:
+        """Move requests whose arrival time has passed to the available queue; their ``start_time``
+        becomes the wall-clock release time (latencies are measured from it), as in the reference."""
         while self.full_request_queue.size > 0 and self.full_request_queue.peek().start_time <= self.passed_time:
             r = self.full_request_queue.get()
-            r.start_time = time.perf_counter() if stamp_wall_clock else r.start_time
+            r.start_time = time.perf_counter()
             self.avaliable_request_queue.put(r)
 
     def simulate_issue(self, estimate_cycle_time: float = 0.175) -> None:
         self.passed_time += estimate_cycle_time
-        self.release_request(stamp_wall_clock=False)
+        self.release_request()
 
     def issue(self) -> None:
         t = time.perf_counter()
