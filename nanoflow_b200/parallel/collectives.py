@@ -61,6 +61,47 @@ class TpCollectives(CollectiveHooks):
         self._epoch = 0
         self._adhoc_flags = self.heap.alloc_bytes(FLAG_BYTES)
 
+    @classmethod
+    def for_analysis(cls, rank: int, world: int, heap_bytes: int = 64 << 20) -> "TpCollectives":
+        """A TpCollectives whose "heap" is a host tensor: builds graphs for static checks (dependency
+        checker, op counts) on a machine without GPUs. Its ops must never be launched."""
+        self = cls.__new__(cls)
+        self.rank, self.tp, self.device = rank, world, torch.device("cpu")
+        self.num_ctas, self.fuse_norm = 16, True
+        self.status = torch.zeros(1, dtype=torch.int32)
+        self._epoch = 0
+
+        class _HostHeap:
+            def __init__(h):
+                h.buf = torch.zeros(heap_bytes, dtype=torch.uint8)
+                h.base, h.nbytes, h._bump = h.buf.data_ptr(), heap_bytes, 0
+                h.peer_base = [h.base] * world
+
+            def alloc_bytes(h, n, align=256):
+                off = (h._bump + align - 1) // align * align
+                if off + n > h.nbytes:
+                    raise RuntimeError("analysis heap exhausted")
+                h._bump = off + n
+                return off
+
+            def alloc(h, shape, dtype):
+                n = 1
+                for x in shape:
+                    n *= int(x)
+                nb = n * torch.empty(0, dtype=dtype).element_size()
+                off = h.alloc_bytes(max(nb, 16))
+                return h.buf[off:off + nb].view(dtype).view(*shape)
+
+            def offset_of(h, t):
+                return t.data_ptr() - h.base
+
+            def close(h):
+                pass
+
+        self.heap = _HostHeap()
+        self._adhoc_flags = self.heap.alloc_bytes(FLAG_BYTES)
+        return self
+
     # ---- plumbing ---------------------------------------------------------------------------------
     def ctx(self) -> CommCtx:
         c = CommCtx()

@@ -34,6 +34,7 @@ from .pipeline import Buffers, CollectiveHooks, IoSpec, build_graph
 
 RING = 3                       # host staging slots (iterations in flight + one being formed)
 DECODE_MAX_CHUNKS = 16
+OFFLOAD_HOST_BYTES = 256 << 20 # pinned host staging per ring slot for the KV offload
 GEMM_WS_BYTES = 160 << 20      # stream-K scratch: tile counters + two fp32 partial tiles per CTA
 DECODE_SPLIT_ROWS = 8192       # workspace rows (request x q head) reserved for split-KV decode
 
@@ -41,7 +42,7 @@ DECODE_SPLIT_ROWS = 8192       # workspace rows (request x q head) reserved for 
 class MetaLayout:
     """Offsets (int32 words) of every per-iteration array inside one contiguous metadata block."""
 
-    def __init__(self, T: int, B: int, nano_sizes: List[int], num_pages: int):
+    def __init__(self, T: int, B: int, nano_sizes: List[int], num_pages: int, offload_cap: int = 0):
         self.T, self.B = T, B
         off = 0
         self.off: Dict[str, int] = {}
@@ -61,6 +62,7 @@ class MetaLayout:
         self.item_caps = [s + 2 for s in nano_sizes]
         for k, cap in enumerate(self.item_caps):
             put(f"items{k}", cap * 3)
+        put("offload_pages", offload_cap)
         self.fixed_words = off
         put("kv_indices", num_pages + B)
         self.total_words = off
@@ -94,7 +96,13 @@ class Engine:
         x0 = plain(T, m.hidden_size)
         x = [x0, alloc(T, m.hidden_size) if weights.tp > 1 else x0]
         self.num_pages = int(num_pages or e.num_pages or self._derive_num_pages(T, B))
-        layout = MetaLayout(T, B, self.nano_sizes, self.num_pages)
+        # KV offload: pages of requests retired in an iteration are gathered layer by layer and
+        # copied to pinned host memory; at most offload_cap pages per iteration.
+        self.page_bytes_layer = 2 * m.kv_heads_local * e.page_size * m.head_dim * 2
+        self.offload_cap = 0
+        if e.offload:
+            self.offload_cap = max(16, min(2048, OFFLOAD_HOST_BYTES // (m.run_layers * self.page_bytes_layer)))
+        layout = MetaLayout(T, B, self.nano_sizes, self.num_pages, self.offload_cap)
         self.layout = layout
         self.meta_dev = torch.zeros(layout.total_words, dtype=torch.int32, device=dev)
         self.meta_host = [torch.zeros(layout.total_words, dtype=torch.int32).pin_memory() for _ in range(RING)]
@@ -119,6 +127,12 @@ class Engine:
             meta=meta, nano_items=nano_items,
             gemm_ws=torch.zeros(GEMM_WS_BYTES // 4, dtype=torch.float32, device=dev))
         io = IoSpec(self.meta_dev, layout.fixed_words, layout.off["kv_indices"])
+        self.offload_host = None
+        if self.offload_cap:
+            io.offload_staging = torch.zeros(self.offload_cap, self.page_bytes_layer // 2, dtype=bf, device=dev)
+            io.offload_pages = view("offload_pages")
+            self.offload_host = [torch.zeros(m.run_layers, self.offload_cap, self.page_bytes_layer // 2,
+                                             dtype=bf).pin_memory() for _ in range(RING)]
         self.graph: OpGraph = build_graph(m, e, weights, self.bufs, self.coll, io)
         self.tokens_host = [torch.zeros(B, dtype=torch.int32).pin_memory() for _ in range(RING)]
         self.tokens_np = [t.numpy() for t in self.tokens_host]
@@ -130,6 +144,7 @@ class Engine:
         self._last_tokens = np.zeros(0, dtype=np.int32)
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
+        self.last_offload = (0, 0)
         self.launches_per_iteration = len(self.graph.ops)
         self.executor_kind = executor
         self._make_executor(executor)
@@ -187,10 +202,19 @@ class Engine:
             put(f"items{k}", nb.items.reshape(-1))
             sym[f"nb{k}_T"], sym[f"nb{k}_items"] = nb.token_count, int(nb.items.shape[0])
             sym[f"nb{k}_dec_begin"], sym[f"nb{k}_dec_count"] = nb.dec_begin, nb.dec_count
+        n_off = 0
+        if self.offload_cap:
+            pages = plan.retired_pages if plan.retired_pages is not None else np.zeros(0, dtype=np.int32)
+            n_off = min(int(pages.size), self.offload_cap)
+            put("offload_pages", pages[:n_off])
+            sym["offload_n"] = n_off
+            host = self.offload_host[slot]
+            for l in range(self.model.run_layers):
+                sym[f"offload_dst_{l}"] = host.data_ptr() + l * host.stride(0) * host.element_size()
         cp, mc = self._decode_split(plan)
         sym["decode_chunk_pages"], sym["decode_max_chunks"] = cp, mc
         self._staged = dict(slot=slot, sym=sym, n_sample=int(plan.sample_rows.size),
-                            kv_words=int(plan.kv_indices.size), plan=plan)
+                            kv_words=int(plan.kv_indices.size), plan=plan, n_offload=n_off)
 
     def _decode_split(self, plan: BatchPlan):
         if self.eng.decode_chunk_pages > 0:
@@ -230,7 +254,7 @@ class Engine:
                 self.py_exec.run(sym, main_stream=self.stream)
                 self.done_events[slot].record(self.stream)
         self.h2d_bytes_last = 4 * (lay.fixed_words + st["kv_words"])
-        self.d2h_bytes_last = 4 * st["n_sample"]
+        self.d2h_bytes_last = 4 * st["n_sample"] + st.get("n_offload", 0) * self.page_bytes_layer * self.model.run_layers
         self._inflight.append(st)
         self._staged = None
         self._iter += 1
@@ -244,7 +268,15 @@ class Engine:
         else:
             self.done_events[st["slot"]].synchronize()
         self._last_tokens = self.tokens_np[st["slot"]][:st["n_sample"]].copy()
+        self.last_offload = (st["slot"], st.get("n_offload", 0))
         return self._last_tokens
+
+    def offloaded_pages(self) -> Optional[torch.Tensor]:
+        """Host copy [layers, n, page_elems] of the pages offloaded by the last waited iteration."""
+        if self.offload_host is None:
+            return None
+        slot, n = self.last_offload
+        return self.offload_host[slot][:, :n]
 
     def timeline(self):
         """(op name, stream class, start_us, end_us) of the last iteration run with ``timed=True``."""

@@ -87,6 +87,8 @@ class IoSpec:
     meta_dev: torch.Tensor      # int32 block on the device
     fixed_words: int            # words [0, fixed_words) are copied every iteration
     kv_off_words: int           # start of the kv_indices array (a prefix of it is copied)
+    offload_staging: Optional[torch.Tensor] = None   # device [cap, page_elems] gather target (KV offload)
+    offload_pages: Optional[torch.Tensor] = None     # int32 view: page ids of requests retired this iteration
 
 
 def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buffers,
@@ -257,11 +259,27 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         last_x_writer[k] = ar2
         h_normed[k] = ar2 if fused2 else None
 
+    def offload_layer(l, pool, pace_dep):
+        """Layer-by-layer KV offload of retired requests: gather their pages of layer l into a
+        staging buffer and copy them to pinned host memory, all on the copy stream beside the
+        layer's compute (the reference's PageAggregator + D2H on stream_cpy, pipeline/src/pipeline.cu:701-716)."""
+        page_bytes = pool[0].numel() * pool.element_size()
+        kp = KvMoveParams(pool=_ptr(pool), staging=_ptr(io.offload_staging), page_ids=_ptr(io.offload_pages),
+                          n_pages=0, page_bytes=page_bytes, num_pages=pool.shape[0], direction=0,
+                          num_ctas=budget.get("offload", 8) or 8, status=_ptr(st))
+        ga = g.add(f"L{l}.kv_gather", kp, "copy" if overlap else "gemm", deps=[pace_dep],
+                   dyn=[("n_pages", g.symbol("offload_n"))], layer=l)
+        cp = MemcpyParams(dst=c_void_p(0), src=_ptr(io.offload_staging), elem_bytes=page_bytes, count=0)
+        g.add(f"L{l}.kv_d2h", cp, "copy" if overlap else "gemm", deps=[ga],
+              dyn=[("dst", g.symbol(f"offload_dst_{l}")), ("count", g.symbol("offload_n"))], layer=l)
+
     rope_of: Dict = {}
     h_normed: List[Optional[int]] = [None] * nn     # op that already wrote normed rows of nano-batch k into h
     for l in range(model.run_layers):
         lw = w.layers[l % model.num_layers]
         pool = bufs.kv_pool[l]
+        if eng.offload and io is not None and io.offload_staging is not None:
+            offload_layer(l, pool, len(g.ops) - 1)
         if overlap and nn > 1:
             # Issue order per layer: (front_k, o_k) for every nano-batch, then ffn_k for every
             # nano-batch. The all-reduce after o_k then runs (on the net stream, its CTAs sharing SMs

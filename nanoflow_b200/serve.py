@@ -38,6 +38,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--stop_on_eos", type=_bool, default=False)
     ap.add_argument("--backend", choices=["gpu", "cpu"], default="gpu")
     ap.add_argument("--until_empty", type=_bool, default=False, help="ignore -r and run until the trace is served")
+    ap.add_argument("--heartbeat", type=_bool, default=False,
+                    help="tensor parallel runs: check before every launch that all ranks are alive")
     return ap
 
 
@@ -94,9 +96,22 @@ def main(argv=None) -> int:
     sch = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=eng_cfg.global_batch_size,
                     nanobatch_sizes=eng_cfg.resolved_nanobatches(), max_batch_size=eng_cfg.max_batch_size,
                     average_prefill_length=rm.average_prefill_length, average_decode_length=rm.average_decode_length,
-                    group_size=model.group_size, eos_token_id=model.eos_token_id, stop_on_eos=args.stop_on_eos)
+                    group_size=model.group_size, eos_token_id=model.eos_token_id, stop_on_eos=args.stop_on_eos,
+                    hold_retired_pages=bool(eng_cfg.offload and args.backend == "gpu"))
     sch.keep_schedule_log = bool(args.output_prefix)
-    loop = ServingLoop(engine, sch, rm, simulated_time=not args.online, est_cycle_time=args.est_cycle_time)
+    offload = None
+    if eng_cfg.offload and args.backend == "gpu":
+        from .serving.offload import KVOffloadManager
+
+        offload = KVOffloadManager(engine)
+    health = None
+    if args.heartbeat and world > 1:
+        from torch.distributed.distributed_c10d import _get_default_store
+        from .parallel.health import Heartbeat
+
+        health = Heartbeat(_get_default_store(), rank, world)
+    loop = ServingLoop(engine, sch, rm, simulated_time=not args.online, est_cycle_time=args.est_cycle_time,
+                       offload=offload, health=health)
     if args.skip_cycles:
         loop.skip_cycles(args.skip_cycles)
     rm.start_processing()

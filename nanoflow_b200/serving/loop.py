@@ -40,11 +40,12 @@ class LoopStats:
 
 class ServingLoop:
     def __init__(self, engine, scheduler: Scheduler, request_manager: RequestManager, *,
-                 simulated_time: bool = True, est_cycle_time: float = 0.175, offload=None):
+                 simulated_time: bool = True, est_cycle_time: float = 0.175, offload=None, health=None):
         self.engine, self.scheduler, self.rm = engine, scheduler, request_manager
         self.simulated_time = simulated_time
         self.est_cycle_time = est_cycle_time
         self.offload = offload
+        self.health = health      # parallel.health.Heartbeat: peers are checked before every launch
         self._prev: Optional[BatchPlan] = None
         self.stats = LoopStats()
 
@@ -74,6 +75,9 @@ class ServingLoop:
         """One cycle. Returns the plan that was launched (None if there was nothing to run)."""
         self._release()
         plan = self.scheduler.schedule()
+        if self.health is not None:
+            self.health.beat()
+            self.health.check()    # raises PeerFailure before anything that waits on a peer is launched
         if plan is not None:
             self.engine.update(plan)
             self.engine.run_async()

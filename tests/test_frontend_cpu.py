@@ -1,0 +1,142 @@
+"""Config schema, trace frontend, KV page accounting, weight files, stats files, trace generators."""
+import glob
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from nanoflow_b200 import config as C
+from nanoflow_b200.datasets import traces
+from nanoflow_b200.models import random_full_weights, shard_weights
+from nanoflow_b200.models.weights import load_rank_weights, rank_state_dicts, save_weights
+from nanoflow_b200.serving import (BatchedDistKVCache, DistKVCache, DistKVPool, KVPoolExhausted, RequestManager)
+
+
+def test_shipped_configs_parse_and_derive_per_gpu_sizes():
+    files = glob.glob(str(C.CONFIG_DIR / "*" / "*.json"))
+    assert len(files) >= 50
+    for f in files:
+        cfg = C.load_config(f)
+        assert cfg.engine.pipeline_type in C.PIPELINE_TYPES
+        assert sum(cfg.engine.resolved_nanobatches()) == cfg.engine.global_batch_size
+    cfg = C.load_config(C.shipped_config_path("llama2-70B", "2048"))
+    m = cfg.model
+    # per-GPU shapes of Llama-2-70B at TP 8 (the reference derives the same: pipeline/include/config.h:90-100)
+    assert (m.hidden_size, m.q_heads_local, m.kv_heads_local, m.ffn_local, m.qkv_size_local) == (8192, 8, 1, 3584, 1280)
+    q = C.load_config(C.shipped_config_path("qwen2-72B", "2048"))
+    assert q.model.qkv_bias and q.engine.pipeline_type == "KQVBIAS" and q.model.vocab_local * 8 >= 152064
+    l31 = C.load_config(C.shipped_config_path("llama3.1-8B", "2048"))
+    assert l31.model.rope_scaling["rope_type"] == "llama3" and l31.engine.pipeline_type == "LOCAL"
+
+
+def test_reference_config_file_loads_unchanged():
+    """A config in the reference's own schema (gemm_op_tag, nanobatch_1_size, kqv sizes) is accepted."""
+    raw = C.make_config("llama2-70B", gpu_num=8, global_batch_size=2048, pipeline_type="PLLM")
+    raw["pipeline_configs"] = {"gemm_op_tag": ["128_128_32_64_64_32_3_5_RowMajor_RowMajor_RowMajor"] * 9,
+                               "global_batch_size": 2048, "nanobatch_1_size": 640, "kqv1_size": 256, "kqv3_size": 768}
+    raw["model_configs"].update({"allocate_kv_data_batch": 1480, "gpu_mem": 68719476736, "page_mem_size": 32768})
+    cfg = C.parse_config(raw)
+    assert cfg.engine.resolved_nanobatches() == [640, 1408]
+    assert cfg.engine.num_pages == 1480 * 64 and len(cfg.engine.gemm_op_tag) == 9
+
+
+@pytest.mark.parametrize("mutate,msg", [
+    (lambda r: r.pop("pipeline_configs"), "missing section"),
+    (lambda r: r["serve_configs"].update(pipeline_type="WARP"), "unknown pipeline_type"),
+    (lambda r: r["pipeline_configs"].update(nanobatch_sizes=[100, 100]), "must sum"),
+    (lambda r: r["model_configs"].update(gpu_num=3), "not divisible"),
+])
+def test_malformed_configs_are_rejected(mutate, msg):
+    raw = C.make_config("llama3-8B", gpu_num=1, global_batch_size=2048)
+    mutate(raw)
+    with pytest.raises(ValueError, match=msg):
+        C.parse_config(raw)
+
+
+def test_trace_reader_and_release_clock(tmp_path):
+    p = tmp_path / "t.csv"
+    p.write_text("idx,input_len,output_len,arrival\n0,10,3,0.0\n1,20,4,0.5\n2,5,2,1.5\n")
+    rm = RequestManager(str(p), vocab_size=100, random_ids=True)
+    rm.read_request()
+    assert rm.full_request_queue.size == 3 and rm.average_prefill_length == 11 and rm.average_decode_length == 3
+    rm.simulate_issue(0.6)
+    assert rm.avaliable_request_queue.size == 2
+    rm.simulate_issue(1.0)
+    assert rm.avaliable_request_queue.size == 3
+    r = rm.avaliable_request_queue.get()
+    assert r.prompt.dtype == np.int32 and r.prompt.size == 10 and r.prompt.max() < 100
+
+
+@pytest.mark.parametrize("body,err", [
+    ("0,10\n", "expected idx"), ("0,abc,3,0.0\n", "invalid literal"), ("0,0,3,0.0\n", "input_len"),
+    ("0,10,0,0.0\n", "output_len"), ("0,-1,3,0.0,hello\n", "no tokenizer"), ("", "no requests")])
+def test_malformed_traces_are_rejected(tmp_path, body, err):
+    p = tmp_path / "bad.csv"
+    p.write_text("idx,input_len,output_len,arrival\n" + body)
+    with pytest.raises(ValueError, match=err):
+        RequestManager(str(p)).read_request()
+
+
+def test_kv_pool_and_cache_accounting():
+    pool = DistKVPool(2, 8, 128, 10, 16, 8)
+    a, b = DistKVCache(pool), DistKVCache(pool)
+    a.allocate_tokens(17)
+    assert a.num_pages == 2 and a.last_page_offset == 1 and pool.num_free_pages == 8
+    a.allocate_tokens(15)
+    assert a.num_pages == 2 and a.seqlen == 32 and a.last_page_offset == 16
+    b.allocate_tokens(100)
+    assert b.num_pages == 7 and pool.num_free_pages == 1
+    with pytest.raises(KVPoolExhausted):
+        a.allocate_tokens(33)
+    assert a.seqlen == 32 and a.num_pages == 2                      # failed allocation changed nothing
+    batched = BatchedDistKVCache([a], [b])
+    assert batched.kv_indptr.tolist() == [0, 2, 9] and batched.kv_last_page_len.tolist() == [16, 4]
+    assert sorted(batched.kv_indices.tolist()) == sorted(a.indicies.tolist() + b.indicies.tolist())
+    b.release()
+    a.release()
+    assert pool.num_free_pages == 10
+    with pytest.raises(ValueError):
+        pool.free_page(3)                                            # double free
+    with pytest.raises(ValueError):
+        DistKVPool(2, 6, 128, 10, 16, 4)                             # heads not divisible by devices
+
+
+def test_weight_files_have_reference_keys_and_layout(tmp_path):
+    cfg = C.builtin_config("tiny", gpu_num=2).model
+    fw = random_full_weights(cfg, seed=3)
+    sds = rank_state_dicts(fw, 2, dtype=torch.float32)
+    keys = set(sds[0])
+    assert {"ModelNorm", "Embed", "LmHead", "O1_0", "O2_0", "U_0", "G_0", "D_0", "KQV_0", "BKQV_0", "LNATT_0", "LNFFN_0"} <= keys
+    h, hd = cfg.hidden_size, cfg.head_dim
+    assert sds[0]["KQV_0"].shape == (h, cfg.qkv_size_local)             # [K, N], K | V | Q packed
+    assert sds[0]["O2_0"].shape == (cfg.q_size_local, h) and sds[0]["D_0"].shape == (cfg.ffn_local, h)
+    assert sds[0]["LmHead"].shape == (h, cfg.vocab_size)
+    kv = cfg.kv_size_local
+    assert torch.equal(sds[1]["KQV_0"][:, :kv].t(), fw.layers[0].wk[kv:2 * kv])
+    assert torch.equal(sds[1]["KQV_0"][:, 2 * kv:].t(), fw.layers[0].wq[cfg.q_size_local:])
+    save_weights(fw, 2, str(tmp_path), dtype=torch.float32)
+    for r in range(2):
+        got = load_rank_weights(str(tmp_path), cfg, r, 2, dtype=torch.float32)
+        want = shard_weights(fw, cfg, r, 2, dtype=torch.float32)
+        assert torch.equal(got.lm_head, want.lm_head)
+        for a, b in zip(got.layers, want.layers):
+            for k in ("wqkv", "wo", "wg", "wu", "wd", "ln_attn", "ln_ffn"):
+                assert torch.equal(getattr(a, k), getattr(b, k)), k
+    with pytest.raises(FileNotFoundError):
+        load_rank_weights(str(tmp_path), cfg, 5, 8)
+
+
+def test_trace_generators():
+    rows = traces.fixed_trace(1024, 512, 10)
+    assert all(r == (1024, 512, 0.0) for r in rows)
+    t1, t2 = traces.poisson_arrivals(1000, 20.0), traces.poisson_arrivals(1000, 20.0)
+    assert np.array_equal(t1, t2) and np.all(np.diff(t1) > 0) and abs(t1[-1] / 1000 - 0.05) < 0.01
+    pairs = traces.lognormal_lengths(5000)
+    ins, outs = np.array(pairs).T
+    assert ins.min() >= 16 and ins.max() <= 4096 and outs.min() >= 1 and outs.max() <= 2048
+    assert 450 < np.median(ins) < 750 and 180 < np.median(outs) < 330
+    kept = traces.filter_lengths([(100, 10), (4000, 10), (3000, 1024), (3072, 1025), (10, 0)])
+    assert kept == [(100, 10), (3000, 1024)]
+    assert len(traces.real_trace([(100, 10), (200, 20)], 7, rate=5.0)) == 7

@@ -1,0 +1,137 @@
+"""Scheduler behaviour: chunked prefill, nano-batch cuts, device feedback indices, admission by
+projected peak pages, retirement timing (EOS at i+2), preemption under KV pressure, page conservation."""
+import numpy as np
+import pytest
+
+from nanoflow_b200.serving import DistKVPool, NewRequestQueue, RequestManager, Scheduler
+
+
+def _mk(pool_pages=400, gbs=64, nano=None, n=10, in_len=50, out_len=8, **kw):
+    rm = RequestManager(vocab_size=1000, random_ids=True)
+    for _ in range(n):
+        rm.add_request(in_len, out_len, 0.0)
+    rm.finalize_stats()
+    rm.simulate_issue(1.0)
+    pool = DistKVPool(2, 2, 64, pool_pages, 16)
+    s = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=gbs, nanobatch_sizes=nano,
+                  average_prefill_length=in_len, average_decode_length=out_len, group_size=2, **kw)
+    return s, pool, rm
+
+
+def _drive(s, tokens_fn=None, max_iter=2000):
+    plans, prev = [], None
+    for _ in range(max_iter):
+        p = s.schedule()
+        if prev is not None:
+            toks = np.zeros(len(prev.sample_reqs), dtype=np.int32) if tokens_fn is None else tokens_fn(prev)
+            s.process_outputs(prev, toks)
+        prev = p
+        if p is None:
+            if not s.has_work:
+                break
+            continue
+        plans.append(p)
+    s.schedule()
+    return plans
+
+
+def test_chunked_prefill_and_layout():
+    s, pool, _ = _mk(gbs=64, n=3, in_len=50, out_len=4)
+    p = s.schedule()
+    # 64 dense tokens: request 0 whole (50), request 1 chunked (14); decode-first layout, none yet
+    assert p.num_tokens == 64 and p.num_decode == 0
+    assert [(r.req_idx, a, n) for r, a, n in p.prefill] == [(0, 0, 50), (1, 0, 14)]
+    assert p.sample_rows.tolist() == [49]                        # only request 0 finished its prompt
+    assert p.positions[:50].tolist() == list(range(50)) and p.positions[50:].tolist() == list(range(14))
+    assert p.kv_indptr.tolist() == [0, 4, 5] and p.kv_last_page_len.tolist() == [2, 14]
+    s.process_outputs(p, np.array([7], dtype=np.int32))
+    p2 = s.schedule()
+    # request 0 decodes (token on device: feedback index = its sample slot), request 1 continues at 14
+    assert p2.num_decode == 1 and p2.feedback_src[0] == -1 and p2.host_ids[0] == 7   # host already saw it
+    assert (p2.prefill[0][0].req_idx, p2.prefill[0][1], p2.prefill[0][2]) == (1, 14, 36)
+    assert p2.prefill[1][0].req_idx == 2 and p2.num_tokens == 64
+    p3 = s.schedule()                                             # formed before p2's tokens are known
+    assert p3.feedback_src[0] == p2.sample_reqs.index(p3.decode[0])
+    assert p3.feedback_src[1] == p2.sample_reqs.index(p3.decode[1])
+
+
+def test_nanobatch_cut_straddles_requests():
+    s, pool, _ = _mk(gbs=64, nano=[24, 40], n=3, in_len=50, out_len=4)
+    p = s.schedule()
+    a, b = p.nano
+    assert (a.token_start, a.token_count, b.token_start, b.token_count) == (0, 24, 24, 40)
+    # request 0 (tokens 0..49) is split across the cut; tiles never cross it; tile = 128/group = 64 tokens
+    assert a.items.tolist() == [[0, 0, 24]]
+    assert b.items.tolist() == [[0, 24, 26], [1, 50, 14]]
+    assert sum(it[2] for nb in p.nano for it in nb.items.tolist()) == p.num_tokens - p.num_decode
+
+
+def test_all_requests_finish_with_exact_lengths_and_pages_return():
+    s, pool, _ = _mk(pool_pages=400, gbs=96, nano=[32, 64], n=25, in_len=37, out_len=9)
+    plans = _drive(s)
+    assert len(s.retired) == 25 and all(len(r.output) == 9 for r in s.retired)
+    assert pool.num_free_pages == 400
+    assert all(p.num_tokens <= 96 for p in plans)
+    # every iteration's sampled slots are unique and in range
+    for p in plans:
+        assert len(set(p.sample_rows.tolist())) == len(p.sample_rows) and (p.sample_rows < p.num_tokens).all()
+
+
+def test_eos_retires_two_iterations_later():
+    s, pool, _ = _mk(gbs=64, n=1, in_len=10, out_len=50, eos_token_id=2, stop_on_eos=True)
+    emitted = {"n": 0}
+
+    def toks(plan):
+        emitted["n"] += 1
+        return np.array([2 if emitted["n"] == 3 else 5] * len(plan.sample_reqs), dtype=np.int32)
+
+    plans = _drive(s, toks)
+    r = s.retired[0]
+    assert r.output == [5, 5, 2]                                  # tokens after EOS are dropped
+    # the EOS was sampled in iteration 2 (0-based). Iteration 3 had already been formed when those
+    # tokens reached the host, so it still ran the request; the request is dropped when iteration 4
+    # (= i + 2) is formed, which therefore has nothing left to run.
+    assert len(plans) == 4
+
+
+def test_admission_respects_projected_peak_pages():
+    # each request will need ceil((50+30)/16) = 5 pages at its peak; 23 pages hold 4 of them, not 5
+    s, pool, _ = _mk(pool_pages=23, gbs=512, n=10, in_len=50, out_len=30)
+    plans = _drive(s)
+    assert len(plans[0].prefill) == 4
+    assert max(len(p.decode) + len(p.prefill) for p in plans) <= 4
+    assert len(s.retired) == 10 and s.preemptions == 0 and pool.num_free_pages == 23
+
+
+def test_usage_curve_matches_brute_force():
+    s, pool, _ = _mk(in_len=100, out_len=50)
+    rng = np.random.default_rng(0)
+    c = rng.integers(1, 200, size=300)
+    L = 152
+    brute = np.zeros(L, dtype=np.int64)
+    for cj in c:
+        for t in range(max(1, min(L, L - 1 - cj))):
+            brute[t] += (cj + t + 15) // 16
+    assert np.array_equal(s._usage_curve(c), brute)
+
+
+def test_preemption_when_outputs_outgrow_the_projection():
+    """Outputs far longer than the trace average: the projection under-estimates, allocation fails,
+    the newest decode request is evicted and recomputed; everything still finishes, no page leaks."""
+    rm = RequestManager(vocab_size=1000, random_ids=True)
+    for _ in range(6):
+        rm.add_request(30, 120, 0.0)
+    rm.finalize_stats()
+    rm.average_decode_length = 10                                  # a lie, to provoke over-admission
+    rm.simulate_issue(1.0)
+    pool = DistKVPool(2, 2, 64, 30, 16)
+    s = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=128, average_prefill_length=30,
+                  average_decode_length=10, group_size=2)
+    _drive(s, max_iter=5000)
+    assert s.preemptions > 0
+    done = {}
+    for r in s.retired:
+        done.setdefault(r.req_idx, 0)
+        done[r.req_idx] += len(r.output)
+    assert sorted(done) == list(range(6))
+    assert pool.num_free_pages == 30
