@@ -545,9 +545,9 @@ Shape choose_shape(const nfk_gemm_params& g, bool swiglu) {
   for (int i = 0; i < ncand; ++i) {
     const int bn = swiglu ? cand_sw[i][0] : cand_lin[i][0];
     const int mt = swiglu ? cand_sw[i][1] : cand_lin[i][1];
-    if (mt > 1 && m_tiles < mt && !(mt == 2 && m_tiles == 2)) {
-      if (m_tiles <= mt / 2) continue;             // most of the M tiles would be empty
-    }
+    // Several M tiles per CTA only pay off when M is small (weight streaming); with many M tiles
+    // the single TMEM accumulator set would serialise epilogue and main loop for nothing.
+    if (mt > 1 && (m_tiles > 4 || m_tiles <= mt / 2)) continue;
     const int out_bn = swiglu ? bn / 2 : bn;
     const int m_groups = (m_tiles + mt - 1) / mt;
     const int n_blocks = (g.N + out_bn - 1) / out_bn;
