@@ -107,6 +107,8 @@ def main():
     ap.add_argument("--nano", default="", help="comma-separated nano-batch sizes (must sum to the dense batch); "
                     "default: two halves for the overlapped pipelines")
     ap.add_argument("--comm-ctas", type=int, default=0)
+    ap.add_argument("--no-fuse-rs", action="store_true", help="K-split GEMMs write partials locally and the "
+                    "collective pulls them, instead of pushing them to their owners from the GEMM epilogue")
     ap.add_argument("--skip-cycles", type=int, default=1600)
     ap.add_argument("--executor", default="auto")
     ap.add_argument("--timeline", default="", help="after the timed regions, time every op of one iteration "
@@ -178,6 +180,8 @@ def main():
                          **({"nanobatch_sizes": nano} if nano else {}))
     if args.comm_ctas:
         cfg.engine.sm_budget["comm"] = args.comm_ctas
+    if args.no_fuse_rs:
+        cfg.engine.fuse_gemm_rs = False
     if args.layers:
         cfg.model.num_layers = args.layers
         cfg.model.run_layers = args.layers
@@ -286,7 +290,7 @@ def main():
             "config": {"model": args.model, "global_batch": gbs, "seq_len": args.input_len + args.output_len,
                        "input_len": args.input_len, "output_len": args.output_len,
                        "parallelism": f"tp{world}", "pipeline_type": ptype, "layers": model.run_layers,
-                       "nanobatches": cfg.engine.resolved_nanobatches(),
+                       "nanobatches": cfg.engine.resolved_nanobatches(), "fused_gemm_reduce_scatter": bool(cfg.engine.fuse_gemm_rs and tp > 1),
                        "kv_pages": eng.num_pages, "tokens_per_step": round(tokens_dev / args.steps, 1),
                        "l2": "inputs larger than L2 (weights per GPU >> 126 MB); no flush",
                        "steady_state": f"{args.skip_cycles} scheduler-only cycles before warm-up",

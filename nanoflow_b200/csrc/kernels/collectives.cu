@@ -82,8 +82,8 @@ __device__ __forceinline__ FlagBlock* flags_of(const nfk_comm_ctx& c, int r, lon
 
 // Entry handshake: tell every rank that this rank's input is complete, wait for everyone's.
 __device__ __forceinline__ void comm_enter(const nfk_comm_ctx& c, long long flag_off, unsigned int epoch,
-                                           unsigned int* status) {
-  if (blockIdx.x == 0 && threadIdx.x < c.nranks)
+                                           unsigned int* status, bool signal = true) {
+  if (signal && blockIdx.x == 0 && threadIdx.x < c.nranks)
     st_release_sys(&flags_of(c, threadIdx.x, flag_off)->ready[c.rank], epoch);
   if (threadIdx.x < c.nranks) {
     if (!wait_flag(&flags_of(c, c.rank, flag_off)->ready[threadIdx.x], epoch))
@@ -150,11 +150,13 @@ allreduce_kernel(nfk_allreduce_params p) {
   constexpr int CH = NR >= 8 ? 2 : (NR >= 4 ? 4 : 8);     // vectors per chunk
   __shared__ float red[8];
   const nfk_comm_ctx& c = p.ctx;
-  comm_enter(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status);
+  // src_mode 1: the producer GEMM pushed the partial rows into local slabs and raised the ready flags
+  comm_enter(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status, p.src_mode == 0);
 
   const int nvec = p.cols >> 3;
   const long long row_bytes = p.ld * 2;
   const uint4* wv = NORM ? reinterpret_cast<const uint4*>(p.norm_w) : nullptr;
+  const char* local_base = reinterpret_cast<const char*>(c.heap[c.rank]) + p.buf_off;
   const char* resid = reinterpret_cast<const char*>(p.resid);
   char* sum_out = reinterpret_cast<char*>(p.sum_out);
   const int owned = (p.rows - c.rank + NR - 1) / NR;       // rows rank, rank+NR, ... (may be <= 0)
@@ -170,9 +172,15 @@ allreduce_kernel(nfk_allreduce_params p) {
       for (int i = 0; i < CH; ++i) {
         const int v = threadIdx.x + (i0 + i) * kArThreads;
         if (v < nvec) {
+          if (p.src_mode == 0) {
 #pragma unroll
-          for (int r = 0; r < NR; ++r)
-            in[i][r] = ld_sys_v4(reinterpret_cast<const char*>(c.heap[r]) + p.buf_off + row * row_bytes + v * 16);
+            for (int r = 0; r < NR; ++r)
+              in[i][r] = ld_sys_v4(reinterpret_cast<const char*>(c.heap[r]) + p.buf_off + row * row_bytes + v * 16);
+          } else {
+#pragma unroll
+            for (int r = 0; r < NR; ++r)
+              in[i][r] = ld_sys_v4(local_base + (static_cast<long long>(r) * p.slab_rows + k) * row_bytes + v * 16);
+          }
           if (resid != nullptr) rs[i] = *reinterpret_cast<const uint4*>(resid + row * p.resid_ld * 2 + v * 16);
         }
       }
@@ -310,6 +318,8 @@ extern "C" int nfk_allreduce(const nfk_allreduce_params* p, cudaStream_t stream)
     return NF_ERR_BAD_ARG;
   if (p->sum_out != nullptr && ((reinterpret_cast<uintptr_t>(p->sum_out) & 15) || p->sum_ld % 8 != 0))
     return NF_ERR_BAD_ARG;
+  if (p->src_mode != 0 && (p->src_mode != 1 || p->push_sum != 0 || p->slab_rows * p->ctx.nranks < p->rows))
+    return NF_ERR_BAD_ARG;   // slab input: the sum cannot be pushed back into a per-rank buffer
   // Even an empty buffer takes part in the handshakes so that all ranks stay in step.
   const int nr = p->ctx.nranks;
   const int owned = (p->rows + nr - 1) / nr;

@@ -90,6 +90,10 @@ struct DevParams {
   int M, N, K;      // N = number of output columns
   int split_k;
   unsigned int* status;
+  // reduce-scatter epilogue (EPI == 2)
+  char* rs_heap[8];
+  int rs_rank, rs_nranks, rs_rows_cap, rs_epoch;
+  long long rs_slab_off, rs_flag_off;
 };
 
 // Wait helper shared by all roles: bounded by wall clock (globaltimer) and by the CTA abort flag.
@@ -361,6 +365,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               }
               continue;
             }
+            if (EPI == 2) {
+              // push the partial row to its owner's slab (posted NVLink stores; the flag raised at
+              // the end of the kernel orders them for the reader)
+              if (row_ok && col0 < p.N) {
+                const int owner = row % p.rs_nranks;
+                __nv_bfloat16* srow = reinterpret_cast<__nv_bfloat16*>(p.rs_heap[owner] + p.rs_slab_off) +
+                                      (static_cast<long long>(p.rs_rank) * p.rs_rows_cap + row / p.rs_nranks) * p.N;
+#pragma unroll
+                for (int g8 = 0; g8 < 4; ++g8) {
+                  const int col = col0 + g8 * 8;
+                  if (col < p.N) {
+                    const float* vv = v + g8 * 8;
+                    uint4 o;
+                    o.x = pack_bf16x2(vv[0], vv[1]);
+                    o.y = pack_bf16x2(vv[2], vv[3]);
+                    o.z = pack_bf16x2(vv[4], vv[5]);
+                    o.w = pack_bf16x2(vv[6], vv[7]);
+                    *reinterpret_cast<uint4*>(srow + col) = o;
+                  }
+                }
+              }
+              continue;
+            }
             if (row_ok && col0 < p.N) {
 #pragma unroll
               for (int g8 = 0; g8 < 4; ++g8) {
@@ -407,11 +434,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   }
 
+  if (EPI == 2) __threadfence_system();   // this thread's pushes are ordered before the flag below
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+  if (EPI == 2 && threadIdx.x == 0) {
+    // The last CTA to get here tells every rank that this rank's partial rows have been pushed.
+    // Flag block layout (collectives.cu): ready[8], done[8], cta_counter.
+    unsigned int* mine = reinterpret_cast<unsigned int*>(p.rs_heap[p.rs_rank] + p.rs_flag_off);
+    const unsigned int prev = atomicAdd(mine + 16, 1u);
+    if (prev == gridDim.x - 1) {
+      mine[16] = 0;
+      __threadfence_system();
+      for (int r = 0; r < p.rs_nranks; ++r) {
+        unsigned int* flag = reinterpret_cast<unsigned int*>(p.rs_heap[r] + p.rs_flag_off) + p.rs_rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(static_cast<unsigned int>(p.rs_epoch))
+                     : "memory");
+      }
+    }
+  }
+}
+
+// Reduce-scatter epilogue with nothing to push (an empty nano-batch): the consumer still waits for
+// this rank's ready flag, so raise it.
+__global__ void rs_signal_only_kernel(DevParams p) {
+  if (threadIdx.x < p.rs_nranks) {
+    unsigned int* flag = reinterpret_cast<unsigned int*>(p.rs_heap[threadIdx.x] + p.rs_flag_off) + p.rs_rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(static_cast<unsigned int>(p.rs_epoch))
+                 : "memory");
   }
 }
 
@@ -512,6 +565,13 @@ int launch(const nfk_gemm_params& g, int split_k, cudaStream_t stream) {
   p.K = g.K;
   p.split_k = split_k;
   p.status = g.status;
+  for (int r = 0; r < 8; ++r) p.rs_heap[r] = reinterpret_cast<char*>(g.rs_heap[r]);
+  p.rs_rank = g.rs_rank;
+  p.rs_nranks = g.rs_nranks;
+  p.rs_rows_cap = g.rs_rows_cap;
+  p.rs_epoch = g.rs_epoch;
+  p.rs_slab_off = g.rs_slab_off;
+  p.rs_flag_off = g.rs_flag_off;
   gemm_tcgen05_kernel<BN, MT, EPI><<<ctas, kGemmThreads, C::SMEM_BYTES, stream>>>(tmA, tmB0, tmB1, p);
   if (cudaGetLastError() != cudaSuccess) return NF_ERR_CUDA;
   if (split_k > 1) {
@@ -557,7 +617,7 @@ Shape choose_shape(const nfk_gemm_params& g, bool swiglu) {
     const double t_mma = 2.0 * BM * mt_eff * bn * BK / 11.0e6;
     const double t_fill = (mt_eff * 16384.0 + bn * 128.0) / 110.0e3;
     const double t_kb = t_mma > t_fill ? t_mma : t_fill;
-    const int max_sk = (swiglu || g.workspace == nullptr) ? 1 : 8;
+    const int max_sk = (swiglu || g.workspace == nullptr || g.epilogue == NFK_EPI_REDUCE_SCATTER) ? 1 : 8;
     for (int sk = 1; sk <= max_sk; ++sk) {
       if (sk > 1 && (num_kb / sk < 8 || static_cast<long long>(sk) * g.M * g.N * 4 > g.workspace_bytes)) break;
       const int units = tiles * sk;
@@ -580,8 +640,20 @@ Shape choose_shape(const nfk_gemm_params& g, bool swiglu) {
 extern "C" int nfk_gemm_bf16(const nfk_gemm_params* g, cudaStream_t stream) {
   using namespace nf;
   if (g == nullptr) return NF_ERR_BAD_ARG;
+  if (g->M == 0 && g->epilogue == NFK_EPI_REDUCE_SCATTER) {
+    if (g->rs_nranks < 1 || g->rs_nranks > 8 || g->rs_rank < 0 || g->rs_rank >= g->rs_nranks) return NF_ERR_BAD_ARG;
+    DevParams p{};
+    for (int r = 0; r < 8; ++r) p.rs_heap[r] = reinterpret_cast<char*>(g->rs_heap[r]);
+    p.rs_rank = g->rs_rank;
+    p.rs_nranks = g->rs_nranks;
+    p.rs_epoch = g->rs_epoch;
+    p.rs_flag_off = g->rs_flag_off;
+    rs_signal_only_kernel<<<1, 32, 0, stream>>>(p);
+    return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
+  }
   if (g->M == 0 || g->N == 0) return NF_OK;  // empty nano-batch: nothing to do
-  if (g->A == nullptr || g->B == nullptr || g->D == nullptr) return NF_ERR_BAD_ARG;
+  if (g->A == nullptr || g->B == nullptr) return NF_ERR_BAD_ARG;
+  if (g->D == nullptr && g->epilogue != NFK_EPI_REDUCE_SCATTER) return NF_ERR_BAD_ARG;
   if (g->M < 0 || g->N < 0 || g->K <= 0) return NF_ERR_BAD_ARG;
   if (g->K % 8 != 0 || g->N % 8 != 0 || g->lda % 8 != 0 || g->ldb % 8 != 0 || g->ldd % 8 != 0)
     return NF_ERR_BAD_ARG;
@@ -591,8 +663,18 @@ extern "C" int nfk_gemm_bf16(const nfk_gemm_params* g, cudaStream_t stream) {
   if (g->workspace != nullptr && (reinterpret_cast<uintptr_t>(g->workspace) & 15) != 0) return NF_ERR_BAD_ARG;
   const bool swiglu = g->epilogue == NFK_EPI_SWIGLU;
   if (swiglu && g->B2 == nullptr) return NF_ERR_BAD_ARG;
+  const bool rs = g->epilogue == NFK_EPI_REDUCE_SCATTER;
+  if (rs) {
+    if (g->rs_nranks < 1 || g->rs_nranks > 8 || g->rs_rank < 0 || g->rs_rank >= g->rs_nranks ||
+        g->rs_rows_cap * g->rs_nranks < g->M || g->rs_slab_off % 16 != 0 || g->rs_flag_off % 16 != 0 ||
+        g->split_k > 1)
+      return NF_ERR_BAD_ARG;
+    for (int r = 0; r < g->rs_nranks; ++r)
+      if (g->rs_heap[r] == nullptr) return NF_ERR_BAD_ARG;
+  }
 
   Shape s = choose_shape(*g, swiglu);
+  if (rs) s.split_k = 1;   // partial tiles go straight to their owners: no K split
   if (g->tile_n != 0 || g->tile_m != 0) {
     // pinned tile shape: fill in the other dimension with its default, split only on request
     s.bn = g->tile_n != 0 ? g->tile_n : 256;
@@ -614,6 +696,17 @@ extern "C" int nfk_gemm_bf16(const nfk_gemm_params* g, cudaStream_t stream) {
       case 2562: return launch<256, 2, 1>(*g, 1, stream);
       case 1282: return launch<128, 2, 1>(*g, 1, stream);
       case 1284: return launch<128, 4, 1>(*g, 1, stream);
+      default: return NF_ERR_UNSUPPORTED;
+    }
+  }
+  if (rs) {
+    switch (key) {
+      case 2561: return launch<256, 1, 2>(*g, 1, stream);
+      case 1281: return launch<128, 1, 2>(*g, 1, stream);
+      case 641: return launch<64, 1, 2>(*g, 1, stream);
+      case 2562: return launch<256, 2, 2>(*g, 1, stream);
+      case 1282: return launch<128, 2, 2>(*g, 1, stream);
+      case 1284: return launch<128, 4, 2>(*g, 1, stream);
       default: return NF_ERR_UNSUPPORTED;
     }
   }

@@ -13,7 +13,7 @@ extern "C" {
 // ------------------------------------------------------------------------------------------------
 // GEMM (gemm.cu)
 // ------------------------------------------------------------------------------------------------
-enum { NFK_EPI_LINEAR = 0, NFK_EPI_SWIGLU = 1 };
+enum { NFK_EPI_LINEAR = 0, NFK_EPI_SWIGLU = 1, NFK_EPI_REDUCE_SCATTER = 2 };
 
 typedef struct nfk_gemm_params {
   const void* A;    // [M,K] bf16, row-major, leading dimension lda
@@ -33,6 +33,17 @@ typedef struct nfk_gemm_params {
   int split_k;      // 0 = choose; > 1 needs `workspace` (fp32 partials, split_k*M*N*4 bytes)
   void* workspace;
   long long workspace_bytes;
+  // NFK_EPI_REDUCE_SCATTER: the epilogue does not write D; it pushes every bf16 partial row straight
+  // into the slab of the rank that owns the row (row i belongs to rank i % rs_nranks), over NVLink:
+  //   heap[owner] + rs_slab_off + ((rs_rank * rs_rows_cap + i / rs_nranks) * N + col) * 2
+  // and, once all CTAs are done, raises ready[rs_rank] = rs_epoch in the flag block at rs_flag_off
+  // on every rank. nfk_allreduce with src_mode 1 then reduces the slabs locally.
+  void* rs_heap[8];
+  int rs_rank, rs_nranks;
+  long long rs_slab_off;
+  int rs_rows_cap;
+  long long rs_flag_off;
+  int rs_epoch;
 } nfk_gemm_params;
 
 int nfk_gemm_bf16(const nfk_gemm_params* p, cudaStream_t stream);
@@ -160,6 +171,10 @@ typedef struct nfk_allreduce_params {
   long long resid_ld;
   void* sum_out;          // optional local bf16 [rows, sum_ld]: owned rows of the sum are stored here
   long long sum_ld;
+  int src_mode;           // 0: pull row i from every rank's buffer. 1: the partials were pushed here by a
+                          //    NFK_EPI_REDUCE_SCATTER GEMM: owned row k of rank r's partial sits in the local
+                          //    slab at buf_off + (r * slab_rows + k) * ld (no NVLink loads, no ready signal)
+  int slab_rows;
 } nfk_allreduce_params;
 int nfk_allreduce(const nfk_allreduce_params* p, cudaStream_t stream);
 

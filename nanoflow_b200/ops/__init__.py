@@ -36,7 +36,9 @@ class GemmParams(Structure):
                 ("beta", c_float), ("M", c_int), ("N", c_int), ("K", c_int),
                 ("epilogue", c_int), ("tile_n", c_int), ("num_ctas", c_int),
                 ("status", c_void_p), ("tile_m", c_int), ("split_k", c_int), ("workspace", c_void_p),
-                ("workspace_bytes", c_longlong)]
+                ("workspace_bytes", c_longlong),
+                ("rs_heap", c_void_p * 8), ("rs_rank", c_int), ("rs_nranks", c_int), ("rs_slab_off", c_longlong),
+                ("rs_rows_cap", c_int), ("rs_flag_off", c_longlong), ("rs_epoch", c_int)]
 
 
 class RopeAppendParams(Structure):

@@ -28,7 +28,7 @@ class AllReduceParams(Structure):
                 ("cols", c_int), ("ld", c_longlong), ("epoch", c_int), ("num_ctas", c_int),
                 ("norm_w", c_void_p), ("norm_out_off", c_longlong), ("norm_ld", c_longlong), ("eps", c_float),
                 ("status", c_void_p), ("push_sum", c_int), ("resid", c_void_p), ("resid_ld", c_longlong),
-                ("sum_out", c_void_p), ("sum_ld", c_longlong)]
+                ("sum_out", c_void_p), ("sum_ld", c_longlong), ("src_mode", c_int), ("slab_rows", c_int)]
 
 
 class AllGatherParams(Structure):
@@ -121,8 +121,11 @@ class TpCollectives(CollectiveHooks):
                    deps, layer: int, nano: int, stream: str = "net", norm_w: Optional[torch.Tensor] = None,
                    norm_out: Optional[torch.Tensor] = None, eps: float = 1e-5, status=None, num_ctas: int = 0,
                    resid: Optional[torch.Tensor] = None, sum_out: Optional[torch.Tensor] = None,
-                   push_sum: bool = True):
+                   push_sum: bool = True, slab: Optional[dict] = None):
         """Append a reduction of ``buf`` rows [row0, row0+rows) over all ranks.
+
+        With ``slab`` (from :meth:`rs_slot`) the partial rows were pushed into local slabs by a GEMM
+        with the reduce-scatter epilogue: the op then reads locally and shares the GEMM's flag block.
 
         ``resid`` / ``sum_out`` are local tensors (rows owned by this rank are read / written);
         ``push_sum`` writes the sum back into ``buf`` on every rank; ``norm_w`` + ``norm_out`` push
@@ -130,8 +133,12 @@ class TpCollectives(CollectiveHooks):
         p = AllReduceParams()
         p.ctx = self.ctx()
         esz = buf.element_size()
-        p.buf_off = self.heap.offset_of(buf) + row0 * buf.stride(0) * esz
-        p.flag_off = self.new_flags()
+        if slab is not None:
+            p.buf_off, p.flag_off = slab["slab_off"], slab["flag_off"]
+            p.src_mode, p.slab_rows = 1, slab["rows_cap"]
+        else:
+            p.buf_off = self.heap.offset_of(buf) + row0 * buf.stride(0) * esz
+            p.flag_off = self.new_flags()
         p.rows, p.cols, p.ld = 0, cols, buf.stride(0)
         p.epoch, p.num_ctas = 0, num_ctas or self.num_ctas
         fused = norm_w is not None and norm_out is not None
@@ -148,6 +155,13 @@ class TpCollectives(CollectiveHooks):
         idx = g.add(name, p, stream, deps=deps, dyn=[("rows", rows_sym), ("epoch", g.symbol("epoch"))],
                     layer=layer, nano=nano)
         return idx, fused
+
+    def rs_slot(self, part: torch.Tensor, slab_row0: int, rows_cap: int) -> dict:
+        """Slab + flag block for one fused GEMM -> reduce-scatter: ``part`` rows
+        [slab_row0, slab_row0 + tp * rows_cap) hold, per source rank, the partial rows this rank owns."""
+        return {"slab_off": self.heap.offset_of(part) + slab_row0 * part.stride(0) * part.element_size(),
+                "rows_cap": rows_cap, "flag_off": self.new_flags(), "heap": list(self.heap.peer_base),
+                "rank": self.rank, "nranks": self.tp}
 
     def all_gather_candidates(self, g: OpGraph, bufs: Buffers, rows_sym: str, deps):
         """cand_val / cand_idx are [tp, B] symmetric arrays; every rank pushes its row to all peers."""

@@ -94,7 +94,7 @@ class Engine:
         # x[0]: residual stream (local). x[1]: under TP the symmetric buffer the K-split GEMMs write
         # their partial products into (peers pull from it); on one GPU it aliases x[0].
         x0 = plain(T, m.hidden_size)
-        x = [x0, alloc(T, m.hidden_size) if weights.tp > 1 else x0]
+        x = [x0, alloc(T + 8 * len(self.nano_sizes), m.hidden_size) if weights.tp > 1 else x0]
         self.num_pages = int(num_pages or e.num_pages or self._derive_num_pages(T, B))
         # KV offload: pages of requests retired in an iteration are gathered layer by layer and
         # copied to pinned host memory; at most offload_cap pages per iteration.

@@ -144,23 +144,32 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
     cur = 0                                             # which residual buffer holds x
 
     def gemm(name, a, wt, out, k, *, residual=None, beta=1.0, bias=None, swiglu_up=None, deps=(), layer=-1,
-             tile_key=None):
+             tile_key=None, rs=None):
         p = GemmParams()
         r0 = starts[k]
-        p.A, p.B, p.D = _ptr(a, r0), _ptr(wt), _ptr(out, r0)
+        p.A, p.B, p.D = _ptr(a, r0), _ptr(wt), (_ptr(out, r0) if out is not None else c_void_p(0))
         p.B2 = _ptr(swiglu_up)
         p.C, p.bias = _ptr(residual, r0) if residual is not None else c_void_p(0), _ptr(bias)
-        p.lda, p.ldb, p.ldd = a.stride(0), wt.stride(0), out.stride(0)
+        p.lda, p.ldb, p.ldd = a.stride(0), wt.stride(0), (out.stride(0) if out is not None else wt.shape[0])
         p.ldc = residual.stride(0) if residual is not None else 0
         p.beta, p.M, p.N, p.K = beta, 0, wt.shape[0], wt.shape[1]
         p.epilogue = 1 if swiglu_up is not None else 0
+        dyn = [("M", nb_T[k])]
+        if rs is not None:
+            # fused GEMM -> reduce-scatter: the epilogue pushes partial rows to their owners' slabs
+            p.epilogue = 2
+            for r, base in enumerate(rs["heap"]):
+                p.rs_heap[r] = base
+            p.rs_rank, p.rs_nranks, p.rs_rows_cap = rs["rank"], rs["nranks"], rs["rows_cap"]
+            p.rs_slab_off, p.rs_flag_off = rs["slab_off"], rs["flag_off"]
+            dyn.append(("rs_epoch", g.symbol("epoch")))
         p.tile_n = eng.gemm_tile_n.get(tile_key or name.split(".")[-1], 0)
         p.num_ctas = budget.get("gemm", 0)
         p.status = _ptr(st)
         if bufs.gemm_ws is not None:
             p.workspace = _ptr(bufs.gemm_ws)
             p.workspace_bytes = bufs.gemm_ws.numel() * bufs.gemm_ws.element_size()
-        return g.add(name, p, "gemm", deps=deps, dyn=[("M", nb_T[k])], layer=layer, nano=k)
+        return g.add(name, p, "gemm", deps=deps, dyn=dyn, layer=layer, nano=k)
 
     def norm(name, x, wt, out, k, deps, layer, resid=None):
         r0 = starts[k]
@@ -226,6 +235,25 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
     # to every rank instead, so `part` then holds the full final hidden state for sampling.
     x_res = bufs.x[0]
     part = bufs.x[1]
+    # Fused GEMM -> reduce-scatter: the K-split GEMMs push their partial rows straight into the owners'
+    # slabs from the epilogue (NVLink stores issued tile by tile while later tiles are still in the
+    # tensor cores); the collective that follows then only reads local memory and pushes normed rows.
+    fuse_rs = tp > 1 and eng.fuse_gemm_rs and hasattr(coll, "rs_slot")
+    rs_geom = []
+    if fuse_rs:
+        row0 = 0
+        for k in range(nn):
+            cap = (sizes[k] + tp - 1) // tp
+            rs_geom.append((row0, cap))
+            row0 += cap * tp
+        if row0 > part.shape[0]:
+            raise ValueError("partial-product buffer too small for the reduce-scatter slabs")
+
+    def rs_slot(k):
+        # the slab region of a nano-batch is reused by every fused GEMM of that nano-batch (they are
+        # ordered by their collectives' exit handshakes); the flag block is private to each GEMM +
+        # collective pair, because flags carry only the iteration's epoch
+        return coll.rs_slot(part, *rs_geom[k])
 
     def o_proj(l, k, lw, dec, pre):
         """O projection -> reduce (+ residual, + fused FFN norm). Returns the op the FFN waits for."""
@@ -233,11 +261,13 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
             o = gemm(f"L{l}.nb{k}.o", bufs.attn_out, lw.wo, x_res, k, residual=x_res, beta=1.0, deps=[dec, pre],
                      layer=l, tile_key="o")
             return norm(f"L{l}.nb{k}.ln_ffn", x_res, lw.ln_ffn, bufs.h, k, [o], l)
-        o = gemm(f"L{l}.nb{k}.o", bufs.attn_out, lw.wo, part, k, deps=[dec, pre, last_x_writer[k]], layer=l,
-                 tile_key="o")
+        slab = rs_slot(k) if fuse_rs else None
+        o = gemm(f"L{l}.nb{k}.o", bufs.attn_out, lw.wo, None if fuse_rs else part, k,
+                 deps=[dec, pre, last_x_writer[k]], layer=l, tile_key="o", rs=slab)
         ar1, _ = coll.all_reduce(g, f"L{l}.nb{k}.ar_o", part, starts[k], nb_T[k], hidden, [o], l, k,
                                  stream=S("net"), norm_w=lw.ln_ffn, norm_out=bufs.h, eps=model.rms_norm_eps,
-                                 status=st, num_ctas=comm_ctas, resid=x_res, sum_out=x_res, push_sum=False)
+                                 status=st, num_ctas=comm_ctas, resid=x_res, sum_out=x_res, push_sum=False,
+                                 slab=slab)
         return ar1
 
     def ffn(l, k, lw, n2):
@@ -249,13 +279,17 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
                      tile_key="down")
             last_x_writer[k] = d
             return
-        d = gemm(f"L{l}.nb{k}.down", bufs.act, lw.wd, part, k, deps=[gu], layer=l, tile_key="down")
         last = l + 1 >= model.run_layers
+        # the last layer's sum must reach every rank in full (sampling reads arbitrary rows), which
+        # the slab form cannot do: it keeps the pull form with push_sum
+        slab = rs_slot(k) if (fuse_rs and not last) else None
+        d = gemm(f"L{l}.nb{k}.down", bufs.act, lw.wd, None if slab else part, k, deps=[gu], layer=l,
+                 tile_key="down", rs=slab)
         nxt = None if last else w.layers[(l + 1) % model.num_layers].ln_attn
         ar2, fused2 = coll.all_reduce(g, f"L{l}.nb{k}.ar_d", part, starts[k], nb_T[k], hidden, [d], l, k,
                                       stream=S("net"), norm_w=nxt, norm_out=None if last else bufs.h,
                                       eps=model.rms_norm_eps, status=st, num_ctas=comm_ctas, resid=x_res,
-                                      sum_out=x_res, push_sum=last)
+                                      sum_out=x_res, push_sum=last, slab=slab)
         last_x_writer[k] = ar2
         h_normed[k] = ar2 if fused2 else None
 

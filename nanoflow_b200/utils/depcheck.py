@@ -77,7 +77,11 @@ def graph_access(graph: OpGraph, nano_starts: List[int], nano_sizes: List[int], 
             add(reads, rng(p.B, p.N, p.ldb, p.K))
             add(reads, rng(p.B2, p.N, p.ldb, p.K))
             add(reads, rng(p.C, rows, p.ldc, p.N))
-            add(writes, rng(p.D, rows, p.ldd, p.N))
+            if p.epilogue == 2:      # reduce-scatter epilogue: pushes into the slabs (this rank's image of them)
+                base = (p.rs_heap[p.rs_rank] or 0) + p.rs_slab_off
+                add(writes, (base, base + p.rs_nranks * p.rs_rows_cap * p.N * 2))
+            else:
+                add(writes, rng(p.D, rows, p.ldd, p.N))
             if p.workspace:
                 add(writes, (int(p.workspace), int(p.workspace) + int(p.workspace_bytes)))
         elif isinstance(p, G.NormParams):
@@ -101,7 +105,10 @@ def graph_access(graph: OpGraph, nano_starts: List[int], nano_sizes: List[int], 
                 add(reads, (int(p.kv_pool), int(p.kv_pool) + kv_pool_bytes))
         elif isinstance(p, AllReduceParams):
             base = heap_base + p.buf_off
-            buf = rng(base, cap, p.ld, p.cols)
+            if p.src_mode == 1:
+                buf = (base, base + p.ctx.nranks * p.slab_rows * p.ld * 2)
+            else:
+                buf = rng(base, cap, p.ld, p.cols)
             add(reads, buf)
             if p.push_sum:
                 add(writes, buf)

@@ -102,6 +102,62 @@ def case_collectives(rank, world, dev):
     coll.close()
 
 
+def case_fused(rank, world, dev):
+    """GEMM with the reduce-scatter epilogue (partial rows pushed to their owners from the epilogue)
+    followed by the slab-reading reduce + residual + norm + all-gather, against plain PyTorch."""
+    import ctypes
+    from nanoflow_b200 import ops
+    from nanoflow_b200.ops import GemmParams
+
+    coll = TpCollectives(rank, world, dev, heap_bytes=256 << 20)
+    for M, N, K in [(300, 512, 256), (1000, 8192, 1024), (77, 256, 128), (2048, 8192, 3584 // 2 * 2)]:
+        g = torch.Generator(device="cpu").manual_seed(11)
+        A = [torch.randn(M, K, generator=g).bfloat16() for _ in range(world)]
+        W = [(torch.randn(N, K, generator=g) * 0.05).bfloat16() for _ in range(world)]
+        resid = torch.randn(M, N, generator=g).bfloat16()
+        wn = (1 + 0.1 * torch.randn(N, generator=g)).bfloat16().to(dev)
+        a, w = A[rank].to(dev), W[rank].to(dev)
+        cap = (M + world - 1) // world
+        part = coll.alloc((world * cap, N), torch.bfloat16)
+        hout = coll.alloc((M, N), torch.bfloat16)
+        x_loc = resid.to(dev).clone()
+        slot = coll.rs_slot(part, 0, cap)
+        for rep in range(2):                      # twice: flags carry the epoch, counters reset themselves
+            epoch = coll._next_epoch()
+            p = GemmParams()
+            p.A, p.B, p.D = a.data_ptr(), w.data_ptr(), 0
+            p.lda, p.ldb, p.ldd = K, K, N
+            p.M, p.N, p.K, p.epilogue = M, N, K, 2
+            for r, base in enumerate(slot["heap"]):
+                p.rs_heap[r] = base
+            p.rs_rank, p.rs_nranks, p.rs_rows_cap = rank, world, cap
+            p.rs_slab_off, p.rs_flag_off, p.rs_epoch = slot["slab_off"], slot["flag_off"], epoch
+            p.status = coll.status.data_ptr()
+            x_loc.copy_(resid.to(dev)); hout.zero_()
+            torch.cuda.synchronize(); dist.barrier()
+            rc = ops.lib().nfk_gemm_bf16(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+            assert rc == 0, rc
+            from nanoflow_b200.parallel.collectives import AllReduceParams
+            q = AllReduceParams()
+            q.ctx = coll.ctx()
+            q.buf_off, q.flag_off, q.src_mode, q.slab_rows = slot["slab_off"], slot["flag_off"], 1, cap
+            q.rows, q.cols, q.ld, q.epoch, q.num_ctas = M, N, N, epoch, 64
+            q.norm_w, q.norm_out_off, q.norm_ld, q.eps = wn.data_ptr(), coll.heap.offset_of(hout), N, 1e-5
+            q.resid, q.resid_ld, q.sum_out, q.sum_ld, q.push_sum = x_loc.data_ptr(), N, x_loc.data_ptr(), N, 0
+            q.status = coll.status.data_ptr()
+            rc = ops.lib().nfk_allreduce(ctypes.byref(q), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+            assert rc == 0, rc
+            torch.cuda.synchronize()
+            coll.check_status()
+            want_x = sum((A[r].float() @ W[r].float().t()).bfloat16().float() for r in range(world)) + resid.float()
+            mine = torch.arange(rank, M, world)
+            tol = 4e-2 * (K / 64) ** 0.5
+            assert torch.allclose(x_loc[mine.to(dev)].float().cpu(), want_x[mine], atol=tol, rtol=2e-2), (M, N, K, rep)
+            want_h = ref.rmsnorm(want_x.bfloat16(), wn.cpu(), 1e-5)
+            assert torch.allclose(hout.float().cpu(), want_h, atol=6e-2, rtol=4e-2), (M, N, K, rep)
+    coll.close()
+
+
 def case_engine(rank, world, dev):
     from nanoflow_b200.config import builtin_config
     from nanoflow_b200.models import ReferenceLlama, random_full_weights, shard_weights
@@ -183,7 +239,7 @@ if __name__ == "__main__":
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     try:
-        {"collectives": case_collectives, "engine": case_engine, "timeout": case_timeout}[case](rank, world, dev)
+        {"collectives": case_collectives, "engine": case_engine, "timeout": case_timeout, "fused": case_fused}[case](rank, world, dev)
     except BaseException:
         import traceback
         print(f"MP_WORKER_FAIL rank {rank}\n" + traceback.format_exc(), flush=True)

@@ -28,7 +28,7 @@ def _host_graph(pipeline_type, tp, nano, gbs=48):
     meta = {n: meta_dev[i * (T + 8):(i + 1) * (T + 8)] for i, n in enumerate(names)}
     x0 = z(T, m.hidden_size)
     pools = [z(16, 2, m.kv_heads_local, 16, m.head_dim) for _ in range(m.run_layers)]
-    bufs = Buffers(x=[x0, sym(T, m.hidden_size) if tp > 1 else x0], h=sym(T, m.hidden_size),
+    bufs = Buffers(x=[x0, sym(T + 8 * len(sizes), m.hidden_size) if tp > 1 else x0], h=sym(T, m.hidden_size),
                    qkv=z(T, m.qkv_size_local), q_rot=z(T, m.q_size_local), attn_out=z(T, m.q_size_local),
                    act=z(T, m.ffn_local), sample_h=z(B, m.hidden_size), sample_hn=z(B, m.hidden_size),
                    logits=z(B, w.lm_head.shape[0]), cand_val=sym(tp, B, dtype=torch.float32),
@@ -56,6 +56,20 @@ def test_graph_has_no_unordered_conflicts(pipeline_type, tp, nano):
         assert all(d < i for d in op.deps + op.after_start)
     bad = depcheck.check(g, acc)
     assert not bad, "unordered conflicting ops: " + ", ".join(f"{g.ops[a].name} <-> {g.ops[b].name}" for a, b in bad[:6])
+
+
+def test_fused_reduce_scatter_ops_are_in_the_tp_graph():
+    g, acc, keep = _host_graph("PLLM", 2, [16, 32])
+    fused = [op for op in g.ops if op.kernel == "nfk_gemm_bf16" and op.params.epilogue == 2]
+    reducers = [op for op in g.ops if op.kernel == "nfk_allreduce" and op.params.src_mode == 1]
+    assert fused and len(fused) == len(reducers)
+    # every layer but the last uses the fused form for both K-split GEMMs
+    assert len(fused) == 2 * (2 * 2 - 1)
+    for ge, ar in zip(fused, reducers):
+        assert ge.params.rs_flag_off == ar.params.flag_off and ge.params.rs_slab_off == ar.params.buf_off
+    # flags carry only the iteration's epoch, so no two collectives of one iteration may share a block
+    offs = [op.params.flag_off for op in g.ops if op.kernel in ("nfk_allreduce", "nfk_allgather")]
+    assert len(offs) == len(set(offs))
 
 
 def test_checker_sees_a_missing_dependency():

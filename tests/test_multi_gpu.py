@@ -29,12 +29,12 @@ def _launch(case, n, port):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("case,port", [("collectives", 29611), ("engine", 29612), ("timeout", 29613)])
+@pytest.mark.parametrize("case,port", [("collectives", 29611), ("fused", 29614), ("engine", 29612), ("timeout", 29613)])
 def test_two_gpus(case, port):
     print(_launch(case, 2, port))
 
 
 @pytest.mark.skipif(_ngpu() < 8, reason="needs 8 GPUs")
-@pytest.mark.parametrize("case,port", [("collectives", 29621)])
+@pytest.mark.parametrize("case,port", [("collectives", 29621), ("fused", 29623)])
 def test_eight_gpus(case, port):
     print(_launch(case, 8, port))
