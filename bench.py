@@ -107,8 +107,8 @@ def main():
     ap.add_argument("--nano", default="", help="comma-separated nano-batch sizes (must sum to the dense batch); "
                     "default: two halves for the overlapped pipelines")
     ap.add_argument("--comm-ctas", type=int, default=0)
-    ap.add_argument("--no-fuse-rs", action="store_true", help="K-split GEMMs write partials locally and the "
-                    "collective pulls them, instead of pushing them to their owners from the GEMM epilogue")
+    ap.add_argument("--fuse-rs", action="store_true", help="K-split GEMMs push their partial rows to the owners "
+                    "from the GEMM epilogue (fused GEMM -> reduce-scatter) instead of the collective pulling them")
     ap.add_argument("--skip-cycles", type=int, default=1600)
     ap.add_argument("--executor", default="auto")
     ap.add_argument("--timeline", default="", help="after the timed regions, time every op of one iteration "
@@ -180,8 +180,7 @@ def main():
                          **({"nanobatch_sizes": nano} if nano else {}))
     if args.comm_ctas:
         cfg.engine.sm_budget["comm"] = args.comm_ctas
-    if args.no_fuse_rs:
-        cfg.engine.fuse_gemm_rs = False
+    cfg.engine.fuse_gemm_rs = bool(args.fuse_rs)
     if args.layers:
         cfg.model.num_layers = args.layers
         cfg.model.run_layers = args.layers

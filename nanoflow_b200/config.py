@@ -153,7 +153,7 @@ class EngineConfig:
     decode_chunk_pages: int = 0            # 0 = choose per iteration
     use_cuda_graph: bool = False
     offload: bool = False
-    fuse_gemm_rs: bool = True              # TP: K-split GEMMs push partial rows to their owners from the epilogue
+    fuse_gemm_rs: bool = False             # TP: K-split GEMMs push partial rows to their owners from the epilogue
     # serving
     model_id: str = ""
     weight_path: str = ""
@@ -225,7 +225,7 @@ def parse_config(raw: Dict[str, Any], *, tp: Optional[int] = None) -> NanoflowCo
         decode_chunk_pages=int(pc.get("decode_chunk_pages", 0)),
         use_cuda_graph=bool(pc.get("use_cuda_graph", False)),
         offload=ptype == "PLLM_OFFLOAD" or bool(pc.get("offload", False)),
-        fuse_gemm_rs=bool(pc.get("fuse_gemm_rs", True)),
+        fuse_gemm_rs=bool(pc.get("fuse_gemm_rs", False)),
         model_id=sc.get("model", ""),
         weight_path=sc.get("weight_path", ""),
         hf_path=sc.get("hf_path", ""),

@@ -165,10 +165,12 @@ def case_engine(rank, world, dev):
     from nanoflow_b200.serving import DistKVPool, RequestManager, Scheduler
     from nanoflow_b200.serving.loop import ServingLoop
 
-    for ptype, nano in (("NON_OVERLAP", None), ("PLLM", [16, 32])):
+    for ptype, nano, fuse in (("NON_OVERLAP", None, False), ("PLLM", [16, 32], False), ("PLLM", [16, 32], True),
+                              ("NON_OVERLAP", None, True)):
         gbs = 48
         cfg = builtin_config("tiny", gpu_num=world, global_batch_size=gbs, pipeline_type=ptype, nanobatch_sizes=nano)
         cfg.engine.max_batch_size = gbs
+        cfg.engine.fuse_gemm_rs = fuse
         fw = random_full_weights(cfg.model, seed=0, std=0.05)
         for lay in fw.layers:
             for k, v in vars(lay).items():

@@ -10,9 +10,10 @@ from nanoflow_b200.runtime.pipeline import Buffers, IoSpec, build_graph
 from nanoflow_b200.utils import depcheck
 
 
-def _host_graph(pipeline_type, tp, nano, gbs=48):
+def _host_graph(pipeline_type, tp, nano, gbs=48, fuse_rs=False):
     cfg = builtin_config("tiny", gpu_num=tp, global_batch_size=gbs, pipeline_type=pipeline_type, nanobatch_sizes=nano)
     m, e = cfg.model, cfg.engine
+    e.fuse_gemm_rs = fuse_rs
     e.max_batch_size = gbs
     fw = random_full_weights(m, seed=0)
     w = shard_weights(fw, m, 0, tp, dtype=torch.bfloat16)
@@ -59,7 +60,8 @@ def test_graph_has_no_unordered_conflicts(pipeline_type, tp, nano):
 
 
 def test_fused_reduce_scatter_ops_are_in_the_tp_graph():
-    g, acc, keep = _host_graph("PLLM", 2, [16, 32])
+    g, acc, keep = _host_graph("PLLM", 2, [16, 32], fuse_rs=True)
+    assert not depcheck.check(g, acc)
     fused = [op for op in g.ops if op.kernel == "nfk_gemm_bf16" and op.params.epilogue == 2]
     reducers = [op for op in g.ops if op.kernel == "nfk_allreduce" and op.params.src_mode == 1]
     assert fused and len(fused) == len(reducers)
