@@ -107,6 +107,7 @@ def main():
     ap.add_argument("--nano", default="", help="comma-separated nano-batch sizes (must sum to the dense batch); "
                     "default: two halves for the overlapped pipelines")
     ap.add_argument("--comm-ctas", type=int, default=0)
+    ap.add_argument("--mem-fraction", type=float, default=0.96, help="share of device memory the engine may use")
     ap.add_argument("--fuse-rs", action="store_true", help="K-split GEMMs push their partial rows to the owners "
                     "from the GEMM epilogue (fused GEMM -> reduce-scatter) instead of the collective pulling them")
     ap.add_argument("--skip-cycles", type=int, default=1600)
@@ -161,14 +162,14 @@ def main():
         probe.model.run_layers = args.layers
     weight_bytes = probe.model.param_count() * 2 / tp + probe.model.vocab_size * probe.model.hidden_size * 2 * (1 - 1 / tp)
     total_mem = torch.cuda.get_device_properties(dev).total_memory
-    kv_budget = total_mem * 0.90 - weight_bytes - (6 << 30)
+    kv_budget = total_mem * args.mem_fraction - weight_bytes - (4 << 30)
     tok_cap = kv_budget / probe.model.kv_bytes_per_token_local()
     avg_ctx = args.input_len + args.output_len / 2
     gbs = args.global_batch
     if gbs == 0:
         max_decode = tok_cap / (avg_ctx * 1.12)
         gbs = int(max_decode * (args.input_len + args.output_len) / args.output_len)
-        gbs = max(256, min(8192, gbs // 128 * 128))
+        gbs = max(256, min(8192, gbs // 64 * 64))
     ptype = args.pipeline or ("PLLM" if tp > 1 else "NON_OVERLAP_LOCAL")
     nano = None
     if args.nano:
@@ -185,6 +186,7 @@ def main():
         cfg.model.num_layers = args.layers
         cfg.model.run_layers = args.layers
     cfg.engine.max_batch_size = gbs
+    cfg.engine.gpu_mem_fraction = args.mem_fraction
     model = cfg.model
 
     t_load = time.perf_counter()

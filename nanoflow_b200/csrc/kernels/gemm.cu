@@ -60,25 +60,32 @@ constexpr int UMMA_K = 16;
 constexpr int kGemmThreads = 192;
 constexpr int kSmemBudget = 227 * 1024 - 2048;
 
-// BN = tile width in weight rows; MT = number of 128-row M tiles one CTA covers with the same B
-// tile (MT > 1 is the small-M, weight-streaming shape: every weight byte enters shared memory once).
-template <int BN, int MT>
-struct Cfg {
-  static constexpr int A_TILE_BYTES = BM * BK * 2;
-  static constexpr int A_BYTES = MT * A_TILE_BYTES;
-  static constexpr int B_BYTES = BN * BK * 2;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES_RAW = kSmemBudget / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int ACC_COLS = MT * BN;                       // fp32 columns of one accumulator set
-  static constexpr int ACC_BUFS = ACC_COLS <= 256 ? 2 : 1;       // ping-pong when TMEM has room
-  static constexpr int TMEM_NEED = ACC_COLS * ACC_BUFS;
-  static constexpr int TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128
-                                   : TMEM_NEED <= 256 ? 256 : 512;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-  static_assert(STAGES >= 2, "tile does not fit shared memory");
-  static_assert(TMEM_NEED <= 512, "accumulators exceed TMEM");
+// Tile geometry. The tile is 128*MT rows by `bn` weight rows (bn: multiple of 32 up to 256, a runtime
+// value so that the tile count can be matched to the SM count); MT = number of 128-row M tiles one
+// CTA covers with the same B tile (MT > 1 is the small-M, weight-streaming shape: every weight byte
+// enters shared memory once). Shared memory: 1 KB of barriers, then `stages` ring slots of
+// (MT*16 KB of A + bn*128 B of B). TMEM: MT*bn fp32 columns per accumulator set, two sets
+// (epilogue of one tile under the main loop of the next) when they fit in 512 columns.
+constexpr int kMaxStages = 8;
+constexpr int A_TILE_BYTES = BM * BK * 2;
+struct Geom {
+  int bn, out_bn, stages, acc_bufs, tmem_cols, stage_bytes, b_bytes, smem_bytes;
 };
+inline Geom make_geom(int bn, int mt, bool swiglu, int smem_budget) {
+  Geom g;
+  g.bn = bn;
+  g.out_bn = swiglu ? bn / 2 : bn;
+  g.b_bytes = bn * BK * 2;
+  g.stage_bytes = mt * A_TILE_BYTES + g.b_bytes;
+  int st = (smem_budget - 2048) / g.stage_bytes;
+  g.stages = st > kMaxStages ? kMaxStages : st;
+  const int acc_cols = mt * bn;
+  g.acc_bufs = acc_cols * 2 <= 512 ? 2 : 1;
+  const int need = acc_cols * g.acc_bufs;
+  g.tmem_cols = need <= 32 ? 32 : need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512;
+  g.smem_bytes = g.stages * g.stage_bytes + 2048;
+  return g;
+}
 
 struct DevParams {
   __nv_bfloat16* D;
@@ -90,6 +97,7 @@ struct DevParams {
   int M, N, K;      // N = number of output columns
   int split_k;
   unsigned int* status;
+  int bn, stages, acc_bufs, tmem_cols;   // tile geometry (see make_geom)
   // reduce-scatter epilogue (EPI == 2)
   char* rs_heap[8];
   int rs_rank, rs_nranks, rs_rows_cap, rs_epoch;
@@ -144,30 +152,34 @@ struct Walk {
   }
 };
 
-template <int BN, int MT, int EPI>
+template <int MT, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                     const __grid_constant__ CUtensorMap tmB1, DevParams p) {
-  using C = Cfg<BN, MT>;
-  constexpr int STAGES = C::STAGES;
-  constexpr int ACC_BUFS = C::ACC_BUFS;
-  constexpr int ACC_COLS = C::ACC_COLS;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C::STAGE_BYTES);
+  uint8_t* smem_al = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                                ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al);
   uint64_t* full_bar = bars;
-  uint64_t* empty_bar = bars + STAGES;
-  uint64_t* tmem_full = bars + 2 * STAGES;
-  uint64_t* tmem_empty = bars + 2 * STAGES + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint64_t* empty_bar = bars + kMaxStages;
+  uint64_t* tmem_full = bars + 2 * kMaxStages;
+  uint64_t* tmem_empty = bars + 2 * kMaxStages + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  
+  uint8_t* smem = smem_al + 1024;     // ring slots
+
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  const int BN = p.bn;
+  const int STAGES = p.stages;
+  const int ACC_BUFS = p.acc_bufs;
+  const int ACC_COLS = MT * BN;
+  const int B_BYTES = BN * BK * 2;
+  const int STAGE_BYTES = MT * A_TILE_BYTES + B_BYTES;
+  constexpr int A_BYTES = MT * A_TILE_BYTES;
   // Output tile width: the SwiGLU epilogue folds a gate half and an up half of BN/2 columns each.
-  constexpr int OUT_BN = (EPI == 1) ? BN / 2 : BN;
+  const int OUT_BN = (EPI == 1) ? BN / 2 : BN;
   const int m_tiles = (p.M + BM - 1) / BM;
   const int m_groups = (m_tiles + MT - 1) / MT;
   const int n_blocks = (p.N + OUT_BN - 1) / OUT_BN;
@@ -191,7 +203,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (EPI == 1) tma_prefetch_desc(&tmB1);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_alloc(tmem_slot, static_cast<uint32_t>(p.tmem_cols));
     tmem_relinquish();
   }
   tc_fence_before();
@@ -201,35 +213,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer ----------------
-    uint32_t it = 0;
+    // ring position kept as (slot, phase) counters: the stage count is a runtime value and a
+    // division per k-block would sit on this thread's issue path
+    uint32_t it = 0, ph = 0;
+    int s = 0;
     bool ok = true;
     Walk walk(blockIdx.x, gridDim.x, tiles, num_kb, sk);
     Segment sg;
     while (ok && walk.next(sg)) {
       const int m_grp = sg.tile % m_groups, n_blk = sg.tile / m_groups;
       const int mt_valid = min(MT, m_tiles - m_grp * MT);
-      for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
+      for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0)) {
         if (!wait_or_abort(&empty_bar[s], ph ^ 1, abort_flag)) {
           report_status(p.status, NF_ST_TIMEOUT_SMEM_EMPTY);
           *abort_flag = 1;
           ok = false;
           break;
         }
-        uint8_t* sa = smem + s * C::STAGE_BYTES;
-        uint8_t* sb = sa + C::A_BYTES;
-        mbar_expect_tx(&full_bar[s], mt_valid * C::A_TILE_BYTES + C::B_BYTES);
+        uint8_t* sa = smem + s * STAGE_BYTES;
+        uint8_t* sb = sa + A_BYTES;
+        mbar_expect_tx(&full_bar[s], mt_valid * A_TILE_BYTES + B_BYTES);
         if (EPI == 1) {
           tma_load_2d(sb, &tmB0, &full_bar[s], kb * BK, n_blk * OUT_BN);
-          tma_load_2d(sb + C::B_BYTES / 2, &tmB1, &full_bar[s], kb * BK, n_blk * OUT_BN);
+          tma_load_2d(sb + B_BYTES / 2, &tmB1, &full_bar[s], kb * BK, n_blk * OUT_BN);
         } else {
           tma_load_2d(sb, &tmB0, &full_bar[s], kb * BK, n_blk * BN);
         }
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
           if (mt < mt_valid)
-            tma_load_2d(sa + mt * C::A_TILE_BYTES, &tmA, &full_bar[s], kb * BK, (m_grp * MT + mt) * BM);
+            tma_load_2d(sa + mt * A_TILE_BYTES, &tmA, &full_bar[s], kb * BK, (m_grp * MT + mt) * BM);
       }
     }
     if (!ok) {
@@ -254,8 +267,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------- MMA issuer ----------------
-    constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
-    uint32_t it = 0, tcount = 0;
+    const uint32_t idesc = umma_idesc_bf16(BM, BN);
+    uint32_t tcount = 0, ph = 0;
+    int s = 0;
     bool ok = true;
     Walk walk(blockIdx.x, gridDim.x, tiles, num_kb, sk);
     Segment sg;
@@ -271,9 +285,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
-      for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
+      for (int kb = sg.kb0; kb < sg.kb1; ++kb, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0)) {
         if (!wait_or_abort(&full_bar[s], ph, abort_flag)) {
           report_status(p.status, NF_ST_TIMEOUT_SMEM_FULL);
           *abort_flag = 1;
@@ -281,14 +293,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           break;
         }
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
-        const uint32_t b_addr = a_addr + C::A_BYTES;
+        const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+        const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           if (mt < mt_valid) {
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
-              const uint64_t da = umma_desc_k_sw128(a_addr + mt * C::A_TILE_BYTES + k * UMMA_K * 2);
+              const uint64_t da = umma_desc_k_sw128(a_addr + mt * A_TILE_BYTES + k * UMMA_K * 2);
               const uint64_t db = umma_desc_k_sw128(b_addr + k * UMMA_K * 2);
               umma_bf16_ss(d_tmem + mt * BN, da, db, idesc, (kb != sg.kb0 || k != 0) ? 1u : 0u);
             }
@@ -329,14 +341,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           __nv_bfloat16* drow = p.D + static_cast<long long>(row) * p.ldd;
           const __nv_bfloat16* crow =
               (EPI == 0 && p.C != nullptr) ? p.C + static_cast<long long>(row) * p.ldc : nullptr;
+          const int tile_col_end = min(p.N, (n_blk + 1) * OUT_BN);   // columns past it belong to the next tile
 #pragma unroll 1
-          for (int c = 0; c < OUT_BN / 32; ++c) {
+          for (int c = 0; c * 32 < OUT_BN; ++c) {
             uint32_t r[32];
             float v[32];
-            tmem_ld_32x32b_x32(t_lane + mt * BN + c * 32, r);
+            const bool tail16 = (c * 32 + 16 == OUT_BN);               // width = 32k + 16: last chunk is half
+            if (tail16) tmem_ld_32x32b_x16(t_lane + mt * BN + c * 32, r);
+            else tmem_ld_32x32b_x32(t_lane + mt * BN + c * 32, r);
             if (EPI == 1) {
               uint32_t uu[32];
-              tmem_ld_32x32b_x32(t_lane + mt * BN + BN / 2 + c * 32, uu);
+              if (tail16) tmem_ld_32x32b_x16(t_lane + mt * BN + BN / 2 + c * 32, uu);
+              else tmem_ld_32x32b_x32(t_lane + mt * BN + BN / 2 + c * 32, uu);
               tmem_ld_wait();
               float gsum[32], usum[32];
 #pragma unroll
@@ -353,12 +369,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
             const int col0 = n_blk * OUT_BN + c * 32;
             if (EPI == 0 && p.partial != nullptr) {
-              if (row_ok && col0 < p.N) {
+              if (row_ok && col0 < tile_col_end) {
                 float* prow = p.partial + (static_cast<long long>(sg.ks) * p.M + row) * p.N;
 #pragma unroll
                 for (int g4 = 0; g4 < 8; ++g4) {
                   const int col = col0 + g4 * 4;
-                  if (col < p.N)
+                  if (col < tile_col_end)
                     *reinterpret_cast<float4*>(prow + col) =
                         make_float4(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2], v[g4 * 4 + 3]);
                 }
@@ -368,14 +384,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (EPI == 2) {
               // push the partial row to its owner's slab (posted NVLink stores; the flag raised at
               // the end of the kernel orders them for the reader)
-              if (row_ok && col0 < p.N) {
+              if (row_ok && col0 < tile_col_end) {
                 const int owner = row % p.rs_nranks;
                 __nv_bfloat16* srow = reinterpret_cast<__nv_bfloat16*>(p.rs_heap[owner] + p.rs_slab_off) +
                                       (static_cast<long long>(p.rs_rank) * p.rs_rows_cap + row / p.rs_nranks) * p.N;
 #pragma unroll
                 for (int g8 = 0; g8 < 4; ++g8) {
                   const int col = col0 + g8 * 8;
-                  if (col < p.N) {
+                  if (col < tile_col_end) {
                     const float* vv = v + g8 * 8;
                     uint4 o;
                     o.x = pack_bf16x2(vv[0], vv[1]);
@@ -388,11 +404,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               }
               continue;
             }
-            if (row_ok && col0 < p.N) {
+            if (row_ok && col0 < tile_col_end) {
 #pragma unroll
               for (int g8 = 0; g8 < 4; ++g8) {
                 const int col = col0 + g8 * 8;
-                if (col < p.N) {  // N is a multiple of 8
+                if (col < tile_col_end) {  // N is a multiple of 8
                   float* vv = v + g8 * 8;
                   if (EPI == 0) {
                     if (p.bias != nullptr) {
@@ -439,7 +455,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, C::TMEM_COLS);
+    tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
   }
   if (EPI == 2 && threadIdx.x == 0) {
     // The last CTA to get here tells every rank that this rank's partial rows have been pushed.
@@ -523,32 +539,35 @@ splitk_reduce_kernel(DevParams p) {
   }
 }
 
-template <int BN, int MT, int EPI>
-int launch(const nfk_gemm_params& g, int split_k, cudaStream_t stream) {
-  using C = Cfg<BN, MT>;
-  constexpr int OUT_BN = (EPI == 1) ? BN / 2 : BN;
+constexpr int kSmemMax = 227 * 1024;
+
+template <int MT, int EPI>
+int launch(const nfk_gemm_params& g, int bn, int split_k, cudaStream_t stream) {
+  int budget = g.smem_budget_kb > 0 ? g.smem_budget_kb * 1024 : kSmemMax;
+  if (budget > kSmemMax) budget = kSmemMax;
+  const Geom geo = make_geom(bn, MT, EPI == 1, budget);
+  if (geo.stages < 2) return NF_ERR_BAD_ARG;      // shared-memory budget too small for this tile
   CUtensorMap tmA, tmB0, tmB1;
   int rc = make_tmap_bf16_2d(&tmA, g.A, g.M, g.K, g.lda, BM, BK);
   if (rc != NF_OK) return rc;
-  rc = make_tmap_bf16_2d(&tmB0, g.B, g.N, g.K, g.ldb, OUT_BN, BK);
+  rc = make_tmap_bf16_2d(&tmB0, g.B, g.N, g.K, g.ldb, geo.out_bn, BK);
   if (rc != NF_OK) return rc;
   if (EPI == 1) {
-    rc = make_tmap_bf16_2d(&tmB1, g.B2, g.N, g.K, g.ldb, OUT_BN, BK);
+    rc = make_tmap_bf16_2d(&tmB1, g.B2, g.N, g.K, g.ldb, geo.out_bn, BK);
     if (rc != NF_OK) return rc;
   } else {
     tmB1 = tmB0;
   }
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, MT, EPI>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             C::SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemMax) != cudaSuccess)
       return NF_ERR_CUDA;
     attr_set = true;
   }
   const int m_tiles = (g.M + BM - 1) / BM;
   const int m_groups = (m_tiles + MT - 1) / MT;
-  const int n_blocks = (g.N + OUT_BN - 1) / OUT_BN;
+  const int n_blocks = (g.N + geo.out_bn - 1) / geo.out_bn;
   const int units = m_groups * n_blocks * split_k;
   int ctas = g.num_ctas > 0 ? g.num_ctas : sm_count();
   if (ctas > units) ctas = units;
@@ -565,6 +584,10 @@ int launch(const nfk_gemm_params& g, int split_k, cudaStream_t stream) {
   p.K = g.K;
   p.split_k = split_k;
   p.status = g.status;
+  p.bn = geo.bn;
+  p.stages = geo.stages;
+  p.acc_bufs = geo.acc_bufs;
+  p.tmem_cols = geo.tmem_cols;
   for (int r = 0; r < 8; ++r) p.rs_heap[r] = reinterpret_cast<char*>(g.rs_heap[r]);
   p.rs_rank = g.rs_rank;
   p.rs_nranks = g.rs_nranks;
@@ -572,7 +595,7 @@ int launch(const nfk_gemm_params& g, int split_k, cudaStream_t stream) {
   p.rs_epoch = g.rs_epoch;
   p.rs_slab_off = g.rs_slab_off;
   p.rs_flag_off = g.rs_flag_off;
-  gemm_tcgen05_kernel<BN, MT, EPI><<<ctas, kGemmThreads, C::SMEM_BYTES, stream>>>(tmA, tmB0, tmB1, p);
+  gemm_tcgen05_kernel<MT, EPI><<<ctas, kGemmThreads, geo.smem_bytes, stream>>>(tmA, tmB0, tmB1, p);
   if (cudaGetLastError() != cudaSuccess) return NF_ERR_CUDA;
   if (split_k > 1) {
     const long long total = static_cast<long long>(g.M) * (g.N >> 3);
@@ -582,6 +605,16 @@ int launch(const nfk_gemm_params& g, int split_k, cudaStream_t stream) {
     if (cudaGetLastError() != cudaSuccess) return NF_ERR_CUDA;
   }
   return NF_OK;
+}
+
+template <int EPI>
+int launch_mt(const nfk_gemm_params& g, int bn, int mt, int split_k, cudaStream_t stream) {
+  switch (mt) {
+    case 1: return launch<1, EPI>(g, bn, split_k, stream);
+    case 2: return launch<2, EPI>(g, bn, split_k, stream);
+    case 4: return launch<4, EPI>(g, bn, split_k, stream);
+    default: return NF_ERR_UNSUPPORTED;
+  }
 }
 
 // Tile-shape choice when the caller leaves it open: a small cost model over the candidate shapes.
@@ -597,14 +630,12 @@ Shape choose_shape(const nfk_gemm_params& g, bool swiglu) {
   const int ctas = g.num_ctas > 0 ? g.num_ctas : sm_count();
   const int m_tiles = (g.M + BM - 1) / BM;
   const int num_kb = (g.K + BK - 1) / BK;
-  static const int cand_lin[][2] = {{256, 1}, {128, 1}, {64, 1}, {256, 2}, {128, 2}, {128, 4}};
-  static const int cand_sw[][2] = {{256, 1}, {128, 1}, {256, 2}, {128, 2}, {128, 4}};
-  const int ncand = swiglu ? 5 : 6;
   Shape best{256, 1, 1};
   double best_cost = 1e30;
-  for (int i = 0; i < ncand; ++i) {
-    const int bn = swiglu ? cand_sw[i][0] : cand_lin[i][0];
-    const int mt = swiglu ? cand_sw[i][1] : cand_lin[i][1];
+  for (int mt = 1; mt <= 4; mt *= 2) {
+   for (int bn = swiglu ? 128 : 64; bn <= 256; bn += 32) {
+    if (mt * bn > 512) continue;
+    if (swiglu && (bn / 2) % 16 != 0) continue;
     // Several M tiles per CTA only pay off when M is small (weight streaming); with many M tiles
     // the single TMEM accumulator set would serialise epilogue and main loop for nothing.
     if (mt > 1 && (m_tiles > 4 || m_tiles <= mt / 2)) continue;
@@ -623,13 +654,17 @@ Shape choose_shape(const nfk_gemm_params& g, bool swiglu) {
       const int units = tiles * sk;
       const int waves = (units + ctas - 1) / ctas;
       const int kb_per = (num_kb + sk - 1) / sk;
-      double cost = waves * (kb_per * t_kb + 2.5 + 0.004 * mt_eff * bn);
+      // per unit: prologue + epilogue; the epilogue hides under the next main loop only when TMEM
+      // holds two accumulator sets
+      const bool single_acc = mt * bn * 2 > 512;
+      double cost = waves * (kb_per * t_kb + 2.0 + (single_acc ? 0.012 : 0.003) * mt_eff * bn);
       if (sk > 1) cost += 3.0 + (sk + 1.0) * g.M * static_cast<double>(g.N) * 4.0 / 4.0e6;  // partial write + reduce
       if (cost < best_cost) {
         best_cost = cost;
         best = Shape{bn, mt, sk};
       }
     }
+   }
   }
   return best;
 }
@@ -688,36 +723,12 @@ extern "C" int nfk_gemm_bf16(const nfk_gemm_params* g, cudaStream_t stream) {
         static_cast<long long>(s.split_k) * g->M * g->N * 4 > g->workspace_bytes)
       return NF_ERR_BAD_ARG;
   }
-  const int key = s.bn * 10 + s.mt;
+  if (s.bn < 32 || s.bn > 256 || s.bn % 32 != 0 || (s.mt != 1 && s.mt != 2 && s.mt != 4) || s.mt * s.bn > 512)
+    return NF_ERR_UNSUPPORTED;
   if (swiglu) {
-    switch (key) {
-      case 2561: return launch<256, 1, 1>(*g, 1, stream);
-      case 1281: return launch<128, 1, 1>(*g, 1, stream);
-      case 2562: return launch<256, 2, 1>(*g, 1, stream);
-      case 1282: return launch<128, 2, 1>(*g, 1, stream);
-      case 1284: return launch<128, 4, 1>(*g, 1, stream);
-      default: return NF_ERR_UNSUPPORTED;
-    }
+    if ((s.bn / 2) % 16 != 0) return NF_ERR_UNSUPPORTED;
+    return launch_mt<1>(*g, s.bn, s.mt, 1, stream);
   }
-  if (rs) {
-    switch (key) {
-      case 2561: return launch<256, 1, 2>(*g, 1, stream);
-      case 1281: return launch<128, 1, 2>(*g, 1, stream);
-      case 641: return launch<64, 1, 2>(*g, 1, stream);
-      case 2562: return launch<256, 2, 2>(*g, 1, stream);
-      case 1282: return launch<128, 2, 2>(*g, 1, stream);
-      case 1284: return launch<128, 4, 2>(*g, 1, stream);
-      default: return NF_ERR_UNSUPPORTED;
-    }
-  }
-  switch (key) {
-    case 2561: return launch<256, 1, 0>(*g, s.split_k, stream);
-    case 1281: return launch<128, 1, 0>(*g, s.split_k, stream);
-    case 641: return launch<64, 1, 0>(*g, s.split_k, stream);
-    case 2562: return launch<256, 2, 0>(*g, s.split_k, stream);
-    case 1282: return launch<128, 2, 0>(*g, s.split_k, stream);
-    case 1284: return launch<128, 4, 0>(*g, s.split_k, stream);
-    case 644: return launch<64, 4, 0>(*g, s.split_k, stream);
-    default: return NF_ERR_UNSUPPORTED;
-  }
+  if (rs) return launch_mt<2>(*g, s.bn, s.mt, 1, stream);
+  return launch_mt<0>(*g, s.bn, s.mt, s.split_k, stream);
 }

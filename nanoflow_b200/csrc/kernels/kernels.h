@@ -26,7 +26,7 @@ typedef struct nfk_gemm_params {
   float beta;
   int M, N, K;
   int epilogue;     // NFK_EPI_*
-  int tile_n;       // 0 = choose; 64 / 128 / 256
+  int tile_n;       // 0 = choose; tile width in weight rows: a multiple of 32 up to 256
   int num_ctas;     // CTA budget of the persistent grid; 0 = one per SM
   unsigned int* status;  // optional device word: first non-zero NF_ST_* code wins
   int tile_m;       // 0 = choose; number of 128-row M tiles one CTA covers: 1 / 2 / 4
@@ -44,6 +44,7 @@ typedef struct nfk_gemm_params {
   int rs_rows_cap;
   long long rs_flag_off;
   int rs_epoch;
+  int smem_budget_kb;  // 0 = all 227 KB; smaller leaves shared memory for a kernel meant to share the SM
 } nfk_gemm_params;
 
 int nfk_gemm_bf16(const nfk_gemm_params* p, cudaStream_t stream);

@@ -199,8 +199,8 @@ def main(argv):
             a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
             w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
             out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-            for (tm, tn, sk) in [(0, 0, 0), (2, 256, 1), (2, 256, 2), (2, 256, 4), (2, 128, 2), (2, 128, 4),
-                                 (1, 256, 4), (1, 128, 1), (1, 128, 2), (1, 64, 1)]:
+            for (tm, tn, sk) in [(0, 0, 0), (2, 256, 1), (2, 256, 4), (2, 224, 3), (2, 224, 4), (2, 192, 3), (2, 128, 2),
+                                 (1, 128, 1)]:
                 try:
                     med, _ = time_ms(lambda: ops.gemm(a, w, out=out, tile_m=tm, tile_n=tn, split_k=sk, workspace=ws))
                 except RuntimeError:
@@ -216,7 +216,7 @@ def main(argv):
             w = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.02
             w2 = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.02
             out = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
-            for (tm, tn) in [(0, 0), (2, 256), (2, 128), (1, 256), (1, 128)]:
+            for (tm, tn) in [(0, 0), (2, 256), (2, 224), (2, 192), (1, 256)]:
                 med, _ = time_ms(lambda: ops.gemm_swiglu(a, w, w2, out=out, tile_m=tm, tile_n=tn, workspace=ws))
                 gbs = (2 * F * K * 2) / med / 1e6
                 print(json.dumps(dict(op="swiglu_smallm", M=M, F=F, K=K, tile_m=tm, tile_n=tn, ms=round(med, 4),

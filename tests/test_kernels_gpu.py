@@ -31,7 +31,7 @@ def _seed():
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (256, 512, 1024), (77, 264, 200),
                                    (1, 128, 128), (640, 1280, 8192), (1408, 1024, 1024),
                                    (300, 8192, 3584)])
-@pytest.mark.parametrize("tile_n", [0, 64, 128, 256])
+@pytest.mark.parametrize("tile_n", [0, 32, 64, 96, 128, 160, 192, 224, 256])
 def test_gemm_plain(M, N, K, tile_n):
     a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
     w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
@@ -44,7 +44,8 @@ def test_gemm_plain(M, N, K, tile_n):
 @pytest.mark.parametrize("M,N,K", [(256, 8192, 8192), (85, 1024, 3584), (300, 2048, 4096), (512, 4096, 1024),
                                    (129, 10240, 2048)])
 @pytest.mark.parametrize("tile_m,tile_n,split_k", [(0, 0, 0), (2, 256, 1), (2, 256, 4), (4, 128, 3), (1, 256, 2),
-                                                   (4, 64, 1), (2, 128, 8), (1, 128, 5), (1, 64, 2)])
+                                                   (4, 64, 1), (2, 128, 8), (1, 128, 5), (1, 64, 2), (2, 224, 3),
+                                                   (2, 160, 1), (4, 96, 2)])
 def test_gemm_small_m_weight_streaming(M, N, K, tile_m, tile_n, split_k):
     """Multi-M-tile CTAs (weights fetched once) and split-K with fp32 partials + reduce pass."""
     a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
@@ -76,7 +77,8 @@ def test_gemm_split_k_large(M, N, K, num_ctas):
 
 
 @pytest.mark.parametrize("M,F,K,tile_m,tile_n", [(256, 3584, 1024, 2, 256), (200, 1792, 2048, 2, 128),
-                                                 (500, 1024, 1024, 4, 128), (256, 28672 // 8, 8192, 0, 0)])
+                                                 (500, 1024, 1024, 4, 128), (256, 28672 // 8, 8192, 0, 0),
+                                                 (256, 3584, 1024, 2, 224), (300, 1000, 512, 2, 192)])
 def test_gemm_swiglu_small_m(M, F, K, tile_m, tile_n):
     a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
     wg = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.05
@@ -114,6 +116,17 @@ def test_gemm_strided_views_and_inplace_residual():
     _close(big_out[:, :N], want, atol=5e-2, rtol=2e-2)
 
 
+def test_gemm_reduced_smem_budget():
+    """A smaller shared-memory budget (fewer TMA stages) leaves room for a co-resident kernel."""
+    a = torch.randn(512, 1024, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(768, 1024, device="cuda", dtype=torch.bfloat16) * 0.05
+    want = ref.gemm(a, w)
+    for kb in (0, 160, 128, 100):
+        _close(ops.gemm(a, w, tile_n=256, smem_budget_kb=kb), want, atol=0.1, rtol=2e-2)
+    with pytest.raises(RuntimeError):
+        ops.gemm(a, w, tile_n=256, smem_budget_kb=60)          # not even two stages fit
+
+
 def test_gemm_empty_and_bad_args():
     a = torch.randn(0, 64, device="cuda", dtype=torch.bfloat16)
     w = torch.randn(128, 64, device="cuda", dtype=torch.bfloat16)
@@ -124,7 +137,7 @@ def test_gemm_empty_and_bad_args():
 
 
 @pytest.mark.parametrize("M,F,K", [(128, 128, 64), (300, 3584, 1024), (1408, 1792, 4096), (17, 264, 136)])
-@pytest.mark.parametrize("tile_n", [0, 128])
+@pytest.mark.parametrize("tile_n", [0, 128, 192, 224, 256])
 def test_gemm_swiglu(M, F, K, tile_n):
     a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
     wg = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.05
