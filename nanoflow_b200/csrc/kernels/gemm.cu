@@ -71,11 +71,11 @@ constexpr int A_TILE_BYTES = BM * BK * 2;
 struct Geom {
   int bn, out_bn, stages, acc_bufs, tmem_cols, stage_bytes, b_bytes, smem_bytes;
 };
-inline Geom make_geom(int bn, int mt, bool swiglu, int smem_budget) {
+inline Geom make_geom(int bn, int mt, bool swiglu, int smem_budget, int cg) {
   Geom g;
   g.bn = bn;
   g.out_bn = swiglu ? bn / 2 : bn;
-  g.b_bytes = bn * BK * 2;
+  g.b_bytes = (bn / cg) * BK * 2;      // a CTA pair splits the weight tile between its two CTAs
   g.stage_bytes = mt * A_TILE_BYTES + g.b_bytes;
   int st = (smem_budget - 2048) / g.stage_bytes;
   g.stages = st > kMaxStages ? kMaxStages : st;
@@ -152,7 +152,11 @@ struct Walk {
   }
 };
 
-template <int MT, int EPI>
+// CG = 1: one CTA per tile. CG = 2 (MT must be 1): the two CTAs of a cluster share a 256-row tile;
+// each stages its own 128 rows of A and BN/2 of the weight rows, the even CTA issues
+// tcgen05.mma.cta_group::2 for both, and each CTA drains its own 128 accumulator rows. Per SM that
+// halves the weight bytes entering shared memory for the same tensor work.
+template <int MT, int EPI, int CG>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                     const __grid_constant__ CUtensorMap tmB1, DevParams p) {
@@ -171,21 +175,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int BN = p.bn;
+  static_assert(CG == 1 || MT == 1, "CTA pairs cover one M tile per CTA");
+  const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;   // position in the CTA pair
+  const bool leader = rank == 0;
+  const int BN = p.bn;                    // tile width = N of one MMA instruction
   const int STAGES = p.stages;
   const int ACC_BUFS = p.acc_bufs;
   const int ACC_COLS = MT * BN;
-  const int B_BYTES = BN * BK * 2;
+  const int B_BYTES = (BN / CG) * BK * 2; // weight rows this CTA stages per k-block
+  // A CTA that gives up tells its peer too, so the pair unwinds together.
+  auto raise_abort = [&]() {
+    *abort_flag = 1;
+    if (CG == 2)
+      st_shared_cluster_u32(mapa_shared(smem_u32(const_cast<int*>(abort_flag)), rank ^ 1u), 1u);
+  };
   const int STAGE_BYTES = MT * A_TILE_BYTES + B_BYTES;
   constexpr int A_BYTES = MT * A_TILE_BYTES;
   // Output tile width: the SwiGLU epilogue folds a gate half and an up half of BN/2 columns each.
   const int OUT_BN = (EPI == 1) ? BN / 2 : BN;
   const int m_tiles = (p.M + BM - 1) / BM;
-  const int m_groups = (m_tiles + MT - 1) / MT;
+  const int m_groups = (m_tiles + MT * CG - 1) / (MT * CG);
   const int n_blocks = (p.N + OUT_BN - 1) / OUT_BN;
   const int num_kb = (p.K + BK - 1) / BK;
   const int tiles = m_groups * n_blocks;
   const int sk = p.split_k;
+  const int worker = blockIdx.x / CG, workers = gridDim.x / CG;   // a CTA, or a CTA pair
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -194,7 +208,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 4);
+      mbar_init(&tmem_empty[a], 4 * CG);   // the epilogue warps of every CTA that shares the tile
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -203,11 +217,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (EPI == 1) tma_prefetch_desc(&tmB1);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, static_cast<uint32_t>(p.tmem_cols));
-    tmem_relinquish();
+    if (CG == 2) {
+      tmem_alloc_pair(tmem_slot, static_cast<uint32_t>(p.tmem_cols));
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, static_cast<uint32_t>(p.tmem_cols));
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if (CG == 2) cluster_sync_all();   // the peer's barriers exist before anything signals them
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -218,7 +238,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t it = 0, ph = 0;
     int s = 0;
     bool ok = true;
-    Walk walk(blockIdx.x, gridDim.x, tiles, num_kb, sk);
+    Walk walk(worker, workers, tiles, num_kb, sk);
     Segment sg;
     while (ok && walk.next(sg)) {
       const int m_grp = sg.tile % m_groups, n_blk = sg.tile / m_groups;
@@ -226,12 +246,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0)) {
         if (!wait_or_abort(&empty_bar[s], ph ^ 1, abort_flag)) {
           report_status(p.status, NF_ST_TIMEOUT_SMEM_EMPTY);
-          *abort_flag = 1;
+          raise_abort();
           ok = false;
           break;
         }
         uint8_t* sa = smem + s * STAGE_BYTES;
         uint8_t* sb = sa + A_BYTES;
+        if (CG == 2) {
+          // Both CTAs' bytes are counted on the even CTA's barrier, which its MMA thread waits on.
+          // A tile past the last row or column is still copied in full (zero filled).
+          const uint32_t fb = mapa_shared(smem_u32(&full_bar[s]), 0);
+          if (leader) mbar_expect_tx(&full_bar[s], 2 * (A_TILE_BYTES + B_BYTES));
+          if (EPI == 1)
+            tma_load_2d_pair(sb, rank == 0 ? &tmB0 : &tmB1, fb, kb * BK, n_blk * OUT_BN);
+          else
+            tma_load_2d_pair(sb, &tmB0, fb, kb * BK, n_blk * BN + static_cast<int>(rank) * (BN / 2));
+          tma_load_2d_pair(sa, &tmA, fb, kb * BK, (m_grp * 2 + static_cast<int>(rank)) * BM);
+          continue;
+        }
         mbar_expect_tx(&full_bar[s], mt_valid * A_TILE_BYTES + B_BYTES);
         if (EPI == 1) {
           tma_load_2d(sb, &tmB0, &full_bar[s], kb * BK, n_blk * OUT_BN);
@@ -245,8 +277,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             tma_load_2d(sa + mt * A_TILE_BYTES, &tmA, &full_bar[s], kb * BK, (m_grp * MT + mt) * BM);
       }
     }
-    if (!ok) {
-      // Drain: give loads already in flight a bounded chance to land before the CTA exits.
+    if (CG == 2 && ok) {
+      // Every arrival that the even CTA's commits send to this CTA's slot barriers has landed once
+      // each slot reads as free again.
+      for (int j = 0; j < STAGES; ++j, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0))
+        if (!wait_or_abort(&empty_bar[s], ph ^ 1, abort_flag)) break;
+    }
+    if (!ok && leader) {
+      // Drain: give loads already in flight a bounded chance to land before the CTA exits (a
+      // pair's loads are all counted on the even CTA's barriers).
       const uint32_t issued = it;
       const uint32_t back = issued < static_cast<uint32_t>(STAGES) ? issued : STAGES;
       for (uint32_t j = issued - back; j < issued; ++j) {
@@ -265,22 +304,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
     }
-  } else if (warp == 1 && lane == 0) {
-    // ---------------- MMA issuer ----------------
-    const uint32_t idesc = umma_idesc_bf16(BM, BN);
+  } else if (warp == 1 && lane == 0 && leader) {
+    // ---------------- MMA issuer (the even CTA of a pair issues for both) ----------------
+    const uint32_t idesc = umma_idesc_bf16(BM * CG, BN);
     uint32_t tcount = 0, ph = 0;
     int s = 0;
     bool ok = true;
-    Walk walk(blockIdx.x, gridDim.x, tiles, num_kb, sk);
+    Walk walk(worker, workers, tiles, num_kb, sk);
     Segment sg;
     while (ok && walk.next(sg)) {
       const int m_grp = sg.tile % m_groups;
-      const int mt_valid = min(MT, m_tiles - m_grp * MT);
+      const int mt_valid = (CG == 2) ? 1 : min(MT, m_tiles - m_grp * MT);
       const uint32_t acc = (ACC_BUFS == 2) ? (tcount & 1) : 0;
       const uint32_t acc_ph = (ACC_BUFS == 2) ? ((tcount >> 1) & 1) : (tcount & 1);
       if (!wait_or_abort(&tmem_empty[acc], acc_ph ^ 1, abort_flag)) {
         report_status(p.status, NF_ST_TIMEOUT_TMEM_EMPTY);
-        *abort_flag = 1;
+        raise_abort();
         break;
       }
       tc_fence_after();
@@ -288,7 +327,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int kb = sg.kb0; kb < sg.kb1; ++kb, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0)) {
         if (!wait_or_abort(&full_bar[s], ph, abort_flag)) {
           report_status(p.status, NF_ST_TIMEOUT_SMEM_FULL);
-          *abort_flag = 1;
+          raise_abort();
           ok = false;
           break;
         }
@@ -302,30 +341,43 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int k = 0; k < BK / UMMA_K; ++k) {
               const uint64_t da = umma_desc_k_sw128(a_addr + mt * A_TILE_BYTES + k * UMMA_K * 2);
               const uint64_t db = umma_desc_k_sw128(b_addr + k * UMMA_K * 2);
-              umma_bf16_ss(d_tmem + mt * BN, da, db, idesc, (kb != sg.kb0 || k != 0) ? 1u : 0u);
+              if (CG == 2) umma_bf16_ss_pair(d_tmem, da, db, idesc, (kb != sg.kb0 || k != 0) ? 1u : 0u);
+              else umma_bf16_ss(d_tmem + mt * BN, da, db, idesc, (kb != sg.kb0 || k != 0) ? 1u : 0u);
             }
           }
         }
-        umma_commit(&empty_bar[s]);  // stage is free once these MMAs have read it
+        // the stage is free (in both CTAs of a pair) once these MMAs have read it
+        if (CG == 2) {
+          umma_commit_pair_both(&empty_bar[s]);
+        } else {
+          umma_commit(&empty_bar[s]);
+        }
       }
-      if (ok) umma_commit(&tmem_full[acc]);
+      if (ok) {
+        if (CG == 2) {
+          umma_commit_pair_both(&tmem_full[acc]);
+        } else {
+          umma_commit(&tmem_full[acc]);
+        }
+      }
       ++tcount;
     }
   } else if (warp >= 2) {
     // ---------------- epilogue (4 warps, 128 threads) ----------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t tcount = 0;
-    Walk walk(blockIdx.x, gridDim.x, tiles, num_kb, sk);
+    Walk walk(worker, workers, tiles, num_kb, sk);
     Segment sg;
     while (walk.next(sg)) {
       const int m_grp = sg.tile % m_groups, n_blk = sg.tile / m_groups;
-      const int mt_valid = min(MT, m_tiles - m_grp * MT);
+      const int m_first = (m_grp * CG + static_cast<int>(rank)) * MT;   // first M tile this CTA drains
+      const int mt_valid = min(MT, m_tiles - m_first);                  // <= 0: tile past the last row
       const uint32_t acc = (ACC_BUFS == 2) ? (tcount & 1) : 0;
       const uint32_t acc_ph = (ACC_BUFS == 2) ? ((tcount >> 1) & 1) : (tcount & 1);
       ++tcount;
       if (!wait_or_abort(&tmem_full[acc], acc_ph, abort_flag)) {
         if (lane == 0) report_status(p.status, NF_ST_TIMEOUT_TMEM_FULL);
-        *abort_flag = 1;
+        raise_abort();
         break;
       }
       __syncwarp();
@@ -336,7 +388,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       {
 #pragma unroll 1
         for (int mt = 0; mt < mt_valid; ++mt) {
-          const int row = (m_grp * MT + mt) * BM + q * 32 + lane;
+          const int row = (m_first + mt) * BM + q * 32 + lane;
           const bool row_ok = row < p.M;
           __nv_bfloat16* drow = p.D + static_cast<long long>(row) * p.ldd;
           const __nv_bfloat16* crow =
@@ -446,16 +498,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (lane == 0) {
+        if (CG == 2) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty[acc]), 0));
+        else mbar_arrive(&tmem_empty[acc]);
+      }
     }
   }
 
   if (EPI == 2) __threadfence_system();   // this thread's pushes are ordered before the flag below
   tc_fence_before();
-  __syncthreads();
+  // Nothing of the pair may still signal this CTA's barriers or read its shared memory or TMEM once
+  // it has exited, so the pair leaves together.
+  __syncwarp();
+  if (CG == 2) cluster_sync_all();
+  else __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
+    if (CG == 2) tmem_dealloc_pair(tmem_base, static_cast<uint32_t>(p.tmem_cols));
+    else tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
   }
   if (EPI == 2 && threadIdx.x == 0) {
     // The last CTA to get here tells every rank that this rank's partial rows have been pushed.
@@ -541,36 +601,63 @@ splitk_reduce_kernel(DevParams p) {
 
 constexpr int kSmemMax = 227 * 1024;
 
-template <int MT, int EPI>
+template <int MT, int EPI, int CG>
 int launch(const nfk_gemm_params& g, int bn, int split_k, cudaStream_t stream) {
   int budget = g.smem_budget_kb > 0 ? g.smem_budget_kb * 1024 : kSmemMax;
   if (budget > kSmemMax) budget = kSmemMax;
-  const Geom geo = make_geom(bn, MT, EPI == 1, budget);
+  const Geom geo = make_geom(bn, MT, EPI == 1, budget, CG);
   if (geo.stages < 2) return NF_ERR_BAD_ARG;      // shared-memory budget too small for this tile
   CUtensorMap tmA, tmB0, tmB1;
   int rc = make_tmap_bf16_2d(&tmA, g.A, g.M, g.K, g.lda, BM, BK);
   if (rc != NF_OK) return rc;
-  rc = make_tmap_bf16_2d(&tmB0, g.B, g.N, g.K, g.ldb, geo.out_bn, BK);
+  // rows of B that one TMA copy brings in: a whole tile, a SwiGLU half, or a CTA pair's half
+  const int b_box = (EPI == 1) ? geo.out_bn : bn / CG;
+  rc = make_tmap_bf16_2d(&tmB0, g.B, g.N, g.K, g.ldb, b_box, BK);
   if (rc != NF_OK) return rc;
   if (EPI == 1) {
-    rc = make_tmap_bf16_2d(&tmB1, g.B2, g.N, g.K, g.ldb, geo.out_bn, BK);
+    rc = make_tmap_bf16_2d(&tmB1, g.B2, g.N, g.K, g.ldb, b_box, BK);
     if (rc != NF_OK) return rc;
   } else {
     tmB1 = tmB0;
   }
   static bool attr_set = false;
+  static int max_workers = 0;    // CTAs (or CTA pairs) that can be resident at once
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<MT, EPI, CG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kSmemMax) != cudaSuccess)
       return NF_ERR_CUDA;
+    max_workers = sm_count() / CG;
+    if (CG == 2) {
+      // Pairs must sit on two SMs of one GPC; ask how many fit so that no pair waits for a second wave.
+      cudaLaunchConfig_t qc = {};
+      qc.gridDim = dim3(sm_count() / 2 * 2);
+      qc.blockDim = dim3(kGemmThreads);
+      qc.dynamicSmemBytes = kSmemMax;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2;
+      qa[0].val.clusterDim.y = 1;
+      qa[0].val.clusterDim.z = 1;
+      qc.attrs = qa;
+      qc.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_kernel<MT, EPI, CG>, &qc) == cudaSuccess && n > 0 &&
+          n < max_workers)
+        max_workers = n;
+      else
+        (void)cudaGetLastError();
+    }
     attr_set = true;
   }
   const int m_tiles = (g.M + BM - 1) / BM;
-  const int m_groups = (m_tiles + MT - 1) / MT;
+  const int m_groups = (m_tiles + MT * CG - 1) / (MT * CG);
   const int n_blocks = (g.N + geo.out_bn - 1) / geo.out_bn;
   const int units = m_groups * n_blocks * split_k;
-  int ctas = g.num_ctas > 0 ? g.num_ctas : sm_count();
-  if (ctas > units) ctas = units;
+  int workers = (g.num_ctas > 0 ? g.num_ctas : sm_count()) / CG;
+  if (workers > max_workers) workers = max_workers;
+  if (workers < 1) workers = 1;
+  if (workers > units) workers = units;
+  const int ctas = workers * CG;
   DevParams p;
   p.D = reinterpret_cast<__nv_bfloat16*>(g.D);
   p.C = reinterpret_cast<const __nv_bfloat16*>(g.C);
@@ -595,8 +682,27 @@ int launch(const nfk_gemm_params& g, int bn, int split_k, cudaStream_t stream) {
   p.rs_epoch = g.rs_epoch;
   p.rs_slab_off = g.rs_slab_off;
   p.rs_flag_off = g.rs_flag_off;
-  gemm_tcgen05_kernel<MT, EPI><<<ctas, kGemmThreads, geo.smem_bytes, stream>>>(tmA, tmB0, tmB1, p);
-  if (cudaGetLastError() != cudaSuccess) return NF_ERR_CUDA;
+  if (CG == 2) {
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(ctas);
+    lc.blockDim = dim3(kGemmThreads);
+    lc.dynamicSmemBytes = geo.smem_bytes;
+    lc.stream = stream;
+    cudaLaunchAttribute la[1];
+    la[0].id = cudaLaunchAttributeClusterDimension;
+    la[0].val.clusterDim.x = 2;
+    la[0].val.clusterDim.y = 1;
+    la[0].val.clusterDim.z = 1;
+    lc.attrs = la;
+    lc.numAttrs = 1;
+    if (cudaLaunchKernelEx(&lc, gemm_tcgen05_kernel<MT, EPI, CG>, tmA, tmB0, tmB1, p) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return NF_ERR_CUDA;
+    }
+  } else {
+    gemm_tcgen05_kernel<MT, EPI, CG><<<ctas, kGemmThreads, geo.smem_bytes, stream>>>(tmA, tmB0, tmB1, p);
+    if (cudaGetLastError() != cudaSuccess) return NF_ERR_CUDA;
+  }
   if (split_k > 1) {
     const long long total = static_cast<long long>(g.M) * (g.N >> 3);
     long long blocks = (total + 255) / 256;
@@ -608,11 +714,12 @@ int launch(const nfk_gemm_params& g, int bn, int split_k, cudaStream_t stream) {
 }
 
 template <int EPI>
-int launch_mt(const nfk_gemm_params& g, int bn, int mt, int split_k, cudaStream_t stream) {
+int launch_mt(const nfk_gemm_params& g, int bn, int mt, int cg, int split_k, cudaStream_t stream) {
+  if (cg == 2) return mt == 1 ? launch<1, EPI, 2>(g, bn, split_k, stream) : NF_ERR_UNSUPPORTED;
   switch (mt) {
-    case 1: return launch<1, EPI>(g, bn, split_k, stream);
-    case 2: return launch<2, EPI>(g, bn, split_k, stream);
-    case 4: return launch<4, EPI>(g, bn, split_k, stream);
+    case 1: return launch<1, EPI, 1>(g, bn, split_k, stream);
+    case 2: return launch<2, EPI, 1>(g, bn, split_k, stream);
+    case 4: return launch<4, EPI, 1>(g, bn, split_k, stream);
     default: return NF_ERR_UNSUPPORTED;
   }
 }
@@ -624,35 +731,42 @@ int launch_mt(const nfk_gemm_params& g, int bn, int mt, int split_k, cudaStream_
 // M tiles with one weight tile (each weight byte enters shared memory once), which wins when M is
 // small and the GEMM is bound by streaming the weight.
 struct Shape {
-  int bn, mt, split_k;
+  int bn, mt, split_k, cg;
 };
 Shape choose_shape(const nfk_gemm_params& g, bool swiglu) {
   const int ctas = g.num_ctas > 0 ? g.num_ctas : sm_count();
   const int m_tiles = (g.M + BM - 1) / BM;
   const int num_kb = (g.K + BK - 1) / BK;
-  Shape best{256, 1, 1};
+  Shape best{256, 1, 1, 1};
   double best_cost = 1e30;
-  for (int mt = 1; mt <= 4; mt *= 2) {
+  const int cg_lo = g.cta_group == 2 ? 2 : 1, cg_hi = g.cta_group == 1 ? 1 : 2;
+  for (int cg = cg_lo; cg <= cg_hi; ++cg) {
+  for (int mt = 1; mt <= (cg == 2 ? 1 : 4); mt *= 2) {
    for (int bn = swiglu ? 128 : 64; bn <= 256; bn += 32) {
     if (mt * bn > 512) continue;
     if (swiglu && (bn / 2) % 16 != 0) continue;
     // Several M tiles per CTA only pay off when M is small (weight streaming); with many M tiles
     // the single TMEM accumulator set would serialise epilogue and main loop for nothing.
     if (mt > 1 && (m_tiles > 4 || m_tiles <= mt / 2)) continue;
+    if (cg == 2 && m_tiles < 2) continue;    // a pair covers two M tiles
     const int out_bn = swiglu ? bn / 2 : bn;
-    const int m_groups = (m_tiles + mt - 1) / mt;
+    const int m_groups = (m_tiles + mt * cg - 1) / (mt * cg);
     const int n_blocks = (g.N + out_bn - 1) / out_bn;
     const int tiles = m_groups * n_blocks;
     const int mt_eff = m_tiles < mt ? m_tiles : mt;
-    // per k-block: tensor time (us) at ~11 TFLOP/s per SM, smem fill at ~110 GB/s per SM
+    // per k-block and SM: tensor time (us) at ~11 TFLOP/s, shared-memory fill at ~100 GB/s (a CTA
+    // of a pair stages only half of the weight tile); measured, a pair's k-block never takes less
+    // than ~0.36 us whatever the tile width
     const double t_mma = 2.0 * BM * mt_eff * bn * BK / 11.0e6;
-    const double t_fill = (mt_eff * 16384.0 + bn * 128.0) / 110.0e3;
-    const double t_kb = t_mma > t_fill ? t_mma : t_fill;
+    const double t_fill = (mt_eff * 16384.0 + bn * 128.0 / cg) / 100.0e3;
+    double t_kb = t_mma > t_fill ? t_mma : t_fill;
+    if (cg == 2 && t_kb < 0.36) t_kb = 0.36;
     const int max_sk = (swiglu || g.workspace == nullptr || g.epilogue == NFK_EPI_REDUCE_SCATTER) ? 1 : 8;
     for (int sk = 1; sk <= max_sk; ++sk) {
       if (sk > 1 && (num_kb / sk < 8 || static_cast<long long>(sk) * g.M * g.N * 4 > g.workspace_bytes)) break;
       const int units = tiles * sk;
-      const int waves = (units + ctas - 1) / ctas;
+      const int workers = ctas / cg > 0 ? ctas / cg : 1;
+      const int waves = (units + workers - 1) / workers;
       const int kb_per = (num_kb + sk - 1) / sk;
       // per unit: prologue + epilogue; the epilogue hides under the next main loop only when TMEM
       // holds two accumulator sets
@@ -661,10 +775,11 @@ Shape choose_shape(const nfk_gemm_params& g, bool swiglu) {
       if (sk > 1) cost += 3.0 + (sk + 1.0) * g.M * static_cast<double>(g.N) * 4.0 / 4.0e6;  // partial write + reduce
       if (cost < best_cost) {
         best_cost = cost;
-        best = Shape{bn, mt, sk};
+        best = Shape{bn, mt, sk, cg};
       }
     }
    }
+  }
   }
   return best;
 }
@@ -715,7 +830,9 @@ extern "C" int nfk_gemm_bf16(const nfk_gemm_params* g, cudaStream_t stream) {
     s.bn = g->tile_n != 0 ? g->tile_n : 256;
     s.mt = g->tile_m != 0 ? g->tile_m : 1;
     s.split_k = 1;
+    s.cg = g->cta_group == 2 ? 2 : 1;
   }
+  if (s.cg == 2 && s.mt != 1) return NF_ERR_UNSUPPORTED;
   if (g->split_k != 0) s.split_k = g->split_k;
   if (s.split_k < 1 || s.split_k > 16) return NF_ERR_BAD_ARG;
   if (s.split_k > 1) {
@@ -727,8 +844,8 @@ extern "C" int nfk_gemm_bf16(const nfk_gemm_params* g, cudaStream_t stream) {
     return NF_ERR_UNSUPPORTED;
   if (swiglu) {
     if ((s.bn / 2) % 16 != 0) return NF_ERR_UNSUPPORTED;
-    return launch_mt<1>(*g, s.bn, s.mt, 1, stream);
+    return launch_mt<1>(*g, s.bn, s.mt, s.cg, 1, stream);
   }
-  if (rs) return launch_mt<2>(*g, s.bn, s.mt, 1, stream);
-  return launch_mt<0>(*g, s.bn, s.mt, s.split_k, stream);
+  if (rs) return launch_mt<2>(*g, s.bn, s.mt, s.cg, 1, stream);
+  return launch_mt<0>(*g, s.bn, s.mt, s.cg, s.split_k, stream);
 }

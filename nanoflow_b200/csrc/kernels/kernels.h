@@ -45,6 +45,7 @@ typedef struct nfk_gemm_params {
   long long rs_flag_off;
   int rs_epoch;
   int smem_budget_kb;  // 0 = all 227 KB; smaller leaves shared memory for a kernel meant to share the SM
+  int cta_group;       // 0 = let the cost model decide; 1 = one CTA per tile; 2 = a CTA pair per 256-row tile
 } nfk_gemm_params;
 
 int nfk_gemm_bf16(const nfk_gemm_params* p, cudaStream_t stream);

@@ -160,6 +160,14 @@ def small_case(which: str):
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         for _ in range(4):
             ops.gemm(a, w, out=out)
+    elif which == "gemm_shapes":
+        # one launch per kernel shape: CTA pair 256 wide, CTA pair 128 wide, single CTA 256 wide
+        M, N, K = 4096, 8192, 8192
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        for cg, tn in ((2, 256), (2, 128), (1, 256)):
+            ops.gemm(a, w, out=out, tile_n=tn, tile_m=1, cta_group=cg)
     elif which == "swiglu":
         M, N, K = 4096, 7168, 8192
         a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)

@@ -127,6 +127,47 @@ def test_gemm_reduced_smem_budget():
         ops.gemm(a, w, tile_n=256, smem_budget_kb=60)          # not even two stages fit
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (384, 768, 512), (200, 264, 192), (1000, 1000, 1024),
+                                   (2048, 1280, 1024), (130, 40, 64), (3712, 1280, 512)])
+@pytest.mark.parametrize("tile_n,split_k,num_ctas", [(256, 1, 0), (128, 1, 0), (224, 2, 0), (64, 1, 37),
+                                                     (32, 1, 0), (160, 3, 100), (256, 1, 2)])
+def test_gemm_cta_pair(M, N, K, tile_n, split_k, num_ctas):
+    """tcgen05.mma.cta_group::2: two CTAs of a cluster share a 256-row tile (odd tile counts, ragged
+    edges, split-K, restricted CTA budgets)."""
+    if split_k > 1 and K // 64 < split_k:
+        pytest.skip("fewer k-blocks than splits")
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    ws = torch.zeros(64 << 20, device="cuda", dtype=torch.float32)
+    st = ops.new_status()
+    out = ops.gemm(a, w, residual=res, beta=0.5, bias=bias, tile_m=1, tile_n=tile_n, split_k=split_k,
+                   workspace=ws, num_ctas=num_ctas, cta_group=2, status=st)
+    ops.check_status(st, "gemm")
+    _close(out, ref.gemm(a, w, res, 0.5, bias), atol=3e-2 * math.sqrt(K / 64), rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,F,K", [(256, 128, 64), (300, 3584, 1024), (1408, 1792, 2048), (129, 264, 136)])
+@pytest.mark.parametrize("tile_n", [128, 192, 224, 256])
+def test_gemm_swiglu_cta_pair(M, F, K, tile_n):
+    """CTA pair with the SwiGLU epilogue: one CTA stages the gate rows, its peer the up rows."""
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    wg = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    wu = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    st = ops.new_status()
+    out = ops.gemm_swiglu(a, wg, wu, tile_m=1, tile_n=tile_n, cta_group=2, status=st)
+    ops.check_status(st, "gemm_swiglu")
+    _close(out, ref.gemm_swiglu(a, wg, wu), atol=3e-2 * math.sqrt(K / 64), rtol=3e-2)
+
+
+def test_gemm_cta_pair_rejects_multi_tile_ctas():
+    a = torch.randn(256, 64, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(128, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        ops.gemm(a, w, tile_m=2, tile_n=128, cta_group=2)
+
+
 def test_gemm_empty_and_bad_args():
     a = torch.randn(0, 64, device="cuda", dtype=torch.bfloat16)
     w = torch.randn(128, 64, device="cuda", dtype=torch.bfloat16)
