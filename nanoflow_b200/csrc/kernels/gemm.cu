@@ -98,6 +98,9 @@ struct DevParams {
   int split_k;
   unsigned int* status;
   int bn, stages, acc_bufs, tmem_cols;   // tile geometry (see make_geom)
+  // stream-K tail (see Walk): tiles from sk_tiles_dp on are cut into k-block ranges of sk_q
+  float* sk_partial;          // fp32 [tile][piece][CTA of pair][rows per CTA][bn]
+  int sk_tiles_dp, sk_q, sk_max_pieces;
   // reduce-scatter epilogue (EPI == 2)
   char* rs_heap[8];
   int rs_rank, rs_nranks, rs_rows_cap, rs_epoch;
@@ -135,20 +138,57 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
 // as an fp32 partial tile and a second pass adds the partials and applies the epilogue.
 struct Segment {
   int tile, ks, kb0, kb1;
+  int sk_tile, piece, n_pieces;   // stream-K tail: index in the tail region, which piece, of how many
 };
+// Pieces that share tile t of the tail region: workers first..last (the ranges are q k-blocks long).
+__host__ __device__ __forceinline__ void sk_tile_pieces(int t, int num_kb, int q, int sk_total, int& first, int& last) {
+  first = (t * num_kb) / q;
+  const int end = (t + 1) * num_kb < sk_total ? (t + 1) * num_kb : sk_total;
+  last = (end - 1) / q;
+}
+// Units come in two phases. First whole tiles (with split-K: (tile, k range) pairs) dealt round-robin:
+// worker w takes units w, w+W, ... Then, when the tile count is not a multiple of W, the k-blocks of
+// the left-over tiles laid end to end and cut into W equal ranges, so that the last wave keeps every
+// worker busy; the pieces of a tile cut that way are fp32 partial sums that sk_fixup_kernel adds up.
 struct Walk {
-  int cur, units, tiles, num_kb, kb_per, step;
-  __device__ __forceinline__ Walk(int cta, int G, int tiles_, int num_kb_, int split_k)
-      : cur(cta), units(tiles_ * split_k), tiles(tiles_), num_kb(num_kb_),
-        kb_per((num_kb_ + split_k - 1) / split_k), step(G) {}
+  int cur, units, tiles_dp, num_kb, kb_per, step;
+  int g, g_end, q, sk_total;
+  __device__ __forceinline__ Walk(int w, int W, int tiles_, int num_kb_, int split_k, int tiles_dp_, int q_)
+      : cur(w), units((q_ > 0 ? tiles_dp_ : tiles_) * split_k), tiles_dp(q_ > 0 ? tiles_dp_ : tiles_),
+        num_kb(num_kb_), kb_per((num_kb_ + split_k - 1) / split_k), step(W), q(q_) {
+    sk_total = q_ > 0 ? (tiles_ - tiles_dp_) * num_kb_ : 0;
+    g = q_ > 0 ? min(w * q_, sk_total) : 0;
+    g_end = q_ > 0 ? min(g + q_, sk_total) : 0;
+  }
   __device__ __forceinline__ bool next(Segment& s) {
-    if (cur >= units) return false;
-    s.tile = cur % tiles;
-    s.ks = cur / tiles;
-    s.kb0 = min(num_kb, s.ks * kb_per);
-    s.kb1 = min(num_kb, s.kb0 + kb_per);
-    cur += step;
-    return true;
+    if (cur < units) {
+      s.tile = cur % tiles_dp;
+      s.ks = cur / tiles_dp;
+      s.kb0 = min(num_kb, s.ks * kb_per);
+      s.kb1 = min(num_kb, s.kb0 + kb_per);
+      s.sk_tile = 0;
+      s.piece = 0;
+      s.n_pieces = 1;
+      cur += step;
+      return true;
+    }
+    if (g < g_end) {
+      const int t = g / num_kb;
+      const int kb0 = g - t * num_kb;
+      const int len = min(num_kb - kb0, g_end - g);
+      s.tile = tiles_dp + t;
+      s.ks = 0;
+      s.kb0 = kb0;
+      s.kb1 = kb0 + len;
+      s.sk_tile = t;
+      int first, last;
+      sk_tile_pieces(t, num_kb, q, sk_total, first, last);
+      s.n_pieces = last - first + 1;
+      s.piece = g / q - first;
+      g += len;
+      return true;
+    }
+    return false;
   }
 };
 
@@ -238,7 +278,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t it = 0, ph = 0;
     int s = 0;
     bool ok = true;
-    Walk walk(worker, workers, tiles, num_kb, sk);
+    Walk walk(worker, workers, tiles, num_kb, sk, p.sk_tiles_dp, p.sk_q);
     Segment sg;
     while (ok && walk.next(sg)) {
       const int m_grp = sg.tile % m_groups, n_blk = sg.tile / m_groups;
@@ -310,7 +350,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t tcount = 0, ph = 0;
     int s = 0;
     bool ok = true;
-    Walk walk(worker, workers, tiles, num_kb, sk);
+    Walk walk(worker, workers, tiles, num_kb, sk, p.sk_tiles_dp, p.sk_q);
     Segment sg;
     while (ok && walk.next(sg)) {
       const int m_grp = sg.tile % m_groups;
@@ -366,7 +406,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------- epilogue (4 warps, 128 threads) ----------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t tcount = 0;
-    Walk walk(worker, workers, tiles, num_kb, sk);
+    Walk walk(worker, workers, tiles, num_kb, sk, p.sk_tiles_dp, p.sk_q);
     Segment sg;
     while (walk.next(sg)) {
       const int m_grp = sg.tile % m_groups, n_blk = sg.tile / m_groups;
@@ -385,11 +425,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * ACC_COLS;
       // a k range that received no k-blocks contributes zeros (its accumulator was never written)
       const bool empty_range = sg.kb0 >= sg.kb1;
-      {
+      // Stream-K tail: the fp32 partial copies of this tile (one slot per piece and CTA of a pair).
+      const long long slot_floats = static_cast<long long>(MT) * BM * BN;
+      float* const sk_tile_base = (EPI != 2 && sg.n_pieces > 1)
+          ? p.sk_partial + (static_cast<long long>(sg.sk_tile) * p.sk_max_pieces * CG) * slot_floats
+          : nullptr;
+      // mode 0: epilogue to the output; mode 1: raw accumulators to this piece's slot.
+      auto drain = [&](const int mode) {
 #pragma unroll 1
         for (int mt = 0; mt < mt_valid; ++mt) {
           const int row = (m_first + mt) * BM + q * 32 + lane;
           const bool row_ok = row < p.M;
+          const long long row_local = static_cast<long long>(mt * BM + q * 32 + lane) * BN;
           __nv_bfloat16* drow = p.D + static_cast<long long>(row) * p.ldd;
           const __nv_bfloat16* crow =
               (EPI == 0 && p.C != nullptr) ? p.C + static_cast<long long>(row) * p.ldc : nullptr;
@@ -399,6 +446,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t r[32];
             float v[32];
             const bool tail16 = (c * 32 + 16 == OUT_BN);               // width = 32k + 16: last chunk is half
+            const int nval = tail16 ? 16 : 32;
             if (tail16) tmem_ld_32x32b_x16(t_lane + mt * BN + c * 32, r);
             else tmem_ld_32x32b_x32(t_lane + mt * BN + c * 32, r);
             if (EPI == 1) {
@@ -412,12 +460,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 gsum[j] = __uint_as_float(r[j]);
                 usum[j] = __uint_as_float(uu[j]);
               }
+              if (mode == 1) {
+                if (row_ok) {
+                  float* own = sk_tile_base + (static_cast<long long>(sg.piece) * CG + rank) * slot_floats + row_local;
+#pragma unroll
+                  for (int g4 = 0; g4 < 8; ++g4)
+                    if (g4 * 4 < nval) {
+                      __stcg(reinterpret_cast<float4*>(own + c * 32) + g4,
+                             make_float4(gsum[g4 * 4], gsum[g4 * 4 + 1], gsum[g4 * 4 + 2], gsum[g4 * 4 + 3]));
+                      __stcg(reinterpret_cast<float4*>(own + BN / 2 + c * 32) + g4,
+                             make_float4(usum[g4 * 4], usum[g4 * 4 + 1], usum[g4 * 4 + 2], usum[g4 * 4 + 3]));
+                    }
+                }
+                continue;
+              }
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = gsum[j] / (1.0f + __expf(-gsum[j])) * usum[j];
             } else {
               tmem_ld_wait();
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = empty_range ? 0.f : __uint_as_float(r[j]);
+              if (EPI == 0 && mode == 1) {
+                if (row_ok) {
+                  float* own = sk_tile_base + (static_cast<long long>(sg.piece) * CG + rank) * slot_floats + row_local;
+#pragma unroll
+                  for (int g4 = 0; g4 < 8; ++g4)
+                    if (g4 * 4 < nval)
+                      __stcg(reinterpret_cast<float4*>(own + c * 32) + g4,
+                             make_float4(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2], v[g4 * 4 + 3]));
+                }
+                continue;
+              }
             }
             const int col0 = n_blk * OUT_BN + c * 32;
             if (EPI == 0 && p.partial != nullptr) {
@@ -495,7 +568,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           }
         }
-      }
+      };
+      // A piece of a tile that several workers share leaves its partial sums in its slot; a second
+      // kernel adds the pieces up and applies the epilogue.
+      if (sk_tile_base != nullptr) drain(1);
+      else drain(0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
@@ -599,10 +676,114 @@ splitk_reduce_kernel(DevParams p) {
   }
 }
 
+// Stream-K tail, second pass: for every tile of the tail region that was cut into pieces, add the
+// pieces' fp32 partial sums and apply the epilogue. One thread per 8 output columns of a row; the
+// loads of the pieces are independent, so many are in flight per thread.
+struct FixupGeom {
+  int mt, cg, bn, out_bn, m_groups, num_kb, rest;
+};
+template <int EPI>
+__global__ void __launch_bounds__(256)
+sk_fixup_kernel(DevParams p, FixupGeom f) {
+  const int rows_cta = f.mt * BM;
+  const int groups = f.out_bn / 8;
+  const long long slot_floats = static_cast<long long>(rows_cta) * f.bn;
+  const int sk_total = f.rest * f.num_kb;
+  const long long per_cta = static_cast<long long>(rows_cta) * groups;
+  const long long per_tile = per_cta * f.cg;
+  const long long total = per_tile * f.rest;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += 256ll * gridDim.x) {
+    const int t = static_cast<int>(i / per_tile);
+    long long r = i - t * per_tile;
+    const int rank = static_cast<int>(r / per_cta);
+    r -= rank * per_cta;
+    const int row_local = static_cast<int>(r / groups);
+    const int gcol = static_cast<int>(r - static_cast<long long>(row_local) * groups) * 8;
+    int first, last;
+    sk_tile_pieces(t, f.num_kb, p.sk_q, sk_total, first, last);
+    const int n_pieces = last - first + 1;
+    if (n_pieces < 2) continue;   // written whole by its only piece
+    const int tile = p.sk_tiles_dp + t;
+    const int m_grp = tile % f.m_groups, n_blk = tile / f.m_groups;
+    const int row = (m_grp * f.cg + rank) * rows_cta + row_local;
+    const int col = n_blk * f.out_bn + gcol;
+    if (row >= p.M || col >= p.N) continue;
+    const float* base = p.sk_partial + (static_cast<long long>(t) * p.sk_max_pieces * f.cg + rank) * slot_floats +
+                        static_cast<long long>(row_local) * f.bn + gcol;
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, u[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll 4
+    for (int pi = 0; pi < n_pieces; ++pi) {
+      const float* src = base + static_cast<long long>(pi) * f.cg * slot_floats;
+      const float4 x0 = __ldcg(reinterpret_cast<const float4*>(src));
+      const float4 x1 = __ldcg(reinterpret_cast<const float4*>(src) + 1);
+      a[0] += x0.x; a[1] += x0.y; a[2] += x0.z; a[3] += x0.w;
+      a[4] += x1.x; a[5] += x1.y; a[6] += x1.z; a[7] += x1.w;
+      if (EPI == 1) {
+        const float4 y0 = __ldcg(reinterpret_cast<const float4*>(src + f.bn / 2));
+        const float4 y1 = __ldcg(reinterpret_cast<const float4*>(src + f.bn / 2) + 1);
+        u[0] += y0.x; u[1] += y0.y; u[2] += y0.z; u[3] += y0.w;
+        u[4] += y1.x; u[5] += y1.y; u[6] += y1.z; u[7] += y1.w;
+      }
+    }
+    if (EPI == 1) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] = a[j] / (1.0f + __expf(-a[j])) * u[j];
+    } else {
+      if (p.bias != nullptr) {
+        const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+        const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 fl = unpack_bf16x2(bw[j]);
+          a[2 * j] += fl.x;
+          a[2 * j + 1] += fl.y;
+        }
+      }
+      if (p.C != nullptr) {
+        const uint4 cv = *reinterpret_cast<const uint4*>(p.C + static_cast<long long>(row) * p.ldc + col);
+        const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 fl = unpack_bf16x2(cw[j]);
+          a[2 * j] += p.beta * fl.x;
+          a[2 * j + 1] += p.beta * fl.y;
+        }
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(a[0], a[1]);
+    o.y = pack_bf16x2(a[2], a[3]);
+    o.z = pack_bf16x2(a[4], a[5]);
+    o.w = pack_bf16x2(a[6], a[7]);
+    *reinterpret_cast<uint4*>(p.D + static_cast<long long>(row) * p.ldd + col) = o;
+  }
+}
+
 constexpr int kSmemMax = 227 * 1024;
 
+// Stream-K tail: with `tiles` tiles on `workers` workers, the tiles_dp tiles of the full waves are
+// whole-tile units; the k-blocks of the rest are cut into ranges of q (>= 8, so a piece is worth its
+// set-up), one per worker.
+struct SkPlan {
+  int tiles_dp, q, max_pieces, rest;
+};
+inline SkPlan plan_stream_k(int tiles, int workers, int num_kb) {
+  SkPlan pl{tiles, 0, 0, 0};
+  const int rest = tiles % workers;
+  if (rest == 0 || num_kb < 2) return pl;
+  int q = (static_cast<long long>(rest) * num_kb + workers - 1) / workers;
+  const int q_min = num_kb < 8 ? num_kb : 8;
+  if (q < q_min) q = q_min;
+  if (q >= num_kb) return pl;           // nothing would be cut
+  pl.tiles_dp = tiles - rest;
+  pl.q = q;
+  pl.max_pieces = (num_kb + q - 1) / q + 1;
+  pl.rest = rest;
+  return pl;
+}
+
 template <int MT, int EPI, int CG>
-int launch(const nfk_gemm_params& g, int bn, int split_k, cudaStream_t stream) {
+int launch(const nfk_gemm_params& g, int bn, int split_k, bool stream_k, cudaStream_t stream) {
   int budget = g.smem_budget_kb > 0 ? g.smem_budget_kb * 1024 : kSmemMax;
   if (budget > kSmemMax) budget = kSmemMax;
   const Geom geo = make_geom(bn, MT, EPI == 1, budget, CG);
@@ -656,13 +837,24 @@ int launch(const nfk_gemm_params& g, int bn, int split_k, cudaStream_t stream) {
   int workers = (g.num_ctas > 0 ? g.num_ctas : sm_count()) / CG;
   if (workers > max_workers) workers = max_workers;
   if (workers < 1) workers = 1;
-  if (workers > units) workers = units;
+  SkPlan sk{m_groups * n_blocks, 0, 0, 0};
+  if (stream_k && split_k == 1 && EPI != 2 && g.workspace != nullptr) {
+    sk = plan_stream_k(m_groups * n_blocks, workers, (g.K + BK - 1) / BK);
+    const long long need = static_cast<long long>(sk.rest) * sk.max_pieces * CG * MT * BM * bn * 4;
+    if (sk.q > 0 && need > g.workspace_bytes)
+      sk = SkPlan{m_groups * n_blocks, 0, 0, 0};
+  }
+  if (sk.q == 0 && workers > units) workers = units;
   const int ctas = workers * CG;
   DevParams p;
   p.D = reinterpret_cast<__nv_bfloat16*>(g.D);
   p.C = reinterpret_cast<const __nv_bfloat16*>(g.C);
   p.bias = reinterpret_cast<const __nv_bfloat16*>(g.bias);
   p.partial = split_k > 1 ? reinterpret_cast<float*>(g.workspace) : nullptr;
+  p.sk_partial = sk.q > 0 ? reinterpret_cast<float*>(g.workspace) : nullptr;
+  p.sk_tiles_dp = sk.tiles_dp;
+  p.sk_q = sk.q;
+  p.sk_max_pieces = sk.max_pieces;
   p.ldd = g.ldd;
   p.ldc = g.ldc;
   p.beta = g.beta;
@@ -703,6 +895,14 @@ int launch(const nfk_gemm_params& g, int bn, int split_k, cudaStream_t stream) {
     gemm_tcgen05_kernel<MT, EPI, CG><<<ctas, kGemmThreads, geo.smem_bytes, stream>>>(tmA, tmB0, tmB1, p);
     if (cudaGetLastError() != cudaSuccess) return NF_ERR_CUDA;
   }
+  if (sk.q > 0 && EPI != 2) {
+    FixupGeom f{MT, CG, bn, geo.out_bn, m_groups, (g.K + BK - 1) / BK, sk.rest};
+    const long long total = static_cast<long long>(sk.rest) * CG * MT * BM * (geo.out_bn / 8);
+    long long blocks = (total + 255) / 256;
+    if (blocks > sm_count() * 8) blocks = sm_count() * 8;
+    sk_fixup_kernel<EPI == 1 ? 1 : 0><<<static_cast<int>(blocks), 256, 0, stream>>>(p, f);
+    if (cudaGetLastError() != cudaSuccess) return NF_ERR_CUDA;
+  }
   if (split_k > 1) {
     const long long total = static_cast<long long>(g.M) * (g.N >> 3);
     long long blocks = (total + 255) / 256;
@@ -714,12 +914,12 @@ int launch(const nfk_gemm_params& g, int bn, int split_k, cudaStream_t stream) {
 }
 
 template <int EPI>
-int launch_mt(const nfk_gemm_params& g, int bn, int mt, int cg, int split_k, cudaStream_t stream) {
-  if (cg == 2) return mt == 1 ? launch<1, EPI, 2>(g, bn, split_k, stream) : NF_ERR_UNSUPPORTED;
+int launch_mt(const nfk_gemm_params& g, int bn, int mt, int cg, int split_k, bool stream_k, cudaStream_t stream) {
+  if (cg == 2) return mt == 1 ? launch<1, EPI, 2>(g, bn, split_k, stream_k, stream) : NF_ERR_UNSUPPORTED;
   switch (mt) {
-    case 1: return launch<1, EPI, 1>(g, bn, split_k, stream);
-    case 2: return launch<2, EPI, 1>(g, bn, split_k, stream);
-    case 4: return launch<4, EPI, 1>(g, bn, split_k, stream);
+    case 1: return launch<1, EPI, 1>(g, bn, split_k, stream_k, stream);
+    case 2: return launch<2, EPI, 1>(g, bn, split_k, stream_k, stream);
+    case 4: return launch<4, EPI, 1>(g, bn, split_k, stream_k, stream);
     default: return NF_ERR_UNSUPPORTED;
   }
 }
@@ -732,13 +932,14 @@ int launch_mt(const nfk_gemm_params& g, int bn, int mt, int cg, int split_k, cud
 // small and the GEMM is bound by streaming the weight.
 struct Shape {
   int bn, mt, split_k, cg;
+  bool stream_k;
 };
 Shape choose_shape(const nfk_gemm_params& g, bool swiglu) {
   const int ctas = g.num_ctas > 0 ? g.num_ctas : sm_count();
   const int m_tiles = (g.M + BM - 1) / BM;
   const int num_kb = (g.K + BK - 1) / BK;
-  Shape best{256, 1, 1, 1};
-  double best_cost = 1e30;
+  Shape best{256, 1, 1, 1, false}, best_tail{256, 1, 1, 1, true};
+  double best_cost = 1e30, best_tail_cost = 1e30;
   const int cg_lo = g.cta_group == 2 ? 2 : 1, cg_hi = g.cta_group == 1 ? 1 : 2;
   for (int cg = cg_lo; cg <= cg_hi; ++cg) {
   for (int mt = 1; mt <= (cg == 2 ? 1 : 4); mt *= 2) {
@@ -763,7 +964,8 @@ Shape choose_shape(const nfk_gemm_params& g, bool swiglu) {
     if (cg == 2 && t_kb < 0.36) t_kb = 0.36;
     const int max_sk = (swiglu || g.workspace == nullptr || g.epilogue == NFK_EPI_REDUCE_SCATTER) ? 1 : 8;
     for (int sk = 1; sk <= max_sk; ++sk) {
-      if (sk > 1 && (num_kb / sk < 8 || static_cast<long long>(sk) * g.M * g.N * 4 > g.workspace_bytes)) break;
+      if (sk > 1 && (num_kb / sk < 8 ||
+                     static_cast<long long>(sk) * g.M * g.N * 4 > g.workspace_bytes)) break;
       const int units = tiles * sk;
       const int workers = ctas / cg > 0 ? ctas / cg : 1;
       const int waves = (units + workers - 1) / workers;
@@ -775,13 +977,35 @@ Shape choose_shape(const nfk_gemm_params& g, bool swiglu) {
       if (sk > 1) cost += 3.0 + (sk + 1.0) * g.M * static_cast<double>(g.N) * 4.0 / 4.0e6;  // partial write + reduce
       if (cost < best_cost) {
         best_cost = cost;
-        best = Shape{bn, mt, sk, cg};
+        best = Shape{bn, mt, sk, cg, false};
+      }
+      // the same shape with a stream-K tail: full waves as above, then one round of k ranges whose
+      // pieces are written out as fp32 and summed by the last piece of each tile
+      if (sk == 1 && g.stream_k != 2 && g.workspace != nullptr && g.epilogue != NFK_EPI_REDUCE_SCATTER) {
+        const SkPlan pl = plan_stream_k(tiles, workers, num_kb);
+        const long long need = static_cast<long long>(pl.rest) * pl.max_pieces * cg * mt * BM * bn * 4;
+        if (pl.q > 0 && need <= g.workspace_bytes) {
+          const double unit_fixed = 2.0 + (single_acc ? 0.012 : 0.003) * mt_eff * bn;
+          const double tile_bytes = mt_eff * BM * bn * 4.0;          // one fp32 copy of a CTA's tile rows
+          const double pieces = static_cast<double>(num_kb) / pl.q + 1.0;
+          // a worker's range may straddle two tiles; its partial copies leave at ~150 GB/s; the second
+          // pass is a launch plus all copies read back at ~3 TB/s
+          const double fix_us = 3.0 + pl.rest * cg * pieces * tile_bytes / 3.0e6;
+          const double tail = pl.q * t_kb + 2.0 * unit_fixed + tile_bytes / 150.0e3 + fix_us;
+          const double c2 = (tiles / workers) * (kb_per * t_kb + unit_fixed) + tail;
+          if (c2 < best_tail_cost) {
+            best_tail_cost = c2;
+            best_tail = Shape{bn, mt, 1, cg, true};
+          }
+        }
       }
     }
    }
   }
   }
-  return best;
+  // The tail's second pass and partial copies are modelled coarsely: take it only for a clear gain.
+  if (g.stream_k == 1 && best_tail_cost < 1e30) return best_tail;
+  return best_tail_cost < 0.88 * best_cost ? best_tail : best;
 }
 
 }  // namespace
@@ -831,7 +1055,10 @@ extern "C" int nfk_gemm_bf16(const nfk_gemm_params* g, cudaStream_t stream) {
     s.mt = g->tile_m != 0 ? g->tile_m : 1;
     s.split_k = 1;
     s.cg = g->cta_group == 2 ? 2 : 1;
+    s.stream_k = false;
   }
+  if (g->stream_k == 1) s.stream_k = true;
+  if (g->stream_k == 2 || s.split_k != 1) s.stream_k = false;
   if (s.cg == 2 && s.mt != 1) return NF_ERR_UNSUPPORTED;
   if (g->split_k != 0) s.split_k = g->split_k;
   if (s.split_k < 1 || s.split_k > 16) return NF_ERR_BAD_ARG;
@@ -844,8 +1071,8 @@ extern "C" int nfk_gemm_bf16(const nfk_gemm_params* g, cudaStream_t stream) {
     return NF_ERR_UNSUPPORTED;
   if (swiglu) {
     if ((s.bn / 2) % 16 != 0) return NF_ERR_UNSUPPORTED;
-    return launch_mt<1>(*g, s.bn, s.mt, s.cg, 1, stream);
+    return launch_mt<1>(*g, s.bn, s.mt, s.cg, 1, s.stream_k, stream);
   }
-  if (rs) return launch_mt<2>(*g, s.bn, s.mt, s.cg, 1, stream);
-  return launch_mt<0>(*g, s.bn, s.mt, s.cg, s.split_k, stream);
+  if (rs) return launch_mt<2>(*g, s.bn, s.mt, s.cg, 1, false, stream);
+  return launch_mt<0>(*g, s.bn, s.mt, s.cg, s.split_k, s.stream_k, stream);
 }

@@ -31,7 +31,7 @@ typedef struct nfk_gemm_params {
   unsigned int* status;  // optional device word: first non-zero NF_ST_* code wins
   int tile_m;       // 0 = choose; number of 128-row M tiles one CTA covers: 1 / 2 / 4
   int split_k;      // 0 = choose; > 1 needs `workspace` (fp32 partials, split_k*M*N*4 bytes)
-  void* workspace;
+  void* workspace;  // scratch for fp32 partial sums (split-K, stream-K tail); GEMMs that may overlap need their own
   long long workspace_bytes;
   // NFK_EPI_REDUCE_SCATTER: the epilogue does not write D; it pushes every bf16 partial row straight
   // into the slab of the rank that owns the row (row i belongs to rank i % rs_nranks), over NVLink:
@@ -46,6 +46,7 @@ typedef struct nfk_gemm_params {
   int rs_epoch;
   int smem_budget_kb;  // 0 = all 227 KB; smaller leaves shared memory for a kernel meant to share the SM
   int cta_group;       // 0 = let the cost model decide; 1 = one CTA per tile; 2 = a CTA pair per 256-row tile
+  int stream_k;        // tail wave cut into k ranges: 0 = cost model (off when the tile shape is pinned), 1 = on, 2 = off
 } nfk_gemm_params;
 
 int nfk_gemm_bf16(const nfk_gemm_params* p, cudaStream_t stream);

@@ -39,7 +39,7 @@ class GemmParams(Structure):
                 ("workspace_bytes", c_longlong),
                 ("rs_heap", c_void_p * 8), ("rs_rank", c_int), ("rs_nranks", c_int), ("rs_slab_off", c_longlong),
                 ("rs_rows_cap", c_int), ("rs_flag_off", c_longlong), ("rs_epoch", c_int), ("smem_budget_kb", c_int),
-                ("cta_group", c_int)]
+                ("cta_group", c_int), ("stream_k", c_int)]
 
 
 class RopeAppendParams(Structure):
@@ -120,7 +120,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
          bias: Optional[torch.Tensor] = None, tile_n: int = 0, num_ctas: int = 0,
          status: Optional[torch.Tensor] = None, tile_m: int = 0, split_k: int = 0,
          workspace: Optional[torch.Tensor] = None, smem_budget_kb: int = 0,
-         cta_group: int = 0) -> torch.Tensor:
+         cta_group: int = 0, stream_k: int = 0) -> torch.Tensor:
     """out[M,N] = a[M,K] @ w[N,K]^T (+ bias) (+ beta * residual). Rows may be strided.
 
     ``tile_n`` / ``tile_m`` / ``split_k`` pin the kernel shape (0 = let the launcher's cost model
@@ -156,6 +156,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     p.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     p.smem_budget_kb = smem_budget_kb
     p.cta_group = cta_group
+    p.stream_k = stream_k
     _check(lib().nfk_gemm_bf16(byref(p), _stream()), "nfk_gemm_bf16")
     return out
 
@@ -163,7 +164,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
 def gemm_swiglu(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, *,
                 out: Optional[torch.Tensor] = None, tile_n: int = 0, num_ctas: int = 0,
                 status: Optional[torch.Tensor] = None, tile_m: int = 0, split_k: int = 0,
-                workspace: Optional[torch.Tensor] = None, cta_group: int = 0) -> torch.Tensor:
+                workspace: Optional[torch.Tensor] = None, cta_group: int = 0,
+                stream_k: int = 0) -> torch.Tensor:
     """out[M,F] = silu(a @ w_gate^T) * (a @ w_up^T), gate and up products fused in one kernel."""
     _bf16(a, "a"); _bf16(w_gate, "w_gate"); _bf16(w_up, "w_up")
     M, K = a.shape
@@ -185,6 +187,7 @@ def gemm_swiglu(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, *,
     p.workspace = _p(workspace)
     p.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     p.cta_group = cta_group
+    p.stream_k = stream_k
     _check(lib().nfk_gemm_bf16(byref(p), _stream()), "nfk_gemm_bf16(swiglu)")
     return out
 

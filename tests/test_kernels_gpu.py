@@ -161,6 +161,48 @@ def test_gemm_swiglu_cta_pair(M, F, K, tile_n):
     _close(out, ref.gemm_swiglu(a, wg, wu), atol=3e-2 * math.sqrt(K / 64), rtol=3e-2)
 
 
+@pytest.mark.parametrize("M,N,K,tile_m,tile_n,cta_group,num_ctas", [
+    (256, 8192, 1024, 2, 256, 1, 0),      # 32 tiles on 148 workers: every tile is cut into k ranges
+    (256, 8192, 1024, 1, 256, 2, 0),
+    (256, 8192, 2048, 1, 128, 1, 0),
+    (300, 4096, 1536, 4, 128, 1, 0),
+    (2048, 1280, 2048, 1, 256, 2, 0),
+    (3712, 1280, 1024, 1, 256, 2, 0),     # 75 pair tiles on 74 pairs: one left over, cut 16 ways
+    (3712, 1280, 1024, 1, 256, 1, 0),
+    (1000, 3000, 1024, 1, 224, 1, 37),
+    (1000, 3000, 1024, 1, 160, 2, 36),
+    (130, 1000, 4096, 2, 96, 1, 0),
+])
+def test_gemm_stream_k_tail(M, N, K, tile_m, tile_n, cta_group, num_ctas):
+    """Left-over tiles of the last wave cut into k-block ranges (fp32 partial copies + second pass);
+    twice through the same workspace."""
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    ws = torch.empty(256 << 20, device="cuda", dtype=torch.uint8)
+    for _ in range(2):
+        res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+        st = ops.new_status()
+        out = ops.gemm(a, w, residual=res, beta=0.5, bias=bias, tile_m=tile_m, tile_n=tile_n, workspace=ws,
+                       cta_group=cta_group, num_ctas=num_ctas, stream_k=1, status=st)
+        ops.check_status(st, "gemm")
+        _close(out, ref.gemm(a, w, res, 0.5, bias), atol=3e-2 * math.sqrt(K / 64), rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,F,K,tile_m,tile_n,cta_group", [(256, 3584, 1024, 2, 256, 1), (256, 3584, 2048, 1, 224, 2),
+                                                            (1408, 1792, 1024, 1, 256, 2), (300, 7168, 512, 1, 192, 1)])
+def test_gemm_swiglu_stream_k_tail(M, F, K, tile_m, tile_n, cta_group):
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    wg = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    wu = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    ws = torch.empty(256 << 20, device="cuda", dtype=torch.uint8)
+    st = ops.new_status()
+    out = ops.gemm_swiglu(a, wg, wu, tile_m=tile_m, tile_n=tile_n, cta_group=cta_group, workspace=ws,
+                          stream_k=1, status=st)
+    ops.check_status(st, "gemm_swiglu")
+    _close(out, ref.gemm_swiglu(a, wg, wu), atol=3e-2 * math.sqrt(K / 64), rtol=3e-2)
+
+
 def test_gemm_cta_pair_rejects_multi_tile_ctas():
     a = torch.randn(256, 64, device="cuda", dtype=torch.bfloat16)
     w = torch.randn(128, 64, device="cuda", dtype=torch.bfloat16)
