@@ -302,6 +302,8 @@ def main():
             "gpu_launches": int(launches),
             "clocks": clocks,
             "executor": "native" if eng.native is not None else "python",
+            "gemm_shapes": {k: {"pick": [v["best"][x] for x in ("tile_m", "tile_n", "cta_group", "split_k", "stream_k")],
+                                "us": v["us"], "model_us": v["auto_us"]} for k, v in eng.gemm_tuning.items()},
             "load_seconds": round(load_s, 1),
         }
         if args.layers:

@@ -263,8 +263,24 @@ allreduce_kernel(nfk_allreduce_params p) {
   comm_exit(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status);
 }
 
+// A collective's CTAs are meant to share SMs with the CTAs of a GEMM that is launched after it. An SM
+// changes its L1 / shared-memory split only while idle, so a kernel that asks for no shared memory
+// would leave its SMs configured with too little for a GEMM CTA until it exits. Asking for the
+// largest shared-memory split keeps those SMs open to GEMM CTAs.
+template <typename K>
+void prefer_max_shared(K kernel) {
+  (void)cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  (void)cudaGetLastError();
+}
+
 template <int NR>
 int launch_allreduce(const nfk_allreduce_params* p, int ctas, cudaStream_t stream) {
+  static bool once = false;
+  if (!once) {
+    prefer_max_shared(allreduce_kernel<NR, true>);
+    prefer_max_shared(allreduce_kernel<NR, false>);
+    once = true;
+  }
   if (p->norm_w != nullptr)
     allreduce_kernel<NR, true><<<ctas, kArThreads, 0, stream>>>(*p);
   else
@@ -343,6 +359,11 @@ extern "C" int nfk_allgather(const nfk_allgather_params* p, cudaStream_t stream)
   long long ctas = p->num_ctas > 0 ? p->num_ctas : 16;
   const long long need = ((p->shard_bytes >> 4) + kCommThreads - 1) / kCommThreads;
   if (ctas > need) ctas = need > 0 ? need : 1;
+  static bool once = false;
+  if (!once) {
+    prefer_max_shared(allgather_kernel);
+    once = true;
+  }
   allgather_kernel<<<static_cast<int>(ctas), kCommThreads, 0, stream>>>(*p);
   return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
 }
@@ -350,6 +371,11 @@ extern "C" int nfk_allgather(const nfk_allgather_params* p, cudaStream_t stream)
 extern "C" int nfk_comm_barrier(const nfk_comm_barrier_params* p, cudaStream_t stream) {
   using namespace nf;
   if (!p || !ctx_ok(p->ctx) || p->flag_off % 16 != 0) return NF_ERR_BAD_ARG;
+  static bool once = false;
+  if (!once) {
+    prefer_max_shared(comm_barrier_kernel);
+    once = true;
+  }
   comm_barrier_kernel<<<1, 32, 0, stream>>>(p->ctx, p->flag_off, p->epoch, p->status);
   return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
 }

@@ -807,6 +807,11 @@ int launch(const nfk_gemm_params& g, int bn, int split_k, bool stream_k, cudaStr
     if (cudaFuncSetAttribute(gemm_tcgen05_kernel<MT, EPI, CG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kSmemMax) != cudaSuccess)
       return NF_ERR_CUDA;
+    // Always the largest shared-memory split: with a reduced budget (smem_budget_kb) the SM then
+    // keeps room for the CTAs of a kernel that runs beside this one, whichever of the two came first.
+    (void)cudaFuncSetAttribute(gemm_tcgen05_kernel<MT, EPI, CG>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                               cudaSharedmemCarveoutMaxShared);
+    (void)cudaGetLastError();
     max_workers = sm_count() / CG;
     if (CG == 2) {
       // Pairs must sit on two SMs of one GPC; ask how many fit so that no pair waits for a second wave.

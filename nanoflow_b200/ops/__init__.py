@@ -165,7 +165,7 @@ def gemm_swiglu(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, *,
                 out: Optional[torch.Tensor] = None, tile_n: int = 0, num_ctas: int = 0,
                 status: Optional[torch.Tensor] = None, tile_m: int = 0, split_k: int = 0,
                 workspace: Optional[torch.Tensor] = None, cta_group: int = 0,
-                stream_k: int = 0) -> torch.Tensor:
+                stream_k: int = 0, smem_budget_kb: int = 0) -> torch.Tensor:
     """out[M,F] = silu(a @ w_gate^T) * (a @ w_up^T), gate and up products fused in one kernel."""
     _bf16(a, "a"); _bf16(w_gate, "w_gate"); _bf16(w_up, "w_up")
     M, K = a.shape
@@ -188,6 +188,7 @@ def gemm_swiglu(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, *,
     p.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     p.cta_group = cta_group
     p.stream_k = stream_k
+    p.smem_budget_kb = smem_budget_kb
     _check(lib().nfk_gemm_bf16(byref(p), _stream()), "nfk_gemm_bf16(swiglu)")
     return out
 

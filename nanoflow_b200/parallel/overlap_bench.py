@@ -19,6 +19,7 @@ import torch.distributed as dist
 
 from nanoflow_b200 import ops
 from nanoflow_b200.parallel.collectives import TpCollectives
+from nanoflow_b200.runtime.pipeline import GEMM_SMEM_KB_SHARED_SM
 
 
 def _t(e0, e1):
@@ -50,9 +51,9 @@ def main():
 
         def gemm():
             if swiglu:
-                ops.gemm_swiglu(a, w, w2, out=out, workspace=ws)
+                ops.gemm_swiglu(a, w, w2, out=out, workspace=ws, smem_budget_kb=GEMM_SMEM_KB_SHARED_SM)
             else:
-                ops.gemm(a, w, out=out, workspace=ws)
+                ops.gemm(a, w, out=out, workspace=ws, smem_budget_kb=GEMM_SMEM_KB_SHARED_SM)
 
         for ctas in (16, 32, 64, 128):
             def ar():

@@ -30,7 +30,7 @@ from ..models.llama import RankWeights
 from ..ops import reference as ref
 from ..serving.scheduler import BatchPlan
 from .graph import OpGraph, PyExecutor
-from .pipeline import Buffers, CollectiveHooks, IoSpec, build_graph
+from .pipeline import GEMM_SMEM_KB_SHARED_SM, Buffers, CollectiveHooks, IoSpec, build_graph
 
 RING = 3                       # host staging slots (iterations in flight + one being formed)
 DECODE_MAX_CHUNKS = 16
@@ -133,6 +133,9 @@ class Engine:
             io.offload_pages = view("offload_pages")
             self.offload_host = [torch.zeros(m.run_layers, self.offload_cap, self.page_bytes_layer // 2,
                                              dtype=bf).pin_memory() for _ in range(RING)]
+        self.gemm_tuning: Dict[str, dict] = {}
+        if e.autotune_gemm:
+            self._autotune_gemms()
         self.graph: OpGraph = build_graph(m, e, weights, self.bufs, self.coll, io)
         self.tokens_host = [torch.zeros(B, dtype=torch.int32).pin_memory() for _ in range(RING)]
         self.tokens_np = [t.numpy() for t in self.tokens_host]
@@ -148,6 +151,43 @@ class Engine:
         self.launches_per_iteration = len(self.graph.ops)
         self.executor_kind = executor
         self._make_executor(executor)
+
+    # ---- GEMM shapes --------------------------------------------------------------------------------
+    def _autotune_gemms(self) -> None:
+        """Time candidate kernel shapes for the four per-layer GEMMs at every nano-batch size, on this
+        engine's buffers and the layers' own weights, and pin the fastest (ops/autotune.py). Shapes
+        given in the configuration are kept."""
+        from ..ops import autotune
+        m, e, w, b = self.model, self.eng, self.w, self.bufs
+        budget = e.sm_budget.get("gemm", 0) if e.overlap else 0
+        tp1 = w.tp == 1
+        x_out = b.x[0] if tp1 else b.x[1]
+        L = w.layers
+        specs = [("qkv", b.h, [l.wqkv for l in L], None, b.qkv, None, L[0].bqkv),
+                 ("o", b.attn_out, [l.wo for l in L], None, x_out, x_out if tp1 else None, None),
+                 ("gate_up", b.h, [l.wg for l in L], [l.wu for l in L], b.act, None, None),
+                 ("down", b.act, [l.wd for l in L], None, x_out, x_out if tp1 else None, None)]
+        for t in (b.h, b.attn_out, b.act):
+            t.normal_()
+        done: Dict[tuple, dict] = {}
+        for k, M in enumerate(self.nano_sizes):
+            if M <= 0:
+                continue
+            for key, a, ws, ups, out, resid, bias in specs:
+                name = f"{key}.nb{k}"
+                if name in e.gemm_shapes or key in e.gemm_tile_n:
+                    continue
+                if (key, M) not in done:
+                    done[(key, M)] = autotune.tune_gemm(
+                        a[:M], ws, out[:M], weights_up=ups, residual=None if resid is None else resid[:M],
+                        bias=bias, num_ctas=budget, workspace=b.gemm_ws,
+                        smem_budget_kb=GEMM_SMEM_KB_SHARED_SM if (e.overlap and w.tp > 1) else 0)
+                r = done[(key, M)]
+                e.gemm_shapes[name] = dict(r["best"])
+                self.gemm_tuning[name] = dict(M=M, best=r["best"], us=r["us"], auto_us=r["auto_us"])
+        torch.cuda.synchronize(self.device)
+        for t in (b.h, b.attn_out, b.act, b.qkv, b.x[0], b.x[1]):
+            t.zero_()
 
     # ---- sizing -----------------------------------------------------------------------------------
     def _derive_num_pages(self, T: int, B: int) -> int:

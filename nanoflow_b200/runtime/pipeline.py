@@ -91,6 +91,11 @@ class IoSpec:
     offload_pages: Optional[torch.Tensor] = None     # int32 view: page ids of requests retired this iteration
 
 
+# Shared memory a GEMM CTA may take when a collective's CTAs are meant to run beside it on the same
+# SM: the SM has 228 KB and every resident CTA reserves 1 KB plus its own static allocation.
+GEMM_SMEM_KB_SHARED_SM = 200
+
+
 def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buffers,
                 coll: Optional[CollectiveHooks] = None, io: Optional[IoSpec] = None) -> OpGraph:
     coll = coll or CollectiveHooks()
@@ -163,8 +168,15 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
             p.rs_rank, p.rs_nranks, p.rs_rows_cap = rs["rank"], rs["nranks"], rs["rows_cap"]
             p.rs_slab_off, p.rs_flag_off = rs["slab_off"], rs["flag_off"]
             dyn.append(("rs_epoch", g.symbol("epoch")))
-        p.tile_n = eng.gemm_tile_n.get(tile_key or name.split(".")[-1], 0)
+        key = tile_key or name.split(".")[-1]
+        p.tile_n = eng.gemm_tile_n.get(key, 0)
+        shape = eng.gemm_shapes.get(f"{key}.nb{k}") if rs is None else None
+        if shape is not None and p.tile_n == 0:
+            # measured at start-up (ops/autotune.py)
+            p.tile_m, p.tile_n, p.cta_group = shape["tile_m"], shape["tile_n"], shape["cta_group"]
+            p.split_k, p.stream_k = shape["split_k"], shape["stream_k"]
         p.num_ctas = budget.get("gemm", 0)
+        p.smem_budget_kb = GEMM_SMEM_KB_SHARED_SM if (overlap and tp > 1) else 0
         p.status = _ptr(st)
         if bufs.gemm_ws is not None:
             p.workspace = _ptr(bufs.gemm_ws)
