@@ -110,6 +110,9 @@ def main():
     ap.add_argument("--mem-fraction", type=float, default=0.96, help="share of device memory the engine may use")
     ap.add_argument("--fuse-rs", action="store_true", help="K-split GEMMs push their partial rows to the owners "
                     "from the GEMM epilogue (fused GEMM -> reduce-scatter) instead of the collective pulling them")
+    ap.add_argument("--virtual-tp", type=int, default=0,
+                    help="one GPU runs rank 0's share of a tensor-parallel job of this degree, collectives reduced "
+                         "to their local part (development aid; the JSON line is marked invalid)")
     ap.add_argument("--skip-cycles", type=int, default=1600)
     ap.add_argument("--executor", default="auto")
     ap.add_argument("--timeline", default="", help="after the timed regions, time every op of one iteration "
@@ -154,6 +157,13 @@ def main():
             torch.distributed.barrier()
 
     tp = world
+    if args.virtual_tp > 1:
+        if world != 1:
+            raise SystemExit("--virtual-tp runs on one GPU")
+        from nanoflow_b200.parallel.collectives import TpCollectives
+
+        tp = args.virtual_tp
+        coll = TpCollectives(0, 1, dev)
     # KV capacity decides how many requests fit, hence the steady-state dense batch: with 1024/512
     # requests a batch of T tokens holds T/3 decode requests of ~1280 tokens each.
     probe = builtin_config(args.model, gpu_num=tp, global_batch_size=2048)
@@ -190,7 +200,7 @@ def main():
     model = cfg.model
 
     t_load = time.perf_counter()
-    weights = random_rank_weights(model, rank, tp, dev, seed=0)
+    weights = random_rank_weights(model, 0 if args.virtual_tp > 1 else rank, tp, dev, seed=0)
     torch.cuda.synchronize()
     eng = Engine(cfg, weights, device=dev, collectives=coll, executor=args.executor)
     load_s = time.perf_counter() - t_load
@@ -306,6 +316,8 @@ def main():
                                 "us": v["us"], "model_us": v["auto_us"]} for k, v in eng.gemm_tuning.items()},
             "load_seconds": round(load_s, 1),
         }
+        if args.virtual_tp > 1:
+            out["invalid"] = f"virtual tensor parallelism: rank 0's share of TP{tp} on one GPU, no communication"
         if args.layers:
             out["invalid"] = "reduced layer count (debug run)"
         print(json.dumps(out))

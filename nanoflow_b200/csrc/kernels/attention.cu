@@ -143,7 +143,7 @@ struct DecCfg {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(kDecThreads, 2)
+__global__ void __launch_bounds__(kDecThreads, 3)
 attn_decode_kernel(nfk_attn_params p) {
   using Cfg = DecCfg<HD>;
   extern __shared__ __align__(128) uint8_t smem[];

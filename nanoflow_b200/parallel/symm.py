@@ -42,7 +42,8 @@ class SymmetricHeap:
         if lib.nfk_ipc_get_handle(ctypes.c_void_p(self.base), handle) != 0:
             raise RuntimeError("cudaIpcGetMemHandle failed")
         handles: List[bytes] = [None] * world
-        dist.all_gather_object(handles, bytes(handle), group=group)
+        if world > 1:
+            dist.all_gather_object(handles, bytes(handle), group=group)
         self.peer_base: List[int] = []
         for r in range(world):
             if r == rank:
@@ -55,7 +56,8 @@ class SymmetricHeap:
             self.peer_base.append(out.value)
         self._bump = 0
         self._bytes_view = torch.as_tensor(_CudaArray(self.base, self.nbytes, self), device=device)
-        dist.barrier(group=group)
+        if world > 1:
+            dist.barrier(group=group)
 
     def alloc_bytes(self, nbytes: int, align: int = 256) -> int:
         off = (self._bump + align - 1) // align * align
