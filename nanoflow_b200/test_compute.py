@@ -14,7 +14,9 @@ and the quickest way to time a pipeline configuration.
 
 Reference: ``test_compute <config.json>`` (pipeline/src/computeMain.cu:16-148: random weights,
 ``createUpdateData(..., 1024, 512)``, init -> config -> update -> run x5 -> finalize, per-iteration
-milliseconds), run by the reference's installer as its smoke test.
+milliseconds), run by the reference's installer as its smoke test. ``--virtual-tp`` is the reference's
+``vnranks`` (pipeline/include/pipeline.h:34-35, pipeline/src/computeMain.cu:34-35): shapes of an
+8-GPU job computed on fewer GPUs.
 """
 from __future__ import annotations
 
@@ -34,6 +36,9 @@ def main(argv=None) -> int:
     ap.add_argument("--skip-cycles", type=int, default=600,
                     help="scheduler-only cycles before the first real iteration (reaches the steady-state mix)")
     ap.add_argument("--pages", type=int, default=0, help="KV pages (0 = from free memory)")
+    ap.add_argument("--virtual-tp", type=int, default=0,
+                    help="on one GPU, run rank 0's share of a tensor-parallel job of this degree with the "
+                         "collectives reduced to their local part (times per-GPU work without the other GPUs)")
     a = ap.parse_args(argv)
 
     import torch
@@ -56,20 +61,28 @@ def main(argv=None) -> int:
 
         dist.init_process_group("nccl", device_id=dev)
         coll = TpCollectives(rank, world, dev)
-    cfg = load_config(a.config, tp=world)
+    tp = world
+    if a.virtual_tp > 1:
+        if world != 1:
+            raise SystemExit("--virtual-tp runs on one GPU")
+        from .parallel.collectives import TpCollectives
+
+        tp = a.virtual_tp
+        coll = TpCollectives(0, 1, dev)
+    cfg = load_config(a.config, tp=tp)
     m, e = cfg.model, cfg.engine
     if a.layers:
         m.num_layers = m.run_layers = a.layers
     gbs = e.global_batch_size
     e.max_batch_size = max(e.max_batch_size, gbs)
-    w = random_rank_weights(m, rank, world, dev)
+    w = random_rank_weights(m, rank, tp, dev)
     eng = Engine(cfg, w, collectives=coll, num_pages=a.pages or None)
     n_req = int((a.skip_cycles + 4 * a.iters + 64) * gbs / (a.input_len + a.output_len)) + 256
     rm = RequestManager(vocab_size=m.vocab_size, random_ids=True, seed=0)
     for _ in range(n_req):
         rm.add_request(a.input_len, a.output_len, 0.0)
     rm.finalize_stats()
-    pool = DistKVPool(m.run_layers, m.num_kv_heads, m.head_dim, eng.num_pages, e.page_size, world)
+    pool = DistKVPool(m.run_layers, m.num_kv_heads, m.head_dim, eng.num_pages, e.page_size, tp)
     sch = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=gbs, nanobatch_sizes=e.resolved_nanobatches(),
                     max_batch_size=e.max_batch_size, average_prefill_length=a.input_len,
                     average_decode_length=a.output_len, group_size=m.group_size)
@@ -97,7 +110,7 @@ def main(argv=None) -> int:
             print(f"iteration {i}: {ms:.3f} ms, {loop.stats.tokens_processed - tok0} tokens", flush=True)
     eng.check_status()
     if rank == 0:
-        print(json.dumps({"config": a.config, "gpus": world, "pipeline": e.pipeline_type, "dense_batch": gbs,
+        print(json.dumps({"config": a.config, "gpus": world, "tp": tp, "pipeline": e.pipeline_type, "dense_batch": gbs,
                           "nanobatches": e.resolved_nanobatches(), "kv_pages": eng.num_pages,
                           "ms_per_iteration": [round(t, 3) for t in times]}))
     eng.finalize()
