@@ -1,4 +1,5 @@
-"""Per-kernel micro-benchmarks: ``python -m nanoflow_b200.ops.microbench [gemm|swiglu|decode|prefill|norm|all]``.
+"""Per-kernel micro-benchmarks: ``python -m nanoflow_b200.ops.microbench [gemm|swiglu|smallm|decode|prefill|norm|hostlink|all]``
+(JSON lines; ``... table rows.jsonl`` turns them into a markdown table).
 
 Each case is timed with CUDA events on the launching stream after warm-up, with an L2 flush (a
 write larger than the 126 MB L2) between timed launches, and reported against the measured peaks
@@ -103,7 +104,7 @@ def _paged(batch, ctx, kv_heads, hd, qo_len=1):
 
 def bench_decode():
     bw_peak, _, how = peaks()
-    for (batch, ctx, kv_heads, group, ctas) in [(683, 1280, 1, 8, 0), (683, 1280, 1, 8, 64), (683, 1280, 1, 8, 32),
+    for (batch, ctx, kv_heads, group, ctas) in [(2731, 1280, 1, 8, 0), (683, 1280, 1, 8, 0), (683, 1280, 1, 8, 64),
                                                  (256, 1280, 8, 8, 0), (1024, 1280, 8, 4, 0), (64, 4096, 8, 8, 0)]:
         hd = 128
         q_heads = kv_heads * group
@@ -194,8 +195,55 @@ def small_case(which: str):
     print("small case done:", which)
 
 
+def bench_hostlink():
+    """Pinned host <-> device copy bandwidth (the per-iteration metadata upload, the sampled tokens and
+    the KV offload go over this link). Counterpart in the reference: pipeline/src/pythonProfiling.py,
+    which measures pinned H2D / D2H bandwidth before compressing its traces."""
+    for mb in (1, 16, 256):
+        n = mb << 20
+        host = torch.empty(n, dtype=torch.uint8).pin_memory()
+        dev = torch.empty(n, dtype=torch.uint8, device="cuda")
+        for name, fn in (("h2d", lambda: dev.copy_(host, non_blocking=True)),
+                         ("d2h", lambda: host.copy_(dev, non_blocking=True))):
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(5):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / 5
+            print(json.dumps(dict(op=f"hostlink_{name}", mbytes=mb, ms=round(ms, 4), gbs=round(n / ms / 1e6, 1))),
+                  flush=True)
+
+
+def table(path: str) -> str:
+    """Markdown table from the JSON lines this module prints (``... all > rows.jsonl``)."""
+    hbm, tf, how = peaks()
+    out = ["| op | shape | ms | TFLOP/s or GB/s | of " + how + " peak | cuBLAS TFLOP/s (same shape) |", "|---|---|---|---|---|---|"]
+    for line in open(path):
+        line = line.strip()
+        if not line.startswith("{"):
+            continue
+        d = json.loads(line)
+        shape = " ".join(f"{k}={d[k]}" for k in ("M", "N", "F", "K", "batch", "ctx", "kv_heads", "group", "rows", "cols",
+                                                  "mbytes", "tile_m", "tile_n", "split_k", "num_ctas") if k in d)
+        if "tflops" in d:
+            rate, frac = f"{d['tflops']} TFLOP/s", d.get("frac_of_peak", round(d["tflops"] / tf, 3))
+        else:
+            rate = f"{d.get('gbs', '')} GB/s"
+            frac = d.get("frac_of_peak", d.get("frac_of_bw", round(d["gbs"] / hbm, 3) if "gbs" in d else ""))
+        out.append(f"| {d['op']} | {shape} | {d.get('ms', '')} | {rate} | {frac} | {d.get('cublas_tflops', '')} |")
+    return "\n".join(out)
+
+
 def main(argv):
     what = argv[1] if len(argv) > 1 else "all"
+    if what == "table":
+        print(table(argv[2]))
+        return
     if what.startswith("small_"):
         small_case(what[len("small_"):])
         return
@@ -241,6 +289,8 @@ def main(argv):
         bench_prefill()
     if what in ("norm", "all"):
         bench_norm()
+    if what in ("hostlink", "all"):
+        bench_hostlink()
 
 
 if __name__ == "__main__":
