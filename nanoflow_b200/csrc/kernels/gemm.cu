@@ -5,8 +5,11 @@
 //   D[M,F] = silu(A * Bg[F,K]^T) .* (A * Bu[F,K]^T)                      (SwiGLU epilogue)
 //
 // Work units are whole output tiles, or with split-K (tile, k range) pairs whose fp32 partial tiles
-// a second pass adds up. For small M one CTA can cover several M tiles with the same weight tile,
-// so each weight byte is fetched into shared memory once. A cost model picks the shape.
+// a second pass adds up; with the stream-K tail only the tiles left over after the full waves are
+// cut, into equal k ranges. For small M one CTA can cover several M tiles with the same weight tile,
+// so each weight byte is fetched into shared memory once; for larger M the two CTAs of a cluster
+// share a 256-row tile (tcgen05.mma.cta_group::2) and each stages half of the weight tile. A cost
+// model picks the shape; engines time the candidates on their own shapes (ops/autotune.py).
 //
 // Roles inside one 192-thread CTA: warp 0 lane 0 = TMA producer, warp 1 = TMEM owner and (lane 0)
 // MMA issuer, warps 2..5 = epilogue (TMEM -> registers -> global). Two TMEM accumulators are

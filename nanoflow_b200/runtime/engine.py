@@ -35,7 +35,7 @@ from .pipeline import GEMM_SMEM_KB_SHARED_SM, Buffers, CollectiveHooks, IoSpec, 
 RING = 3                       # host staging slots (iterations in flight + one being formed)
 DECODE_MAX_CHUNKS = 16
 OFFLOAD_HOST_BYTES = 256 << 20 # pinned host staging per ring slot for the KV offload
-GEMM_WS_BYTES = 160 << 20      # stream-K scratch: tile counters + two fp32 partial tiles per CTA
+GEMM_WS_BYTES = 160 << 20      # fp32 partial sums of split-K / stream-K-tail GEMMs (the GEMMs of one engine share a stream)
 DECODE_SPLIT_ROWS = 8192       # workspace rows (request x q head) reserved for split-KV decode
 
 
