@@ -114,7 +114,8 @@ def main():
                     help="one GPU runs rank 0's share of a tensor-parallel job of this degree, collectives reduced "
                          "to their local part (development aid; the JSON line is marked invalid)")
     ap.add_argument("--skip-cycles", type=int, default=1600)
-    ap.add_argument("--executor", default="auto")
+    ap.add_argument("--executor", default="auto", help="auto | native | graph (native executor, iterations "
+                    "captured and launched as CUDA graphs) | python")
     ap.add_argument("--timeline", default="", help="after the timed regions, time every op of one iteration "
                     "with CUDA events and write the aggregate + Chrome trace to this file")
     args = ap.parse_args()
@@ -204,7 +205,10 @@ def main():
     t_load = time.perf_counter()
     weights = random_rank_weights(model, 0 if args.virtual_tp > 1 else rank, tp, dev, seed=0)
     torch.cuda.synchronize()
-    eng = Engine(cfg, weights, device=dev, collectives=coll, executor=args.executor)
+    # One GPU: iterations go out as CUDA graphs (measured 45.5 against 47.1 ms per iteration); with
+    # several ranks the launch gaps already hide under the other streams and plain launches are kept.
+    executor = args.executor if args.executor != "auto" else ("graph" if world == 1 and args.virtual_tp <= 1 else "auto")
+    eng = Engine(cfg, weights, device=dev, collectives=coll, executor=executor)
     load_s = time.perf_counter() - t_load
 
     # synthetic trace: constant-length requests, all available at t=0 (offline)
@@ -313,7 +317,9 @@ def main():
                     "ms_per_step": round(e2e_ms / args.steps, 3), "timer": "host wall clock"},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "executor": "native" if eng.native is not None else "python",
+            "executor": ("python" if eng.native is None else
+                         "native+cuda-graph %d launches, %d rebuilds" % eng.native.graph_stats
+                         if eng.native.graph_stats[0] else "native"),
             "gemm_shapes": {k: {"pick": [v["best"][x] for x in ("tile_m", "tile_n", "cta_group", "split_k", "stream_k")],
                                 "us": v["us"], "model_us": v["auto_us"]} for k, v in eng.gemm_tuning.items()},
             "load_seconds": round(load_s, 1),

@@ -12,6 +12,12 @@
 // stream classes (gemm, attn, net, other, copy) fork from and join back into the caller's main
 // stream, so consecutive iterations stay ordered and torch work queued on that stream composes.
 //
+// Graph mode (set_graph_mode): after two plain iterations the same issue sequence is recorded by
+// stream capture on a private stream, the executable graph of the previous iteration is updated
+// in place with the new parameters (cudaGraphExecUpdate; re-instantiated if the topology changed)
+// and launched on the main stream as one unit. The parameter blocks are passed by value, so an
+// iteration whose token counts differ is still one update, not a rebuild.
+//
 // This takes the place of the reference's per-GPU Worker thread + hand-written Pipeline::run
 // (pipeline/src/computeBound.cu:163-193, :255-290; pipeline/src/pipeline.cu:599-789) and of its
 // OperatorWrapper run/wait/wait_for_start event plumbing (pipeline/include/operatorWrapper.cuh:98-144).
@@ -106,6 +112,8 @@ class Executor {
       if (op.t0) cudaEventDestroy(op.t0);
       if (op.t1) cudaEventDestroy(op.t1);
     }
+    if (exec_) cudaGraphExecDestroy(exec_);
+    if (cap_) cudaStreamDestroy(cap_);
     if (!single_stream_)
       for (int i = 0; i < kNumStreamClasses; ++i) cudaStreamDestroy(streams_[i]);
     for (int i = 0; i < kNumStreamClasses; ++i) cudaEventDestroy(join_[i]);
@@ -210,6 +218,10 @@ class Executor {
     return out;
   }
 
+  void set_graph_mode(bool on) { graph_mode_ = on; }
+  uint64_t graph_launches() const { return graph_launches_.load(); }
+  uint64_t graph_rebuilds() const { return graph_rebuilds_.load(); }
+
   int num_ops() const { return static_cast<int>(ops_.size()); }
   uint64_t launches() const { return launches_.load(); }
 
@@ -241,13 +253,61 @@ class Executor {
   }
 
   void issue(const Job& job) {
+    if (graph_mode_ && !job.timed && plain_iterations_ >= 2) {
+      issue_graph(job);
+    } else {
+      issue_ops(job, main_);
+      ++plain_iterations_;
+    }
+    check(cudaEventRecord(done_[job.ticket % kTickets], main_), "record(done)");
+  }
+
+  // Record the iteration on the capture stream and run it on the main stream as one graph launch.
+  void issue_graph(const Job& job) {
+    if (!cap_) check(cudaStreamCreateWithFlags(&cap_, cudaStreamNonBlocking), "cudaStreamCreate(capture)");
+    check(cudaStreamBeginCapture(cap_, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+    cudaGraph_t graph = nullptr;
+    try {
+      issue_ops(job, cap_);
+    } catch (...) {
+      cudaStreamEndCapture(cap_, &graph);
+      if (graph) cudaGraphDestroy(graph);
+      throw;
+    }
+    check(cudaStreamEndCapture(cap_, &graph), "cudaStreamEndCapture");
+    bool ok = false;
+    if (exec_) {
+      cudaGraphExecUpdateResultInfo info;
+      ok = cudaGraphExecUpdate(exec_, graph, &info) == cudaSuccess;
+      if (!ok) {
+        (void)cudaGetLastError();
+        cudaGraphExecDestroy(exec_);
+        exec_ = nullptr;
+      }
+    }
+    if (!ok) {
+      cudaError_t e = cudaGraphInstantiate(&exec_, graph, 0);
+      if (e != cudaSuccess) {
+        cudaGraphDestroy(graph);
+        exec_ = nullptr;
+        check(e, "cudaGraphInstantiate");
+      }
+      graph_rebuilds_.fetch_add(1);
+    }
+    cudaGraphDestroy(graph);
+    check(cudaGraphLaunch(exec_, main_), "cudaGraphLaunch");
+    graph_launches_.fetch_add(1);
+  }
+
+  // The iteration's launches, forked from and joined back into `origin`.
+  void issue_ops(const Job& job, cudaStream_t origin) {
     if (!single_stream_) {
-      check(cudaEventRecord(fork_, main_), "cudaEventRecord(fork)");
+      check(cudaEventRecord(fork_, origin), "cudaEventRecord(fork)");
       for (int i = 0; i < kNumStreamClasses; ++i) check(cudaStreamWaitEvent(streams_[i], fork_, 0), "wait(fork)");
     }
     bool used[kNumStreamClasses] = {false, false, false, false, false};
     for (auto& op : ops_) {
-      cudaStream_t st = streams_[op.stream_class];
+      cudaStream_t st = single_stream_ ? origin : streams_[op.stream_class];
       used[op.stream_class] = true;
       for (const Patch& p : op.patches) {
         const int64_t v = job.syms[p.sym];
@@ -281,12 +341,11 @@ class Executor {
     }
     if (!single_stream_) {
       for (int i = 0; i < kNumStreamClasses; ++i) {
-        if (!used[i]) continue;
+        if (!used[i] && origin == main_) continue;   // under capture every forked stream must join back
         check(cudaEventRecord(join_[i], streams_[i]), "record(join)");
-        check(cudaStreamWaitEvent(main_, join_[i], 0), "wait(join)");
+        check(cudaStreamWaitEvent(origin, join_[i], 0), "wait(join)");
       }
     }
-    check(cudaEventRecord(done_[job.ticket % kTickets], main_), "record(done)");
   }
 
   cudaStream_t main_;
@@ -308,6 +367,11 @@ class Executor {
   std::string error_;
   std::thread worker_;
   std::atomic<uint64_t> launches_{0};
+  bool graph_mode_ = false;
+  int plain_iterations_ = 0;
+  cudaStream_t cap_ = nullptr;
+  cudaGraphExec_t exec_ = nullptr;
+  std::atomic<uint64_t> graph_launches_{0}, graph_rebuilds_{0};
 };
 
 }  // namespace
@@ -324,5 +388,8 @@ PYBIND11_MODULE(_executor, m) {
       .def("timeline", &Executor::timeline)
       .def("num_ops", &Executor::num_ops)
       .def("launches", &Executor::launches)
+      .def("set_graph_mode", &Executor::set_graph_mode)
+      .def("graph_launches", &Executor::graph_launches)
+      .def("graph_rebuilds", &Executor::graph_rebuilds)
       .def("close", &Executor::close);
 }

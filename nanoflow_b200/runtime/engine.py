@@ -205,13 +205,14 @@ class Engine:
     def _make_executor(self, kind: str) -> None:
         self.native = None
         single = not self.eng.overlap
-        if kind in ("auto", "native"):
+        if kind in ("auto", "native", "graph"):
             try:
                 from .native import NativeExecutor
                 self.native = NativeExecutor(self.graph, self.stream, single_stream=single,
-                                             device=self.device.index or 0)
+                                             device=self.device.index or 0,
+                                             use_cuda_graph=(kind == "graph" or self.eng.use_cuda_graph))
             except ImportError:
-                if kind == "native":
+                if kind != "auto":
                     raise
         self.py_exec = None if self.native is not None else PyExecutor(self.graph, single_stream=single)
 

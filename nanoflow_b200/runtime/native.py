@@ -14,7 +14,8 @@ def _load():
 
 
 class NativeExecutor:
-    def __init__(self, graph: OpGraph, main_stream, single_stream: bool = False, device: int = 0):
+    def __init__(self, graph: OpGraph, main_stream, single_stream: bool = False, device: int = 0,
+                 use_cuda_graph: bool = False):
         mod = _load()
         lib = _ops.lib()
         self.graph = graph
@@ -32,6 +33,9 @@ class NativeExecutor:
             self.ex.add_op(op.name, fn, bytes(op.params), STREAM_CLASSES.index(op.stream), list(op.deps),
                            list(op.after_start), patches)
         self.ex.freeze()
+        # CUDA-graph mode: each iteration is captured, patched into the previous executable graph and
+        # launched as one unit (see csrc/executor/executor.cpp)
+        self.ex.set_graph_mode(bool(use_cuda_graph))
         self._keep = graph   # parameter blocks hold raw pointers into tensors owned by the engine
 
     def submit(self, symbols: Dict[str, int], timed: bool = False) -> int:
@@ -46,6 +50,11 @@ class NativeExecutor:
     @property
     def launches(self) -> int:
         return self.ex.launches()
+
+    @property
+    def graph_stats(self):
+        """(iterations launched as a CUDA graph, times the executable graph had to be rebuilt)."""
+        return self.ex.graph_launches(), self.ex.graph_rebuilds()
 
     def close(self) -> None:
         self.ex.close()

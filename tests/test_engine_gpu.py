@@ -68,6 +68,13 @@ def test_engine_matches_oracle_native_executor():
     _run("LOCAL", [16, 32], "native")
 
 
+@pytest.mark.parametrize("pipeline_type,nano", [("NON_OVERLAP_LOCAL", None), ("LOCAL", [16, 32])])
+def test_engine_cuda_graph_executor(pipeline_type, nano):
+    """Iterations captured and launched as CUDA graphs (single stream and forked streams): the token
+    counts change from iteration to iteration, so every launch goes through the in-place update."""
+    _run(pipeline_type, nano, "graph")
+
+
 def test_kv_offload_and_restore():
     """PLLM_OFFLOAD: pages of retired requests reach pinned host memory layer by layer, match the
     oracle's rotated K / V, and can be scattered back into fresh pages."""
