@@ -109,8 +109,20 @@ typedef struct nfk_rope_append_params {
   const int* kv_indices; // page ids
   int T, q_heads, kv_heads, head_dim, page_size, num_pages;
   unsigned int* status;
+  const float* cos_sin;  // optional [T][head_dim/2][2] (cos, sin) of every token's angles (nfk_rope_table);
+                         // null: the kernel computes them itself
 } nfk_rope_append_params;
 int nfk_rope_append(const nfk_rope_append_params* p, cudaStream_t stream);
+
+// cos / sin of pos[t] * inv_freq[i] for the T tokens of an iteration: every layer rotates by the same
+// angles, so they are computed once per iteration instead of once per layer.
+typedef struct nfk_rope_table_params {
+  float* cos_sin;        // out [T][half][2]
+  const float* inv_freq; // [half]
+  const int* positions;  // [T]
+  int T, half;
+} nfk_rope_table_params;
+int nfk_rope_table(const nfk_rope_table_params* p, cudaStream_t stream);
 
 // ------------------------------------------------------------------------------------------------
 // Attention over the paged KV pool (attention.cu)

@@ -49,7 +49,12 @@ class RopeAppendParams(Structure):
                 ("positions", c_void_p), ("token_req", c_void_p), ("kv_indptr", c_void_p),
                 ("kv_indices", c_void_p),
                 ("T", c_int), ("q_heads", c_int), ("kv_heads", c_int), ("head_dim", c_int),
-                ("page_size", c_int), ("num_pages", c_int), ("status", c_void_p)]
+                ("page_size", c_int), ("num_pages", c_int), ("status", c_void_p), ("cos_sin", c_void_p)]
+
+
+class RopeTableParams(Structure):
+    _fields_ = [("cos_sin", c_void_p), ("inv_freq", c_void_p), ("positions", c_void_p), ("T", c_int),
+                ("half", c_int)]
 
 
 class AttnParams(Structure):
@@ -332,7 +337,7 @@ def rope_append(qkv: torch.Tensor, q_out: torch.Tensor, kv_pool: torch.Tensor,
                 inv_freq: torch.Tensor, positions: torch.Tensor, token_req: torch.Tensor,
                 kv_indptr: torch.Tensor, kv_indices: torch.Tensor, *, q_heads: int, kv_heads: int,
                 head_dim: int, q_off: int, k_off: int, v_off: int,
-                status: Optional[torch.Tensor] = None):
+                status: Optional[torch.Tensor] = None, cos_sin: Optional[torch.Tensor] = None):
     """Rotate q/k, write q to q_out and k/v into their page slots (see csrc/kernels/rope_append.cu).
 
     kv_pool: [num_pages, 2, kv_heads, page_size, head_dim] bf16 (one layer).
@@ -355,7 +360,24 @@ def rope_append(qkv: torch.Tensor, q_out: torch.Tensor, kv_pool: torch.Tensor,
     p.T, p.q_heads, p.kv_heads, p.head_dim = qkv.shape[0], q_heads, kv_heads, head_dim
     p.page_size, p.num_pages = page_size, num_pages
     p.status = _p(status)
+    if cos_sin is not None:
+        if cos_sin.dtype != torch.float32 or cos_sin.numel() < qkv.shape[0] * head_dim or not cos_sin.is_contiguous():
+            raise RuntimeError("rope_append: cos_sin must be contiguous fp32 [T, head_dim/2, 2]")
+        p.cos_sin = _p(cos_sin)
     _check(lib().nfk_rope_append(byref(p), _stream()), "nfk_rope_append")
+
+
+def rope_table(inv_freq: torch.Tensor, positions: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """[T, head_dim/2, 2] fp32 (cos, sin) of positions[t] * inv_freq[i]: the angles every layer's
+    rope_append of one iteration shares."""
+    _i32(positions, "positions")
+    T, half = positions.numel(), inv_freq.numel()
+    if out is None:
+        out = torch.empty((T, half, 2), dtype=torch.float32, device=positions.device)
+    p = RopeTableParams()
+    p.cos_sin, p.inv_freq, p.positions, p.T, p.half = _p(out), _p(inv_freq), _p(positions), T, half
+    _check(lib().nfk_rope_table(byref(p), _stream()), "nfk_rope_table")
+    return out
 
 
 def _attn_common(q, out, kv_pool, qo_indptr, kv_indptr, kv_indices, kv_last_page_len, q_heads,

@@ -125,7 +125,8 @@ class Engine:
             decode_ws=torch.empty(DECODE_SPLIT_ROWS * DECODE_MAX_CHUNKS * (m.head_dim + 2), dtype=torch.float32,
                                   device=dev),
             meta=meta, nano_items=nano_items,
-            gemm_ws=torch.zeros(GEMM_WS_BYTES // 4, dtype=torch.float32, device=dev))
+            gemm_ws=torch.zeros(GEMM_WS_BYTES // 4, dtype=torch.float32, device=dev),
+            rope_table=torch.zeros(T, m.head_dim // 2, 2, dtype=torch.float32, device=dev))
         io = IoSpec(self.meta_dev, layout.fixed_words, layout.off["kv_indices"])
         self.offload_host = None
         if self.offload_cap:

@@ -70,10 +70,12 @@ class KvMoveParams(Structure):
 
 GemmParams = _ops.GemmParams
 RopeAppendParams = _ops.RopeAppendParams
+RopeTableParams = _ops.RopeTableParams
 AttnParams = _ops.AttnParams
 
 KERNEL_OF = {
-    GemmParams: "nfk_gemm_bf16", RopeAppendParams: "nfk_rope_append", NormParams: "nfk_norm_p",
+    GemmParams: "nfk_gemm_bf16", RopeAppendParams: "nfk_rope_append", RopeTableParams: "nfk_rope_table",
+    NormParams: "nfk_norm_p",
     EmbeddingParams: "nfk_embedding_p", GatherParams: "nfk_gather_p", ArgmaxParams: "nfk_argmax_p",
     ArgmaxCombineParams: "nfk_argmax_combine_p", CopyColsParams: "nfk_copy_cols_p",
     MemcpyParams: "nfk_memcpy_p", KvMoveParams: "nfk_kv_move_p",

@@ -32,7 +32,7 @@ import torch
 
 from ..config import EngineConfig, ModelConfig
 from ..models.llama import RankWeights
-from .graph import (ArgmaxCombineParams, ArgmaxParams, AttnParams, EmbeddingParams, GatherParams, GemmParams,
+from .graph import (ArgmaxCombineParams, ArgmaxParams, AttnParams, EmbeddingParams, GatherParams, GemmParams, RopeTableParams,
                     KvMoveParams, MemcpyParams, NormParams, OpGraph, RopeAppendParams)
 
 
@@ -64,6 +64,7 @@ class Buffers:
     meta: Dict[str, torch.Tensor]    # int32 views into the metadata block (see engine.MetaLayout)
     nano_items: List[torch.Tensor]   # per nano-batch [cap,3] int32 views
     gemm_ws: Optional[torch.Tensor] = None   # split-K partial sums (fp32); all GEMMs share one stream
+    rope_table: Optional[torch.Tensor] = None  # [T, head_dim/2, 2] fp32 angles of the iteration's tokens
 
 
 class CollectiveHooks:
@@ -142,6 +143,12 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
                           elem_bytes=4, count=0)
         pre.append(g.add("kv_indices_h2d", c2, S("other"),
                          dyn=[("src", g.symbol("kv_src")), ("count", g.symbol("kv_words"))]))
+    if bufs.rope_table is not None:
+        # cos / sin of every token's rotary angles, once per iteration for all layers
+        tp_ = RopeTableParams()
+        tp_.cos_sin, tp_.inv_freq, tp_.positions = _ptr(bufs.rope_table), _ptr(bufs.inv_freq), _ptr(m["positions"])
+        tp_.T, tp_.half = 0, hd // 2
+        pre.append(g.add("rope_table", tp_, S("other"), deps=list(pre), dyn=[("T", T_all)]))
     emb = g.add("embedding", ep, S("other"), deps=pre, dyn=[("n_tokens", T_all)])
 
     last_x_writer: List[Optional[int]] = [emb] * nn     # op that last wrote nano-batch k's residual rows
@@ -208,6 +215,8 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         rp.kv_indptr, rp.kv_indices = _ptr(m["kv_indptr"]), _ptr(m["kv_indices"])
         rp.T, rp.q_heads, rp.kv_heads, rp.head_dim = 0, model.q_heads_local, model.kv_heads_local, hd
         rp.page_size, rp.num_pages, rp.status = eng.page_size, pool.shape[0], _ptr(st)
+        if bufs.rope_table is not None:
+            rp.cos_sin = _ptr(bufs.rope_table, r0)   # rows of this nano-batch
         ro = g.add(f"L{l}.nb{k}.rope_append", rp, "gemm" if overlap else S("other"), deps=[q],
                    dyn=[("T", nb_T[k])], layer=l, nano=k)
 

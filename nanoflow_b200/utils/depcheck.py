@@ -93,8 +93,11 @@ def graph_access(graph: OpGraph, nano_starts: List[int], nano_sizes: List[int], 
             width = (p.q_heads + 2 * p.kv_heads) * p.head_dim
             add(reads, rng(p.qkv, cap, p.ld_qkv, width))
             add(writes, rng(p.q_out, cap, p.q_heads * p.head_dim, p.q_heads * p.head_dim))
+            add(reads, rng(p.cos_sin, cap, p.head_dim, p.head_dim, 4))
             if kv_pool_bytes:
                 add(writes, (int(p.kv_pool), int(p.kv_pool) + kv_pool_bytes))
+        elif isinstance(p, G.RopeTableParams):
+            add(writes, rng(p.cos_sin, total, 2 * p.half, 2 * p.half, 4))
         elif isinstance(p, G.AttnParams):
             # q / out rows of the whole dense batch are addressable; the op touches its nano-batch's rows
             r0 = nano_starts[op.nano] if op.nano >= 0 else 0

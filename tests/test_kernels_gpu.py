@@ -438,7 +438,8 @@ def test_attn_prefill_split_request_across_items():
 
 
 @pytest.mark.parametrize("q_heads,kv_heads,hd", [(8, 1, 128), (32, 8, 128), (4, 4, 64)])
-def test_rope_append(q_heads, kv_heads, hd):
+@pytest.mark.parametrize("table", [False, True])
+def test_rope_append(q_heads, kv_heads, hd, table):
     lens = [40, 1, 17, 300]
     qo_lens = [40, 1, 3, 100]
     pool, qo, kvp, kvi, last = _make_paged(lens, qo_lens, kv_heads, hd)
@@ -457,8 +458,14 @@ def test_rope_append(q_heads, kv_heads, hd):
     inv = ref.rope_inv_freq(hd, 500000.0, scaling).cuda()
     q_out = torch.empty(T, q_heads * hd, device="cuda", dtype=torch.bfloat16)
     st = ops.new_status()
+    cos_sin = None
+    if table:   # angles from the per-iteration table instead of computed per token
+        cos_sin = ops.rope_table(inv, positions)
+        ang = positions.float()[:, None] * inv[None, :]
+        _close(cos_sin, torch.stack([ang.cos(), ang.sin()], dim=-1), atol=2e-4, rtol=1e-4)
     ops.rope_append(qkv, q_out, pool, inv, positions, token_req, kvp, kvi, q_heads=q_heads,
-                    kv_heads=kv_heads, head_dim=hd, q_off=q_off, k_off=k_off, v_off=v_off, status=st)
+                    kv_heads=kv_heads, head_dim=hd, q_off=q_off, k_off=k_off, v_off=v_off, status=st,
+                    cos_sin=cos_sin)
     ops.check_status(st, "rope_append")
     pool_ref = torch.zeros_like(pool)
     q_ref = ref.rope_append(qkv, pool_ref, inv, positions.cpu(), token_req.cpu(), kvp.cpu(), kvi.cpu(),
