@@ -55,7 +55,7 @@ def main():
             else:
                 ops.gemm(a, w, out=out, workspace=ws, smem_budget_kb=GEMM_SMEM_KB_SHARED_SM)
 
-        for ctas in (16, 32, 64, 128):
+        for ctas in (32, 64, 148, 296, 444):
             def ar():
                 coll.all_reduce_(buf, norm_w=wn, norm_out=hout, num_ctas=ctas)
 
