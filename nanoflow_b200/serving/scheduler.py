@@ -99,7 +99,7 @@ class Scheduler:
                  global_batch_size: int, nanobatch_sizes: Optional[Sequence[int]] = None,
                  max_batch_size: Optional[int] = None, average_prefill_length: int = 1024,
                  average_decode_length: int = 512, group_size: int = 8, eos_token_id: Optional[int] = None,
-                 stop_on_eos: bool = False, hold_retired_pages: bool = False):
+                 stop_on_eos: bool = False, hold_retired_pages: bool = False, prefill_ctas: int = 148):
         self._memory_pool = memory_pool
         self._request_queue = request_queue
         self.global_batch_size = int(global_batch_size)
@@ -110,6 +110,7 @@ class Scheduler:
         self.average_prefill_length = int(average_prefill_length)
         self.average_decode_length = int(average_decode_length)
         self.tile_tokens = max(1, 128 // group_size)    # query tokens per prefill work item
+        self.prefill_ctas = int(prefill_ctas)           # persistent CTAs of the prefill attention kernel
         self.eos_token_id = eos_token_id
         self.stop_on_eos = stop_on_eos
         self.hold_retired_pages = hold_retired_pages
@@ -368,6 +369,16 @@ class Scheduler:
                 page_usage=self._memory_pool.num_used_pages / max(1, self._memory_pool.capacity),
                 queue=self._request_queue.size, retired=len(retired_now)))
 
+    def _balanced_order(self, cost: np.ndarray) -> np.ndarray:
+        """Order in which the attention kernel's persistent CTAs (CTA c takes items c, c + G, ...)
+        get near-equal total cost: items sorted by falling cost, dealt in rounds of G that alternate
+        direction, so the CTA that drew the dearest item of one round draws the cheapest of the next."""
+        G = max(1, self.prefill_ctas)
+        order = np.argsort(-cost, kind="stable")
+        for r in range(1, (order.size + G - 1) // G, 2):
+            order[r * G:(r + 1) * G] = order[r * G:(r + 1) * G][::-1].copy()
+        return order
+
     def _cut_nanobatches(self, T: int, D: int, prefill, qo_indptr) -> List[NanoBatchPlan]:
         out = []
         start = 0
@@ -379,7 +390,7 @@ class Scheduler:
                 out.append(NanoBatchPlan(t0 if t0 < T else T, 0, min(D, t0), 0, np.zeros((0, 3), dtype=np.int32)))
                 continue
             d0, d1 = min(D, t0), min(D, t1)
-            items = []
+            items, kv_ends = [], []
             for j, (req, s, n) in enumerate(prefill):
                 q0, q1 = int(qo_indptr[D + j]), int(qo_indptr[D + j + 1])
                 a, b = max(q0, t0), min(q1, t1)
@@ -388,7 +399,10 @@ class Scheduler:
                 starts = np.arange(a, b, tq, dtype=np.int32)
                 cnt = np.minimum(tq, b - starts).astype(np.int32)
                 items.append(np.stack([np.full_like(starts, D + j), starts, cnt], axis=1))
+                kv_ends.append(s + (starts - q0) + cnt)     # context each item attends to = its cost
             it = np.concatenate(items) if items else np.zeros((0, 3), dtype=np.int32)
+            if it.shape[0] > 1:
+                it = it[self._balanced_order(np.concatenate(kv_ends))]
             out.append(NanoBatchPlan(t0, t1 - t0, d0, d1 - d0, it))
         return out
 

@@ -135,3 +135,32 @@ def test_preemption_when_outputs_outgrow_the_projection():
         done[r.req_idx] += len(r.output)
     assert sorted(done) == list(range(6))
     assert pool.num_free_pages == 30
+
+
+def test_prefill_items_balanced_over_persistent_ctas():
+    """Work items are dealt so that CTA c (items c, c+G, ...) gets close to the average context length."""
+    pool = DistKVPool(1, 8, 128, 4096, 16)
+    rm = RequestManager(vocab_size=100, random_ids=True)
+    for n in (900, 700, 500, 300, 100, 60):
+        rm.add_request(n, 4, 0.0)
+    rm.finalize_stats()
+    rm.simulate_issue(1.0)
+    sch = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=4096, average_prefill_length=400,
+                    average_decode_length=4, group_size=8, prefill_ctas=8)
+    plan = sch.schedule()
+    items = plan.nano[0].items
+    assert items.shape[0] == sum(-(-n // 16) for n in (900, 700, 500, 300, 100, 60))
+    # every token of every prompt is covered exactly once
+    covered = np.zeros(plan.num_tokens, dtype=np.int32)
+    for req, start, cnt in items:
+        covered[start:start + cnt] += 1
+    assert (covered[plan.num_decode:] == 1).all()
+    # cost of an item = position of its last token within its prompt (all prompts start at 0 here)
+    qo = plan.qo_indptr
+    cost = np.array([start - qo[req] + cnt for req, start, cnt in items])
+    G = 8
+    per_cta = np.array([cost[c::G].sum() for c in range(G)])
+    assert per_cta.max() <= 1.1 * per_cta.mean()
+    naive = np.sort(cost)            # the order a plain token walk would give: short contexts first
+    naive_per_cta = np.array([naive[c::G].sum() for c in range(G)])
+    assert per_cta.max() - per_cta.min() < naive_per_cta.max() - naive_per_cta.min()
