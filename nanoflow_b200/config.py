@@ -151,6 +151,7 @@ class EngineConfig:
     sm_budget: Dict[str, int] = field(default_factory=lambda: {"gemm": 0, "attn_decode": 0, "attn_prefill": 0, "comm": 64, "offload": 8})
     gemm_tile_n: Dict[str, int] = field(default_factory=dict)
     autotune_gemm: bool = True             # time candidate GEMM shapes at start-up and pin the fastest per op
+    prefill_tc: bool = True                # head_dim 128: prefill attention on tcgen05 (else the mma.sync kernel)
     gemm_shapes: Dict[str, Dict[str, int]] = field(default_factory=dict)   # "<op>.nb<k>" -> pinned launcher arguments
     decode_chunk_pages: int = 0            # 0 = choose per iteration
     use_cuda_graph: bool = False
@@ -229,6 +230,7 @@ def parse_config(raw: Dict[str, Any], *, tp: Optional[int] = None) -> NanoflowCo
         offload=ptype == "PLLM_OFFLOAD" or bool(pc.get("offload", False)),
         fuse_gemm_rs=bool(pc.get("fuse_gemm_rs", False)),
         autotune_gemm=bool(pc.get("autotune_gemm", True)),
+        prefill_tc=bool(pc.get("prefill_tc", True)),
         model_id=sc.get("model", ""),
         weight_path=sc.get("weight_path", ""),
         hf_path=sc.get("hf_path", ""),

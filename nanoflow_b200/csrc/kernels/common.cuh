@@ -89,6 +89,24 @@ NF_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return false;
 }
 
+// Bounded wait that polls without suspending: for barriers on a short critical path, where the
+// wake-up granularity of try_wait would cost more than the spinning does. Returns false on timeout.
+NF_DEVICE bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t it = 0; it < (1u << 26); ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
 NF_DEVICE void report_status(unsigned int* status, unsigned int code) {
   if (status != nullptr) atomicCAS(status, 0u, code);
 }
@@ -197,6 +215,19 @@ NF_DEVICE void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[32]) {
   for (int i = 16; i < 32; ++i) r[i] = 0u;
 }
 NF_DEVICE void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Registers -> TMEM, same shape as the x32 load: thread t writes lane (base_lane + t), 32 columns.
+NF_DEVICE void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+      "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+      "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+NF_DEVICE void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---- CTA pairs (cta_group::2): two CTAs of a 2-CTA cluster work on one 256-row tile --------------
 // Each CTA stages its own 128 rows of A and half of the B tile; the even CTA issues the MMAs, which

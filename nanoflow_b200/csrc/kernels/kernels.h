@@ -150,6 +150,8 @@ typedef struct nfk_attn_params {
 } nfk_attn_params;
 int nfk_attn_decode(const nfk_attn_params* p, cudaStream_t stream);
 int nfk_attn_prefill(const nfk_attn_params* p, cudaStream_t stream);
+// Same contract as nfk_attn_prefill for head_dim 128, on tcgen05 tensor cores (attention_tc.cu).
+int nfk_attn_prefill_tc(const nfk_attn_params* p, cudaStream_t stream);
 
 // ------------------------------------------------------------------------------------------------
 // KV offload (kv_offload.cu): gather / scatter whole pages between the pool and a staging buffer

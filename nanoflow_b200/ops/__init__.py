@@ -422,13 +422,19 @@ def attn_decode(q, out, kv_pool, qo_indptr, kv_indptr, kv_indices, kv_last_page_
 
 def attn_prefill(q, out, kv_pool, qo_indptr, kv_indptr, kv_indices, kv_last_page_len, items, *,
                  q_heads: int, sm_scale: Optional[float] = None, num_ctas: int = 0,
-                 status: Optional[torch.Tensor] = None):
-    """Causal attention for work items [(request, first token, token count)] over the paged pool."""
+                 status: Optional[torch.Tensor] = None, impl: str = "auto"):
+    """Causal attention for work items [(request, first token, token count)] over the paged pool.
+
+    ``impl``: "tc" = tcgen05 kernel (head_dim 128), "mma" = warp-level mma.sync kernel, "auto" = tc when
+    the head size allows."""
     p = _attn_common(q, out, kv_pool, qo_indptr, kv_indptr, kv_indices, kv_last_page_len, q_heads,
                      sm_scale, num_ctas, status)
     _i32(items, "items")
     p.items, p.num_items = _p(items), items.shape[0]
-    _check(lib().nfk_attn_prefill(byref(p), _stream()), "nfk_attn_prefill")
+    if impl == "tc" or (impl == "auto" and kv_pool.shape[-1] == 128):
+        _check(lib().nfk_attn_prefill_tc(byref(p), _stream()), "nfk_attn_prefill_tc")
+    else:
+        _check(lib().nfk_attn_prefill(byref(p), _stream()), "nfk_attn_prefill")
     return out
 
 

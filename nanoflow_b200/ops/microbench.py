@@ -122,7 +122,7 @@ def bench_decode():
 
 def bench_prefill():
     _, tf_peak, how = peaks()
-    for (batch, ctx, kv_heads, group) in [(2, 1024, 1, 8), (2, 1024, 8, 8), (8, 1024, 8, 4), (1, 4096, 8, 8)]:
+    for (batch, ctx, kv_heads, group) in [(2, 1024, 1, 8), (4, 1024, 1, 8), (2, 1024, 8, 8), (8, 1024, 8, 4), (1, 4096, 8, 8)]:
         hd = 128
         q_heads = kv_heads * group
         pool, qo, kvp, kvi, last = _paged(batch, ctx, kv_heads, hd, qo_len=ctx)
@@ -131,12 +131,13 @@ def bench_prefill():
         tq = 128 // group
         items = torch.tensor([[b, b * ctx + t, min(tq, ctx - t)] for b in range(batch)
                               for t in range(0, ctx, tq)], dtype=torch.int32, device="cuda")
-        fn = lambda: ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, items, q_heads=q_heads)
-        med, best = time_ms(fn)
         flops = 4.0 * batch * q_heads * hd * ctx * ctx / 2
-        print(json.dumps(dict(op="attn_prefill", batch=batch, ctx=ctx, kv_heads=kv_heads, group=group,
-                              ms=round(med, 4), tflops=round(flops / med / 1e9, 1),
-                              frac_of_peak=round(flops / med / 1e9 / tf_peak, 3), peak=how)), flush=True)
+        for impl in ("tc", "mma"):
+            fn = lambda: ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, items, q_heads=q_heads, impl=impl)
+            med, best = time_ms(fn)
+            print(json.dumps(dict(op="attn_prefill_" + impl, batch=batch, ctx=ctx, kv_heads=kv_heads, group=group,
+                                  ms=round(med, 4), tflops=round(flops / med / 1e9, 1),
+                                  frac_of_peak=round(flops / med / 1e9 / tf_peak, 3), peak=how)), flush=True)
 
 
 def bench_norm():
@@ -183,6 +184,14 @@ def small_case(which: str):
         out = torch.empty_like(q)
         for _ in range(4):
             ops.attn_decode(q, out, pool, qo, kvp, kvi, last, q_heads=64, req_begin=0, req_count=512)
+    elif which == "prefill_tc":
+        pool, qo, kvp, kvi, last = _paged(4, 1024, 8, 128, qo_len=1024)
+        q = torch.randn(4096, 64 * 128, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        items = torch.tensor([[b, b * 1024 + t, 16] for b in range(4) for t in range(0, 1024, 16)],
+                             dtype=torch.int32, device="cuda")
+        for _ in range(3):
+            ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, items, q_heads=64, impl="tc")
     elif which == "prefill":
         pool, qo, kvp, kvi, last = _paged(4, 1024, 8, 128, qo_len=1024)
         q = torch.randn(4096, 64 * 128, device="cuda", dtype=torch.bfloat16)
@@ -190,7 +199,7 @@ def small_case(which: str):
         items = torch.tensor([[b, b * 1024 + t, 16] for b in range(4) for t in range(0, 1024, 16)],
                              dtype=torch.int32, device="cuda")
         for _ in range(4):
-            ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, items, q_heads=64)
+            ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, items, q_heads=64, impl="mma")
     torch.cuda.synchronize()
     print("small case done:", which)
 

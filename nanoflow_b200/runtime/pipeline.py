@@ -241,7 +241,9 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         pp = attn_params()
         pp.num_ctas = budget.get("attn_prefill", 0)
         pp.items = _ptr(bufs.nano_items[k])
-        pre = g.add(f"L{l}.nb{k}.attn_prefill", pp, S("attn"), deps=[ro] + straddle, kernel="nfk_attn_prefill",
+        # head_dim 128: the tcgen05 kernel; other head sizes: the warp-level mma.sync kernel
+        pre_kernel = "nfk_attn_prefill_tc" if (hd == 128 and eng.prefill_tc) else "nfk_attn_prefill"
+        pre = g.add(f"L{l}.nb{k}.attn_prefill", pp, S("attn"), deps=[ro] + straddle, kernel=pre_kernel,
                     dyn=[("num_items", nb_items[k])], layer=l, nano=k)
         rope_of[(l, k)] = ro
         return dec, pre

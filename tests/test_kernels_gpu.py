@@ -399,7 +399,10 @@ def _prefill_items(qo_indptr, group, reqs=None):
 
 @pytest.mark.parametrize("kv_heads,group,hd", [(1, 8, 128), (8, 8, 128), (4, 4, 128), (2, 1, 128), (2, 2, 64)])
 @pytest.mark.parametrize("case", ["short", "long", "chunked", "mixed"])
-def test_attn_prefill(kv_heads, group, hd, case):
+@pytest.mark.parametrize("impl", ["mma", "tc"])
+def test_attn_prefill(kv_heads, group, hd, case, impl):
+    if impl == "tc" and hd != 128:
+        pytest.skip("the tcgen05 prefill kernel is built for head_dim 128")
     q_heads = kv_heads * group
     if case == "short":
         qo_lens, kv_lens = [1, 5, 16, 17, 33], [1, 5, 16, 17, 33]
@@ -416,7 +419,7 @@ def test_attn_prefill(kv_heads, group, hd, case):
     items = _prefill_items(qo.tolist(), group)
     st = ops.new_status()
     ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, items, q_heads=q_heads, num_ctas=0 if case != "long" else 11,
-                     status=st)
+                     status=st, impl=impl)
     ops.check_status(st, "attn_prefill")
     want = ref.paged_attention(q, pool, qo.cpu(), kvp.cpu(), kvi, last.cpu(), q_heads=q_heads)
     _close(out, want, atol=1e-2, rtol=2e-2)
@@ -431,8 +434,8 @@ def test_attn_prefill_split_request_across_items():
     out = torch.zeros_like(q)
     it_a = torch.tensor([[0, t, min(16, 203 - t)] for t in range(0, 203, 16)], dtype=torch.int32, device="cuda")
     it_b = torch.tensor([[0, t, min(16, 500 - t)] for t in range(203, 500, 16)], dtype=torch.int32, device="cuda")
-    ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, it_a, q_heads=q_heads)
-    ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, it_b, q_heads=q_heads)
+    ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, it_a, q_heads=q_heads, impl="tc")
+    ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, it_b, q_heads=q_heads, impl="mma")
     want = ref.paged_attention(q, pool, qo.cpu(), kvp.cpu(), kvi, last.cpu(), q_heads=q_heads)
     _close(out, want, atol=1e-2, rtol=2e-2)
 
