@@ -182,7 +182,7 @@ attn_prefill_tc_kernel(nfk_attn_params p) {
       __syncwarp();
       // The previous tile's PV product still reads V^T and P (and writes O) until bar_o fires.
       if (t > 0) {
-        if (!mbar_wait_spin(bar_o, ph_o)) {
+        if (!mbar_wait(bar_o, ph_o)) {
           report_status(p.status, NF_ST_TIMEOUT_TMEM_FULL);
           *abort_flag = 1;
         }
@@ -207,7 +207,7 @@ attn_prefill_tc_kernel(nfk_attn_params p) {
                        : "memory");
         }
       }
-      if (!mbar_wait_spin(bar_s, ph_s)) {
+      if (!mbar_wait(bar_s, ph_s)) {
         report_status(p.status, NF_ST_TIMEOUT_TMEM_FULL);
         *abort_flag = 1;
       }
@@ -224,15 +224,19 @@ attn_prefill_tc_kernel(nfk_attn_params p) {
         tmem_ld_32x32b_x32(t_lane + 32, r1);
         tmem_ld_wait();
         const int cbase = t * kTile;
+        // Only the tile(s) on the diagonal need the causal mask; the row maximum is taken on the raw
+        // scores (the scale is positive) and the scale folded into the exponent's multiply-add.
+        if (cbase + kTile - 1 > pos) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (cbase + j > pos) r0[j] = 0xff800000u;        // -inf
+            if (cbase + 32 + j > pos) r1[j] = 0xff800000u;
+          }
+        }
         float mx = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float a = (cbase + j <= pos) ? __uint_as_float(r0[j]) * scale : -INFINITY;
-          const float b = (cbase + 32 + j <= pos) ? __uint_as_float(r1[j]) * scale : -INFINITY;
-          r0[j] = __float_as_uint(a);
-          r1[j] = __float_as_uint(b);
-          mx = fmaxf(mx, fmaxf(a, b));
-        }
+        for (int j = 0; j < 32; ++j) mx = fmaxf(mx, fmaxf(__uint_as_float(r0[j]), __uint_as_float(r1[j])));
+        mx *= scale;
         // Reference maximum: follows the row maximum only when that outgrows it by 2^kRescaleGap;
         // then O (in TMEM) and the row sum are brought to the new reference. Warp-wide because the
         // TMEM accesses are.
@@ -262,10 +266,10 @@ attn_prefill_tc_kernel(nfk_attn_params p) {
           uint32_t w0[4], w1[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float x0 = fast_exp2(__uint_as_float(r0[c * 8 + 2 * e]) - ms);
-            const float x1 = fast_exp2(__uint_as_float(r0[c * 8 + 2 * e + 1]) - ms);
-            const float y0 = fast_exp2(__uint_as_float(r1[c * 8 + 2 * e]) - ms);
-            const float y1 = fast_exp2(__uint_as_float(r1[c * 8 + 2 * e + 1]) - ms);
+            const float x0 = fast_exp2(fmaf(__uint_as_float(r0[c * 8 + 2 * e]), scale, -ms));
+            const float x1 = fast_exp2(fmaf(__uint_as_float(r0[c * 8 + 2 * e + 1]), scale, -ms));
+            const float y0 = fast_exp2(fmaf(__uint_as_float(r1[c * 8 + 2 * e]), scale, -ms));
+            const float y1 = fast_exp2(fmaf(__uint_as_float(r1[c * 8 + 2 * e + 1]), scale, -ms));
             rs += (x0 + x1) + (y0 + y1);
             w0[e] = pack_bf16x2(x0, x1);
             w1[e] = pack_bf16x2(y0, y1);
@@ -295,7 +299,7 @@ attn_prefill_tc_kernel(nfk_attn_params p) {
     }
     cp_async_wait<0>();
     if (alive) {
-      if (!mbar_wait_spin(bar_o, ph_o)) {
+      if (!mbar_wait(bar_o, ph_o)) {
         report_status(p.status, NF_ST_TIMEOUT_TMEM_FULL);
         *abort_flag = 1;
       }
