@@ -99,7 +99,7 @@ class Scheduler:
                  global_batch_size: int, nanobatch_sizes: Optional[Sequence[int]] = None,
                  max_batch_size: Optional[int] = None, average_prefill_length: int = 1024,
                  average_decode_length: int = 512, group_size: int = 8, eos_token_id: Optional[int] = None,
-                 stop_on_eos: bool = False, hold_retired_pages: bool = False, prefill_ctas: int = 148):
+                 stop_on_eos: bool = False, hold_retired_pages: bool = False, prefill_ctas: int = 296):
         self._memory_pool = memory_pool
         self._request_queue = request_queue
         self.global_batch_size = int(global_batch_size)
@@ -110,7 +110,7 @@ class Scheduler:
         self.average_prefill_length = int(average_prefill_length)
         self.average_decode_length = int(average_decode_length)
         self.tile_tokens = max(1, 128 // group_size)    # query tokens per prefill work item
-        self.prefill_ctas = int(prefill_ctas)           # persistent CTAs of the prefill attention kernel
+        self.prefill_ctas = int(prefill_ctas)           # persistent CTAs of the prefill attention kernel (two per SM)
         self.eos_token_id = eos_token_id
         self.stop_on_eos = stop_on_eos
         self.hold_retired_pages = hold_retired_pages
