@@ -5,8 +5,8 @@
 //
 //   S[128 x 64]  = Q K^T          tcgen05.mma, Q and K staged K-major / 128B-swizzled in shared memory,
 //                                 accumulator in TMEM columns [0, 64)
-//   P            = exp2(S*scale - m)   one thread per row reads its S row from TMEM, keeps the running
-//                                 max / sum, writes P (bf16) back to shared memory as the next A operand
+//   P            = exp2(S*scale - m)   two threads per row read the halves of its S row from TMEM, keep the
+//                                 running max / sum, write P (bf16) back to shared memory as the next A operand
 //   O[128 x 128] += P V           tcgen05.mma accumulating in TMEM columns [64, 192) across the tiles; V
 //                                 arrives token-major, so the tile is first transposed shared->shared
 //                                 (ldmatrix.trans + stmatrix) into the K-major form the B operand needs
@@ -16,8 +16,9 @@
 // by more than 2^8, which after the first tiles is rare; the row sum is kept in fp32 and divides the
 // result at the end. K / V pages are gathered with cp.async (16-byte chunks placed directly in the
 // swizzled layouts); the next tile's loads are issued as soon as this tile's K and V have been
-// consumed (after the S product and the transposes) and run under its softmax and PV product. Two 128-thread CTAs share an SM (96 KB of shared memory and
-// 256 TMEM columns each), so one CTA's softmax runs under the other's MMAs. Every wait on an
+// consumed (after the S product and the transposes) and run under its softmax and PV product. Two
+// 256-thread CTAs share an SM (97 KB of shared memory and 256 TMEM columns each), so one CTA's
+// softmax runs under the other's MMAs. Every wait on an
 // mbarrier is bounded and failures end in the status word.
 //
 // Takes the place of the reference's FlashInfer BatchPrefillWithPagedKVCacheKernel
@@ -31,7 +32,8 @@ namespace {
 constexpr int HD = 128;
 constexpr int kPage = 16;
 constexpr int kTile = 64;            // kv tokens per tile
-constexpr int kThreads = 128;        // one per query row
+constexpr int kThreads = 256;        // two per query row: warps 0-3 take the first half of a row's columns,
+                                     // warps 4-7 the second (a warp reaches the 32 TMEM lanes of its index mod 4)
 constexpr float kLog2e = 1.4426950408889634f;
 
 // shared-memory map (bytes from a 1024-aligned base); every MMA operand region is 1024-aligned
@@ -41,7 +43,8 @@ constexpr int V_OFF = K_OFF + 16384;             // [64 tok][128 hd] (token-majo
 constexpr int VT_OFF = V_OFF + 16384;            // [128 hd][64 tok]               16 KB
 constexpr int P_OFF = VT_OFF + 16384;            // [128 rows][64 tok]             16 KB
 constexpr int BAR_OFF = P_OFF + 16384;
-constexpr int kSmemBytes = BAR_OFF + 64 + 1024;  // + alignment slack
+constexpr int EXCH_OFF = BAR_OFF + 64;           // [2 halves][128 rows] fp32: what the two threads of a row exchange
+constexpr int kSmemBytes = EXCH_OFF + 1024 + 1024;  // + alignment slack
 constexpr float kRescaleGap = 8.0f;              // log2 of how far a row maximum may outgrow its reference
 
 __device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gptr) {
@@ -77,8 +80,10 @@ attn_prefill_tc_kernel(nfk_attn_params p) {
   uint64_t* bar_o = bar_s + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_s + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile float* exch = reinterpret_cast<volatile float*>(smem + EXCH_OFF);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = threadIdx.x;
+  const int half = warp >> 2;                       // which half of the row's columns this thread handles
+  const int row = (warp & 3) * 32 + lane;           // query row = TMEM lane
 
   if (threadIdx.x == 0) {
     mbar_init(bar_s, 1);
@@ -94,7 +99,9 @@ attn_prefill_tc_kernel(nfk_attn_params p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t t_lane = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+  const uint32_t t_lane = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+  const uint32_t t_s = t_lane + half * 32;          // this thread's 32 S columns
+  const uint32_t t_o = t_lane + 64 + half * 64;     // this thread's 64 O columns
   const uint32_t idesc_s = umma_idesc_bf16(128, kTile), idesc_o = umma_idesc_bf16(128, HD);
   uint32_t ph_s = 0, ph_o = 0;
 
@@ -127,7 +134,7 @@ attn_prefill_tc_kernel(nfk_attn_params p) {
 
     // ---- Q tile: 128 rows x 16 chunks, zero rows past the item ----
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
+    for (int j = 0; j < 8; ++j) {
       const int idx = threadIdx.x + kThreads * j;
       const int r = idx >> 4, c = idx & 15;
       const int rt = r / group;
@@ -142,7 +149,7 @@ attn_prefill_tc_kernel(nfk_attn_params p) {
     auto issue = [&](int t) {
       if (t < n_tiles) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 4; ++j) {
           const int idx = threadIdx.x + kThreads * j;
           const int r = idx >> 4, c = idx & 15;
           int pslot = t * (kTile / kPage) + r / kPage;
@@ -162,7 +169,7 @@ attn_prefill_tc_kernel(nfk_attn_params p) {
     };
     issue(0);
 
-    float m_ref = -INFINITY, l = 0.f;
+    float m_ref = -INFINITY, l = 0.f;   // l: this thread's half of the row sum
 
     for (int t = 0; t < n_tiles; ++t) {
       cp_async_wait<0>();
@@ -189,13 +196,15 @@ attn_prefill_tc_kernel(nfk_attn_params p) {
         ph_o ^= 1;
         tc_fence_after();
       }
-      // ---- V^T for the PV product: 8x8 blocks, ldmatrix.trans -> stmatrix (under the S MMAs) ----
+      // ---- V^T for the PV product: 8x8 blocks, ldmatrix.trans -> stmatrix (under the S MMAs);
+      //      a warp takes four hd blocks (one per 8 lanes) x four token blocks ----
       {
         const uint32_t vsrc = sb + V_OFF;
         const int j = lane >> 3, i = lane & 7;
-        const int hb = 4 * warp + j;                    // hd block of this lane's matrix
+        const int hb = 4 * (warp & 3) + j;              // hd block of this lane's matrix
 #pragma unroll
-        for (int tb = 0; tb < 8; ++tb) {
+        for (int q = 0; q < 4; ++q) {
+          const int tb = 4 * half + q;
           uint32_t d0, d1, d2, d3;
           asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                        : "=r"(d0), "=r"(d1), "=r"(d2), "=r"(d3)
@@ -213,46 +222,44 @@ attn_prefill_tc_kernel(nfk_attn_params p) {
       }
       ph_s ^= 1;
       tc_fence_after();
+      // ---- softmax of this thread's half row ----
+      uint32_t r0[32];
+      tmem_ld_32x32b_x32(t_s, r0);
+      tmem_ld_wait();
+      const int cbase = t * kTile + half * 32;
+      // Only the tile(s) on the diagonal need the causal mask; the row maximum is taken on the raw
+      // scores (the scale is positive) and the scale folded into the exponent's multiply-add.
+      if (cbase + 31 > pos) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (cbase + j > pos) r0[j] = 0xff800000u;        // -inf
+      }
+      float mxp = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) mxp = fmaxf(mxp, __uint_as_float(r0[j]));
+      exch[half * 128 + row] = mxp;
       // K has been consumed by the S product and, once every warp is past its transposes, V too:
       // the next tile's loads start now and run under this tile's softmax and PV product.
       __syncthreads();
       issue(t + 1);
-      // ---- softmax of this thread's row ----
       {
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32b_x32(t_lane, r0);
-        tmem_ld_32x32b_x32(t_lane + 32, r1);
-        tmem_ld_wait();
-        const int cbase = t * kTile;
-        // Only the tile(s) on the diagonal need the causal mask; the row maximum is taken on the raw
-        // scores (the scale is positive) and the scale folded into the exponent's multiply-add.
-        if (cbase + kTile - 1 > pos) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (cbase + j > pos) r0[j] = 0xff800000u;        // -inf
-            if (cbase + 32 + j > pos) r1[j] = 0xff800000u;
-          }
-        }
-        float mx = -INFINITY;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) mx = fmaxf(mx, fmaxf(__uint_as_float(r0[j]), __uint_as_float(r1[j])));
-        mx *= scale;
+        const float mx = fmaxf(mxp, exch[(half ^ 1) * 128 + row]) * scale;   // the same in both threads of the row
         // Reference maximum: follows the row maximum only when that outgrows it by 2^kRescaleGap;
         // then O (in TMEM) and the row sum are brought to the new reference. Warp-wide because the
-        // TMEM accesses are.
+        // TMEM accesses are; the two warps that share these rows take the same decision.
         const bool grow = mx > m_ref + kRescaleGap || (m_ref == -INFINITY && mx > -INFINITY);
         if (t == 0) {
           m_ref = mx;
         } else if (__any_sync(0xffffffffu, grow)) {
           const float alpha = grow ? (m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - mx)) : 1.f;
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             uint32_t ov[32];
-            tmem_ld_32x32b_x32(t_lane + 64 + c * 32, ov);
+            tmem_ld_32x32b_x32(t_o + c * 32, ov);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * alpha);
-            tmem_st_32x32b_x32(t_lane + 64 + c * 32, ov);
+            tmem_st_32x32b_x32(t_o + c * 32, ov);
           }
           tmem_st_wait();
           l *= alpha;
@@ -263,19 +270,15 @@ attn_prefill_tc_kernel(nfk_attn_params p) {
         const uint32_t prow = sb + P_OFF;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          uint32_t w0[4], w1[4];
+          uint32_t w0[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float x0 = fast_exp2(fmaf(__uint_as_float(r0[c * 8 + 2 * e]), scale, -ms));
             const float x1 = fast_exp2(fmaf(__uint_as_float(r0[c * 8 + 2 * e + 1]), scale, -ms));
-            const float y0 = fast_exp2(fmaf(__uint_as_float(r1[c * 8 + 2 * e]), scale, -ms));
-            const float y1 = fast_exp2(fmaf(__uint_as_float(r1[c * 8 + 2 * e + 1]), scale, -ms));
-            rs += (x0 + x1) + (y0 + y1);
+            rs += x0 + x1;
             w0[e] = pack_bf16x2(x0, x1);
-            w1[e] = pack_bf16x2(y0, y1);
           }
-          st_shared_v4(prow + sw128(row, c), w0[0], w0[1], w0[2], w0[3]);          // tokens 8c .. 8c+7
-          st_shared_v4(prow + sw128(row, 4 + c), w1[0], w1[1], w1[2], w1[3]);      // tokens 32+8c ..
+          st_shared_v4(prow + sw128(row, half * 4 + c), w0[0], w0[1], w0[2], w0[3]);   // tokens 32*half + 8c ..
         }
         l += rs;
       }
@@ -305,12 +308,15 @@ attn_prefill_tc_kernel(nfk_attn_params p) {
       }
       ph_o ^= 1;
       tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = outp + (static_cast<long long>(tok0 + tl) * p.q_heads + kvh * group + hh) * HD;
+      exch[half * 128 + row] = l;
+      __syncthreads();
+      const float lsum = l + exch[(half ^ 1) * 128 + row];
+      const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+      __nv_bfloat16* dst = outp + (static_cast<long long>(tok0 + tl) * p.q_heads + kvh * group + hh) * HD + half * 64;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(t_lane + 64 + c * 32, r);
+        tmem_ld_32x32b_x32(t_o + c * 32, r);
         tmem_ld_wait();
         if (row_valid) {
 #pragma unroll
@@ -326,7 +332,7 @@ attn_prefill_tc_kernel(nfk_attn_params p) {
       }
       tc_fence_before();
     }
-    __syncthreads();   // Q, S and O are rewritten by the next item
+    __syncthreads();   // Q, S, O and the exchange words are rewritten by the next item
     if (*abort_flag) alive = false;
   }
 
