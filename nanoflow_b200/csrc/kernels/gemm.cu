@@ -104,6 +104,11 @@ struct DevParams {
   // stream-K tail (see Walk): tiles from sk_tiles_dp on are cut into k-block ranges of sk_q
   float* sk_partial;          // fp32 [tile][piece][CTA of pair][rows per CTA][bn]
   int sk_tiles_dp, sk_q, sk_max_pieces;
+  // RMSNorm of the result rows, fused into the split-K reduce pass
+  const __nv_bfloat16* norm_w;
+  __nv_bfloat16* norm_out;
+  long long norm_ld;
+  float norm_eps;
   // reduce-scatter epilogue (EPI == 2)
   char* rs_heap[8];
   int rs_rank, rs_nranks, rs_rows_cap, rs_epoch;
@@ -679,6 +684,94 @@ splitk_reduce_kernel(DevParams p) {
   }
 }
 
+// Split-K second pass with the RMSNorm of the result folded in: one CTA per row (N <= 16384), every
+// thread keeps its columns of the row in registers, so the norm costs one block reduction and one
+// more store instead of a kernel that reads the row back.
+constexpr int kRowVec = 8;   // 8-column groups per thread: 8 * 8 * 256 threads = 16384 columns
+__global__ void __launch_bounds__(256)
+splitk_reduce_norm_kernel(DevParams p) {
+  __shared__ float red[8];
+  const int nvec = p.N >> 3;
+  const long long slab = static_cast<long long>(p.M) * p.N;
+  for (int row = blockIdx.x; row < p.M; row += gridDim.x) {
+    float v[kRowVec][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < kRowVec; ++i) {
+      const int vi = threadIdx.x + i * 256;
+      if (vi < nvec) {
+        const int col = vi * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+        for (int sidx = 0; sidx < p.split_k; ++sidx) {
+          const float4* src = reinterpret_cast<const float4*>(p.partial + sidx * slab + static_cast<long long>(row) * p.N + col);
+          const float4 a = src[0], b = src[1];
+          v[i][0] += a.x; v[i][1] += a.y; v[i][2] += a.z; v[i][3] += a.w;
+          v[i][4] += b.x; v[i][5] += b.y; v[i][6] += b.z; v[i][7] += b.w;
+        }
+        if (p.bias != nullptr) {
+          const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+          const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = unpack_bf16x2(bw[j]);
+            v[i][2 * j] += f.x;
+            v[i][2 * j + 1] += f.y;
+          }
+        }
+        if (p.C != nullptr) {
+          const uint4 cv = *reinterpret_cast<const uint4*>(p.C + static_cast<long long>(row) * p.ldc + col);
+          const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = unpack_bf16x2(cw[j]);
+            v[i][2 * j] += p.beta * f.x;
+            v[i][2 * j + 1] += p.beta * f.y;
+          }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(v[i][0], v[i][1]);
+        o.y = pack_bf16x2(v[i][2], v[i][3]);
+        o.z = pack_bf16x2(v[i][4], v[i][5]);
+        o.w = pack_bf16x2(v[i][6], v[i][7]);
+        *reinterpret_cast<uint4*>(p.D + static_cast<long long>(row) * p.ldd + col) = o;
+        // normalise what was stored (bf16-rounded), as the standalone norm kernel would read it
+        const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(ow[j]);
+          v[i][2 * j] = f.x;
+          v[i][2 * j + 1] = f.y;
+          ss += f.x * f.x + f.y * f.y;
+        }
+      }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = (threadIdx.x & 31) < 8 ? red[threadIdx.x & 31] : 0.f;
+    tot = warp_sum(tot);
+    __syncthreads();
+    const float inv = rsqrtf(tot / static_cast<float>(p.N) + p.norm_eps);
+#pragma unroll
+    for (int i = 0; i < kRowVec; ++i) {
+      const int vi = threadIdx.x + i * 256;
+      if (vi < nvec) {
+        const uint4 ww = *reinterpret_cast<const uint4*>(p.norm_w + vi * 8);
+        const uint32_t wv[4] = {ww.x, ww.y, ww.z, ww.w};
+        uint32_t ov[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 g = unpack_bf16x2(wv[j]);
+          ov[j] = pack_bf16x2(v[i][2 * j] * inv * g.x, v[i][2 * j + 1] * inv * g.y);
+        }
+        *reinterpret_cast<uint4*>(p.norm_out + static_cast<long long>(row) * p.norm_ld + vi * 8) =
+            make_uint4(ov[0], ov[1], ov[2], ov[3]);
+      }
+    }
+  }
+}
+
 // Stream-K tail, second pass: for every tile of the tail region that was cut into pieces, add the
 // pieces' fp32 partial sums and apply the epilogue. One thread per 8 output columns of a row; the
 // loads of the pieces are independent, so many are in flight per thread.
@@ -911,12 +1004,27 @@ int launch(const nfk_gemm_params& g, int bn, int split_k, bool stream_k, cudaStr
     sk_fixup_kernel<EPI == 1 ? 1 : 0><<<static_cast<int>(blocks), 256, 0, stream>>>(p, f);
     if (cudaGetLastError() != cudaSuccess) return NF_ERR_CUDA;
   }
+  p.norm_w = reinterpret_cast<const __nv_bfloat16*>(g.norm_w);
+  p.norm_out = reinterpret_cast<__nv_bfloat16*>(g.norm_out);
+  p.norm_ld = g.norm_ld;
+  p.norm_eps = g.norm_eps;
+  const bool want_norm = EPI == 0 && g.norm_w != nullptr;
+  if (split_k > 1 && want_norm && g.N <= kRowVec * 8 * 256) {
+    const int blocks = g.M < 16 * sm_count() ? g.M : 16 * sm_count();
+    splitk_reduce_norm_kernel<<<blocks, 256, 0, stream>>>(p);
+    return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
+  }
   if (split_k > 1) {
     const long long total = static_cast<long long>(g.M) * (g.N >> 3);
     long long blocks = (total + 255) / 256;
     if (blocks > 4ll * sm_count()) blocks = 4ll * sm_count();
     splitk_reduce_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(p);
     if (cudaGetLastError() != cudaSuccess) return NF_ERR_CUDA;
+  }
+  if (want_norm) {
+    // the result rows are complete in D (contiguous rows required): a plain norm launch follows
+    if (g.ldd != g.N || g.norm_ld != g.N) return NF_ERR_UNSUPPORTED;
+    return nfk_rmsnorm(g.norm_out, g.D, g.norm_w, g.M, g.N, g.norm_eps, stream);
   }
   return NF_OK;
 }

@@ -47,6 +47,13 @@ typedef struct nfk_gemm_params {
   int smem_budget_kb;  // 0 = all 227 KB; smaller leaves shared memory for a kernel meant to share the SM
   int cta_group;       // 0 = let the cost model decide; 1 = one CTA per tile; 2 = a CTA pair per 256-row tile
   int stream_k;        // tail wave cut into k ranges: 0 = cost model (off when the tile shape is pinned), 1 = on, 2 = off
+  // Optional RMSNorm of the result rows: norm_out[M, N] = RMSNorm(D) * norm_w (what the next layer's
+  // first GEMM reads). With split-K the reduce pass produces it from the rows it already holds;
+  // otherwise the launcher adds a norm launch after the GEMM. Linear epilogue only.
+  const void* norm_w;   // [N] bf16, null = no norm
+  void* norm_out;       // [M, norm_ld] bf16
+  long long norm_ld;
+  float norm_eps;
 } nfk_gemm_params;
 
 int nfk_gemm_bf16(const nfk_gemm_params* p, cudaStream_t stream);

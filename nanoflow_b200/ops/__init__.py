@@ -39,7 +39,8 @@ class GemmParams(Structure):
                 ("workspace_bytes", c_longlong),
                 ("rs_heap", c_void_p * 8), ("rs_rank", c_int), ("rs_nranks", c_int), ("rs_slab_off", c_longlong),
                 ("rs_rows_cap", c_int), ("rs_flag_off", c_longlong), ("rs_epoch", c_int), ("smem_budget_kb", c_int),
-                ("cta_group", c_int), ("stream_k", c_int)]
+                ("cta_group", c_int), ("stream_k", c_int),
+                ("norm_w", c_void_p), ("norm_out", c_void_p), ("norm_ld", c_longlong), ("norm_eps", c_float)]
 
 
 class RopeAppendParams(Structure):
@@ -125,8 +126,12 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
          bias: Optional[torch.Tensor] = None, tile_n: int = 0, num_ctas: int = 0,
          status: Optional[torch.Tensor] = None, tile_m: int = 0, split_k: int = 0,
          workspace: Optional[torch.Tensor] = None, smem_budget_kb: int = 0,
-         cta_group: int = 0, stream_k: int = 0) -> torch.Tensor:
+         cta_group: int = 0, stream_k: int = 0, norm_w: Optional[torch.Tensor] = None,
+         norm_out: Optional[torch.Tensor] = None, norm_eps: float = 1e-5) -> torch.Tensor:
     """out[M,N] = a[M,K] @ w[N,K]^T (+ bias) (+ beta * residual). Rows may be strided.
+
+    With ``norm_w`` / ``norm_out`` the call also leaves ``norm_out = RMSNorm(out) * norm_w`` (from the
+    split-K reduce pass when K is split, by a norm launch otherwise).
 
     ``tile_n`` / ``tile_m`` / ``split_k`` pin the kernel shape (0 = let the launcher's cost model
     choose); split-K needs ``workspace`` (any dtype, >= split_k*M*N*4 bytes)."""
@@ -162,6 +167,9 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     p.smem_budget_kb = smem_budget_kb
     p.cta_group = cta_group
     p.stream_k = stream_k
+    if norm_w is not None:
+        _bf16(norm_w, "norm_w"); _bf16(norm_out, "norm_out")
+        p.norm_w, p.norm_out, p.norm_ld, p.norm_eps = _p(norm_w), _p(norm_out), norm_out.stride(0), norm_eps
     _check(lib().nfk_gemm_bf16(byref(p), _stream()), "nfk_gemm_bf16")
     return out
 

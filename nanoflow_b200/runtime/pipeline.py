@@ -156,7 +156,7 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
     cur = 0                                             # which residual buffer holds x
 
     def gemm(name, a, wt, out, k, *, residual=None, beta=1.0, bias=None, swiglu_up=None, deps=(), layer=-1,
-             tile_key=None, rs=None):
+             tile_key=None, rs=None, norm=None):
         p = GemmParams()
         r0 = starts[k]
         p.A, p.B, p.D = _ptr(a, r0), _ptr(wt), (_ptr(out, r0) if out is not None else c_void_p(0))
@@ -166,6 +166,10 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         p.ldc = residual.stride(0) if residual is not None else 0
         p.beta, p.M, p.N, p.K = beta, 0, wt.shape[0], wt.shape[1]
         p.epilogue = 1 if swiglu_up is not None else 0
+        if norm is not None:
+            # RMSNorm of the result rows for the next GEMM, from the same call (see kernels.h)
+            p.norm_w, p.norm_out = _ptr(norm[0]), _ptr(norm[1], r0)
+            p.norm_ld, p.norm_eps = norm[1].stride(0), model.rms_norm_eps
         dyn = [("M", nb_T[k])]
         if rs is not None:
             # fused GEMM -> reduce-scatter: the epilogue pushes partial rows to their owners' slabs
@@ -281,9 +285,13 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
     def o_proj(l, k, lw, dec, pre):
         """O projection -> reduce (+ residual, + fused FFN norm). Returns the op the FFN waits for."""
         if tp == 1:
-            o = gemm(f"L{l}.nb{k}.o", bufs.attn_out, lw.wo, x_res, k, residual=x_res, beta=1.0, deps=[dec, pre],
-                     layer=l, tile_key="o")
-            return norm(f"L{l}.nb{k}.ln_ffn", x_res, lw.ln_ffn, bufs.h, k, [o], l)
+            if not eng.fuse_gemm_norm:
+                o = gemm(f"L{l}.nb{k}.o", bufs.attn_out, lw.wo, x_res, k, residual=x_res, beta=1.0, deps=[dec, pre],
+                         layer=l, tile_key="o")
+                return norm(f"L{l}.nb{k}.ln_ffn", x_res, lw.ln_ffn, bufs.h, k, [o], l)
+            # the FFN's input norm comes out of the same call (fused into the split-K reduce when K is split)
+            return gemm(f"L{l}.nb{k}.o", bufs.attn_out, lw.wo, x_res, k, residual=x_res, beta=1.0, deps=[dec, pre],
+                        layer=l, tile_key="o", norm=(lw.ln_ffn, bufs.h))
         slab = rs_slot(k) if fuse_rs else None
         o = gemm(f"L{l}.nb{k}.o", bufs.attn_out, lw.wo, None if fuse_rs else part, k,
                  deps=[dec, pre, last_x_writer[k]], layer=l, tile_key="o", rs=slab)
@@ -298,9 +306,14 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         gu = gemm(f"L{l}.nb{k}.gate_up", bufs.h, lw.wg, bufs.act, k, swiglu_up=lw.wu, deps=[n2], layer=l,
                   tile_key="gate_up")
         if tp == 1:
+            # the next layer's attention norm comes out of the same call (not after the last layer:
+            # the final norm runs on the sampled rows only)
+            nxt1 = None if (l + 1 >= model.run_layers or not eng.fuse_gemm_norm) else \
+                (w.layers[(l + 1) % model.num_layers].ln_attn, bufs.h)
             d = gemm(f"L{l}.nb{k}.down", bufs.act, lw.wd, x_res, k, residual=x_res, beta=1.0, deps=[gu], layer=l,
-                     tile_key="down")
+                     tile_key="down", norm=nxt1)
             last_x_writer[k] = d
+            h_normed[k] = d if nxt1 is not None else None
             return
         last = l + 1 >= model.run_layers
         # the last layer's sum must reach every rank in full (sampling reads arbitrary rows), which

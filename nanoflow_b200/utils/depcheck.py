@@ -84,6 +84,8 @@ def graph_access(graph: OpGraph, nano_starts: List[int], nano_sizes: List[int], 
                 add(writes, rng(p.D, rows, p.ldd, p.N))
             if p.workspace:
                 add(writes, (int(p.workspace), int(p.workspace) + int(p.workspace_bytes)))
+            if p.norm_w:
+                add(writes, rng(p.norm_out, rows, p.norm_ld, p.N))
         elif isinstance(p, G.NormParams):
             add(reads, rng(p.x, cap, p.cols, p.cols))
             add(writes, rng(p.out, cap, p.cols, p.cols))

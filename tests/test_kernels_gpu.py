@@ -210,6 +210,29 @@ def test_gemm_cta_pair_rejects_multi_tile_ctas():
         ops.gemm(a, w, tile_m=2, tile_n=128, cta_group=2)
 
 
+@pytest.mark.parametrize("M,N,K,kw", [
+    (256, 8192, 1024, dict(split_k=4, tile_m=2, tile_n=256)),       # norm out of the split-K reduce pass
+    (100, 1024, 2048, dict(split_k=3, tile_m=1, tile_n=128)),
+    (256, 4096, 8192, dict()),                                       # the cost model's shape
+    (1000, 1024, 512, dict(split_k=1, tile_m=1, tile_n=256)),       # not split: norm launch after the GEMM
+    (512, 2048, 1024, dict(cta_group=2, tile_m=1, tile_n=256, stream_k=1)),
+])
+def test_gemm_with_rmsnorm_of_result(M, N, K, kw):
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    nw = 1.0 + 0.1 * torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    ws = torch.zeros(64 << 20, device="cuda", dtype=torch.float32)
+    normed = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    st = ops.new_status()
+    out = ops.gemm(a, w, residual=res, beta=1.0, workspace=ws, status=st, norm_w=nw, norm_out=normed, norm_eps=1e-5,
+                   **kw)
+    ops.check_status(st, "gemm")
+    _close(out, ref.gemm(a, w, res, 1.0), atol=3e-2 * math.sqrt(K / 64), rtol=2e-2)
+    # the norm is taken on the stored (bf16) rows, as a separate norm kernel would
+    _close(normed, ref.rmsnorm(out, nw, 1e-5), atol=2e-2, rtol=2e-2)
+
+
 def test_gemm_empty_and_bad_args():
     a = torch.randn(0, 64, device="cuda", dtype=torch.bfloat16)
     w = torch.randn(128, 64, device="cuda", dtype=torch.bfloat16)
