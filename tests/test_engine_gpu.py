@@ -75,6 +75,34 @@ def test_engine_cuda_graph_executor(pipeline_type, nano):
     _run(pipeline_type, nano, "graph")
 
 
+def test_virtual_tensor_parallel_rank_runs_alone():
+    """One GPU runs rank 0's share of a two-way tensor-parallel job with the collectives reduced to
+    their local part (the reference's vnranks aid): shapes, nano-batch overlap and the fused
+    all-reduce + norm path are exercised without a second GPU; tokens are not meaningful."""
+    from nanoflow_b200.parallel.collectives import TpCollectives
+    from nanoflow_b200.runtime.engine import Engine
+
+    gbs = 48
+    cfg = builtin_config("tiny", gpu_num=2, global_batch_size=gbs, pipeline_type="PLLM", nanobatch_sizes=[16, 32])
+    cfg.engine.max_batch_size = gbs
+    fw = random_full_weights(cfg.model, seed=0, std=0.05)
+    coll = TpCollectives(0, 1, torch.device("cuda", 0), heap_bytes=64 << 20)
+    eng = Engine(cfg, shard_weights(fw, cfg.model, 0, 2, device="cuda"), collectives=coll, num_pages=64)
+    rm = RequestManager(vocab_size=1024, random_ids=True)
+    for _ in range(4):
+        rm.add_request(32, 8, 0.0)
+    rm.finalize_stats()
+    pool = DistKVPool(2, 2, 64, 64, 16, 2)
+    sch = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=gbs,
+                    nanobatch_sizes=cfg.engine.resolved_nanobatches(), average_prefill_length=32,
+                    average_decode_length=8, group_size=2)
+    st = ServingLoop(eng, sch, rm, est_cycle_time=1.0).run()
+    eng.check_status()
+    eng.finalize()
+    assert len(st.retired) == 4 and all(len(r.output) == 8 for r in st.retired)
+    assert all(0 <= t < 1024 for r in st.retired for t in r.output)
+
+
 def test_kv_offload_and_restore():
     """PLLM_OFFLOAD: pages of retired requests reach pinned host memory layer by layer, match the
     oracle's rotated K / V, and can be scattered back into fresh pages."""
