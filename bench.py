@@ -33,7 +33,7 @@ import sys
 import threading
 import time
 
-REF_UNAVAILABLE = ("reference is not installable or buildable offline: /root/reference has no setup.py/pyproject "
+REF_UNAVAILABLE = ("reference is not installable or buildable offline: its checkout has no setup.py/pyproject "
                    "(pip: 'Neither setup.py nor pyproject.toml found'); its CMake build needs the empty "
                    "3rdparty submodules (cutlass, flashinfer, mscclpp, spdlog) and targets sm_80 only")
 
