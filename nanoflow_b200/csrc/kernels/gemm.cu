@@ -1124,8 +1124,82 @@ Shape choose_shape(const nfk_gemm_params& g, bool swiglu) {
   return best_tail_cost < 0.88 * best_cost ? best_tail : best;
 }
 
+// Shape of this call: the cost model's, or the caller's pinned one, checked against what is built.
+int resolve_shape(const nfk_gemm_params& gp, bool swiglu, bool rs, Shape& s) {
+  const nfk_gemm_params* g = &gp;
+  s = choose_shape(*g, swiglu);
+  if (rs) s.split_k = 1;   // partial tiles go straight to their owners: no K split
+  if (g->tile_n != 0 || g->tile_m != 0) {
+    // pinned tile shape: fill in the other dimension with its default, split only on request
+    s.bn = g->tile_n != 0 ? g->tile_n : 256;
+    s.mt = g->tile_m != 0 ? g->tile_m : 1;
+    s.split_k = 1;
+    s.cg = g->cta_group == 2 ? 2 : 1;
+    s.stream_k = false;
+  }
+  if (g->stream_k == 1) s.stream_k = true;
+  if (g->stream_k == 2 || s.split_k != 1) s.stream_k = false;
+  if (s.cg == 2 && s.mt != 1) return NF_ERR_UNSUPPORTED;
+  if (g->split_k != 0) s.split_k = g->split_k;
+  if (s.split_k < 1 || s.split_k > 16) return NF_ERR_BAD_ARG;
+  if (s.split_k > 1) {
+    if (swiglu || g->workspace == nullptr ||
+        static_cast<long long>(s.split_k) * g->M * g->N * 4 > g->workspace_bytes)
+      return NF_ERR_BAD_ARG;
+  }
+  if (s.bn < 32 || s.bn > 256 || s.bn % 32 != 0 || (s.mt != 1 && s.mt != 2 && s.mt != 4) || s.mt * s.bn > 512)
+    return NF_ERR_UNSUPPORTED;
+  if (swiglu && (s.bn / 2) % 16 != 0) return NF_ERR_UNSUPPORTED;
+  return NF_OK;
+}
+
 }  // namespace
 }  // namespace nf
+
+// What nfk_gemm_bf16 would launch for these parameters, without launching: tile shape, number of
+// tiles and workers, and the stream-K tail (first tile of the tail region, k-blocks per worker, most
+// pieces a tile can be cut into). Needs no GPU (the SM count falls back to 148), so planners and
+// tests can check the work distribution on any machine.
+extern "C" int nfk_gemm_describe(const nfk_gemm_params* g, nfk_gemm_plan* out) {
+  using namespace nf;
+  if (g == nullptr || out == nullptr || g->M <= 0 || g->N <= 0 || g->K <= 0) return NF_ERR_BAD_ARG;
+  const bool swiglu = g->epilogue == NFK_EPI_SWIGLU, rs = g->epilogue == NFK_EPI_REDUCE_SCATTER;
+  Shape s;
+  const int rc = resolve_shape(*g, swiglu, rs, s);
+  if (rc != NF_OK) return rc;
+  int budget = g->smem_budget_kb > 0 ? g->smem_budget_kb * 1024 : kSmemMax;
+  if (budget > kSmemMax) budget = kSmemMax;
+  const Geom geo = make_geom(s.bn, s.mt, swiglu, budget, s.cg);
+  if (geo.stages < 2) return NF_ERR_BAD_ARG;
+  const int m_tiles = (g->M + BM - 1) / BM;
+  const int m_groups = (m_tiles + s.mt * s.cg - 1) / (s.mt * s.cg);
+  const int n_blocks = (g->N + geo.out_bn - 1) / geo.out_bn;
+  const int tiles = m_groups * n_blocks;
+  int workers = (g->num_ctas > 0 ? g->num_ctas : sm_count()) / s.cg;
+  if (workers > sm_count() / s.cg) workers = sm_count() / s.cg;
+  if (workers < 1) workers = 1;
+  SkPlan sk{tiles, 0, 0, 0};
+  if (s.stream_k && s.split_k == 1 && !rs && g->workspace != nullptr) {
+    sk = plan_stream_k(tiles, workers, (g->K + BK - 1) / BK);
+    const long long need = static_cast<long long>(sk.rest) * sk.max_pieces * s.cg * s.mt * BM * s.bn * 4;
+    if (sk.q > 0 && need > g->workspace_bytes) sk = SkPlan{tiles, 0, 0, 0};
+  }
+  if (sk.q == 0 && workers > tiles * s.split_k) workers = tiles * s.split_k;
+  out->tile_n = s.bn;
+  out->tile_m = s.mt;
+  out->cta_group = s.cg;
+  out->split_k = s.split_k;
+  out->stream_k = sk.q > 0 ? 1 : 0;
+  out->tiles = tiles;
+  out->workers = workers;
+  out->num_kb = (g->K + BK - 1) / BK;
+  out->tail_first_tile = sk.tiles_dp;
+  out->tail_range_kb = sk.q;
+  out->tail_max_pieces = sk.max_pieces;
+  out->stages = geo.stages;
+  out->smem_bytes = geo.smem_bytes;
+  return NF_OK;
+}
 
 extern "C" int nfk_gemm_bf16(const nfk_gemm_params* g, cudaStream_t stream) {
   using namespace nf;
@@ -1163,28 +1237,9 @@ extern "C" int nfk_gemm_bf16(const nfk_gemm_params* g, cudaStream_t stream) {
       if (g->rs_heap[r] == nullptr) return NF_ERR_BAD_ARG;
   }
 
-  Shape s = choose_shape(*g, swiglu);
-  if (rs) s.split_k = 1;   // partial tiles go straight to their owners: no K split
-  if (g->tile_n != 0 || g->tile_m != 0) {
-    // pinned tile shape: fill in the other dimension with its default, split only on request
-    s.bn = g->tile_n != 0 ? g->tile_n : 256;
-    s.mt = g->tile_m != 0 ? g->tile_m : 1;
-    s.split_k = 1;
-    s.cg = g->cta_group == 2 ? 2 : 1;
-    s.stream_k = false;
-  }
-  if (g->stream_k == 1) s.stream_k = true;
-  if (g->stream_k == 2 || s.split_k != 1) s.stream_k = false;
-  if (s.cg == 2 && s.mt != 1) return NF_ERR_UNSUPPORTED;
-  if (g->split_k != 0) s.split_k = g->split_k;
-  if (s.split_k < 1 || s.split_k > 16) return NF_ERR_BAD_ARG;
-  if (s.split_k > 1) {
-    if (swiglu || g->workspace == nullptr ||
-        static_cast<long long>(s.split_k) * g->M * g->N * 4 > g->workspace_bytes)
-      return NF_ERR_BAD_ARG;
-  }
-  if (s.bn < 32 || s.bn > 256 || s.bn % 32 != 0 || (s.mt != 1 && s.mt != 2 && s.mt != 4) || s.mt * s.bn > 512)
-    return NF_ERR_UNSUPPORTED;
+  Shape s;
+  const int rcs = resolve_shape(*g, swiglu, rs, s);
+  if (rcs != NF_OK) return rcs;
   if (swiglu) {
     if ((s.bn / 2) % 16 != 0) return NF_ERR_UNSUPPORTED;
     return launch_mt<1>(*g, s.bn, s.mt, s.cg, 1, s.stream_k, stream);

@@ -58,6 +58,14 @@ typedef struct nfk_gemm_params {
 
 int nfk_gemm_bf16(const nfk_gemm_params* p, cudaStream_t stream);
 
+typedef struct nfk_gemm_plan {
+  int tile_n, tile_m, cta_group, split_k, stream_k;
+  int tiles, workers, num_kb;          // output tiles, CTAs (or CTA pairs), 64-wide k-blocks
+  int tail_first_tile, tail_range_kb, tail_max_pieces;   // stream-K tail (tail_range_kb 0 = none)
+  int stages, smem_bytes;
+} nfk_gemm_plan;
+int nfk_gemm_describe(const nfk_gemm_params* p, nfk_gemm_plan* out);
+
 // ------------------------------------------------------------------------------------------------
 // Elementwise / normalisation / gather kernels (elementwise.cu)
 // ------------------------------------------------------------------------------------------------

@@ -174,6 +174,30 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     return out
 
 
+class GemmPlan(Structure):
+    _fields_ = [("tile_n", c_int), ("tile_m", c_int), ("cta_group", c_int), ("split_k", c_int), ("stream_k", c_int),
+                ("tiles", c_int), ("workers", c_int), ("num_kb", c_int),
+                ("tail_first_tile", c_int), ("tail_range_kb", c_int), ("tail_max_pieces", c_int),
+                ("stages", c_int), ("smem_bytes", c_int)]
+
+
+def gemm_plan(M: int, N: int, K: int, *, swiglu: bool = False, tile_n: int = 0, tile_m: int = 0, cta_group: int = 0,
+              split_k: int = 0, stream_k: int = 0, num_ctas: int = 0, workspace_bytes: int = 0,
+              smem_budget_kb: int = 0) -> dict:
+    """What ``gemm`` / ``gemm_swiglu`` would launch for these sizes (tile shape, tiles, workers, stream-K
+    tail) without launching anything; works without a GPU. ``workspace_bytes`` > 0 stands for a caller
+    that passes a workspace of that size."""
+    p = GemmParams()
+    p.M, p.N, p.K = M, N, K
+    p.epilogue, p.tile_n, p.tile_m, p.cta_group = (1 if swiglu else 0), tile_n, tile_m, cta_group
+    p.split_k, p.stream_k, p.num_ctas, p.smem_budget_kb = split_k, stream_k, num_ctas, smem_budget_kb
+    if workspace_bytes > 0:
+        p.workspace, p.workspace_bytes = c_void_p(256), workspace_bytes    # never dereferenced by the planner
+    out = GemmPlan()
+    _check(lib().nfk_gemm_describe(byref(p), byref(out)), "nfk_gemm_describe")
+    return {f: getattr(out, f) for f, _ in GemmPlan._fields_}
+
+
 def gemm_swiglu(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, *,
                 out: Optional[torch.Tensor] = None, tile_n: int = 0, num_ctas: int = 0,
                 status: Optional[torch.Tensor] = None, tile_m: int = 0, split_k: int = 0,

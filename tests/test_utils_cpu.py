@@ -57,3 +57,56 @@ def test_autotune_candidates():
             assert not (x["cta_group"] == 2 and (x["tile_m"] != 1 or M <= 128))
             assert not (sw and x["split_k"] != 1)
             assert not (x["split_k"] > 1 and x["stream_k"] == 1)
+
+
+def _walk(w, W, tiles, num_kb, split_k, tail_first, q):
+    """The kernel's work distribution (csrc/kernels/gemm.cu, struct Walk) restated: worker w's units."""
+    out = []
+    dp_tiles = tail_first if q > 0 else tiles
+    units, kb_per = dp_tiles * split_k, -(-num_kb // split_k)
+    cur = w
+    while cur < units:
+        ks = cur // dp_tiles
+        kb0 = min(num_kb, ks * kb_per)
+        out.append((cur % dp_tiles, kb0, min(num_kb, kb0 + kb_per), 1))
+        cur += W
+    if q > 0:
+        total = (tiles - tail_first) * num_kb
+        g = min(w * q, total)
+        g_end = min(g + q, total)
+        while g < g_end:
+            t, kb0 = divmod(g, num_kb)
+            n = min(num_kb - kb0, g_end - g)
+            first, last = (t * num_kb) // q, (min((t + 1) * num_kb, total) - 1) // q
+            out.append((tail_first + t, kb0, kb0 + n, last - first + 1))
+            g += n
+    return out
+
+
+def test_gemm_plan_covers_every_tile_once():
+    """The launcher's plan (shape choice + stream-K tail), asked for without a GPU, tiles the whole
+    problem: every (tile, k-block) belongs to exactly one worker and no tile is cut into more pieces
+    than the partial-sum slots the plan reserves."""
+    from nanoflow_b200 import ops
+
+    cases = [dict(M=256, N=8192, K=8192), dict(M=4096, N=1280, K=8192), dict(M=3712, N=8192, K=3584),
+             dict(M=2048, N=28672, K=8192, swiglu=True), dict(M=3712, N=1280, K=1024, cta_group=2, tile_n=256,
+                                                                tile_m=1, stream_k=1),
+             dict(M=300, N=4096, K=1536, tile_m=4, tile_n=128, stream_k=1), dict(M=1000, N=3000, K=1024, num_ctas=37),
+             dict(M=256, N=8192, K=2048, split_k=4, tile_m=2, tile_n=256), dict(M=130, N=40, K=64)]
+    for c in cases:
+        pl = ops.gemm_plan(workspace_bytes=256 << 20, **c)
+        assert pl["stages"] >= 2 and pl["smem_bytes"] <= 227 * 1024
+        assert 1 <= pl["workers"] <= 148 // pl["cta_group"]
+        seen = {}
+        for w in range(pl["workers"]):
+            for tile, kb0, kb1, pieces in _walk(w, pl["workers"], pl["tiles"], pl["num_kb"], pl["split_k"],
+                                                pl["tail_first_tile"], pl["tail_range_kb"]):
+                assert kb1 > kb0 or pl["split_k"] > 1
+                assert pieces <= max(1, pl["tail_max_pieces"])
+                seen.setdefault(tile, []).append((kb0, kb1))
+        assert sorted(seen) == list(range(pl["tiles"])), c
+        for tile, segs in seen.items():
+            segs = sorted(s for s in segs if s[1] > s[0])
+            assert segs[0][0] == 0 and segs[-1][1] == pl["num_kb"]
+            assert all(a[1] == b[0] for a, b in zip(segs, segs[1:])), (c, tile, segs)
