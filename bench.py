@@ -111,6 +111,8 @@ def main():
     ap.add_argument("--fuse-rs", action="store_true", help="K-split GEMMs push their partial rows to the owners "
                     "from the GEMM epilogue (fused GEMM -> reduce-scatter) instead of the collective pulling them")
     ap.add_argument("--no-fuse-norm", action="store_true", help="one GPU: separate RMSNorm launches after O / down")
+    ap.add_argument("--serial-attention", action="store_true",
+                    help="prefill attention after decode attention on one stream instead of beside it")
     ap.add_argument("--virtual-tp", type=int, default=0,
                     help="one GPU runs rank 0's share of a tensor-parallel job of this degree, collectives reduced "
                          "to their local part (development aid; the JSON line is marked invalid)")
@@ -197,6 +199,7 @@ def main():
         cfg.engine.sm_budget["comm"] = args.comm_ctas
     cfg.engine.fuse_gemm_rs = bool(args.fuse_rs)
     cfg.engine.fuse_gemm_norm = not args.no_fuse_norm
+    cfg.engine.prefill_beside_decode = not args.serial_attention
     if args.layers:
         cfg.model.num_layers = args.layers
         cfg.model.run_layers = args.layers

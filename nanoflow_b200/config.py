@@ -153,6 +153,7 @@ class EngineConfig:
     autotune_gemm: bool = True             # time candidate GEMM shapes at start-up and pin the fastest per op
     prefill_tc: bool = True                # head_dim 128: prefill attention on tcgen05 (else the mma.sync kernel)
     fuse_gemm_norm: bool = True            # one GPU: the RMSNorm after O / down comes out of the GEMM call
+    prefill_beside_decode: bool = True     # prefill attention on a stream of its own, beside the decode kernel
     gemm_shapes: Dict[str, Dict[str, int]] = field(default_factory=dict)   # "<op>.nb<k>" -> pinned launcher arguments
     decode_chunk_pages: int = 0            # 0 = choose per iteration
     use_cuda_graph: bool = False
@@ -233,6 +234,7 @@ def parse_config(raw: Dict[str, Any], *, tp: Optional[int] = None) -> NanoflowCo
         autotune_gemm=bool(pc.get("autotune_gemm", True)),
         prefill_tc=bool(pc.get("prefill_tc", True)),
         fuse_gemm_norm=bool(pc.get("fuse_gemm_norm", True)),
+        prefill_beside_decode=bool(pc.get("prefill_beside_decode", True)),
         model_id=sc.get("model", ""),
         weight_path=sc.get("weight_path", ""),
         hf_path=sc.get("hf_path", ""),

@@ -8,8 +8,8 @@
 // the GPU issues the iteration, so the Python scheduler forms the next batch while this one is
 // being launched; `wait(ticket)` blocks until the GPU has finished that iteration.
 //
-// Dependencies across streams are CUDA events; ops on one stream rely on stream order. The five
-// stream classes (gemm, attn, net, other, copy) fork from and join back into the caller's main
+// Dependencies across streams are CUDA events; ops on one stream rely on stream order. The six
+// stream classes (gemm, attn, net, other, copy, attn2) fork from and join back into the caller's main
 // stream, so consecutive iterations stay ordered and torch work queued on that stream composes.
 //
 // Graph mode (set_graph_mode): after two plain iterations the same issue sequence is recorded by
@@ -41,7 +41,7 @@ namespace py = pybind11;
 
 namespace {
 
-constexpr int kNumStreamClasses = 5;
+constexpr int kNumStreamClasses = 6;
 constexpr int kTickets = 8;
 
 using LaunchFn = int (*)(const void*, cudaStream_t);
@@ -305,7 +305,7 @@ class Executor {
       check(cudaEventRecord(fork_, origin), "cudaEventRecord(fork)");
       for (int i = 0; i < kNumStreamClasses; ++i) check(cudaStreamWaitEvent(streams_[i], fork_, 0), "wait(fork)");
     }
-    bool used[kNumStreamClasses] = {false, false, false, false, false};
+    bool used[kNumStreamClasses] = {};
     for (auto& op : ops_) {
       cudaStream_t st = single_stream_ ? origin : streams_[op.stream_class];
       used[op.stream_class] = true;

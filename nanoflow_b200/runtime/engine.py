@@ -205,7 +205,7 @@ class Engine:
 
     def _make_executor(self, kind: str) -> None:
         self.native = None
-        single = not self.eng.overlap
+        single = not (self.eng.overlap or any(op.stream != "gemm" for op in self.graph.ops))
         if kind in ("auto", "native", "graph"):
             try:
                 from .native import NativeExecutor

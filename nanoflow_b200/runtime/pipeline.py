@@ -119,6 +119,12 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         S = lambda cls: "net" if cls == "net" else "gemm"
     else:
         S = lambda cls: cls
+    # Prefill and decode attention of one nano-batch touch different requests. The decode kernel's work
+    # items rarely fill its last round of CTAs, so the prefill kernel, on a stream of its own, runs in
+    # the SMs that round leaves idle. Not under tensor parallelism with overlap: there the next
+    # nano-batch's GEMM is already queued, and a persistent GEMM that finds SMs taken loses more than
+    # the short prefill kernel gains.
+    prefill_stream = "attn2" if (eng.prefill_beside_decode and (tp == 1 or not overlap)) else S("attn")
 
     T_all = g.symbol("T")
     n_sample = g.symbol("n_sample")
@@ -247,7 +253,7 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         pp.items = _ptr(bufs.nano_items[k])
         # head_dim 128: the tcgen05 kernel; other head sizes: the warp-level mma.sync kernel
         pre_kernel = "nfk_attn_prefill_tc" if (hd == 128 and eng.prefill_tc) else "nfk_attn_prefill"
-        pre = g.add(f"L{l}.nb{k}.attn_prefill", pp, S("attn"), deps=[ro] + straddle, kernel=pre_kernel,
+        pre = g.add(f"L{l}.nb{k}.attn_prefill", pp, prefill_stream, deps=[ro] + straddle, kernel=pre_kernel,
                     dyn=[("num_items", nb_items[k])], layer=l, nano=k)
         rope_of[(l, k)] = ro
         return dec, pre

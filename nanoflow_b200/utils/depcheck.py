@@ -105,7 +105,15 @@ def graph_access(graph: OpGraph, nano_starts: List[int], nano_sizes: List[int], 
             r0 = nano_starts[op.nano] if op.nano >= 0 else 0
             w = p.q_heads * p.head_dim
             add(reads, rng(p.q + r0 * w * 2, cap, w, w))
-            add(writes, rng(p.out + r0 * w * 2, cap, w, w))
+            # A nano-batch holds its decode tokens first and its prompt tokens after them, and the two
+            # kernels write only their own tokens' rows. The boundary moves every iteration; the check
+            # stands for it with the middle of the nano-batch, which keeps the two writers disjoint
+            # from each other and both in conflict with every reader of the rows.
+            half = cap // 2
+            if op.kernel == "nfk_attn_decode":
+                add(writes, rng(p.out + r0 * w * 2, half, w, w))
+            else:
+                add(writes, rng(p.out + (r0 + half) * w * 2, cap - half, w, w))
             if kv_pool_bytes:
                 add(reads, (int(p.kv_pool), int(p.kv_pool) + kv_pool_bytes))
         elif isinstance(p, AllReduceParams):

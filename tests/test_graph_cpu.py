@@ -80,3 +80,20 @@ def test_checker_sees_a_missing_dependency():
     victim = next(i for i, op in enumerate(g.ops) if op.name.endswith("attn_decode") and op.stream == "attn")
     g.ops[victim].deps = []
     assert depcheck.check(g, acc)
+
+
+@pytest.mark.parametrize("pipeline_type,tp,nano,beside", [
+    ("NON_OVERLAP_LOCAL", 1, None, True), ("LOCAL", 1, [16, 32], True), ("NON_OVERLAP", 2, None, True),
+    ("PLLM", 2, [16, 32], False)])
+def test_prefill_attention_gets_its_own_stream_where_nothing_else_is_queued(pipeline_type, tp, nano, beside):
+    g, acc, keep = _host_graph(pipeline_type, tp, nano)
+    pre = [i for i, op in enumerate(g.ops) if op.name.endswith("attn_prefill")]
+    dec = [i for i, op in enumerate(g.ops) if op.name.endswith("attn_decode")]
+    assert pre and len(pre) == len(dec)
+    assert all((g.ops[i].stream == "attn2") == beside for i in pre)
+    if beside:
+        hb = g.happens_before()
+        # the two attention kernels of a nano-batch are unordered, everything that reads their rows waits for both
+        assert all(d not in hb[p] and p not in hb[d] for p, d in zip(pre, dec))
+        g.ops[pre[1]].deps = []
+        assert depcheck.check(g, acc)
