@@ -121,10 +121,9 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         S = lambda cls: cls
     # Prefill and decode attention of one nano-batch touch different requests. The decode kernel's work
     # items rarely fill its last round of CTAs, so the prefill kernel, on a stream of its own, runs in
-    # the SMs that round leaves idle. Not under tensor parallelism with overlap: there the next
-    # nano-batch's GEMM is already queued, and a persistent GEMM that finds SMs taken loses more than
-    # the short prefill kernel gains.
-    prefill_stream = "attn2" if (eng.prefill_beside_decode and (tp == 1 or not overlap)) else S("attn")
+    # the SMs that round leaves idle. The O projection, next on the GEMM stream, waits for both, so no
+    # GEMM is ever queued beside the pair.
+    prefill_stream = "attn2" if eng.prefill_beside_decode else S("attn")
 
     T_all = g.symbol("T")
     n_sample = g.symbol("n_sample")

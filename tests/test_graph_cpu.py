@@ -84,8 +84,8 @@ def test_checker_sees_a_missing_dependency():
 
 @pytest.mark.parametrize("pipeline_type,tp,nano,beside", [
     ("NON_OVERLAP_LOCAL", 1, None, True), ("LOCAL", 1, [16, 32], True), ("NON_OVERLAP", 2, None, True),
-    ("PLLM", 2, [16, 32], False)])
-def test_prefill_attention_gets_its_own_stream_where_nothing_else_is_queued(pipeline_type, tp, nano, beside):
+    ("PLLM", 2, [16, 32], True)])
+def test_prefill_attention_gets_its_own_stream(pipeline_type, tp, nano, beside):
     g, acc, keep = _host_graph(pipeline_type, tp, nano)
     pre = [i for i, op in enumerate(g.ops) if op.name.endswith("attn_prefill")]
     dec = [i for i, op in enumerate(g.ops) if op.name.endswith("attn_decode")]
