@@ -90,10 +90,21 @@ class Engine:
             return self.coll.alloc(shape, dtype) if hasattr(self.coll, "alloc") else \
                 torch.zeros(*shape, dtype=dtype, device=dev)
 
-        plain = lambda *shape, dtype=bf: torch.zeros(*shape, dtype=dtype, device=dev)
+        # debug_guards: every local activation buffer sits between guard words that check_status()
+        # compares after the iteration (utils/guards.py)
+        self.guards = None
+        if e.debug_guards:
+            from ..utils.guards import GuardedArena
+            self.guards = GuardedArena(dev)
+
+        def plain(*shape, dtype=bf, name="activation"):
+            if self.guards is not None:
+                return self.guards.zeros(name, shape, dtype)
+            return torch.zeros(*shape, dtype=dtype, device=dev)
+
         # x[0]: residual stream (local). x[1]: under TP the symmetric buffer the K-split GEMMs write
         # their partial products into (peers pull from it); on one GPU it aliases x[0].
-        x0 = plain(T, m.hidden_size)
+        x0 = plain(T, m.hidden_size, name="x")
         x = [x0, alloc(T + 8 * len(self.nano_sizes), m.hidden_size) if weights.tp > 1 else x0]
         self.num_pages = int(num_pages or e.num_pages or self._derive_num_pages(T, B))
         # KV offload: pages of requests retired in an iteration are gathered layer by layer and
@@ -114,12 +125,13 @@ class Engine:
         kv_pool = [torch.zeros(self.num_pages, 2, m.kv_heads_local, e.page_size, m.head_dim, dtype=bf, device=dev)
                    for _ in range(m.run_layers)]
         self.bufs = Buffers(
-            x=x, h=alloc(T, m.hidden_size) if weights.tp > 1 else plain(T, m.hidden_size), qkv=plain(T, m.qkv_size_local), q_rot=plain(T, m.q_size_local),
-            attn_out=plain(T, m.q_size_local), act=plain(T, m.ffn_local),
-            sample_h=plain(B, m.hidden_size), sample_hn=plain(B, m.hidden_size),
-            logits=plain(B, weights.lm_head.shape[0]),
+            x=x, h=alloc(T, m.hidden_size) if weights.tp > 1 else plain(T, m.hidden_size, name="h"),
+            qkv=plain(T, m.qkv_size_local, name="qkv"), q_rot=plain(T, m.q_size_local, name="q_rot"),
+            attn_out=plain(T, m.q_size_local, name="attn_out"), act=plain(T, m.ffn_local, name="act"),
+            sample_h=plain(B, m.hidden_size, name="sample_h"), sample_hn=plain(B, m.hidden_size, name="sample_hn"),
+            logits=plain(B, weights.lm_head.shape[0], name="logits"),
             cand_val=alloc(weights.tp, B, dtype=torch.float32), cand_idx=alloc(weights.tp, B, dtype=torch.int32),
-            sampled=plain(B, dtype=torch.int32), kv_pool=kv_pool,
+            sampled=plain(B, dtype=torch.int32, name="sampled"), kv_pool=kv_pool,
             inv_freq=ref.rope_inv_freq(m.head_dim, m.rope_theta, m.rope_scaling).to(dev),
             status=torch.zeros(1, dtype=torch.int32, device=dev),
             decode_ws=torch.empty(DECODE_SPLIT_ROWS * DECODE_MAX_CHUNKS * (m.head_dim + 2), dtype=torch.float32,
@@ -338,6 +350,13 @@ class Engine:
 
     def check_status(self) -> None:
         ops.check_status(self.bufs.status, "engine iteration")
+        if self.guards is not None:
+            torch.cuda.synchronize(self.device)
+            bad = self.guards.check()
+            if bad:
+                self.guards.restore()
+                raise RuntimeError("write outside an activation buffer: " +
+                                   ", ".join(f"{n} ({side} guard, byte {off})" for n, side, off in bad))
 
     def finalize(self) -> None:
         torch.cuda.synchronize(self.device)

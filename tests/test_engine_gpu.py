@@ -12,12 +12,13 @@ from nanoflow_b200.serving import DistKVPool, RequestManager, Scheduler
 from nanoflow_b200.serving.loop import ServingLoop
 
 
-def _run(pipeline_type, nano, executor, gbs=48):
+def _run(pipeline_type, nano, executor, gbs=48, guards=False):
     from nanoflow_b200.runtime.engine import Engine
 
     cfg = builtin_config("tiny", gpu_num=1, global_batch_size=gbs, pipeline_type=pipeline_type,
                          nanobatch_sizes=nano)
     cfg.engine.max_batch_size = gbs
+    cfg.engine.debug_guards = guards
     fw = random_full_weights(cfg.model, seed=0, std=0.05)
     # the oracle sees the same bf16-rounded weights; only activation rounding differs
     for lay in fw.layers:
@@ -40,6 +41,15 @@ def _run(pipeline_type, nano, executor, gbs=48):
     loop = ServingLoop(eng, sch, rm, est_cycle_time=1.0)
     st = loop.run()
     eng.check_status()
+    if guards:
+        # every activation buffer is fenced and no kernel wrote outside its rows and columns; a byte
+        # changed from the host behind one of them is reported with the buffer's name
+        assert len(eng.guards) >= 9 and not eng.guards.check()
+        raw = eng.bufs.attn_out.view(torch.uint8).view(-1)
+        torch.as_strided(raw, (1,), (1,), raw.storage_offset() + raw.numel() + 3).fill_(0)
+        with pytest.raises(RuntimeError, match="attn_out .rear guard, byte 3"):
+            eng.check_status()
+        eng.check_status()       # guards were restored
     eng.finalize()
     assert len(st.retired) == 4
     exact = 0
@@ -62,6 +72,10 @@ def _run(pipeline_type, nano, executor, gbs=48):
                                                 ("LOCAL", [16, 32])])
 def test_engine_matches_oracle_py_executor(pipeline_type, nano):
     _run(pipeline_type, nano, "python")   # asserts greedy consistency with the oracle
+
+
+def test_engine_keeps_inside_guarded_buffers():
+    _run("LOCAL", [16, 32], "native", guards=True)
 
 
 def test_engine_matches_oracle_native_executor():

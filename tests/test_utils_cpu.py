@@ -110,3 +110,33 @@ def test_gemm_plan_covers_every_tile_once():
             segs = sorted(s for s in segs if s[1] > s[0])
             assert segs[0][0] == 0 and segs[-1][1] == pl["num_kb"]
             assert all(a[1] == b[0] for a, b in zip(segs, segs[1:])), (c, tile, segs)
+
+
+def test_guarded_arena_reports_writes_outside_a_buffer():
+    import torch
+
+    from nanoflow_b200.utils.guards import GUARD_BYTES, GuardedArena
+
+    arena = GuardedArena("cpu")
+    a = arena.zeros("a", (5, 7), torch.bfloat16)        # 70 bytes: the rear guard starts inside the 16-byte padding
+    b = arena.zeros("b", (4,), torch.int32)
+    c = arena.zeros("a", (3,), torch.float32)           # a second buffer of the same name gets a suffix
+    assert a.shape == (5, 7) and a.dtype == torch.bfloat16 and a.is_contiguous() and a.data_ptr() % 16 == 0
+    assert not a.any() and not b.any() and len(arena) == 3
+    a.fill_(1.0); b.fill_(-1); c.fill_(2.0)             # full use of the payloads leaves the guards alone
+    assert arena.check() == []
+    flat = a.view(torch.uint8).view(-1)
+    past = torch.as_strided(flat, (2,), (1,), flat.storage_offset() + flat.numel())   # the two bytes after a's last element
+    past.fill_(0)
+    before = torch.as_strided(b.view(torch.uint8).view(-1), (1,), (1,), GUARD_BYTES - 4)   # 4 bytes before b's first
+    before.fill_(7)
+    assert arena.check() == [("a", "rear", 0), ("b", "front", GUARD_BYTES - 4)]
+    arena.restore()
+    assert arena.check() == []
+    assert (a == 1.0).all() and (b == -1).all() and (c == 2.0).all()
+    try:
+        GuardedArena("cpu", guard_bytes=24)
+    except ValueError:
+        pass
+    else:
+        raise AssertionError("guard size must be a multiple of 16")
