@@ -24,7 +24,11 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#ifdef NF_HOST_CUDA
+#include "host_cuda.h"   // host-only build: the runtime calls are logged instead of made
+#else
 #include <cuda_runtime.h>
+#endif
 
 #include <atomic>
 #include <condition_variable>
@@ -333,6 +337,9 @@ class Executor {
         }
         check(cudaEventRecord(op.t0, st), "record(t0)");
       }
+#ifdef NF_HOST_CUDA
+      host_cuda::note_launch(st, static_cast<int>(&op - ops_.data()), op.params);
+#endif
       const int rc = op.fn(op.params.data(), st);
       if (rc != 0) throw std::runtime_error("op " + op.name + " rejected its arguments (code " + std::to_string(rc) + ")");
       launches_.fetch_add(1);
@@ -376,8 +383,33 @@ class Executor {
 
 }  // namespace
 
-PYBIND11_MODULE(_executor, m) {
+#ifndef NF_EXECUTOR_MODULE
+#define NF_EXECUTOR_MODULE _executor
+#endif
+
+PYBIND11_MODULE(NF_EXECUTOR_MODULE, m) {
   m.doc() = "Native op-graph executor (one worker thread per GPU)";
+#ifdef NF_HOST_CUDA
+  // Host-only build: the log of runtime calls, and a launch function that does nothing.
+  m.attr("host_only") = true;
+  m.def("noop_fn", [] { return reinterpret_cast<uintptr_t>(&host_cuda::noop_launch); });
+  m.def("failing_fn", [] { return reinterpret_cast<uintptr_t>(&host_cuda::failing_launch); });
+  m.def("host_log", [] {
+    std::lock_guard<std::mutex> lk(host_cuda::state().mu);
+    py::list out;
+    for (const auto& r : host_cuda::state().log)
+      out.append(py::make_tuple(r.kind, r.stream, r.event, r.op, r.captured, py::bytes(r.params)));
+    return out;
+  });
+  m.def("host_log_clear", [] {
+    std::lock_guard<std::mutex> lk(host_cuda::state().mu);
+    host_cuda::state().log.clear();
+  });
+  m.def("fail_next_graph_update", [] {
+    std::lock_guard<std::mutex> lk(host_cuda::state().mu);
+    host_cuda::state().fail_next_update = true;
+  });
+#endif
   py::class_<Executor>(m, "Executor")
       .def(py::init<uintptr_t, int, bool, int>(), py::arg("main_stream"), py::arg("device"),
            py::arg("single_stream"), py::arg("num_symbols"))

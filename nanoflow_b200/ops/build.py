@@ -95,9 +95,41 @@ def build_executor(verbose: bool = False) -> Path:
     return out
 
 
+def executor_host_lib_path() -> Path:
+    suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+    return PKG / "runtime" / f"_executor_host{suffix}"
+
+
+def build_executor_host(verbose: bool = False, sanitize: str = "") -> Path:
+    """The executor compiled against ``csrc/executor/host_cuda.h`` instead of the CUDA runtime: the
+    same worker thread, symbol patching, event wiring and graph-mode logic, with every runtime call
+    logged instead of made. Links nothing from CUDA, so it loads and runs on a machine without a GPU.
+    ``sanitize="thread"`` (or ``"address"``) builds an instrumented copy under ``build/<sanitize>/``
+    for a run with the sanitizer's runtime preloaded."""
+    import pybind11
+
+    out = executor_host_lib_path()
+    if sanitize:
+        out = BUILD_DIR / sanitize / out.name
+        out.parent.mkdir(parents=True, exist_ok=True)
+    sources = sorted(EXEC_DIR.glob("*.cpp"))
+    if not sources:
+        return out
+    if _newer(out, sources + list(EXEC_DIR.glob("*.h"))):
+        inc = sysconfig.get_paths()["include"]
+        cmd = ["g++", "-O1", "-g", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden",
+               "-DNF_HOST_CUDA", "-DNF_EXECUTOR_MODULE=_executor_host",
+               "-I", pybind11.get_include(), "-I", inc, "-I", EXEC_DIR, *sources, "-o", out, "-lpthread"]
+        if sanitize:
+            cmd.insert(1, f"-fsanitize={sanitize}")
+        _run(cmd, verbose)
+    return out
+
+
 def build_all(verbose: bool = False) -> None:
     build_kernels(verbose)
     build_executor(verbose)
+    build_executor_host(verbose)
 
 
 if __name__ == "__main__":

@@ -13,19 +13,31 @@ def _load():
     return _executor
 
 
+def load_host_module():
+    """The host-only build of the executor (every CUDA runtime call logged instead of made); built
+    on first use."""
+    from ..ops import build
+    build.build_executor_host()
+    from . import _executor_host  # noqa: WPS433
+    return _executor_host
+
+
 class NativeExecutor:
     def __init__(self, graph: OpGraph, main_stream, single_stream: bool = False, device: int = 0,
-                 use_cuda_graph: bool = False):
-        mod = _load()
-        lib = _ops.lib()
+                 use_cuda_graph: bool = False, host_only: bool = False):
+        """``host_only``: drive the host-only build. No kernel runs; ``self.mod.host_log()`` lists the
+        stream / event / graph calls the executor made (used by the CPU tests of the event wiring)."""
+        mod = load_host_module() if host_only else _load()
+        lib = None if host_only else _ops.lib()
+        self.mod = mod
         self.graph = graph
         self.sym_names: List[str] = [None] * len(graph.symbols)
         for name, idx in graph.symbols.items():
             self.sym_names[idx] = name
-        self.ex = mod.Executor(int(main_stream.cuda_stream), int(device), bool(single_stream),
+        self.ex = mod.Executor(0 if host_only else int(main_stream.cuda_stream), int(device), bool(single_stream),
                                len(self.sym_names))
         for op in graph.ops:
-            fn = ctypes.cast(getattr(lib, op.kernel), ctypes.c_void_p).value
+            fn = mod.noop_fn() if host_only else ctypes.cast(getattr(lib, op.kernel), ctypes.c_void_p).value
             patches = []
             for f, s in op.dyn:
                 desc = getattr(type(op.params), f)

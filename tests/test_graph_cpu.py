@@ -97,3 +97,177 @@ def test_prefill_attention_gets_its_own_stream(pipeline_type, tp, nano, beside):
         assert all(d not in hb[p] and p not in hb[d] for p, d in zip(pre, dec))
         g.ops[pre[1]].deps = []
         assert depcheck.check(g, acc)
+
+
+# ---- the C++ executor, built against a logging stand-in for the CUDA runtime ------------------------
+LAUNCH, RECORD, WAIT, BEGIN_CAPTURE, END_CAPTURE, INSTANTIATE, UPDATE, GRAPH_LAUNCH, EVENT_SYNC = range(9)
+
+
+def _ancestors(log):
+    """Happens-before implied by a log of runtime calls: program order per stream, and a wait on an
+    event orders what follows it after that event's latest record at the time of the call. Returns one
+    bit set per log entry (its ancestors, itself included)."""
+    anc = [0] * len(log)
+    last_on_stream, last_record = {}, {}
+    for i, (kind, stream, event, op, captured, params) in enumerate(log):
+        a = 1 << i
+        if stream >= 0 and stream in last_on_stream:
+            a |= anc[last_on_stream[stream]]
+        if kind == WAIT and event in last_record:
+            a |= anc[last_record[event]]
+        anc[i] = a
+        if stream >= 0:
+            last_on_stream[stream] = i
+        if kind == RECORD:
+            last_record[event] = i
+    return anc
+
+
+def _host_executor(pipeline_type, tp, nano, graph_mode=False):
+    from nanoflow_b200.runtime.native import NativeExecutor
+
+    g, acc, keep = _host_graph(pipeline_type, tp, nano)
+    single = all(op.stream == "gemm" for op in g.ops)
+    ex = NativeExecutor(g, None, single_stream=single, use_cuda_graph=graph_mode, host_only=True)
+    ex.mod.host_log_clear()
+    return g, ex, keep
+
+
+def _symbols(g, it):
+    return {name: 3 + it + 2 * idx for name, idx in g.symbols.items()}
+
+
+@pytest.mark.parametrize("pipeline_type,tp,nano", [("NON_OVERLAP_LOCAL", 1, None), ("LOCAL", 1, [16, 32]),
+                                                   ("PLLM", 2, [16, 32]), ("NON_OVERLAP", 2, None)])
+def test_executor_event_wiring_enforces_the_graph(pipeline_type, tp, nano):
+    g, ex, keep = _host_executor(pipeline_type, tp, nano)
+    n = len(g.ops)
+    for it in range(2):
+        ex.wait(ex.submit(_symbols(g, it)))
+    log = ex.mod.host_log()
+    ex.close()
+    launches = [i for i, r in enumerate(log) if r[0] == LAUNCH]
+    assert [log[i][3] for i in launches] == list(range(n)) * 2          # issue order = graph order, twice
+    assert not any(r[4] for r in log)                                    # nothing captured in plain mode
+    anc = _ancestors(log)
+    first, second = launches[:n], launches[n:]
+    for it_launches in (first, second):
+        for j, op in enumerate(g.ops):
+            for d in op.deps:
+                assert anc[it_launches[j]] >> it_launches[d] & 1, f"{g.ops[d].name} -> {op.name} is not enforced"
+    # every launch of an iteration precedes the event the host waits on, and the next iteration's launches
+    syncs = [r[2] for r in log if r[0] == EVENT_SYNC]
+    done = [max(i for i, r in enumerate(log) if r[0] == RECORD and r[2] == ev and r[1] == 0 and i < (launches[n] if k == 0 else len(log)))
+            for k, ev in enumerate(syncs)]
+    assert all(anc[done[0]] >> i & 1 for i in first) and all(anc[done[1]] >> i & 1 for i in second)
+    assert all(anc[second[0]] >> i & 1 for i in first)
+    # streams: ops run where the graph put them (one stream per class, the main stream when there is only one)
+    by_class = {}
+    for i in first:
+        by_class.setdefault(g.ops[log[i][3]].stream, set()).add(log[i][1])
+    assert all(len(s) == 1 for s in by_class.values())
+    assert len({next(iter(s)) for s in by_class.values()}) == len(by_class)
+
+
+def test_executor_patches_symbols_into_parameter_blocks():
+    g, ex, keep = _host_executor("LOCAL", 1, [16, 32])
+    syms = _symbols(g, 0)
+    ex.wait(ex.submit(syms))
+    log = [r for r in ex.mod.host_log() if r[0] == LAUNCH]
+    ex.close()
+    checked = 0
+    for r, op in zip(log, g.ops):
+        blob = r[5]
+        assert len(blob) == len(bytes(op.params))
+        want = bytearray(bytes(op.params))
+        for field, sym in op.dyn:
+            desc = getattr(type(op.params), field)
+            want[desc.offset:desc.offset + desc.size] = int(syms[sym]).to_bytes(desc.size, "little", signed=True)
+            checked += 1
+        assert blob == bytes(want), op.name
+    assert checked > len(g.ops) // 2
+
+
+@pytest.mark.parametrize("pipeline_type,tp,nano", [("NON_OVERLAP_LOCAL", 1, None), ("LOCAL", 1, [16, 32])])
+def test_executor_graph_mode_captures_whole_iterations(pipeline_type, tp, nano):
+    g, ex, keep = _host_executor(pipeline_type, tp, nano, graph_mode=True)
+    n = len(g.ops)
+    for it in range(5):
+        if it == 4:
+            ex.mod.fail_next_graph_update()          # the runtime refuses the in-place update once
+        ex.wait(ex.submit(_symbols(g, it)))
+    assert ex.graph_stats == (3, 2)                  # two plain iterations first; built, updated, rebuilt
+    log = ex.mod.host_log()
+    ex.close()
+    anc = _ancestors(log)
+    begins = [i for i, r in enumerate(log) if r[0] == BEGIN_CAPTURE]
+    ends = [i for i, r in enumerate(log) if r[0] == END_CAPTURE]
+    assert len(begins) == len(ends) == 3
+    plain = [i for i, r in enumerate(log) if r[0] == LAUNCH and i < begins[0]]
+    assert len(plain) == 2 * n and not any(log[i][4] for i in plain)
+    for b, e in zip(begins, ends):
+        inside = [i for i in range(b + 1, e) if log[i][0] == LAUNCH]
+        assert [log[i][3] for i in inside] == list(range(n))
+        assert all(log[i][4] for i in inside), "a launch escaped the capture and ran eagerly"
+        # every stream that joined the capture is joined back into the origin before the capture ends
+        touched = [i for i in range(b + 1, e) if log[i][4]]
+        assert all(anc[e] >> i & 1 for i in touched), "unjoined work at cudaStreamEndCapture"
+        for j, op in enumerate(g.ops):
+            for d in op.deps:
+                assert anc[inside[j]] >> inside[d] & 1
+        # the captured iteration is launched on the main stream as one unit, before the host's event
+        after = log[e + 1:e + 6]
+        kinds = [r[0] for r in after]
+        assert GRAPH_LAUNCH in kinds and RECORD in kinds[kinds.index(GRAPH_LAUNCH):]
+        assert after[kinds.index(GRAPH_LAUNCH)][1] == 0
+    assert [r[0] for r in log if r[0] in (INSTANTIATE, UPDATE)] == [INSTANTIATE, UPDATE, UPDATE, INSTANTIATE]
+
+
+def test_executor_reports_a_rejected_op_and_bounds_iterations_in_flight():
+    from nanoflow_b200.runtime.native import load_host_module
+
+    mod = load_host_module()
+    ex = mod.Executor(0, 0, False, 1)
+    ex.add_op("a", mod.noop_fn(), bytes(8), 0, [], [], [(0, 0, 4)])
+    ex.add_op("b", mod.failing_fn(), bytes(8), 1, [0], [], [])
+    with pytest.raises(RuntimeError, match="earlier op"):
+        ex.add_op("c", mod.noop_fn(), bytes(8), 0, [5], [], [])
+    with pytest.raises(RuntimeError, match="bad patch"):
+        ex.add_op("c", mod.noop_fn(), bytes(8), 0, [], [], [(6, 0, 4)])
+    t = ex.submit([7])
+    with pytest.raises(RuntimeError, match="op b rejected its arguments .code 3."):
+        ex.wait(t)
+    ex.close()
+    ok = mod.Executor(0, 0, True, 0)
+    ok.add_op("a", mod.noop_fn(), bytes(8), 0, [], [], [])
+    tickets = [ok.submit([]) for _ in range(8)]
+    with pytest.raises(RuntimeError, match="too many iterations in flight"):
+        ok.submit([])
+    for t in tickets:
+        ok.wait(t)
+    ok.wait(ok.submit([]))
+    assert ok.launches() == 9
+    ok.close()
+
+
+def test_executor_threads_are_race_free_under_thread_sanitizer():
+    """The worker thread, the submitting thread and the waiting thread share the job queue, the ticket
+    counters and the error string: 200 iterations with six in flight under ThreadSanitizer."""
+    import os
+    import subprocess
+    import sys
+
+    from nanoflow_b200.ops import build
+
+    res = subprocess.run(["gcc", "-print-file-name=libtsan.so"], capture_output=True, text=True)
+    tsan = res.stdout.strip()
+    if res.returncode != 0 or not os.path.isabs(tsan) or not os.path.exists(tsan):
+        pytest.skip("no ThreadSanitizer runtime on this machine")
+    mod = build.build_executor_host(sanitize="thread")
+    env = dict(os.environ, LD_PRELOAD=tsan, TSAN_OPTIONS="report_signal_unsafe=0 exitcode=66")
+    script = os.path.join(os.path.dirname(__file__), "executor_host_stress.py")
+    run = subprocess.run([sys.executable, script, str(mod.parent)], capture_output=True, text=True, env=env,
+                         timeout=600)
+    assert "ThreadSanitizer" not in run.stderr, run.stderr[-3000:]
+    assert run.returncode == 0, run.stderr[-3000:]
+    assert "launches 8000 graph launches 194 rebuilds 1" in run.stdout
