@@ -292,15 +292,18 @@ __global__ void __launch_bounds__(kCommThreads)
 allgather_kernel(nfk_allgather_params p) {
   const nfk_comm_ctx& c = p.ctx;
   if (p.handshake_in) comm_enter(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status);
-  const long long nvec = p.shard_bytes >> 4;
-  const char* src = reinterpret_cast<const char*>(c.heap[c.rank]) + p.buf_off + c.rank * p.shard_stride;
+  const long long row_vec = p.shard_bytes >> 4;                  // 16-byte vectors of this rank's shard per row
+  const long long rows = p.rows > 1 ? p.rows : 1;
+  const long long nvec = row_vec * rows;
+  const long long mine = p.buf_off + c.rank * p.shard_stride;    // same offset in every rank's heap
+  const char* src = reinterpret_cast<const char*>(c.heap[c.rank]) + mine;
   for (long long v = blockIdx.x * static_cast<long long>(kCommThreads) + threadIdx.x; v < nvec;
        v += static_cast<long long>(gridDim.x) * kCommThreads) {
-    const uint4 val = *reinterpret_cast<const uint4*>(src + v * 16);
+    const long long off = rows > 1 ? (v / row_vec) * p.row_stride + (v % row_vec) * 16 : v * 16;
+    const uint4 val = *reinterpret_cast<const uint4*>(src + off);
 #pragma unroll
     for (int r = 0; r < 8; ++r)
-      if (r < c.nranks && r != c.rank)
-        st_sys_v4(reinterpret_cast<char*>(c.heap[r]) + p.buf_off + c.rank * p.shard_stride + v * 16, val);
+      if (r < c.nranks && r != c.rank) st_sys_v4(reinterpret_cast<char*>(c.heap[r]) + mine + off, val);
   }
   comm_exit(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status);
 }
@@ -356,8 +359,10 @@ extern "C" int nfk_allgather(const nfk_allgather_params* p, cudaStream_t stream)
   if (p->shard_bytes < 0 || p->shard_bytes % 16 != 0 || p->shard_stride % 16 != 0 || p->buf_off % 16 != 0 ||
       p->flag_off % 16 != 0 || p->shard_stride < p->shard_bytes)
     return NF_ERR_BAD_ARG;
+  if (p->rows < 0 || (p->rows > 1 && (p->row_stride % 16 != 0 || p->row_stride < p->ctx.nranks * p->shard_stride)))
+    return NF_ERR_BAD_ARG;
   long long ctas = p->num_ctas > 0 ? p->num_ctas : 16;
-  const long long need = ((p->shard_bytes >> 4) + kCommThreads - 1) / kCommThreads;
+  const long long need = ((p->shard_bytes >> 4) * (p->rows > 1 ? p->rows : 1) + kCommThreads - 1) / kCommThreads;
   if (ctas > need) ctas = need > 0 ? need : 1;
   static bool once = false;
   if (!once) {

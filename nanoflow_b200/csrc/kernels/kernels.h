@@ -216,6 +216,11 @@ typedef struct nfk_allgather_params {
   long long shard_bytes, shard_stride, flag_off;
   int epoch, num_ctas, handshake_in;
   unsigned int* status;
+  // Column-wise form (rows > 1): the buffer is [rows][...] with row_stride bytes between rows, and
+  // rank r owns the shard_bytes starting at byte r*shard_stride of every row (its column block).
+  // rows <= 1 is the flat form above.
+  int rows;
+  long long row_stride;
 } nfk_allgather_params;
 int nfk_allgather(const nfk_allgather_params* p, cudaStream_t stream);
 

@@ -34,7 +34,7 @@ class AllReduceParams(Structure):
 class AllGatherParams(Structure):
     _fields_ = [("ctx", CommCtx), ("buf_off", c_longlong), ("shard_bytes", c_longlong),
                 ("shard_stride", c_longlong), ("flag_off", c_longlong), ("epoch", c_int), ("num_ctas", c_int),
-                ("handshake_in", c_int), ("status", c_void_p)]
+                ("handshake_in", c_int), ("status", c_void_p), ("rows", c_int), ("row_stride", c_longlong)]
 
 
 class BarrierParams(Structure):
@@ -226,6 +226,97 @@ class TpCollectives(CollectiveHooks):
         if rc != 0:
             raise RuntimeError(f"nfk_allgather: {_ops.ERRORS.get(rc, rc)}")
         return buf
+
+    def all_gather_columns_(self, buf: torch.Tensor, *, num_ctas: int = 0):
+        """Column-wise all-gather: ``buf`` is a symmetric [rows, world * w] tensor whose column block
+        ``rank`` this rank has filled; afterwards every rank holds all blocks. The reference gathers the
+        attention output and the N-split O projection this way (pipeline/src/comm.cu:116-167,
+        ``columnwiseAllgatherKernelEntryPoint``)."""
+        rows, width = buf.shape
+        if buf.stride(1) != 1 or width % self.tp != 0:
+            raise ValueError("column-wise all-gather needs unit column stride and world | columns")
+        esz = buf.element_size()
+        p = AllGatherParams()
+        p.ctx = self.ctx()
+        p.buf_off = self.heap.offset_of(buf)
+        p.shard_bytes = p.shard_stride = (width // self.tp) * esz
+        p.rows, p.row_stride = rows, buf.stride(0) * esz
+        if rows == 1:
+            p.rows = 0                       # one row is the flat form
+        p.flag_off = self._adhoc_flags
+        p.epoch, p.num_ctas, p.handshake_in = self._next_epoch(), num_ctas or self.num_ctas, 1
+        p.status = self.status.data_ptr()
+        rc = _ops.lib().nfk_allgather(byref(p), c_void_p(torch.cuda.current_stream().cuda_stream))
+        if rc != 0:
+            raise RuntimeError(f"nfk_allgather: {_ops.ERRORS.get(rc, rc)}")
+        return buf
+
+    def reduce_scatter_(self, buf: torch.Tensor, out: torch.Tensor, *, rows: Optional[int] = None,
+                        resid: Optional[torch.Tensor] = None, num_ctas: int = 0):
+        """Sum of a symmetric bf16 [rows, cols] tensor over all ranks, scattered by rows: rank r gets
+        rows r, r + world, r + 2*world, ... written into the same rows of the local tensor ``out``
+        (its other rows, and ``buf`` on every rank, are left as they are). The pull phase of the
+        all-reduce on its own (pipeline/src/comm.cu:169-282, ``reduceScatterKernel``; the reference
+        gives each rank a contiguous block of rows, here ownership is interleaved so that any prefix of
+        the rows is spread evenly)."""
+        return self.all_reduce_(buf, rows=rows, resid=resid, sum_out=out, push_sum=False, num_ctas=num_ctas)
+
+    # ---- copy-engine forms: peer-to-peer cudaMemcpyAsync, one copy per peer on a stream of its own -----
+    def _peer_streams(self):
+        if not hasattr(self, "_pstreams"):
+            self._pstreams = [torch.cuda.Stream(device=self.device) for _ in range(self.tp)]
+        return self._pstreams
+
+    def _copy_to_peer(self, peer: int, dst_off: int, src: torch.Tensor, stream) -> None:
+        from ..runtime.graph import MemcpyParams
+        p = MemcpyParams(dst=self.heap.peer_base[peer] + dst_off, src=src.data_ptr(), elem_bytes=src.element_size(),
+                         count=src.numel())
+        rc = _ops.lib().nfk_memcpy_p(byref(p), c_void_p(stream.cuda_stream))
+        if rc != 0:
+            raise RuntimeError(f"peer copy: {_ops.ERRORS.get(rc, rc)}")
+
+    def _fan_out(self, copies) -> None:
+        """Run ``copies`` = [(peer, dst_off, src)] on the per-peer streams between two barriers: peers are
+        done with the destination before the first byte lands, and see all of it after the second."""
+        cur = torch.cuda.current_stream()
+        self.barrier_()
+        start = torch.cuda.Event()
+        start.record(cur)
+        streams = self._peer_streams()
+        for peer, dst_off, src in copies:
+            st = streams[peer]
+            st.wait_event(start)
+            self._copy_to_peer(peer, dst_off, src, st)
+            done = torch.cuda.Event()
+            done.record(st)
+            cur.wait_event(done)
+        self.barrier_()
+
+    def all_gather_copy_(self, buf: torch.Tensor):
+        """All-gather of a symmetric [world, ...] tensor (row ``rank`` filled locally) by the copy engines
+        instead of SMs: one peer-to-peer copy per destination, each on its own stream. Counterpart of the
+        reference's ``NetAllGatherAsync`` (pipeline/include/netWrapper.cuh:501-559)."""
+        if not buf[self.rank].is_contiguous():
+            raise ValueError("shards must be contiguous")
+        off = self.heap.offset_of(buf) + self.rank * buf.stride(0) * buf.element_size()
+        self._fan_out([(r, off, buf[self.rank]) for r in range(self.tp) if r != self.rank])
+        return buf
+
+    def reduce_scatter_copy_(self, buf: torch.Tensor, scratch: torch.Tensor, out: torch.Tensor):
+        """Reduce-scatter of contiguous shards by the copy engines: ``buf`` [world, n] holds this rank's
+        partial sums (any memory), ``scratch`` is a symmetric [world, n] tensor of the same dtype; every
+        rank copies its shard ``r`` into row ``rank`` of rank r's ``scratch``, and after the barrier adds up
+        the rows it received (fp32 accumulation) into ``out`` [n]. Counterpart of the reference's
+        ``NetReduceScatterAsync`` + ``asyncReduceKernel`` (pipeline/include/netWrapper.cuh:562-634,
+        pipeline/src/comm.cu:487-530)."""
+        if buf.shape != scratch.shape or buf.shape[0] != self.tp or not buf.is_contiguous() or not scratch.is_contiguous():
+            raise ValueError("buf and scratch must be contiguous [world, n] tensors")
+        row_bytes = scratch.stride(0) * scratch.element_size()
+        base = self.heap.offset_of(scratch) + self.rank * row_bytes
+        scratch[self.rank].copy_(buf[self.rank])
+        self._fan_out([(r, base, buf[r]) for r in range(self.tp) if r != self.rank])
+        out.copy_(scratch.float().sum(dim=0).to(out.dtype))      # local memory only
+        return out
 
     def barrier_(self):
         p = BarrierParams()

@@ -80,6 +80,57 @@ def case_collectives(rank, world, dev):
     coll.check_status()
     want = torch.stack([torch.arange(4096, dtype=torch.int32) + 1000 * r for r in range(world)]).to(dev)
     assert torch.equal(ag, want)
+    # column-wise all-gather: rank r owns column block r of every row (also as a view into a wider tensor)
+    for rows_c, w, pad in [(37, 64, 0), (1, 256, 0), (300, 1024, 128)]:
+        wide = coll.alloc((rows_c, world * w + 2 * pad), torch.bfloat16)
+        wide.fill_(-2.0)
+        cg = wide[:, pad:pad + world * w]
+        pat = lambda r: ((torch.arange(rows_c * w, device=dev).reshape(rows_c, w) * (r + 3)) % 251).to(torch.bfloat16)
+        cg[:, rank * w:(rank + 1) * w] = pat(rank)
+        torch.cuda.synchronize(); dist.barrier()
+        coll.all_gather_columns_(cg)
+        coll.barrier_()
+        torch.cuda.synchronize()
+        coll.check_status()
+        assert torch.equal(cg, torch.cat([pat(r) for r in range(world)], dim=1)), f"column all-gather {rows_c}x{w}"
+        if pad:
+            assert bool((wide[:, :pad] == -2.0).all()) and bool((wide[:, pad + world * w:] == -2.0).all())
+    # reduce-scatter: the owners' rows of the sum land in a local tensor, nothing else is written
+    rows, cols = 203, 1024
+    parts = [torch.randn(rows, cols, generator=g).bfloat16() for _ in range(world)]
+    buf = coll.alloc((rows, cols), torch.bfloat16)
+    buf.copy_(parts[rank].to(dev))
+    got = torch.full((rows, cols), -1.0, dtype=torch.bfloat16, device=dev)
+    torch.cuda.synchronize(); dist.barrier()
+    coll.reduce_scatter_(buf, got)
+    coll.barrier_()
+    torch.cuda.synchronize()
+    coll.check_status()
+    total = sum(p.float() for p in parts).to(dev)
+    mine = torch.arange(rank, rows, world, device=dev)
+    others = torch.tensor([i for i in range(rows) if i % world != rank], device=dev)
+    assert torch.allclose(got[mine].float(), total[mine], atol=3e-2, rtol=1e-2)
+    assert bool((got[others] == -1.0).all()) and torch.equal(buf, parts[rank].to(dev))
+    # the same two collectives through the copy engines (one peer-to-peer copy per destination)
+    ag2 = coll.alloc((world, 3, 1000), torch.float32)
+    ag2.zero_(); ag2[rank] = torch.arange(3000, device=dev, dtype=torch.float32).reshape(3, 1000) + 10000 * rank
+    torch.cuda.synchronize(); dist.barrier()
+    coll.all_gather_copy_(ag2)
+    torch.cuda.synchronize()
+    coll.check_status()
+    want = torch.stack([torch.arange(3000, dtype=torch.float32).reshape(3, 1000) + 10000 * r for r in range(world)])
+    assert torch.equal(ag2, want.to(dev))
+    n = 4096
+    ar = torch.arange(n, device=dev)
+    partial = torch.stack([((ar * (rank + 1) + r) % 7).to(torch.bfloat16) for r in range(world)])
+    scratch = coll.alloc((world, n), torch.bfloat16)
+    red = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    for _ in range(2):                      # twice: the second round reuses the scratch rows
+        coll.reduce_scatter_copy_(partial, scratch, red)
+        torch.cuda.synchronize()
+        coll.check_status()
+        want = sum(((ar * (s_ + 1) + rank) % 7).float() for s_ in range(world))
+        assert torch.equal(red.float(), want), "copy-engine reduce-scatter"
     # bandwidth (device-timed, max over ranks)
     rows, cols = 2048, 8192
     buf = coll.alloc((rows, cols), torch.bfloat16)
