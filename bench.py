@@ -113,6 +113,8 @@ def main():
     ap.add_argument("--no-fuse-norm", action="store_true", help="one GPU: separate RMSNorm launches after O / down")
     ap.add_argument("--serial-attention", action="store_true",
                     help="prefill attention after decode attention on one stream instead of beside it")
+    ap.add_argument("--decode-tail", type=float, default=0.0,
+                    help="share of the decode requests' context scheduled into the last nano-batch (0 = all first)")
     ap.add_argument("--virtual-tp", type=int, default=0,
                     help="one GPU runs rank 0's share of a tensor-parallel job of this degree, collectives reduced "
                          "to their local part (development aid; the JSON line is marked invalid)")
@@ -226,7 +228,7 @@ def main():
     sch = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=gbs,
                     nanobatch_sizes=cfg.engine.resolved_nanobatches(), max_batch_size=gbs,
                     average_prefill_length=args.input_len, average_decode_length=args.output_len,
-                    group_size=model.group_size)
+                    group_size=model.group_size, decode_tail_fraction=args.decode_tail)
     loop = ServingLoop(eng, sch, rm, simulated_time=True, est_cycle_time=1.0)
     loop.skip_cycles(args.skip_cycles)
 

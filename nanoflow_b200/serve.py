@@ -97,7 +97,8 @@ def main(argv=None) -> int:
                     nanobatch_sizes=eng_cfg.resolved_nanobatches(), max_batch_size=eng_cfg.max_batch_size,
                     average_prefill_length=rm.average_prefill_length, average_decode_length=rm.average_decode_length,
                     group_size=model.group_size, eos_token_id=model.eos_token_id, stop_on_eos=args.stop_on_eos,
-                    hold_retired_pages=bool(eng_cfg.offload and args.backend == "gpu"))
+                    hold_retired_pages=bool(eng_cfg.offload and args.backend == "gpu"),
+                    decode_tail_fraction=eng_cfg.decode_tail_fraction)
     sch.keep_schedule_log = bool(args.output_prefix)
     offload = None
     if eng_cfg.offload and args.backend == "gpu":

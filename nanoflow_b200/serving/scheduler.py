@@ -73,7 +73,7 @@ class BatchPlan:
     decode: List[FlyRequestInfo]
     prefill: List[Tuple[FlyRequestInfo, int, int]]      # (request, chunk start, chunk length)
     num_tokens: int
-    num_decode: int
+    num_decode: int                                     # decode requests in all (head + tail)
     host_ids: np.ndarray
     feedback_src: np.ndarray
     positions: np.ndarray
@@ -88,6 +88,10 @@ class BatchPlan:
     max_kv_pages: int = 0
     retired_pages: Optional[np.ndarray] = None          # pages of requests retired at this step (offload)
     retired_reqs: List[FlyRequestInfo] = field(default_factory=list)
+    # Request order of the batch: ``num_decode - num_tail_decode`` decode requests, the prompt chunks, then
+    # ``num_tail_decode`` decode requests whose tokens are the last of the batch (they fall into the last
+    # nano-batch). ``decode`` lists head then tail.
+    num_tail_decode: int = 0
 
     @property
     def num_requests(self) -> int:
@@ -99,7 +103,8 @@ class Scheduler:
                  global_batch_size: int, nanobatch_sizes: Optional[Sequence[int]] = None,
                  max_batch_size: Optional[int] = None, average_prefill_length: int = 1024,
                  average_decode_length: int = 512, group_size: int = 8, eos_token_id: Optional[int] = None,
-                 stop_on_eos: bool = False, hold_retired_pages: bool = False, prefill_ctas: int = 296):
+                 stop_on_eos: bool = False, hold_retired_pages: bool = False, prefill_ctas: int = 296,
+                 decode_tail_fraction: float = 0.0):
         self._memory_pool = memory_pool
         self._request_queue = request_queue
         self.global_batch_size = int(global_batch_size)
@@ -114,6 +119,13 @@ class Scheduler:
         self.eos_token_id = eos_token_id
         self.stop_on_eos = stop_on_eos
         self.hold_retired_pages = hold_retired_pages
+        # Share of the decode requests' context (KV tokens to read) that goes to the end of the batch, and
+        # so into the last nano-batch, instead of the front. With all decode requests in the first
+        # nano-batch its attention takes several times longer than the last one's, and under tensor
+        # parallelism the collective of one nano-batch has to hide behind the other's compute.
+        if not 0.0 <= decode_tail_fraction <= 1.0:
+            raise ValueError("decode_tail_fraction must be within [0, 1]")
+        self.decode_tail_fraction = float(decode_tail_fraction)
 
         self._decode_workset = WorkingSet()
         self._prefill_workset = WorkingSet()
@@ -298,35 +310,48 @@ class Scheduler:
             self._finish_retire_log(retired_now)
             return None
 
-        # 4. arrays
-        B = D + len(prefill)
+        # 4. arrays. Request (and token) order: head decode requests, prompt chunks, tail decode requests.
+        P = len(prefill)
+        B = D + P
+        Dt = self._tail_decode_count(decode, T)
+        Dh = D - Dt
         host_ids = np.zeros(T, dtype=np.int32)
         feedback = np.full(T, -1, dtype=np.int32)
         positions = np.empty(T, dtype=np.int32)
         token_req = np.empty(T, dtype=np.int32)
         qo_indptr = np.zeros(B + 1, dtype=np.int32)
-        if D:
+
+        def fill_decode(reqs, tok0, req0):
+            n = len(reqs)
+            if n == 0:
+                return
             # Newest token still on the device (launched last iteration, not yet seen by the host):
             # feed it back there. A request that sat out an iteration has it on the host already.
-            feedback[:D] = np.fromiter((r.slot if r.pending > 0 else -1 for r in decode), dtype=np.int32, count=D)
-            host_ids[:D] = np.fromiter((r.output[-1] if (r.pending == 0 and r.output) else 0 for r in decode),
-                                       dtype=np.int32, count=D)
-            positions[:D] = np.fromiter((r.kv_cache.seqlen - 1 for r in decode), dtype=np.int32, count=D)
-            token_req[:D] = np.arange(D, dtype=np.int32)
-            qo_indptr[1:D + 1] = np.arange(1, D + 1, dtype=np.int32)
-        t = D
-        sample_rows = list(range(D))
-        sample_reqs = list(decode)
+            feedback[tok0:tok0 + n] = np.fromiter((r.slot if r.pending > 0 else -1 for r in reqs), dtype=np.int32, count=n)
+            host_ids[tok0:tok0 + n] = np.fromiter((r.output[-1] if (r.pending == 0 and r.output) else 0 for r in reqs),
+                                                  dtype=np.int32, count=n)
+            positions[tok0:tok0 + n] = np.fromiter((r.kv_cache.seqlen - 1 for r in reqs), dtype=np.int32, count=n)
+            token_req[tok0:tok0 + n] = np.arange(req0, req0 + n, dtype=np.int32)
+            qo_indptr[req0 + 1:req0 + n + 1] = np.arange(tok0 + 1, tok0 + n + 1, dtype=np.int32)
+
+        head, tail = decode[:Dh], decode[Dh:]
+        fill_decode(head, 0, 0)
+        t = Dh
+        sample_rows = list(range(Dh))
+        sample_reqs = list(head)
         for j, (req, s, n) in enumerate(prefill):
             host_ids[t:t + n] = req.prompt[s:s + n]
             positions[t:t + n] = np.arange(s, s + n, dtype=np.int32)
-            token_req[t:t + n] = D + j
+            token_req[t:t + n] = Dh + j
             t += n
-            qo_indptr[D + j + 1] = t
+            qo_indptr[Dh + j + 1] = t
             if s + n == req.input_len:
                 sample_rows.append(t - 1)
                 sample_reqs.append(req)
-        kvs = [r.kv_cache for r in decode] + [r.kv_cache for r, _, _ in prefill]
+        fill_decode(tail, t, Dh + P)
+        sample_rows.extend(range(t, t + Dt))
+        sample_reqs.extend(tail)
+        kvs = [r.kv_cache for r in head] + [r.kv_cache for r, _, _ in prefill] + [r.kv_cache for r in tail]
         counts = np.fromiter((kv.num_pages for kv in kvs), dtype=np.int32, count=B)
         kv_indptr = np.zeros(B + 1, dtype=np.int32)
         np.cumsum(counts, out=kv_indptr[1:])
@@ -344,14 +369,14 @@ class Scheduler:
                 self._decode_workset.put(req)
 
         # 6. nano-batches
-        nano = self._cut_nanobatches(T, D, prefill, qo_indptr)
+        nano = self._cut_nanobatches(T, Dh, Dt, prefill, qo_indptr)
 
         plan = BatchPlan(iteration=self.iteration, decode=decode, prefill=prefill, num_tokens=T, num_decode=D,
                          host_ids=host_ids, feedback_src=feedback, positions=positions, token_req=token_req,
                          qo_indptr=qo_indptr, kv_indptr=kv_indptr, kv_indices=kv_indices,
                          kv_last_page_len=kv_last, sample_rows=np.asarray(sample_rows, dtype=np.int32),
                          sample_reqs=sample_reqs, nano=nano, max_kv_pages=int(counts.max()) if B else 0,
-                         retired_reqs=retired_now)
+                         retired_reqs=retired_now, num_tail_decode=Dt)
         if self.hold_retired_pages and retired_now:
             plan.retired_pages = np.concatenate([r.kv_cache.indicies for r in retired_now]).astype(np.int32)
         self._finish_retire_log(retired_now, plan)
@@ -379,26 +404,52 @@ class Scheduler:
             order[r * G:(r + 1) * G] = order[r * G:(r + 1) * G][::-1].copy()
         return order
 
-    def _cut_nanobatches(self, T: int, D: int, prefill, qo_indptr) -> List[NanoBatchPlan]:
+    def _tail_decode_count(self, decode: List[FlyRequestInfo], T: int) -> int:
+        """How many of the decode requests (the last ones of ``decode``) go to the end of the batch:
+        enough to carry ``decode_tail_fraction`` of the context, within what keeps a single range of
+        decode requests per nano-batch (no head request in the last nano-batch, no tail request
+        outside it)."""
+        D = len(decode)
+        if self.decode_tail_fraction <= 0.0 or len(self.nanobatch_sizes) < 2 or D == 0:
+            return 0
+        last_start = self.global_batch_size - self.nanobatch_sizes[-1]
+        hi = min(D, max(0, T - last_start))               # tail tokens must lie inside the last nano-batch
+        lo = max(0, D - last_start)                       # head tokens must end before it
+        if hi <= 0:
+            return 0
+        ctx = np.fromiter((r.kv_cache.seqlen for r in decode), dtype=np.int64, count=D)
+        from_end = np.cumsum(ctx[::-1])
+        want = int(np.searchsorted(from_end, self.decode_tail_fraction * float(from_end[-1]), side="left")) + 1
+        return int(min(hi, max(lo, want)))
+
+    def _cut_nanobatches(self, T: int, Dh: int, Dt: int, prefill, qo_indptr) -> List[NanoBatchPlan]:
         out = []
         start = 0
         tq = self.tile_tokens
+        P = len(prefill)
+        tail0 = T - Dt                                     # first tail decode token
         for size in self.nanobatch_sizes:
             t0, t1 = start, min(T, start + size)
             start += size
             if t1 <= t0:
-                out.append(NanoBatchPlan(t0 if t0 < T else T, 0, min(D, t0), 0, np.zeros((0, 3), dtype=np.int32)))
+                out.append(NanoBatchPlan(t0 if t0 < T else T, 0, min(Dh, t0), 0, np.zeros((0, 3), dtype=np.int32)))
                 continue
-            d0, d1 = min(D, t0), min(D, t1)
+            d0, d1 = min(Dh, t0), min(Dh, t1)              # head decode requests: request index = token index
+            a0, a1 = max(t0, tail0), t1                    # tail decode tokens of this nano-batch
+            if a1 > a0:
+                if d1 > d0:
+                    raise AssertionError("a nano-batch holds decode requests from both ends of the batch")
+                d0 = Dh + P + (a0 - tail0)
+                d1 = d0 + (a1 - a0)
             items, kv_ends = [], []
             for j, (req, s, n) in enumerate(prefill):
-                q0, q1 = int(qo_indptr[D + j]), int(qo_indptr[D + j + 1])
+                q0, q1 = int(qo_indptr[Dh + j]), int(qo_indptr[Dh + j + 1])
                 a, b = max(q0, t0), min(q1, t1)
                 if b <= a:
                     continue
                 starts = np.arange(a, b, tq, dtype=np.int32)
                 cnt = np.minimum(tq, b - starts).astype(np.int32)
-                items.append(np.stack([np.full_like(starts, D + j), starts, cnt], axis=1))
+                items.append(np.stack([np.full_like(starts, Dh + j), starts, cnt], axis=1))
                 kv_ends.append(s + (starts - q0) + cnt)     # context each item attends to = its cost
             it = np.concatenate(items) if items else np.zeros((0, 3), dtype=np.int32)
             if it.shape[0] > 1:

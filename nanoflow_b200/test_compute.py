@@ -85,7 +85,8 @@ def main(argv=None) -> int:
     pool = DistKVPool(m.run_layers, m.num_kv_heads, m.head_dim, eng.num_pages, e.page_size, tp)
     sch = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=gbs, nanobatch_sizes=e.resolved_nanobatches(),
                     max_batch_size=e.max_batch_size, average_prefill_length=a.input_len,
-                    average_decode_length=a.output_len, group_size=m.group_size)
+                    average_decode_length=a.output_len, group_size=m.group_size,
+                    decode_tail_fraction=e.decode_tail_fraction)
     loop = ServingLoop(eng, sch, rm, simulated_time=True, est_cycle_time=1.0)
     loop.skip_cycles(a.skip_cycles)
     loop.step()

@@ -34,6 +34,17 @@ def _serve(tp, gbs, nano, prompts, out_len, pages=64, model="tiny", **sched_kw):
     return st, oracle, pool
 
 
+def test_greedy_decode_matches_oracle_with_decode_requests_at_both_ends_of_the_batch():
+    """``decode_tail_fraction``: part of the decode requests sit after the prompt chunks (in the last
+    nano-batch); outputs are the oracle's, token for token."""
+    rng = np.random.default_rng(1)
+    prompts = [rng.integers(0, 1024, size=int(n), dtype=np.int32) for n in (32, 9, 21, 40, 17, 33)]
+    st, oracle, pool = _serve(2, 48, [16, 32], prompts, 12, decode_tail_fraction=0.5)
+    assert len(st.retired) == 6 and pool.num_free_pages == 64
+    for r in st.retired:
+        assert r.output == oracle.generate(prompts[r.req_idx].tolist(), 12)
+
+
 @pytest.mark.parametrize("tp,gbs,nano", [(1, 48, None), (1, 48, [16, 32]), (2, 48, [16, 32]), (2, 160, [64, 96])])
 def test_greedy_decode_matches_oracle(tp, gbs, nano):
     rng = np.random.default_rng(0)

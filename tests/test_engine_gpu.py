@@ -12,7 +12,7 @@ from nanoflow_b200.serving import DistKVPool, RequestManager, Scheduler
 from nanoflow_b200.serving.loop import ServingLoop
 
 
-def _run(pipeline_type, nano, executor, gbs=48, guards=False):
+def _run(pipeline_type, nano, executor, gbs=48, guards=False, tail=0.0):
     from nanoflow_b200.runtime.engine import Engine
 
     cfg = builtin_config("tiny", gpu_num=1, global_batch_size=gbs, pipeline_type=pipeline_type,
@@ -36,7 +36,7 @@ def _run(pipeline_type, nano, executor, gbs=48, guards=False):
     pool = DistKVPool(2, 2, 64, 64, 16, 1)
     sch = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=gbs,
                     nanobatch_sizes=cfg.engine.resolved_nanobatches(), average_prefill_length=32,
-                    average_decode_length=16, group_size=2)
+                    average_decode_length=16, group_size=2, decode_tail_fraction=tail)
     eng = Engine(cfg, shard_weights(fw, cfg.model, 0, 1, device="cuda"), num_pages=64, executor=executor)
     loop = ServingLoop(eng, sch, rm, est_cycle_time=1.0)
     st = loop.run()
@@ -76,6 +76,12 @@ def test_engine_matches_oracle_py_executor(pipeline_type, nano):
 
 def test_engine_keeps_inside_guarded_buffers():
     _run("LOCAL", [16, 32], "native", guards=True)
+
+
+def test_engine_with_decode_requests_at_both_ends_of_the_batch():
+    """Part of the decode requests scheduled behind the prompt chunks, into the last nano-batch: the
+    decode kernel of that nano-batch starts at a request index past the prompts."""
+    _run("LOCAL", [16, 32], "native", tail=0.5)
 
 
 def test_engine_matches_oracle_native_executor():

@@ -164,3 +164,53 @@ def test_prefill_items_balanced_over_persistent_ctas():
     naive = np.sort(cost)            # the order a plain token walk would give: short contexts first
     naive_per_cta = np.array([naive[c::G].sum() for c in range(G)])
     assert per_cta.max() - per_cta.min() < naive_per_cta.max() - naive_per_cta.min()
+
+
+@pytest.mark.parametrize("nano,frac", [([48, 48], 0.5), ([32, 64], 0.5), ([64, 32], 0.3), ([32, 32, 32], 0.5), ([48, 48], 1.0)])
+def test_decode_tail_puts_a_share_of_the_decode_context_into_the_last_nanobatch(nano, frac):
+    """With ``decode_tail_fraction`` the batch is [head decode | prompt chunks | tail decode]: every
+    token and request is covered exactly once, each nano-batch sees one contiguous range of decode
+    requests whose tokens lie inside it, and the tail carries about the requested share of context."""
+    gbs = sum(nano)
+    s, pool, _ = _mk(pool_pages=2000, gbs=gbs, nano=nano, n=60, in_len=41, out_len=24, decode_tail_fraction=frac)
+    s.max_batch_size = gbs
+    plans = _drive(s)
+    assert len(s.retired) == 60 and all(len(r.output) == 24 for r in s.retired)
+    mixed = 0
+    for p in plans:
+        D, Dt, T, B = p.num_decode, p.num_tail_decode, p.num_tokens, p.num_requests
+        Dh, P = D - Dt, len(p.prefill)
+        assert 0 <= Dt <= D and p.qo_indptr[0] == 0 and p.qo_indptr[B] == T
+        assert (np.diff(p.qo_indptr[:B + 1]) > 0).all()
+        # token -> request map agrees with qo_indptr, decode requests have one token each
+        assert (np.repeat(np.arange(B), np.diff(p.qo_indptr[:B + 1])) == p.token_req).all()
+        lens = np.diff(p.qo_indptr[:B + 1])
+        assert (lens[:Dh] == 1).all() and (lens[Dh + P:] == 1).all()
+        assert [r for r in p.decode] == p.sample_reqs[:Dh] + p.sample_reqs[len(p.sample_reqs) - Dt:]
+        # per nano-batch: the decode range is inside the nano-batch, ranges tile all decode requests
+        seen = []
+        covered = np.zeros(T, dtype=np.int32)
+        for nb in p.nano:
+            t0, t1 = nb.token_start, nb.token_start + nb.token_count
+            for req in range(nb.dec_begin, nb.dec_begin + nb.dec_count):
+                assert req < Dh or req >= Dh + P
+                tok = int(p.qo_indptr[req])
+                assert t0 <= tok < t1
+                covered[tok] += 1
+                seen.append(req)
+            for req, start, cnt in nb.items.tolist():
+                assert Dh <= req < Dh + P and t0 <= start and start + cnt <= t1
+                assert p.qo_indptr[req] <= start and start + cnt <= p.qo_indptr[req + 1]
+                covered[start:start + cnt] += 1
+        assert (covered == 1).all()
+        assert sorted(seen) == list(range(Dh)) + list(range(Dh + P, B))
+        if Dt and Dh:
+            mixed += 1
+            last0 = gbs - nano[-1]
+            assert Dh <= last0 and T - Dt >= last0
+            if T == gbs and len(nano) == 2 and Dt < min(D, T - last0) and Dt > max(0, D - last0):
+                # unclamped: the tail is the shortest suffix of the decode requests that reaches the share
+                ctx = np.concatenate([p.positions[:Dh], p.positions[T - Dt:]]).astype(np.int64) + 1
+                tail_sum, total = ctx[Dh:].sum(), ctx.sum()
+                assert tail_sum >= frac * total > tail_sum - ctx[Dh]
+    assert mixed > 5 or frac == 1.0
