@@ -110,6 +110,8 @@ def main():
     ap.add_argument("--mem-fraction", type=float, default=0.96, help="share of device memory the engine may use")
     ap.add_argument("--fuse-rs", action="store_true", help="K-split GEMMs push their partial rows to the owners "
                     "from the GEMM epilogue (fused GEMM -> reduce-scatter) instead of the collective pulling them")
+    ap.add_argument("--fuse-rs-staged", action="store_true", help="with --fuse-rs: rows leave the epilogue through "
+                    "shared memory and one 256-byte bulk copy per row and 128 columns")
     ap.add_argument("--no-fuse-norm", action="store_true", help="one GPU: separate RMSNorm launches after O / down")
     ap.add_argument("--serial-attention", action="store_true",
                     help="prefill attention after decode attention on one stream instead of beside it")
@@ -200,6 +202,7 @@ def main():
     if args.comm_ctas:
         cfg.engine.sm_budget["comm"] = args.comm_ctas
     cfg.engine.fuse_gemm_rs = bool(args.fuse_rs)
+    cfg.engine.gemm_rs_staged = bool(args.fuse_rs_staged)
     cfg.engine.fuse_gemm_norm = not args.no_fuse_norm
     cfg.engine.prefill_beside_decode = not args.serial_attention
     if args.layers:

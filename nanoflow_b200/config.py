@@ -161,6 +161,7 @@ class EngineConfig:
     use_cuda_graph: bool = False
     offload: bool = False
     fuse_gemm_rs: bool = False             # TP: K-split GEMMs push partial rows to their owners from the epilogue
+    gemm_rs_staged: bool = False           # ... through shared memory and 256-byte bulk copies instead of 16-byte stores
     # serving
     model_id: str = ""
     weight_path: str = ""
@@ -233,6 +234,7 @@ def parse_config(raw: Dict[str, Any], *, tp: Optional[int] = None) -> NanoflowCo
         use_cuda_graph=bool(pc.get("use_cuda_graph", False)),
         offload=ptype == "PLLM_OFFLOAD" or bool(pc.get("offload", False)),
         fuse_gemm_rs=bool(pc.get("fuse_gemm_rs", False)),
+        gemm_rs_staged=bool(pc.get("gemm_rs_staged", False)),
         autotune_gemm=bool(pc.get("autotune_gemm", True)),
         prefill_tc=bool(pc.get("prefill_tc", True)),
         fuse_gemm_norm=bool(pc.get("fuse_gemm_norm", True)),

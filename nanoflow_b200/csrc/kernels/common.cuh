@@ -137,6 +137,13 @@ NF_DEVICE void tma_store_2d(const CUtensorMap* tm, const void* smem_src, int x, 
       "r"(smem_u32(smem_src)), "r"(x), "r"(y)
       : "memory");
 }
+// Untiled bulk copy shared -> global (both addresses 16-byte aligned, size a multiple of 16 bytes),
+// tracked by the issuing thread's bulk group like a tensor store.
+NF_DEVICE void bulk_store_1d(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst),
+               "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
 NF_DEVICE void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 NF_DEVICE void tma_store_wait_read() {

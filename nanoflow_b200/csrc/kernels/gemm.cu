@@ -74,19 +74,26 @@ constexpr int A_TILE_BYTES = BM * BK * 2;
 struct Geom {
   int bn, out_bn, stages, acc_bufs, tmem_cols, stage_bytes, b_bytes, smem_bytes;
 };
-inline Geom make_geom(int bn, int mt, bool swiglu, int smem_budget, int cg) {
+// Reduce-scatter epilogue, staged form: each epilogue warp keeps a [32 rows][128 columns] bf16 piece of
+// its rows in shared memory (row pitch 272 B, so that the 32 lanes' 16-byte stores spread over all
+// banks) and sends each row's 256 bytes to its owner with one bulk copy.
+constexpr int kRsRunCols = 128;
+constexpr int kRsRowPitch = kRsRunCols * 2 + 16;
+constexpr int kRsStageBytes = 4 * 32 * kRsRowPitch;     // four epilogue warps
+
+inline Geom make_geom(int bn, int mt, bool swiglu, int smem_budget, int cg, int extra = 0) {
   Geom g;
   g.bn = bn;
   g.out_bn = swiglu ? bn / 2 : bn;
   g.b_bytes = (bn / cg) * BK * 2;      // a CTA pair splits the weight tile between its two CTAs
   g.stage_bytes = mt * A_TILE_BYTES + g.b_bytes;
-  int st = (smem_budget - 2048) / g.stage_bytes;
+  int st = (smem_budget - 2048 - extra) / g.stage_bytes;
   g.stages = st > kMaxStages ? kMaxStages : st;
   const int acc_cols = mt * bn;
   g.acc_bufs = acc_cols * 2 <= 512 ? 2 : 1;
   const int need = acc_cols * g.acc_bufs;
   g.tmem_cols = need <= 32 ? 32 : need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512;
-  g.smem_bytes = g.stages * g.stage_bytes + 2048;
+  g.smem_bytes = g.stages * g.stage_bytes + 2048 + extra;   // the extra region follows the ring slots
   return g;
 }
 
@@ -113,6 +120,7 @@ struct DevParams {
   char* rs_heap[8];
   int rs_rank, rs_nranks, rs_rows_cap, rs_epoch;
   long long rs_slab_off, rs_flag_off;
+  int rs_staged;     // partial rows leave through shared memory and bulk copies instead of 16-byte stores
 };
 
 // Wait helper shared by all roles: bounded by wall clock (globaltimer) and by the CTA abort flag.
@@ -514,6 +522,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               }
               continue;
             }
+            if (EPI == 2 && p.rs_staged) {
+              // Staged push: this lane's 32 columns go to its row of the warp's staging piece; when a
+              // run of 128 columns (or the tile's last columns) is complete, one bulk copy per lane
+              // sends the row's run to the owner's slab. A lane only ever reads back what it wrote, so
+              // the generic -> async proxy fence is all the ordering the copy needs.
+              uint8_t* stage_row = smem + STAGES * STAGE_BYTES + (q * 32 + lane) * kRsRowPitch;
+#pragma unroll
+              for (int g8 = 0; g8 < 4; ++g8) {
+                if (g8 * 8 < nval) {
+                  const float* vv = v + g8 * 8;
+                  uint4 o;
+                  o.x = pack_bf16x2(vv[0], vv[1]);
+                  o.y = pack_bf16x2(vv[2], vv[3]);
+                  o.z = pack_bf16x2(vv[4], vv[5]);
+                  o.w = pack_bf16x2(vv[6], vv[7]);
+                  *reinterpret_cast<uint4*>(stage_row + (c & 3) * 64 + g8 * 16) = o;
+                }
+              }
+              const bool run_done = (c & 3) == 3 || (c + 1) * 32 >= OUT_BN;
+              if (run_done) {
+                const int run_col0 = n_blk * OUT_BN + (c & ~3) * 32;
+                int run_end = n_blk * OUT_BN + c * 32 + nval;
+                if (run_end > tile_col_end) run_end = tile_col_end;
+                fence_proxy_async_smem();
+                if (row_ok && run_end > run_col0) {
+                  const int owner = row % p.rs_nranks;
+                  __nv_bfloat16* srow = reinterpret_cast<__nv_bfloat16*>(p.rs_heap[owner] + p.rs_slab_off) +
+                                        (static_cast<long long>(p.rs_rank) * p.rs_rows_cap + row / p.rs_nranks) * p.N;
+                  bulk_store_1d(srow + run_col0, stage_row, static_cast<uint32_t>(run_end - run_col0) * 2u);
+                }
+                tma_store_commit();
+                tma_store_wait_read<0>();   // the staging row may be rewritten
+              }
+              continue;
+            }
             if (EPI == 2) {
               // push the partial row to its owner's slab (posted NVLink stores; the flag raised at
               // the end of the kernel orders them for the reader)
@@ -590,7 +633,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   }
 
-  if (EPI == 2) __threadfence_system();   // this thread's pushes are ordered before the flag below
+  if (EPI == 2) {
+    tma_store_wait<0>();                    // bulk copies of the staged form have been written
+    __threadfence_system();                 // this thread's pushes are ordered before the flag below
+  }
   tc_fence_before();
   // Nothing of the pair may still signal this CTA's barriers or read its shared memory or TMEM once
   // it has exited, so the pair leaves together.
@@ -882,7 +928,8 @@ template <int MT, int EPI, int CG>
 int launch(const nfk_gemm_params& g, int bn, int split_k, bool stream_k, cudaStream_t stream) {
   int budget = g.smem_budget_kb > 0 ? g.smem_budget_kb * 1024 : kSmemMax;
   if (budget > kSmemMax) budget = kSmemMax;
-  const Geom geo = make_geom(bn, MT, EPI == 1, budget, CG);
+  const bool rs_staged = EPI == 2 && g.rs_staged != 0;
+  const Geom geo = make_geom(bn, MT, EPI == 1, budget, CG, rs_staged ? kRsStageBytes : 0);
   if (geo.stages < 2) return NF_ERR_BAD_ARG;      // shared-memory budget too small for this tile
   CUtensorMap tmA, tmB0, tmB1;
   int rc = make_tmap_bf16_2d(&tmA, g.A, g.M, g.K, g.lda, BM, BK);
@@ -975,6 +1022,7 @@ int launch(const nfk_gemm_params& g, int bn, int split_k, bool stream_k, cudaStr
   p.rs_epoch = g.rs_epoch;
   p.rs_slab_off = g.rs_slab_off;
   p.rs_flag_off = g.rs_flag_off;
+  p.rs_staged = rs_staged ? 1 : 0;
   if (CG == 2) {
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(ctas);
@@ -1169,7 +1217,7 @@ extern "C" int nfk_gemm_describe(const nfk_gemm_params* g, nfk_gemm_plan* out) {
   if (rc != NF_OK) return rc;
   int budget = g->smem_budget_kb > 0 ? g->smem_budget_kb * 1024 : kSmemMax;
   if (budget > kSmemMax) budget = kSmemMax;
-  const Geom geo = make_geom(s.bn, s.mt, swiglu, budget, s.cg);
+  const Geom geo = make_geom(s.bn, s.mt, swiglu, budget, s.cg, (rs && g->rs_staged) ? kRsStageBytes : 0);
   if (geo.stages < 2) return NF_ERR_BAD_ARG;
   const int m_tiles = (g->M + BM - 1) / BM;
   const int m_groups = (m_tiles + s.mt * s.cg - 1) / (s.mt * s.cg);

@@ -54,6 +54,9 @@ typedef struct nfk_gemm_params {
   void* norm_out;       // [M, norm_ld] bf16
   long long norm_ld;
   float norm_eps;
+  // Reduce-scatter epilogue: 1 = rows leave through a shared-memory staging piece and one bulk copy per
+  // row and 128 columns (256-byte NVLink writes); 0 = 16-byte stores straight from registers.
+  int rs_staged;
 } nfk_gemm_params;
 
 int nfk_gemm_bf16(const nfk_gemm_params* p, cudaStream_t stream);

@@ -40,7 +40,8 @@ class GemmParams(Structure):
                 ("rs_heap", c_void_p * 8), ("rs_rank", c_int), ("rs_nranks", c_int), ("rs_slab_off", c_longlong),
                 ("rs_rows_cap", c_int), ("rs_flag_off", c_longlong), ("rs_epoch", c_int), ("smem_budget_kb", c_int),
                 ("cta_group", c_int), ("stream_k", c_int),
-                ("norm_w", c_void_p), ("norm_out", c_void_p), ("norm_ld", c_longlong), ("norm_eps", c_float)]
+                ("norm_w", c_void_p), ("norm_out", c_void_p), ("norm_ld", c_longlong), ("norm_eps", c_float),
+                ("rs_staged", c_int)]
 
 
 class RopeAppendParams(Structure):

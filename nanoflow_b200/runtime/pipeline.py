@@ -183,6 +183,7 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
                 p.rs_heap[r] = base
             p.rs_rank, p.rs_nranks, p.rs_rows_cap = rs["rank"], rs["nranks"], rs["rows_cap"]
             p.rs_slab_off, p.rs_flag_off = rs["slab_off"], rs["flag_off"]
+            p.rs_staged = 1 if eng.gemm_rs_staged else 0
             dyn.append(("rs_epoch", g.symbol("epoch")))
         key = tile_key or name.split(".")[-1]
         p.tile_n = eng.gemm_tile_n.get(key, 0)

@@ -173,9 +173,10 @@ def case_fused(rank, world, dev):
         hout = coll.alloc((M, N), torch.bfloat16)
         x_loc = resid.to(dev).clone()
         slot = coll.rs_slot(part, 0, cap)
-        for rep in range(2):                      # twice: flags carry the epoch, counters reset themselves
-            epoch = coll._next_epoch()
+        for rep in range(4):                      # repeated: flags carry the epoch, counters reset themselves;
+            epoch = coll._next_epoch()            # the last two rounds use the staged (bulk-copy) epilogue
             p = GemmParams()
+            p.rs_staged = 1 if rep >= 2 else 0
             p.A, p.B, p.D = a.data_ptr(), w.data_ptr(), 0
             p.lda, p.ldb, p.ldd = K, K, N
             p.M, p.N, p.K, p.epilogue = M, N, K, 2

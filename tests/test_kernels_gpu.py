@@ -511,3 +511,61 @@ def test_kv_move_pages_roundtrip():
     ops.kv_move_pages(pool2, staging, ids, to_staging=False)
     assert torch.equal(pool2[ids.long()], pool[ids.long()])
     assert int((pool2 != 0).sum()) == int((pool[ids.long()] != 0).sum())  # nothing else written
+
+
+@pytest.mark.parametrize("M,N,K,tile_n,cta_group", [(300, 1024, 512, 0, 0), (1000, 2048, 256, 224, 2), (77, 256, 128, 96, 1),
+                                                    (640, 4096, 1024, 256, 2), (129, 1504, 192, 160, 1)])
+def test_gemm_reduce_scatter_epilogue_staged_equals_direct(M, N, K, tile_n, cta_group):
+    """The reduce-scatter epilogue on one GPU: the slabs of all four owners live in one local buffer, so
+    a single launch (rank 1 of 4) can be checked address by address. The staged form (shared memory +
+    one bulk copy per row and 128 columns) must leave exactly what the direct form leaves, in the same
+    places: row i at slab[owner i % 4][rank 1][i // 4], nothing outside, the ready flag of rank 1 raised
+    on every owner."""
+    import ctypes
+
+    from nanoflow_b200 import ops
+    from nanoflow_b200.ops import GemmParams
+
+    world, rank = 4, 1
+    g = torch.Generator(device="cpu").manual_seed(5)
+    a = torch.randn(M, K, generator=g).bfloat16().cuda()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().cuda()
+    cap = (M + world - 1) // world
+    region = ((world * cap * N * 2 + 255) // 256 + 2) * 256          # per-owner "heap": flags (256 B) + slabs + guard
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    outs = []
+    for staged in (0, 1):
+        heap = torch.full((world * region,), 0x7F, dtype=torch.uint8, device="cuda")
+        for r in range(world):
+            heap[r * region:r * region + 256] = 0                       # flag blocks start cleared
+        p = GemmParams()
+        p.A, p.B, p.D = a.data_ptr(), w.data_ptr(), 0
+        p.lda, p.ldb, p.ldd = K, K, N
+        p.M, p.N, p.K, p.epilogue = M, N, K, 2
+        p.tile_n, p.cta_group = tile_n, cta_group
+        for r in range(world):
+            p.rs_heap[r] = heap.data_ptr() + r * region
+        p.rs_rank, p.rs_nranks, p.rs_rows_cap = rank, world, cap
+        p.rs_slab_off, p.rs_flag_off, p.rs_epoch = 256, 0, 7
+        p.rs_staged = staged
+        p.status = status.data_ptr()
+        rc = ops.lib().nfk_gemm_bf16(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert rc == 0, rc
+        torch.cuda.synchronize()
+        ops.check_status(status, "gemm")
+        outs.append(heap)
+    direct, staged = outs
+    assert torch.equal(direct, staged)
+    want = (a.float() @ w.float().t())
+    for owner in range(world):
+        base = owner * region
+        flags = staged[base:base + 256].view(torch.int32)
+        assert flags[rank].item() == 7 and flags[16].item() == 0 and int((flags != 0).sum()) == 1
+        slabs = staged[base + 256:base + 256 + world * cap * N * 2].view(torch.bfloat16).view(world, cap, N)
+        rows = torch.arange(owner, M, world, device="cuda")
+        got = slabs[rank, :rows.numel()].float()
+        assert torch.allclose(got, want[rows], atol=4e-2 * (K / 64) ** 0.5, rtol=2e-2)
+        untouched = torch.ones(world, cap, dtype=torch.bool, device="cuda")
+        untouched[rank, :rows.numel()] = False
+        assert bool((slabs.view(torch.int16)[untouched] == 0x7F7F).all())
+        assert bool((staged[base + 256 + world * cap * N * 2:base + region] == 0x7F).all())
