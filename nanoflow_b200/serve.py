@@ -9,7 +9,8 @@ mix), ``--est_cycle_time`` (simulated seconds per cycle while skipping / in simu
 ``--empty_weight`` (random-init weights instead of converted checkpoints), ``-o`` output prefix,
 ``--allocate_page_num`` (KV pages per GPU; 0 = size from free memory). For tensor parallel runs launch
 one process per GPU with ``python -m torch.distributed.run --nproc-per-node N -m nanoflow_b200.serve ...``.
-Outputs: ``<prefix>.stat / .stat.csv / .req_time / .req_tokens / .schedule`` (see serving/stats.py).
+Outputs: ``<prefix>.stat / .stat.csv / .req_time / .req_tokens / .req_tokens.uniq / .schedule`` (see
+serving/stats.py), ``.req_words`` with a tokenizer, ``.trace.json.gz`` with ``--profile_mode``.
 """
 from __future__ import annotations
 
@@ -33,6 +34,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("-o", "--output_prefix", type=str, default="")
     ap.add_argument("--allocate_page_num", type=int, default=0)
     ap.add_argument("--empty_weight", type=_bool, default=False)
+    ap.add_argument("--output_idx", type=_bool, default=False, help="number the requests in <prefix>.req_words")
+    ap.add_argument("--profile_mode", type=_bool, default=False,
+                    help="run 10 cycles under torch.profiler and write <prefix>.trace.json.gz (Chrome trace)")
     ap.add_argument("--online", type=_bool, default=False, help="release requests by wall clock (arrival times)")
     ap.add_argument("--random_ids", type=_bool, default=True, help="synthetic prompts use uniform-random token ids")
     ap.add_argument("--stop_on_eos", type=_bool, default=False)
@@ -62,8 +66,19 @@ def main(argv=None) -> int:
     if world > 1 and world != model.tp:
         raise SystemExit(f"config is for tp={model.tp} but WORLD_SIZE={world}")
 
+    # A tokenizer is used only when the config names a local directory that holds one (hf_path): trace
+    # rows with input_len == -1 are tokenised with it and <prefix>.req_words is written with it.
+    detok, tok_dir = None, None
+    if eng_cfg.hf_path and os.path.isdir(eng_cfg.hf_path):
+        try:
+            from transformers import AutoTokenizer
+
+            tk = AutoTokenizer.from_pretrained(eng_cfg.hf_path)
+            detok, tok_dir = (lambda ids: tk.decode(list(ids), skip_special_tokens=True)), eng_cfg.hf_path
+        except Exception as e:   # noqa: BLE001  (no tokenizer files there: go on without)
+            print(f"no tokenizer under {eng_cfg.hf_path}: {e}", file=sys.stderr)
     rm = RequestManager(args.trace_path, vocab_size=model.vocab_size, random_ids=args.random_ids)
-    rm.read_request(eng_cfg.model_id if False else None)
+    rm.read_request(tok_dir)
 
     coll = None
     if args.backend == "gpu":
@@ -117,7 +132,28 @@ def main(argv=None) -> int:
         loop.skip_cycles(args.skip_cycles)
     rm.start_processing()
     t0 = time.perf_counter()
-    loop.run(max_cycles=None if args.until_empty else args.run_cycles, until_empty=True)
+    if args.profile_mode:
+        # the older serving loops of the reference export a Chrome trace of ten cycles this way
+        # (pipeline/utils/scheduler.py:434-477)
+        import gzip
+        import tempfile
+        from torch.profiler import ProfilerActivity, profile, record_function
+
+        acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if args.backend == "gpu" else [])
+        with profile(activities=acts, record_shapes=True) as prof:
+            with record_function("model_inference"):
+                loop.run(max_cycles=10, until_empty=True)
+        if rank == 0:
+            out = (args.output_prefix or "serve") + ".trace.json.gz"
+            os.makedirs(os.path.dirname(os.path.abspath(out)) or ".", exist_ok=True)
+            with tempfile.TemporaryDirectory() as tmp:
+                raw = os.path.join(tmp, "trace.json")
+                prof.export_chrome_trace(raw)
+                with open(raw, "rb") as fi, gzip.open(out, "wb") as fo:
+                    fo.write(fi.read())
+            print(f"profile written to {out}")
+    else:
+        loop.run(max_cycles=None if args.until_empty else args.run_cycles, until_empty=True)
     wall = time.perf_counter() - t0
     engine.check_status()
     st = loop.stats
@@ -127,7 +163,8 @@ def main(argv=None) -> int:
               f"(per GPU {summary.token_per_second_per_gpu:.1f})  cycle {summary.cycle_time * 1e3:.2f} ms")
         if args.output_prefix:
             os.makedirs(os.path.dirname(os.path.abspath(args.output_prefix)) or ".", exist_ok=True)
-            write_outputs(args.output_prefix, summary, st.retired, sch.schedule_log)
+            write_outputs(args.output_prefix, summary, st.retired, sch.schedule_log, output_idx=args.output_idx,
+                          detokenize=detok)
     engine.finalize()
     if world > 1:
         torch.distributed.destroy_process_group()

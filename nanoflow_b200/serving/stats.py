@@ -66,7 +66,11 @@ def summarize(retired: Sequence[FlyRequestInfo], wall_seconds: float, cycles: in
 
 def write_outputs(prefix: str, summary: RunSummary, retired: Sequence[FlyRequestInfo],
                   schedule_log: Optional[List[dict]] = None,
-                  detokenize: Optional[Callable[[List[int]], str]] = None) -> List[str]:
+                  detokenize: Optional[Callable[[List[int]], str]] = None, output_idx: bool = False) -> List[str]:
+    """``output_idx``: ``.req_words`` gets a ``Req <n>:`` line before every request, as the reference's
+    flag of that name does (pipeline/utils/serve_8B.py:723-725). ``.req_tokens.uniq`` counts identical
+    output sequences (the reference's ``sort | uniq -c``, serve_8B.py:731): identical prompts must give
+    identical greedy outputs."""
     files = []
     with open(prefix + ".stat", "w") as f:
         f.write(f"TOTAL Time taken: {summary.total_time}\n")
@@ -93,9 +97,19 @@ def write_outputs(prefix: str, summary: RunSummary, retired: Sequence[FlyRequest
         for r in sorted(retired, key=lambda r: r.req_idx):
             f.write(f"{r.req_idx}: {' '.join(str(t) for t in r.output)}\n")
     files.append(prefix + ".req_tokens")
+    counts: dict = {}
+    for r in retired:
+        key = " ".join(str(t) for t in list(r.prompt.tolist()) + list(r.output))
+        counts[key] = counts.get(key, 0) + 1
+    with open(prefix + ".req_tokens.uniq", "w") as f:
+        for key in sorted(counts):
+            f.write(f"{counts[key]:7d} {key}\n")
+    files.append(prefix + ".req_tokens.uniq")
     if detokenize is not None:
         with open(prefix + ".req_words", "w") as f:
-            for r in sorted(retired, key=lambda r: r.req_idx):
+            for n, r in enumerate(sorted(retired, key=lambda r: r.req_idx)):
+                if output_idx:
+                    f.write(f"Req {n}:\n")
                 f.write(f"{r.req_idx}: {detokenize(r.output)}\n")
         files.append(prefix + ".req_words")
     if schedule_log:

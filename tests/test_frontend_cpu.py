@@ -140,3 +140,43 @@ def test_trace_generators():
     kept = traces.filter_lengths([(100, 10), (4000, 10), (3000, 1024), (3072, 1025), (10, 0)])
     assert kept == [(100, 10), (3000, 1024)]
     assert len(traces.real_trace([(100, 10), (200, 20)], 7, rate=5.0)) == 7
+
+
+def test_serve_command_line_on_the_cpu_backend(tmp_path):
+    """``python -m nanoflow_b200.serve`` end to end on the CPU backend: a config file, a trace with identical
+    prompts, the reference's flags, and every output file it promises."""
+    import csv
+    import gzip
+    import json
+
+    from nanoflow_b200 import serve
+    from nanoflow_b200.config import make_config
+
+    cfg = make_config("tiny", gpu_num=2, global_batch_size=48, pipeline_type="PLLM", nanobatch_sizes=[16, 32])
+    cfg_path = tmp_path / "tiny.json"
+    cfg_path.write_text(json.dumps(cfg))
+    trace = tmp_path / "trace.csv"
+    with open(trace, "w") as f:
+        f.write("idx,input_len,output_len,arrival\n")
+        for i in range(6):
+            f.write(f"{i},20,5,0.0\n")
+    prefix = str(tmp_path / "out" / "run")
+    rc = serve.main(["-t", str(trace), "-c", str(cfg_path), "--backend", "cpu", "--until_empty", "true",
+                     "--random_ids", "false", "-o", prefix, "--allocate_page_num", "64", "--output_idx", "true"])
+    assert rc == 0
+    for ext in (".stat", ".stat.csv", ".req_time", ".req_tokens", ".req_tokens.uniq", ".schedule"):
+        assert (tmp_path / "out" / ("run" + ext)).exists(), ext
+    rows = list(csv.DictReader(open(prefix + ".stat.csv")))
+    assert len(rows) == 1 and float(rows[0]["token_per_second"]) > 0
+    # synthetic prompts are range(len): six identical prompts must give one distinct output
+    uniq = open(prefix + ".req_tokens.uniq").read().strip().splitlines()
+    assert len(uniq) == 1 and uniq[0].split()[0] == "6"
+    assert len(open(prefix + ".req_tokens").read().strip().splitlines()) == 6
+    # profile mode: ten cycles under torch.profiler, Chrome trace written compressed
+    prefix2 = str(tmp_path / "prof" / "run")
+    rc = serve.main(["-t", str(trace), "-c", str(cfg_path), "--backend", "cpu", "--random_ids", "false", "-o", prefix2,
+                     "--allocate_page_num", "64", "--profile_mode", "true"])
+    assert rc == 0
+    with gzip.open(prefix2 + ".trace.json.gz", "rt") as f:
+        tr = json.load(f)
+    assert any(ev.get("name") == "model_inference" for ev in tr["traceEvents"])
