@@ -7,6 +7,8 @@ result file exists), so an interrupted sweep resumes where it stopped.
     python -m nanoflow_b200.eval.harness online        --model llama3-70B --gpus 8 --rates 5 10 20 40 60 --out results/
     python -m nanoflow_b200.eval.harness ablation      --model llama2-70B --gpus 8 --out results/
     python -m nanoflow_b200.eval.harness summarize     --out results/
+    python -m nanoflow_b200.eval.harness merge         --model llama2-70B --out results/   # pllm.json, the reference's layout
+    python -m nanoflow_b200.eval.harness plot          --out results/                      # figures from pllm.json
 
 Experiment families and defaults follow the reference (pipeline/eval/eval-fix-offline/run.py:42-50:
 empty weights, skip cycles then 1500 run cycles; pipeline/eval/eval-real-online-2048/run.py:45-49,
@@ -149,9 +151,102 @@ def summarize(a) -> Dict:
     return res
 
 
+ABLATION_LABELS = {"non-overlap": "Non-overlap", "nanobatch-only": "Nanobatch-only", "2048": "Nanoflow",
+                   "pllm-offload": "Nanoflow-offload"}
+
+
+def merge(a) -> Dict:
+    """Write ``pllm.json`` in the layout of the reference's merged results
+    (pipeline/eval/merge_results.py:10-62 plus the ``ablation`` block pipeline/eval/plot_all.py:52-53
+    reads): tokens/s/GPU per fixed and per real-length workload, request rate -> normalised latency per
+    online sweep, tokens/s/GPU per ablation variant. Points that were not run are left out."""
+    res = {"offline_throughput_const": {}, "offline_throughput_real_trace": {}, "online_throughput": {}, "ablation": {}}
+    for fn in sorted(os.listdir(a.out)):
+        if not fn.endswith(".stat.csv"):
+            continue
+        name = fn[:-len(".stat.csv")]
+        st = read_stat(os.path.join(a.out, fn))
+        kind, _, rest = name.partition("-")
+        if not rest.startswith(a.model + "-"):
+            continue
+        tail = rest[len(a.model) + 1:]
+        if kind == "fixed":
+            res["offline_throughput_const"][tail] = st["token_per_second_per_gpu"]
+        elif kind == "real":
+            res["offline_throughput_real_trace"][tail] = st["token_per_second_per_gpu"]
+        elif kind == "ablation":
+            res["ablation"][ABLATION_LABELS.get(tail, tail)] = {"1024-512": st["token_per_second_per_gpu"]}
+        elif kind == "online":
+            batch, _, rate = tail.rpartition("-r")
+            sweep = res["online_throughput"].setdefault(batch, {"request_rate": [], "normalized_latency": []})
+            sweep["request_rate"].append(float(rate))
+            sweep["normalized_latency"].append(st["average_normalize_latency"])
+    for sweep in res["online_throughput"].values():
+        order = sorted(range(len(sweep["request_rate"])), key=lambda i: sweep["request_rate"][i])
+        sweep["request_rate"] = [sweep["request_rate"][i] for i in order]
+        sweep["normalized_latency"] = [sweep["normalized_latency"][i] for i in order]
+    with open(os.path.join(a.out, "pllm.json"), "w") as f:
+        json.dump(res, f, indent=1)
+    return res
+
+
+def plot(a) -> Dict:
+    """Figures from ``pllm.json`` (run ``merge`` first): offline throughput per workload beside the
+    published numbers of the other systems, normalised latency over request rate, the ablation bars.
+    PNG files with matplotlib; without it the same series as one text file of bar charts. The
+    reference draws these with pipeline/eval/plot_all.py:62-326."""
+    from .baseline_data import OFFLINE_REAL
+    with open(os.path.join(a.out, "pllm.json")) as f:
+        data = json.load(f)
+    series = []          # (title, unit, [(label, value)])
+    for title, block, published in (("Offline throughput, constant lengths", "offline_throughput_const", OFFLINE_FIXED),
+                                    ("Offline throughput, real length distributions", "offline_throughput_real_trace",
+                                     OFFLINE_REAL)):
+        for wl, ours in data.get(block, {}).items():
+            bars = [(f"{k} (published, A100)", float(v)) for k, v in published.get(wl, {}).items()]
+            series.append((f"{title}: {wl}", "tokens/s/GPU", bars + [("this engine", float(ours))]))
+    for batch, sweep in data.get("online_throughput", {}).items():
+        series.append((f"Online, {batch}: normalised latency by request rate", "s/token",
+                       [(f"{r:g} req/s", float(v)) for r, v in zip(sweep["request_rate"], sweep["normalized_latency"])]))
+    if data.get("ablation"):
+        series.append(("Ablation, 1024-512", "tokens/s/GPU",
+                       [(k, float(v["1024-512"])) for k, v in data["ablation"].items()]))
+    written = []
+    try:
+        import matplotlib
+        matplotlib.use("Agg")
+        import matplotlib.pyplot as plt
+    except ImportError:
+        plt = None
+    if plt is not None:
+        for n, (title, unit, bars) in enumerate(series):
+            fig, ax = plt.subplots(figsize=(8, 4))
+            ax.bar([b[0] for b in bars], [b[1] for b in bars])
+            ax.set_title(title)
+            ax.set_ylabel(unit)
+            ax.tick_params(axis="x", rotation=30)
+            fig.tight_layout()
+            path = os.path.join(a.out, f"figure_{n}.png")
+            fig.savefig(path)
+            plt.close(fig)
+            written.append(path)
+    else:
+        path = os.path.join(a.out, "figures.txt")
+        with open(path, "w") as f:
+            for title, unit, bars in series:
+                f.write(f"{title} [{unit}]\n")
+                top = max([v for _, v in bars] + [1e-30])
+                width = max(len(b[0]) for b in bars) if bars else 0
+                for label, v in bars:
+                    f.write(f"  {label:<{width}} {'#' * max(1, int(round(50 * v / top)))} {v:.6g}\n")
+                f.write("\n")
+        written.append(path)
+    return {"figures": written, "series": len(series)}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("family", choices=["fixed-offline", "real-offline", "online", "ablation", "summarize"])
+    ap.add_argument("family", choices=["fixed-offline", "real-offline", "online", "ablation", "summarize", "merge", "plot"])
     ap.add_argument("--model", default="llama2-70B")
     ap.add_argument("--gpus", type=int, default=8)
     ap.add_argument("--batch", type=int, default=2048)
@@ -167,7 +262,7 @@ def main(argv=None) -> int:
     ap.add_argument("--dry_run", action="store_true")
     a = ap.parse_args(argv)
     fn = {"fixed-offline": fixed_offline, "real-offline": real_offline, "online": online, "ablation": ablation,
-          "summarize": summarize}[a.family]
+          "summarize": summarize, "merge": merge, "plot": plot}[a.family]
     print(json.dumps(fn(a), indent=1))
     return 0
 

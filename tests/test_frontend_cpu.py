@@ -180,3 +180,31 @@ def test_serve_command_line_on_the_cpu_backend(tmp_path):
     with gzip.open(prefix2 + ".trace.json.gz", "rt") as f:
         tr = json.load(f)
     assert any(ev.get("name") == "model_inference" for ev in tr["traceEvents"])
+
+
+def test_eval_harness_runs_resumes_merges_and_plots_on_the_cpu_backend(tmp_path):
+    """One fixed-length point, a two-rate online sweep and the summary / merge / plot steps of the
+    experiment runner on the tiny model (CPU backend, one process per point)."""
+    import json
+    import os
+
+    from nanoflow_b200.eval import harness
+
+    out = str(tmp_path / "res")
+    common = ["--model", "tiny", "--gpus", "1", "--batch", "48", "--out", out, "--backend", "cpu",
+              "--run_cycles", "40", "--skip_cycles", "0"]
+    assert harness.main(["fixed-offline", "--workloads", "512-2", *common]) == 0
+    stat = os.path.join(out, "fixed-tiny-512-2.stat.csv")
+    assert os.path.exists(stat)
+    before = os.path.getmtime(stat)
+    assert harness.main(["fixed-offline", "--workloads", "512-2", *common]) == 0     # finished point: skipped
+    assert os.path.getmtime(stat) == before
+    assert harness.main(["online", "--rates", "40", "80", "--requests", "6", *common]) == 0
+    assert harness.main(["summarize", "--out", out]) == 0
+    assert harness.main(["merge", "--model", "tiny", "--out", out]) == 0
+    merged = json.load(open(os.path.join(out, "pllm.json")))
+    assert merged["offline_throughput_const"]["512-2"] > 0
+    sweep = merged["online_throughput"]["b48"]
+    assert sweep["request_rate"] == [40.0, 80.0] and all(v > 0 for v in sweep["normalized_latency"])
+    assert harness.main(["plot", "--out", out]) == 0
+    assert os.path.exists(os.path.join(out, "figures.txt")) or os.path.exists(os.path.join(out, "figure_0.png"))
