@@ -93,3 +93,44 @@ def test_qwen_style_bias_and_llama31_rope_scaling_paths():
                 assert r.output == oracle.generate(prompts[r.req_idx].tolist(), 6)
         finally:
             del C.MODEL_ARCHS[name]
+
+
+def test_module_level_api_with_the_reference_bindings_names():
+    """setModelConfig -> createModelWeight -> init -> config -> update / run_async / run_async_wait ->
+    getPipelineOutput -> finalize, as a user of the reference's ``pllm_python`` module would call them."""
+    import nanoflow_b200.pllm_python as pllm
+    from nanoflow_b200.config import make_config
+    from nanoflow_b200.models import random_full_weights
+
+    raw = make_config("tiny", gpu_num=2, global_batch_size=48, pipeline_type="PLLM", nanobatch_sizes=[16, 32])
+    cfg = pllm.setModelConfig(raw, backend="cpu")
+    with pytest.raises(RuntimeError, match="init first"):
+        pllm.config()
+    weights = pllm.createModelWeight(seed=0)
+    assert len(weights) == 2
+    pllm.init(weights, pllm.createInitData(num_pages=64))
+    pllm.config()
+    assert pllm.num_pages() == 64
+    oracle = ReferenceLlama(cfg.model, random_full_weights(cfg.model, seed=0))
+    prompt = np.arange(5, 25, dtype=np.int32)
+    rm = RequestManager(vocab_size=cfg.model.vocab_size)
+    rm.add_request(len(prompt), 6, 0.0, prompt=prompt)
+    rm.finalize_stats()
+    rm.simulate_issue(1.0)
+    pool = DistKVPool(cfg.model.run_layers, cfg.model.num_kv_heads, cfg.model.head_dim, 64, 16, 2)
+    sch = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=48, nanobatch_sizes=[16, 32],
+                    average_prefill_length=20, average_decode_length=6, group_size=cfg.model.group_size)
+    out = []
+    while True:
+        plan = sch.schedule()
+        if plan is None:
+            break
+        pllm.update(plan)
+        pllm.run_async()
+        toks = pllm.run_async_wait()
+        assert (pllm.getPipelineOutput() == toks).all()
+        sch.process_outputs(plan, toks)
+        out.extend(int(t) for t in toks)
+    pllm.finalize()
+    assert pllm.engine() is None
+    assert out[:6] == oracle.generate(prompt.tolist(), 6)
