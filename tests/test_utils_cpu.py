@@ -1,6 +1,8 @@
 """Command-line helpers and the GEMM autotuner's candidate list (no GPU needed)."""
 import csv
 
+import pytest
+
 from nanoflow_b200.ops import autotune
 from nanoflow_b200.utils import schedule_tools as st
 
@@ -140,3 +142,31 @@ def test_guarded_arena_reports_writes_outside_a_buffer():
         pass
     else:
         raise AssertionError("guard size must be a multiple of 16")
+
+
+def test_parameter_search_finds_the_best_point_and_writes_a_loadable_config(tmp_path):
+    from nanoflow_b200.config import load_config
+    from nanoflow_b200.eval import search as S
+
+    assert S.split_sizes(8192, 0.5) == [4096, 4096] and S.split_sizes(8192, 0.44) == [3584, 4608]
+    assert S.split_sizes(1408, 0.01) == [128, 1280] and S.split_sizes(1408, 0.99) == [1280, 128]
+    with pytest.raises(ValueError):
+        S.split_sizes(200, 0.5)
+    calls = []
+
+    def runner(pt):       # a separable surface with its top at share 0.45 (3712 of 8192), 96 CTAs, tail 0.25
+        calls.append(pt)
+        return 50000 - 4e-3 * (pt["nano"][0] - 3712) ** 2 - 2.0 * abs(pt["comm_ctas"] - 96) - 4000 * abs(pt["decode_tail"] - 0.25)
+
+    best, v, log = S.search(8192, [0.40, 0.45, 0.50, 0.55, 0.60], [64, 96, 128], [0.0, 0.25, 0.5], runner, rounds=3)
+    assert best["nano"] == [3712, 4480] and best["comm_ctas"] == 96 and best["decode_tail"] == 0.25
+    assert v == max(r["value"] for r in log) and len(log) == len(calls)
+    keys = [(tuple(c["nano"]), c["comm_ctas"], c["decode_tail"]) for c in calls]
+    assert len(set(keys)) == len(keys)                      # no point measured twice
+    assert len(calls) < 5 * 3 * 3                           # and far fewer than the full grid
+    files = S.write_results(str(tmp_path), "llama2-70B", 8, 8192, "PLLM", best, v, log)
+    cfg = load_config(files[0], tp=8)
+    assert cfg.engine.resolved_nanobatches() == [3712, 4480] and cfg.engine.sm_budget["comm"] == 96
+    assert cfg.engine.decode_tail_fraction == 0.25 and cfg.engine.pipeline_type == "PLLM"
+    rows = open(files[1]).read().strip().splitlines()
+    assert rows[0] == "nano_0,nano_1,comm_ctas,decode_tail,tokens_per_s" and len(rows) == len(log) + 1
