@@ -115,6 +115,8 @@ def main():
     ap.add_argument("--no-fuse-norm", action="store_true", help="one GPU: separate RMSNorm launches after O / down")
     ap.add_argument("--serial-attention", action="store_true",
                     help="prefill attention after decode attention on one stream instead of beside it")
+    ap.add_argument("--net-streams", type=int, default=1, choices=[1, 2],
+                    help="2: the collectives of odd nano-batches run on a second network stream")
     ap.add_argument("--decode-tail", type=float, default=0.0,
                     help="share of the decode requests' context scheduled into the last nano-batch (0 = all first)")
     ap.add_argument("--virtual-tp", type=int, default=0,
@@ -203,6 +205,7 @@ def main():
         cfg.engine.sm_budget["comm"] = args.comm_ctas
     cfg.engine.fuse_gemm_rs = bool(args.fuse_rs)
     cfg.engine.gemm_rs_staged = bool(args.fuse_rs_staged)
+    cfg.engine.net_streams = args.net_streams
     cfg.engine.fuse_gemm_norm = not args.no_fuse_norm
     cfg.engine.prefill_beside_decode = not args.serial_attention
     if args.layers:

@@ -156,6 +156,7 @@ class EngineConfig:
     prefill_beside_decode: bool = True     # prefill attention on a stream of its own, beside the decode kernel
     debug_guards: bool = False             # guard words around activation buffers, checked with the status word
     decode_tail_fraction: float = 0.0      # share of the decode context scheduled into the last nano-batch
+    net_streams: int = 1                   # 2: collectives of odd nano-batches get a second network stream
     gemm_shapes: Dict[str, Dict[str, int]] = field(default_factory=dict)   # "<op>.nb<k>" -> pinned launcher arguments
     decode_chunk_pages: int = 0            # 0 = choose per iteration
     use_cuda_graph: bool = False
@@ -241,6 +242,7 @@ def parse_config(raw: Dict[str, Any], *, tp: Optional[int] = None) -> NanoflowCo
         prefill_beside_decode=bool(pc.get("prefill_beside_decode", True)),
         debug_guards=bool(pc.get("debug_guards", False)),
         decode_tail_fraction=float(pc.get("decode_tail_fraction", 0.0)),
+        net_streams=int(pc.get("net_streams", 1)),
         model_id=sc.get("model", ""),
         weight_path=sc.get("weight_path", ""),
         hf_path=sc.get("hf_path", ""),

@@ -8,8 +8,8 @@
 // the GPU issues the iteration, so the Python scheduler forms the next batch while this one is
 // being launched; `wait(ticket)` blocks until the GPU has finished that iteration.
 //
-// Dependencies across streams are CUDA events; ops on one stream rely on stream order. The six
-// stream classes (gemm, attn, net, other, copy, attn2) fork from and join back into the caller's main
+// Dependencies across streams are CUDA events; ops on one stream rely on stream order. The seven
+// stream classes (gemm, attn, net, other, copy, attn2, net2) fork from and join back into the caller's main
 // stream, so consecutive iterations stay ordered and torch work queued on that stream composes.
 //
 // Graph mode (set_graph_mode): after two plain iterations the same issue sequence is recorded by
@@ -45,7 +45,7 @@ namespace py = pybind11;
 
 namespace {
 
-constexpr int kNumStreamClasses = 6;
+constexpr int kNumStreamClasses = 7;
 constexpr int kTickets = 8;
 
 using LaunchFn = int (*)(const void*, cudaStream_t);

@@ -2,7 +2,7 @@
 
 A graph is an ordered list of :class:`Op`: a kernel entry point of ``libnanoflow_kernels.so`` in the
 uniform ``int fn(const params*, cudaStream_t)`` form, its parameter block (a ``ctypes.Structure``),
-the *stream class* it runs on (``gemm``, ``attn``, ``net``, ``other``, ``copy``, ``attn2``), the ops it must
+the *stream class* it runs on (``gemm``, ``attn``, ``net``, ``other``, ``copy``, ``attn2``, ``net2``), the ops it must
 wait for, and a list of *dynamic fields*: integer members of the parameter block that are
 overwritten from a symbol table before every launch (token counts of a nano-batch, request ranges,
 number of attention work items, ...). Buffers never move, so an iteration is replayed by updating
@@ -24,7 +24,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 from .. import ops as _ops
 
-STREAM_CLASSES = ("gemm", "attn", "net", "other", "copy", "attn2")
+STREAM_CLASSES = ("gemm", "attn", "net", "other", "copy", "attn2", "net2")
 
 
 class NormParams(Structure):

@@ -124,6 +124,10 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
     # the SMs that round leaves idle. The O projection, next on the GEMM stream, waits for both, so no
     # GEMM is ever queued beside the pair.
     prefill_stream = "attn2" if eng.prefill_beside_decode else S("attn")
+    # Collectives of one nano-batch never depend on those of another, and each is bound by the latency of
+    # its peer loads rather than by the links; with two network streams the collective of an odd
+    # nano-batch starts when its GEMM is done instead of queueing behind the previous one.
+    net_of = lambda k: "net2" if (eng.net_streams > 1 and S("net") == "net" and k % 2 == 1) else S("net")
 
     T_all = g.symbol("T")
     n_sample = g.symbol("n_sample")
@@ -302,7 +306,7 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         o = gemm(f"L{l}.nb{k}.o", bufs.attn_out, lw.wo, None if fuse_rs else part, k,
                  deps=[dec, pre, last_x_writer[k]], layer=l, tile_key="o", rs=slab)
         ar1, _ = coll.all_reduce(g, f"L{l}.nb{k}.ar_o", part, starts[k], nb_T[k], hidden, [o], l, k,
-                                 stream=S("net"), norm_w=lw.ln_ffn, norm_out=bufs.h, eps=model.rms_norm_eps,
+                                 stream=net_of(k), norm_w=lw.ln_ffn, norm_out=bufs.h, eps=model.rms_norm_eps,
                                  status=st, num_ctas=comm_ctas, resid=x_res, sum_out=x_res, push_sum=False,
                                  slab=slab)
         return ar1
@@ -329,7 +333,7 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
                  tile_key="down", rs=slab)
         nxt = None if last else w.layers[(l + 1) % model.num_layers].ln_attn
         ar2, fused2 = coll.all_reduce(g, f"L{l}.nb{k}.ar_d", part, starts[k], nb_T[k], hidden, [d], l, k,
-                                      stream=S("net"), norm_w=nxt, norm_out=None if last else bufs.h,
+                                      stream=net_of(k), norm_w=nxt, norm_out=None if last else bufs.h,
                                       eps=model.rms_norm_eps, status=st, num_ctas=comm_ctas, resid=x_res,
                                       sum_out=x_res, push_sum=last, slab=slab)
         last_x_writer[k] = ar2
