@@ -170,3 +170,39 @@ def test_parameter_search_finds_the_best_point_and_writes_a_loadable_config(tmp_
     assert cfg.engine.decode_tail_fraction == 0.25 and cfg.engine.pipeline_type == "PLLM"
     rows = open(files[1]).read().strip().splitlines()
     assert rows[0] == "nano_0,nano_1,comm_ctas,decode_tail,tokens_per_s" and len(rows) == len(log) + 1
+
+
+def test_whatif_replay_of_an_op_graph():
+    from nanoflow_b200.utils import whatif
+
+    g = whatif.structural_graph(8, [4096, 4096], layers=3)
+    names = [op.name for op in g.ops]
+    assert "L2.nb1.ar_d" in names and "L0.nb0.attn_prefill" in names
+    kind = lambda op: op.name.split(".")[-1]
+    base = {"qkv": 90, "rope_append": 14, "attn_decode": 300, "attn_prefill": 60, "o": 70, "gate_up": 390, "down": 176,
+            "ar_o": 420, "ar_d": 480}
+    dur = [float(base.get(kind(op), 5)) for op in g.ops]
+    sim = whatif.simulate(g, dur)
+    # dependencies and stream order hold in the replay
+    last = {}
+    for i, op in enumerate(g.ops):
+        assert all(sim["start"][i] >= sim["end"][d] - 1e-9 for d in op.deps)
+        if op.stream in last:
+            assert sim["start"][i] >= sim["end"][last[op.stream]] - 1e-9
+        last[op.stream] = i
+        assert abs(sim["end"][i] - sim["start"][i] - dur[i]) < 1e-9
+    path = sim["critical_path"]
+    assert sim["end"][path[-1]] == sim["makespan"] and sim["start"][path[0]] == 0.0
+    assert all(abs(sim["start"][b] - sim["end"][a]) < 1e-9 for a, b in zip(path, path[1:]))
+    # a single stream adds everything up; overlap can only be shorter; a faster collective never hurts
+    assert abs(whatif.simulate(g, dur, single_stream=True)["makespan"] - sum(dur)) < 1e-6
+    assert sim["makespan"] < sum(dur)
+    faster = whatif.scale_durations(g, dur, {"ar_o": "0.5", "ar_d.nb1": "-100"})
+    assert faster[names.index("L1.nb0.ar_o")] == 210 and faster[names.index("L1.nb1.ar_d")] == 380
+    assert faster[names.index("L1.nb0.ar_d")] == 480
+    assert whatif.simulate(g, faster)["makespan"] <= sim["makespan"]
+    assert whatif.stream_gaps(g, sim, "gemm") > 0
+    # durations come from a timeline by op name
+    ev = [{"ph": "X", "name": "L1.nb0.qkv", "dur": 77.0}, {"ph": "M", "name": "x"}]
+    d2 = whatif.durations_from_timeline(g, ev, default_us=4.0, launch_gap_us=1.0)
+    assert d2[names.index("L1.nb0.qkv")] == 78.0 and d2[names.index("L0.nb0.qkv")] == 5.0
