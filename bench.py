@@ -294,8 +294,17 @@ def main():
         toks = eng.run_async_wait()
         sch.process_outputs(plan, toks)
         ev = eng.timeline()
+        per_rank = [ev]
+        if world > 1:
+            # every rank's timeline goes into the file: a collective's duration on a rank that reaches it
+            # early contains the wait for the last rank, which only the comparison across ranks shows
+            per_rank = [None] * world
+            torch.distributed.all_gather_object(per_rank, [tuple(e) for e in ev])
         if rank == 0:
-            tl.dump(ev, args.timeline, pid=rank)
+            if world > 1:
+                print("timeline ranks:", json.dumps(tl.dump_ranks(per_rank, args.timeline)), file=sys.stderr)
+            else:
+                tl.dump(ev, args.timeline, pid=rank)
             agg = tl.aggregate(ev)
             print("timeline:", json.dumps({k: v for k, v in list(agg.items())[:14]}), file=sys.stderr)
 

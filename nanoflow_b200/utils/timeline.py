@@ -53,3 +53,25 @@ def to_chrome_trace(events: Iterable[Event], pid: int = 0) -> dict:
 def dump(events: List[Event], path: str, pid: int = 0) -> None:
     with open(path, "w") as f:
         json.dump({"aggregate": aggregate(events), **to_chrome_trace(events, pid)}, f)
+
+
+def dump_ranks(per_rank: List[List[Event]], path: str) -> Dict[str, Dict[str, float]]:
+    """One trace file with a process per rank, plus per rank the busy time of its compute stream and the
+    total time of its collectives: on the ranks that reach a collective early its duration contains the
+    wait for the last rank, so a rank whose collectives are short and whose compute stream is busiest
+    is the one the others wait for."""
+    events: List[dict] = []
+    summary: Dict[str, Dict[str, float]] = {}
+    for rank, ev in enumerate(per_rank):
+        tr = to_chrome_trace(ev, pid=rank)
+        events.extend(tr["traceEvents"])
+        events.append({"name": "process_name", "ph": "M", "pid": rank, "args": {"name": f"rank {rank}"}})
+        span = (max(e[3] for e in ev) - min(e[2] for e in ev)) if ev else 0.0
+        summary[f"rank{rank}"] = {
+            "iteration_us": round(span, 1),
+            "compute_stream_busy_us": round(sum(b - a for _n, st, a, b in ev if st == "gemm"), 1),
+            "collectives_us": round(sum(b - a for n, _st, a, b in ev if op_kind(n).startswith(("ar_", "ag_"))), 1)}
+    with open(path, "w") as f:
+        json.dump({"ranks": summary, "aggregate": aggregate(per_rank[0]) if per_rank else {},
+                   "traceEvents": events, "displayTimeUnit": "ms"}, f)
+    return summary

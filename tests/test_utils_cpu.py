@@ -206,3 +206,19 @@ def test_whatif_replay_of_an_op_graph():
     ev = [{"ph": "X", "name": "L1.nb0.qkv", "dur": 77.0}, {"ph": "M", "name": "x"}]
     d2 = whatif.durations_from_timeline(g, ev, default_us=4.0, launch_gap_us=1.0)
     assert d2[names.index("L1.nb0.qkv")] == 78.0 and d2[names.index("L0.nb0.qkv")] == 5.0
+
+
+def test_timeline_of_several_ranks_in_one_trace(tmp_path):
+    import json
+
+    from nanoflow_b200.utils import timeline as tl
+
+    r0 = [("L0.nb0.qkv", "gemm", 0.0, 90.0), ("L0.nb0.ar_o", "net", 90.0, 500.0), ("L0.nb0.gate_up", "gemm", 500.0, 900.0)]
+    r1 = [("L0.nb0.qkv", "gemm", 0.0, 300.0), ("L0.nb0.ar_o", "net", 300.0, 500.0), ("L0.nb0.gate_up", "gemm", 500.0, 900.0)]
+    path = tmp_path / "t.json"
+    s = tl.dump_ranks([r0, r1], str(path))
+    assert s["rank0"]["collectives_us"] == 410.0 and s["rank1"]["collectives_us"] == 200.0
+    assert s["rank1"]["compute_stream_busy_us"] == 700.0 > s["rank0"]["compute_stream_busy_us"]     # rank 1 is the late one
+    d = json.load(open(path))
+    assert {e["pid"] for e in d["traceEvents"]} == {0, 1} and d["ranks"] == s
+    assert d["aggregate"]["_iteration"]["total_us"] == 900.0
