@@ -208,3 +208,21 @@ def test_eval_harness_runs_resumes_merges_and_plots_on_the_cpu_backend(tmp_path)
     assert sweep["request_rate"] == [40.0, 80.0] and all(v > 0 for v in sweep["normalized_latency"])
     assert harness.main(["plot", "--out", out]) == 0
     assert os.path.exists(os.path.join(out, "figures.txt")) or os.path.exists(os.path.join(out, "figure_0.png"))
+
+
+def test_bench_reference_arm_reports_why_it_cannot_run():
+    """``bench.py --impl reference`` must print one JSON line with ``impl`` and ``unavailable`` and exit 0
+    wherever the reference cannot be installed (it is a CMake project with empty submodules here)."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "1",
+                          "--steps", "2", "--warmup", "3"], capture_output=True, text=True, timeout=300, cwd=root)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [ln for ln in res.stdout.strip().splitlines() if ln.startswith("{")]
+    assert len(lines) == 1
+    out = json.loads(lines[0])
+    assert out["impl"] == "reference" and isinstance(out["unavailable"], str) and "\n" not in out["unavailable"]
