@@ -134,3 +134,64 @@ def test_module_level_api_with_the_reference_bindings_names():
     pllm.finalize()
     assert pllm.engine() is None
     assert out[:6] == oracle.generate(prompt.tolist(), 6)
+
+
+def test_oracle_agrees_with_the_hugging_face_llama_implementation():
+    """The fp32 oracle every engine test is compared with, against an independent implementation: the
+    tiny model's weights loaded into ``transformers.LlamaForCausalLM`` (the reference's ground truth is HF
+    greedy decoding, groundtruth/test.py:12-38). Logits of a 32-token prompt and 16 greedy tokens; also
+    with Llama-3.1 rotary scaling and with QKV bias (Qwen2)."""
+    transformers = pytest.importorskip("transformers")
+    from nanoflow_b200.models import random_full_weights
+
+    def hf_model(cfg, fw, cls, conf_cls, **extra):
+        conf = conf_cls(hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size, num_hidden_layers=cfg.num_layers,
+                        num_attention_heads=cfg.num_q_heads, num_key_value_heads=cfg.num_kv_heads,
+                        vocab_size=cfg.vocab_size, rms_norm_eps=cfg.rms_norm_eps, max_position_embeddings=4096,
+                        tie_word_embeddings=False, attn_implementation="eager", **extra)
+        model = cls(conf).float().eval()
+        sd = {"model.embed_tokens.weight": fw.embed, "model.norm.weight": fw.norm, "lm_head.weight": fw.lm_head}
+        for l, lay in enumerate(fw.layers):
+            p = f"model.layers.{l}."
+            sd.update({p + "self_attn.q_proj.weight": lay.wq, p + "self_attn.k_proj.weight": lay.wk,
+                       p + "self_attn.v_proj.weight": lay.wv, p + "self_attn.o_proj.weight": lay.wo,
+                       p + "mlp.gate_proj.weight": lay.wg, p + "mlp.up_proj.weight": lay.wu,
+                       p + "mlp.down_proj.weight": lay.wd, p + "input_layernorm.weight": lay.ln_attn,
+                       p + "post_attention_layernorm.weight": lay.ln_ffn})
+            if lay.bq is not None:
+                sd.update({p + "self_attn.q_proj.bias": lay.bq, p + "self_attn.k_proj.bias": lay.bk,
+                           p + "self_attn.v_proj.bias": lay.bv})
+        missing, unexpected = model.load_state_dict({k: v.float() for k, v in sd.items()}, strict=False)
+        assert not unexpected and all("rotary" in m or "inv_freq" in m for m in missing), (missing, unexpected)
+        return model
+
+    import dataclasses
+
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, 1024, size=32, dtype=np.int64)
+    base = builtin_config("tiny").model
+    llama31 = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+               "original_max_position_embeddings": 64}
+    cases = [("llama", base, transformers.LlamaForCausalLM, transformers.LlamaConfig, {}),
+             ("llama-3.1 rope", dataclasses.replace(base, rope_scaling=dict(llama31)), transformers.LlamaForCausalLM,
+              transformers.LlamaConfig, {"rope_scaling": dict(llama31)}),
+             ("qwen2 bias", dataclasses.replace(base, qkv_bias=True), transformers.Qwen2ForCausalLM,
+              transformers.Qwen2Config, {})]
+    for name, cfg, cls, conf_cls, extra in cases:
+        fw = random_full_weights(cfg, seed=0, std=0.05)
+        assert (fw.layers[0].bq is not None) == cfg.qkv_bias
+        oracle = ReferenceLlama(cfg, fw)
+        rope = dict(extra.pop("rope_scaling", None) or {"rope_type": "default"}, rope_theta=cfg.rope_theta)
+        try:
+            hf = hf_model(cfg, fw, cls, conf_cls, rope_parameters=rope, **extra)
+        except TypeError:      # older transformers: separate rope_theta / rope_scaling arguments
+            sc = {k: v for k, v in rope.items() if k != "rope_theta"}
+            hf = hf_model(cfg, fw, cls, conf_cls, rope_theta=cfg.rope_theta,
+                          rope_scaling=None if sc == {"rope_type": "default"} else sc, **extra)
+        with torch.no_grad():
+            want = hf(torch.from_numpy(prompt)[None]).logits[0]
+            got, _ = oracle.forward(torch.from_numpy(prompt))
+            assert torch.allclose(got, want, atol=2e-4, rtol=1e-4), (name, (got - want).abs().max())
+            gen = hf.generate(torch.from_numpy(prompt)[None], max_new_tokens=16, do_sample=False,
+                              pad_token_id=0)[0, 32:].tolist()
+        assert oracle.generate(prompt.tolist(), 16) == gen, name
