@@ -156,3 +156,46 @@ def load_weights(nranks: int, weight_dir: str, cfg: ModelConfig, device="cpu", d
     """All ranks' shards, loaded in a thread pool like the reference loader."""
     with ThreadPoolExecutor(max_workers=min(8, nranks)) as ex:
         return list(ex.map(lambda r: load_rank_weights(weight_dir, cfg, r, nranks, device, dtype), range(nranks)))
+
+
+def convert_hf_checkpoint(hf_path: str, weight_dir: str, nranks: int, dtype=torch.bfloat16) -> List[str]:
+    """Hugging Face snapshot directory -> ``weight_rank_<i>.pt`` files for ``nranks`` ranks."""
+    os.makedirs(weight_dir, exist_ok=True)
+    return save_weights(load_hf_checkpoint(hf_path), nranks, weight_dir, dtype=dtype)
+
+
+def ensure_converted(weight_dir: str, hf_path: str, nranks: int, dtype=torch.bfloat16) -> bool:
+    """Convert once: if ``weight_dir`` lacks the per-rank files and ``hf_path`` is a local snapshot with
+    safetensors files, write them (the reference's serving script does the same when its weight path is
+    missing, pipeline/utils/serve_8B.py:613-623). Returns whether the per-rank files exist afterwards."""
+    have = weight_dir and all(os.path.exists(os.path.join(weight_dir, f"weight_rank_{r}.pt")) for r in range(nranks))
+    if have:
+        return True
+    if not (weight_dir and hf_path and os.path.isdir(hf_path) and
+            any(fn.endswith(".safetensors") for fn in os.listdir(hf_path))):
+        return False
+    convert_hf_checkpoint(hf_path, weight_dir, nranks, dtype)
+    return True
+
+
+def main(argv=None) -> int:
+    """``python -m nanoflow_b200.models.weights --hf <snapshot dir> --out <dir> --nranks 8``"""
+    import argparse
+
+    ap = argparse.ArgumentParser(description="Hugging Face safetensors -> per-rank weight files "
+                                             "(the reference's weightSaver.py layout)")
+    ap.add_argument("--hf", required=True, help="local snapshot directory (config.json + *.safetensors)")
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--nranks", type=int, default=8)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32"])
+    a = ap.parse_args(argv)
+    dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[a.dtype]
+    for path in convert_hf_checkpoint(a.hf, a.out, a.nranks, dt):
+        print(path)
+    return 0
+
+
+if __name__ == "__main__":
+    import sys
+
+    sys.exit(main())

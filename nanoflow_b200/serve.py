@@ -53,7 +53,7 @@ def main(argv=None) -> int:
 
     from .config import load_config
     from .models import random_full_weights, random_rank_weights, shard_weights
-    from .models.weights import load_rank_weights
+    from .models.weights import ensure_converted, load_rank_weights, load_weights
     from .serving import DistKVPool, RequestManager, Scheduler
     from .serving.loop import ServingLoop
     from .serving.stats import summarize, write_outputs
@@ -92,7 +92,15 @@ def main(argv=None) -> int:
 
             dist.init_process_group("nccl", device_id=dev)
             coll = TpCollectives(rank, world, dev)
-        if args.empty_weight or not eng_cfg.weight_path or not os.path.isdir(eng_cfg.weight_path):
+        have_files = False
+        if not args.empty_weight and eng_cfg.weight_path:
+            # converted per-rank files; written first from the Hugging Face snapshot if they are missing
+            if rank == 0:
+                have_files = ensure_converted(eng_cfg.weight_path, eng_cfg.hf_path, max(1, world))
+            if world > 1:
+                torch.distributed.barrier()
+            have_files = ensure_converted(eng_cfg.weight_path, "", max(1, world))
+        if not have_files:
             weights = random_rank_weights(model, rank, max(1, world), dev)
         else:
             weights = load_rank_weights(eng_cfg.weight_path, model, rank, max(1, world), device=dev)
@@ -102,10 +110,14 @@ def main(argv=None) -> int:
         from .runtime.cpu_backend import CpuEngine
 
         tp = model.tp
-        fw = random_full_weights(model, seed=0)
         num_pages = args.allocate_page_num or 4096
-        engine = CpuEngine(cfg, [shard_weights(fw, model, r, tp, dtype=torch.float32) for r in range(tp)],
-                           num_pages=num_pages)
+        if not args.empty_weight and eng_cfg.weight_path and ensure_converted(eng_cfg.weight_path, eng_cfg.hf_path, tp,
+                                                                                dtype=torch.float32):
+            shards = load_weights(tp, eng_cfg.weight_path, model, dtype=torch.float32)
+        else:
+            fw = random_full_weights(model, seed=0)
+            shards = [shard_weights(fw, model, r, tp, dtype=torch.float32) for r in range(tp)]
+        engine = CpuEngine(cfg, shards, num_pages=num_pages)
 
     pool = DistKVPool(model.run_layers, model.num_kv_heads, model.head_dim, num_pages, eng_cfg.page_size, model.tp)
     sch = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=eng_cfg.global_batch_size,

@@ -192,6 +192,7 @@ def test_oracle_agrees_with_the_hugging_face_llama_implementation():
             want = hf(torch.from_numpy(prompt)[None]).logits[0]
             got, _ = oracle.forward(torch.from_numpy(prompt))
             assert torch.allclose(got, want, atol=2e-4, rtol=1e-4), (name, (got - want).abs().max())
-            gen = hf.generate(torch.from_numpy(prompt)[None], max_new_tokens=16, do_sample=False,
+            ids = torch.from_numpy(prompt)[None]
+            gen = hf.generate(ids, attention_mask=torch.ones_like(ids), max_new_tokens=16, do_sample=False,
                               pad_token_id=0)[0, 32:].tolist()
         assert oracle.generate(prompt.tolist(), 16) == gen, name

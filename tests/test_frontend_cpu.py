@@ -226,3 +226,53 @@ def test_bench_reference_arm_reports_why_it_cannot_run():
     assert len(lines) == 1
     out = json.loads(lines[0])
     assert out["impl"] == "reference" and isinstance(out["unavailable"], str) and "\n" not in out["unavailable"]
+
+
+def test_hugging_face_snapshot_is_converted_and_served(tmp_path):
+    """A Hugging Face snapshot directory (config.json + safetensors) named by ``hf_path``: serve writes the
+    per-rank weight files on first use, loads them, and the generated tokens are those of
+    ``transformers`` greedy decoding on the same prompt; the converter's command line gives the same files."""
+    import json
+
+    transformers = pytest.importorskip("transformers")
+    pytest.importorskip("safetensors")
+    from nanoflow_b200 import serve
+    from nanoflow_b200.config import make_config
+    from nanoflow_b200.models import weights as W
+
+    torch.manual_seed(0)
+    conf = transformers.LlamaConfig(hidden_size=256, intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
+                                    num_key_value_heads=2, vocab_size=1024, rms_norm_eps=1e-5,
+                                    max_position_embeddings=4096, tie_word_embeddings=False,
+                                    attn_implementation="eager")
+    hf = transformers.LlamaForCausalLM(conf).float().eval()
+    for prm in hf.parameters():                      # larger weights: well-separated logits
+        prm.data.mul_(3.0)
+    hf_dir = tmp_path / "hf"
+    hf.save_pretrained(str(hf_dir), safe_serialization=True)
+    wdir = tmp_path / "converted"
+    cfg = make_config("tiny", gpu_num=2, global_batch_size=48, pipeline_type="PLLM", nanobatch_sizes=[16, 32])
+    cfg["serve_configs"]["weight_path"], cfg["serve_configs"]["hf_path"] = str(wdir), str(hf_dir)
+    cfg_path = tmp_path / "tiny.json"
+    cfg_path.write_text(json.dumps(cfg))
+    trace = tmp_path / "trace.csv"
+    trace.write_text("idx,input_len,output_len,arrival\n0,20,8,0.0\n1,33,8,0.0\n")
+    prefix = str(tmp_path / "run")
+    assert serve.main(["-t", str(trace), "-c", str(cfg_path), "--backend", "cpu", "--until_empty", "true",
+                       "--random_ids", "false", "-o", prefix, "--allocate_page_num", "64"]) == 0
+    assert sorted(p.name for p in wdir.iterdir()) == ["weight_rank_0.pt", "weight_rank_1.pt"]
+    got = {}
+    for line in open(prefix + ".req_tokens").read().strip().splitlines():
+        idx, toks = line.split(":")
+        got[int(idx)] = [int(t) for t in toks.split()]
+    for idx, n in ((0, 20), (1, 33)):
+        prompt = torch.arange(n)[None]               # synthetic prompts are 0, 1, 2, ... (not random here)
+        with torch.no_grad():
+            want = hf.generate(prompt, attention_mask=torch.ones_like(prompt), max_new_tokens=8, do_sample=False,
+                               pad_token_id=0)[0, n:].tolist()
+        assert got[idx] == want, idx
+    # the command-line converter writes the same tensors
+    out2 = tmp_path / "cli"
+    assert W.main(["--hf", str(hf_dir), "--out", str(out2), "--nranks", "2", "--dtype", "fp32"]) == 0
+    a, b = torch.load(out2 / "weight_rank_1.pt"), torch.load(wdir / "weight_rank_1.pt")
+    assert a.keys() == b.keys() and all(torch.equal(a[k], b[k]) for k in a)
