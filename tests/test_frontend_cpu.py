@@ -276,3 +276,22 @@ def test_hugging_face_snapshot_is_converted_and_served(tmp_path):
     assert W.main(["--hf", str(hf_dir), "--out", str(out2), "--nranks", "2", "--dtype", "fp32"]) == 0
     a, b = torch.load(out2 / "weight_rank_1.pt"), torch.load(wdir / "weight_rank_1.pt")
     assert a.keys() == b.keys() and all(torch.equal(a[k], b[k]) for k in a)
+
+
+def test_demo_entry_points(tmp_path, capsys):
+    """``demo serve`` (trace of identical prompts -> serve -> first output) on the tiny model and CPU backend;
+    ``demo perf --dry_run`` lists one serve command per experiment point without running any."""
+    from nanoflow_b200 import demo
+
+    out = tmp_path / "d"
+    assert demo.main(["serve", "--model", "tiny", "--backend", "cpu", "--decode-length", "5", "--requests", "4",
+                      "--out", str(out), "--prompt", "one two three four five six"]) == 0
+    txt = capsys.readouterr().out
+    assert "first request (demo.req_tokens): 0:" in txt
+    lines = open(out / "demo.req_tokens").read().strip().splitlines()
+    assert len(lines) == 4 and len({ln.split(":")[1] for ln in lines}) == 1      # identical prompts, identical outputs
+    assert open(out / "trace.csv").read().splitlines()[1].startswith("0,6,5,")   # six words -> six synthetic ids
+    assert demo.main(["perf", "--model", "tiny", "--gpus", "1", "--backend", "cpu", "--out", str(tmp_path / "p"),
+                      "--dry_run", "--batch", "48"]) == 0
+    cmds = [ln for ln in capsys.readouterr().out.splitlines() if "nanoflow_b200.serve" in ln]
+    assert len(cmds) >= 5 + 1 + 7      # fixed workloads, one length distribution, the request-rate sweep
