@@ -122,6 +122,9 @@ def main():
     ap.add_argument("--virtual-tp", type=int, default=0,
                     help="one GPU runs rank 0's share of a tensor-parallel job of this degree, collectives reduced "
                          "to their local part (development aid; the JSON line is marked invalid)")
+    ap.add_argument("--fake-wire-us-per-row", type=float, default=0.0,
+                    help="with --virtual-tp: every all-reduce is followed on its stream by a sleep of this many "
+                         "microseconds per row of its nano-batch, standing in for the absent ranks")
     ap.add_argument("--skip-cycles", type=int, default=1600)
     ap.add_argument("--executor", default="auto", help="auto | native | graph (native executor, iterations "
                     "captured and launched as CUDA graphs) | python")
@@ -174,6 +177,7 @@ def main():
 
         tp = args.virtual_tp
         coll = TpCollectives(0, 1, dev)
+        coll.fake_wire_us_per_row = args.fake_wire_us_per_row
     # KV capacity decides how many requests fit, hence the steady-state dense batch: with 1024/512
     # requests a batch of T tokens holds T/3 decode requests of ~1280 tokens each.
     probe = builtin_config(args.model, gpu_num=tp, global_batch_size=2048)

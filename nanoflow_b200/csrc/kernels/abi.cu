@@ -40,6 +40,10 @@ extern "C" int nfk_memcpy_p(const nfk_memcpy_params* p, cudaStream_t s) {
   return cudaMemcpyAsync(p->dst, p->src, static_cast<size_t>(bytes), cudaMemcpyDefault, s) == cudaSuccess
              ? NF_OK : NF_ERR_CUDA;
 }
+extern "C" int nfk_sleep_p(const nfk_sleep_params* p, cudaStream_t s) {
+  if (!p) return NF_ERR_BAD_ARG;
+  return p->micros == 0 ? NF_OK : nfk_sleep(p->micros, s);
+}
 extern "C" int nfk_kv_move_p(const nfk_kv_move_params* p, cudaStream_t s) {
   if (!p) return NF_ERR_BAD_ARG;
   return nfk_kv_move_pages(p->pool, p->staging, p->page_ids, p->n_pages, p->page_bytes, p->num_pages,

@@ -282,6 +282,8 @@ int nfk_argmax_p(const nfk_argmax_params* p, cudaStream_t s);
 int nfk_argmax_combine_p(const nfk_argmax_combine_params* p, cudaStream_t s);
 int nfk_copy_cols_p(const nfk_copy_cols_params* p, cudaStream_t s);
 int nfk_memcpy_p(const nfk_memcpy_params* p, cudaStream_t s);
+typedef struct nfk_sleep_params { int micros; } nfk_sleep_params;   // nfk_sleep as an op of the graph
+int nfk_sleep_p(const nfk_sleep_params* p, cudaStream_t s);
 int nfk_kv_move_p(const nfk_kv_move_params* p, cudaStream_t s);
 
 #ifdef __cplusplus

@@ -58,6 +58,7 @@ class TpCollectives(CollectiveHooks):
         self.num_ctas = num_ctas
         self.fuse_norm = fuse_norm
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.fake_wire_us_per_row = 0.0     # see all_reduce(): sleep standing in for absent ranks
         self._epoch = 0
         self._adhoc_flags = self.heap.alloc_bytes(FLAG_BYTES)
 
@@ -68,6 +69,7 @@ class TpCollectives(CollectiveHooks):
         self = cls.__new__(cls)
         self.rank, self.tp, self.device = rank, world, torch.device("cpu")
         self.num_ctas, self.fuse_norm = 16, True
+        self.fake_wire_us_per_row = 0.0
         self.status = torch.zeros(1, dtype=torch.int32)
         self._epoch = 0
 
@@ -154,6 +156,14 @@ class TpCollectives(CollectiveHooks):
         p.status = (status if status is not None else self.status).data_ptr()
         idx = g.add(name, p, stream, deps=deps, dyn=[("rows", rows_sym), ("epoch", g.symbol("epoch"))],
                     layer=layer, nano=nano)
+        if self.fake_wire_us_per_row > 0 and nano >= 0:
+            # Stand-in for the time on the wire when the other ranks are not there (virtual tensor
+            # parallelism on one GPU): a one-thread sleep on the collective's stream, as long as the
+            # nano-batch's rows times ``fake_wire_us_per_row``. The reference does the same with its
+            # SleepWrapper when built without ENABLE_NETWORK (pipeline/include/pipeline.h:98-100).
+            from ..runtime.graph import SleepParams
+            idx = g.add(name + ".wire", SleepParams(0), stream, deps=[idx],
+                        dyn=[("micros", g.symbol(f"nb{nano}_wire_us"))], layer=layer, nano=nano)
         return idx, fused
 
     def rs_slot(self, part: torch.Tensor, slab_row0: int, rows_cap: int) -> dict:

@@ -62,6 +62,10 @@ class MemcpyParams(Structure):
     _fields_ = [("dst", c_void_p), ("src", c_void_p), ("elem_bytes", c_longlong), ("count", c_int)]
 
 
+class SleepParams(Structure):
+    _fields_ = [("micros", c_int)]
+
+
 class KvMoveParams(Structure):
     _fields_ = [("pool", c_void_p), ("staging", c_void_p), ("page_ids", c_void_p), ("n_pages", c_int),
                 ("page_bytes", c_longlong), ("num_pages", c_int), ("direction", c_int), ("num_ctas", c_int),
@@ -78,7 +82,7 @@ KERNEL_OF = {
     NormParams: "nfk_norm_p",
     EmbeddingParams: "nfk_embedding_p", GatherParams: "nfk_gather_p", ArgmaxParams: "nfk_argmax_p",
     ArgmaxCombineParams: "nfk_argmax_combine_p", CopyColsParams: "nfk_copy_cols_p",
-    MemcpyParams: "nfk_memcpy_p", KvMoveParams: "nfk_kv_move_p",
+    MemcpyParams: "nfk_memcpy_p", KvMoveParams: "nfk_kv_move_p", SleepParams: "nfk_sleep_p",
 }
 
 

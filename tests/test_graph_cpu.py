@@ -10,7 +10,7 @@ from nanoflow_b200.runtime.pipeline import Buffers, IoSpec, build_graph
 from nanoflow_b200.utils import depcheck
 
 
-def _host_graph(pipeline_type, tp, nano, gbs=48, fuse_rs=False, net_streams=1):
+def _host_graph(pipeline_type, tp, nano, gbs=48, fuse_rs=False, net_streams=1, fake_wire=0.0):
     cfg = builtin_config("tiny", gpu_num=tp, global_batch_size=gbs, pipeline_type=pipeline_type, nanobatch_sizes=nano)
     m, e = cfg.model, cfg.engine
     e.fuse_gemm_rs = fuse_rs
@@ -19,6 +19,8 @@ def _host_graph(pipeline_type, tp, nano, gbs=48, fuse_rs=False, net_streams=1):
     fw = random_full_weights(m, seed=0)
     w = shard_weights(fw, m, 0, tp, dtype=torch.bfloat16)
     coll = TpCollectives.for_analysis(0, tp) if tp > 1 else None
+    if coll is not None:
+        coll.fake_wire_us_per_row = fake_wire
     bf = torch.bfloat16
     z = lambda *s, dtype=bf: torch.zeros(*s, dtype=dtype)
     sym = (lambda *s, dtype=bf: coll.alloc(s, dtype)) if coll else z
@@ -299,3 +301,36 @@ def test_second_network_stream_keeps_the_graph_ordered(nano, fuse_rs):
     for j, op in enumerate(g.ops):
         for d in op.deps:
             assert anc[launches[j]] >> launches[d] & 1
+
+
+def test_sleep_ops_stand_in_for_the_wire_time_of_absent_ranks():
+    """fake_wire_us_per_row: every all-reduce is followed on its stream by a sleep op whose length is a
+    symbol (rows of the nano-batch x the factor, set per iteration), and whatever waited for the
+    all-reduce now waits for the sleep."""
+    import ctypes
+
+    from nanoflow_b200.runtime.graph import SleepParams
+    from nanoflow_b200.runtime.native import NativeExecutor
+
+    g, acc, keep = _host_graph("PLLM", 2, [16, 32], fake_wire=0.11)
+    plain, _, keep2 = _host_graph("PLLM", 2, [16, 32])
+    ars = [i for i, op in enumerate(g.ops) if op.kernel == "nfk_allreduce"]
+    wires = [i for i, op in enumerate(g.ops) if op.kernel == "nfk_sleep_p"]
+    assert len(wires) == len(ars) == len([op for op in plain.ops if op.kernel == "nfk_allreduce"])
+    assert len(g.ops) == len(plain.ops) + len(wires) and {"nb0_wire_us", "nb1_wire_us"} <= set(g.symbols)
+    for a, w in zip(ars, wires):
+        assert w == a + 1 and g.ops[w].deps == [a] and g.ops[w].stream == g.ops[a].stream
+        assert g.ops[w].name == g.ops[a].name + ".wire" and isinstance(g.ops[w].params, SleepParams)
+        users = [op for op in g.ops if a in op.deps]
+        assert users == [g.ops[w]]                       # nothing else waits for the bare all-reduce
+    assert not depcheck.check(g, acc)
+    ex = NativeExecutor(g, None, single_stream=False, host_only=True)
+    ex.mod.host_log_clear()
+    syms = _symbols(g, 0)
+    syms["nb0_wire_us"], syms["nb1_wire_us"] = 123, 456
+    ex.wait(ex.submit(syms))
+    launches = [r for r in ex.mod.host_log() if r[0] == LAUNCH]
+    ex.close()
+    for w in wires:
+        micros = ctypes.c_int.from_buffer_copy(launches[w][5][:4]).value
+        assert micros == (123 if g.ops[w].nano == 0 else 456)
