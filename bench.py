@@ -334,6 +334,9 @@ def main():
                        "input_len": args.input_len, "output_len": args.output_len,
                        "parallelism": f"tp{world}", "pipeline_type": ptype, "layers": model.run_layers,
                        "nanobatches": cfg.engine.resolved_nanobatches(), "fused_gemm_reduce_scatter": bool(cfg.engine.fuse_gemm_rs and tp > 1),
+                       "collective_ctas": cfg.engine.sm_budget.get("comm", 0) if tp > 1 else 0,
+                       "prefill_beside_decode": bool(cfg.engine.prefill_beside_decode),
+                       "decode_tail": args.decode_tail, "net_streams": cfg.engine.net_streams,
                        "kv_pages": eng.num_pages, "tokens_per_step": round(tokens_dev / args.steps, 1),
                        "l2": "inputs larger than L2 (weights per GPU >> 126 MB); no flush",
                        "steady_state": f"{args.skip_cycles} scheduler-only cycles before warm-up",
