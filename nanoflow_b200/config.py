@@ -395,6 +395,18 @@ def shipped_variants(model: str) -> Dict[str, Dict[str, Any]]:
     big = 4096 if small else 8192
     out[f"b200-{big}"] = make_config(model, gpu_num=gpus, global_batch_size=big, pipeline_type=full,
                                      nanobatch_sizes=[big // 2, big // 2])
+    # The reference's two scaled-down sets (pipeline/config_all/<model>/fewer_layers, correct_40G):
+    # four layers' worth of weights with all layers run (weights re-used round-robin, so the timing is
+    # that of the full model at a fraction of the memory), and a fixed small KV pool.
+    for name in ("768", "1024", "2048", "non-overlap", "nanobatch-only"):
+        few = copy.deepcopy(out[name])
+        few["model_configs"]["run_layer"] = hf["num_hidden_layers"]
+        few["model"]["num_hidden_layers"] = 4
+        out[f"fewer_layers/{name}"] = few
+    for name in ("1024" if small else "2048", "non-overlap", "nanobatch-only"):
+        kv = copy.deepcopy(out[name])
+        kv["model_configs"]["allocate_kv_data_batch"] = 100 if small else 400      # x 64 pages
+        out[f"small_kv/{name}"] = kv
     return out
 
 

@@ -29,6 +29,19 @@ def test_shipped_configs_parse_and_derive_per_gpu_sizes():
     assert q.model.qkv_bias and q.engine.pipeline_type == "KQVBIAS" and q.model.vocab_local * 8 >= 152064
     l31 = C.load_config(C.shipped_config_path("llama3.1-8B", "2048"))
     assert l31.model.rope_scaling["rope_type"] == "llama3" and l31.engine.pipeline_type == "LOCAL"
+    # the scaled-down sets: few layers' weights run as the full depth; a fixed small KV pool
+    nested = glob.glob(str(C.CONFIG_DIR / "*" / "*" / "*.json"))
+    assert len(nested) >= 8 * len(glob.glob(str(C.CONFIG_DIR / "*")))
+    for f in nested:
+        C.load_config(f)
+    few = C.load_config(C.shipped_config_path("llama2-70B", "fewer_layers/2048"))
+    assert (few.model.num_layers, few.model.run_layers) == (4, 80) and few.model.param_count() < 5e9
+    small = C.load_config(C.shipped_config_path("llama2-70B", "small_kv/2048"))
+    assert small.engine.num_pages == 400 * 64 and small.model.num_layers == 80
+    # the files on disk are what the generator writes
+    import json
+    for name, raw in C.shipped_variants("llama3-8B").items():
+        assert json.load(open(C.shipped_config_path("llama3-8B", name))) == raw, name
 
 
 def test_reference_config_file_loads_unchanged():
