@@ -45,18 +45,6 @@ NF_DEVICE uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-NF_DEVICE uint32_t lane_id() { return threadIdx.x & 31; }
-
-NF_DEVICE bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(pred));
-  return pred != 0;
-}
-
 // ---- mbarrier ----------------------------------------------------------------------------------
 NF_DEVICE void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
@@ -89,23 +77,6 @@ NF_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return false;
 }
 
-// Bounded wait that polls without suspending: for barriers on a short critical path, where the
-// wake-up granularity of try_wait would cost more than the spinning does. Returns false on timeout.
-NF_DEVICE bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t it = 0; it < (1u << 26); ++it) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
 
 NF_DEVICE void report_status(unsigned int* status, unsigned int code) {
   if (status != nullptr) atomicCAS(status, 0u, code);
@@ -120,21 +91,6 @@ NF_DEVICE void tma_load_2d(void* smem_dst, const CUtensorMap* tm, uint64_t* bar,
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
       "l"(reinterpret_cast<uint64_t>(tm)), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
-NF_DEVICE void tma_load_3d(void* smem_dst, const CUtensorMap* tm, uint64_t* bar, int x, int y,
-                           int z) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(smem_dst)),
-      "l"(reinterpret_cast<uint64_t>(tm)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
-      : "memory");
-}
-NF_DEVICE void tma_store_2d(const CUtensorMap* tm, const void* smem_src, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
-          reinterpret_cast<uint64_t>(tm)),
-      "r"(smem_u32(smem_src)), "r"(x), "r"(y)
       : "memory");
 }
 // Untiled bulk copy shared -> global (both addresses 16-byte aligned, size a multiple of 16 bytes),
@@ -290,18 +246,13 @@ NF_DEVICE void umma_bf16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// Arrives once on the barrier at `bar_cluster_addr` (either CTA of the pair) when every pair MMA
-// issued so far by this thread has completed.
+// Arrives once on the barrier at `bar`'s offset in both CTAs of the pair when every pair MMA issued
+// so far by this thread has completed.
 NF_DEVICE void umma_commit_pair_both(uint64_t* bar) {
   const uint16_t mask = 3;
   asm volatile(
       "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
           smem_u32(bar)), "h"(mask)
-      : "memory");
-}
-NF_DEVICE void umma_commit_pair(uint32_t bar_cluster_addr) {
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
       : "memory");
 }
 
@@ -326,11 +277,6 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
 NF_DEVICE float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-NF_DEVICE float warp_max(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
 NF_DEVICE uint32_t pack_bf16x2(float lo, float hi) {
