@@ -27,7 +27,7 @@ from typing import Dict, List, Optional
 
 from ..config import CONFIG_DIR, make_config, shipped_variants
 from ..datasets.traces import FIXED_WORKLOADS, fixed_trace, lognormal_lengths, poisson_arrivals, write_trace
-from .baseline_data import OFFLINE_FIXED, OPTIMAL_LLAMA2_70B_A100
+from .baseline_data import OFFLINE_FIXED, OPTIMAL_LLAMA2_70B_A100, speedup_table
 
 
 def _serve_cmd(gpus: int, args: List[str], port: int = 29540) -> List[str]:
@@ -144,7 +144,7 @@ def summarize(a) -> Dict:
             res[name] = st
             for wl, row in OFFLINE_FIXED.items():
                 if name.endswith(wl) and name.startswith("fixed-llama2-70B"):
-                    st["speedup_vs_published"] = {k: st["token_per_second_per_gpu"] / v for k, v in row.items()}
+                    st["speedup_vs_published"] = speedup_table(st["token_per_second_per_gpu"], wl)
                     st["fraction_of_a100_optimal"] = st["token_per_second_per_gpu"] / OPTIMAL_LLAMA2_70B_A100
     with open(os.path.join(a.out, "results.json"), "w") as f:
         json.dump(res, f, indent=1)

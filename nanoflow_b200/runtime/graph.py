@@ -148,10 +148,6 @@ class OpGraph:
         return hb
 
 
-def field_offset(params: Structure, name: str) -> int:
-    return getattr(type(params), name).offset
-
-
 class PyExecutor:
     """Replays a graph from Python on torch streams (reference semantics for the C++ executor)."""
 

@@ -139,7 +139,15 @@ def main(argv=None) -> int:
 
         health = Heartbeat(_get_default_store(), rank, world)
     loop = ServingLoop(engine, sch, rm, simulated_time=not args.online, est_cycle_time=args.est_cycle_time,
-                       offload=offload, health=health)
+                       offload=offload, health=health, trace_phases=args.profile_mode)
+    log = None
+    if args.output_prefix:
+        # one log file per rank beside the outputs (the reference writes log_<rank>.txt, pipeline/src/pipeline.cu:15-19)
+        from .utils.logging import rank_logger
+        log = rank_logger(rank, os.path.dirname(os.path.abspath(args.output_prefix)) or ".")
+        log.info("serving %s: %d GPUs, pipeline %s, dense batch %d, nano-batches %s, %d KV pages, trace %s",
+                 eng_cfg.model_id or args.config_path, model.tp, eng_cfg.pipeline_type, eng_cfg.global_batch_size,
+                 eng_cfg.resolved_nanobatches(), num_pages, args.trace_path)
     if args.skip_cycles:
         loop.skip_cycles(args.skip_cycles)
     rm.start_processing()
@@ -170,6 +178,9 @@ def main(argv=None) -> int:
     engine.check_status()
     st = loop.stats
     summary = summarize(st.retired, wall, st.cycles, model.tp, rm.average_prefill_length, rm.average_decode_length)
+    if log is not None:
+        log.info("done: %d cycles, %d requests retired, %.1f tokens/s, %.2f ms per cycle", st.cycles, summary.retired,
+                 summary.token_per_second, summary.cycle_time * 1e3)
     if rank == 0:
         print(f"cycles {st.cycles}  retired {summary.retired}  tokens/s {summary.token_per_second:.1f} "
               f"(per GPU {summary.token_per_second_per_gpu:.1f})  cycle {summary.cycle_time * 1e3:.2f} ms")

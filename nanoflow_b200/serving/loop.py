@@ -40,7 +40,14 @@ class LoopStats:
 
 class ServingLoop:
     def __init__(self, engine, scheduler: Scheduler, request_manager: RequestManager, *,
-                 simulated_time: bool = True, est_cycle_time: float = 0.175, offload=None, health=None):
+                 simulated_time: bool = True, est_cycle_time: float = 0.175, offload=None, health=None,
+                 trace_phases: bool = False):
+        """``trace_phases``: put a named range (NVTX + profiler) around every phase of a cycle: schedule,
+        update, launch, wait_previous, process_outputs."""
+        import contextlib
+
+        from ..utils.nvtx import nvtx_range
+        self._phase = nvtx_range if trace_phases else (lambda name: contextlib.nullcontext())
         self.engine, self.scheduler, self.rm = engine, scheduler, request_manager
         self.simulated_time = simulated_time
         self.est_cycle_time = est_cycle_time
@@ -73,19 +80,25 @@ class ServingLoop:
 
     def step(self) -> Optional[BatchPlan]:
         """One cycle. Returns the plan that was launched (None if there was nothing to run)."""
+        phase = self._phase
         self._release()
-        plan = self.scheduler.schedule()
+        with phase("schedule"):
+            plan = self.scheduler.schedule()
         if self.health is not None:
             self.health.beat()
             self.health.check()    # raises PeerFailure before anything that waits on a peer is launched
         if plan is not None:
-            self.engine.update(plan)
-            self.engine.run_async()
+            with phase("update"):
+                self.engine.update(plan)
+            with phase("launch"):
+                self.engine.run_async()
             if self.offload is not None:
                 self.offload.on_iteration(plan)
         if self._prev is not None:
-            tokens = self.engine.run_async_wait()
-            self.scheduler.process_outputs(self._prev, tokens)
+            with phase("wait_previous"):
+                tokens = self.engine.run_async_wait()
+            with phase("process_outputs"):
+                self.scheduler.process_outputs(self._prev, tokens)
             if self.offload is not None:
                 self.offload.on_complete(self._prev, self.scheduler)
             self.stats.tokens_processed += self._prev.num_tokens

@@ -192,7 +192,11 @@ def test_serve_command_line_on_the_cpu_backend(tmp_path):
     assert rc == 0
     with gzip.open(prefix2 + ".trace.json.gz", "rt") as f:
         tr = json.load(f)
-    assert any(ev.get("name") == "model_inference" for ev in tr["traceEvents"])
+    names = {ev.get("name") for ev in tr["traceEvents"]}
+    assert {"model_inference", "schedule", "update", "launch", "wait_previous", "process_outputs"} <= names
+    # one log file per rank beside the outputs
+    text = open(tmp_path / "out" / "log_0.txt").read()
+    assert "serving" in text and "done:" in text and "requests retired" in text
 
 
 def test_eval_harness_runs_resumes_merges_and_plots_on_the_cpu_backend(tmp_path):
