@@ -75,7 +75,7 @@ def main(argv=None) -> int:
 
             tk = AutoTokenizer.from_pretrained(eng_cfg.hf_path)
             detok, tok_dir = (lambda ids: tk.decode(list(ids), skip_special_tokens=True)), eng_cfg.hf_path
-        except Exception as e:   # noqa: BLE001  (no tokenizer files there: go on without)
+        except (OSError, ValueError, KeyError, ImportError) as e:   # no tokenizer files there: go on without
             print(f"no tokenizer under {eng_cfg.hf_path}: {e}", file=sys.stderr)
     rm = RequestManager(args.trace_path, vocab_size=model.vocab_size, random_ids=args.random_ids)
     rm.read_request(tok_dir)
