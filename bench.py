@@ -115,6 +115,7 @@ def main():
     ap.add_argument("--no-fuse-norm", action="store_true", help="one GPU: separate RMSNorm launches after O / down")
     ap.add_argument("--serial-attention", action="store_true",
                     help="prefill attention after decode attention on one stream instead of beside it")
+    ap.add_argument("--ar-wide", action="store_true", help="8 GPUs: all-reduce with twice the loads in flight per phase")
     ap.add_argument("--net-streams", type=int, default=1, choices=[1, 2],
                     help="2: the collectives of odd nano-batches run on a second network stream")
     ap.add_argument("--decode-tail", type=float, default=0.0,
@@ -164,6 +165,7 @@ def main():
 
         dist.init_process_group("nccl", device_id=dev)
         coll = TpCollectives(rank, world, dev)
+        coll.wide = bool(args.ar_wide)
 
     def barrier():
         if world > 1:

@@ -144,10 +144,17 @@ __device__ __forceinline__ float block_sum_ar(float v, float* red) {
 // next to a resident GEMM CTA: the collective then runs beside the GEMMs of another nano-batch
 // instead of waiting for SMs. Loads over NVLink have microseconds of latency, so each thread keeps
 // 16 independent 16-byte loads in flight (CH vectors x NR ranks) before it reduces and pushes.
-template <int NR, bool NORM>
+//
+// WIDE doubles the loads a thread has in flight per phase (32 instead of 16; used with 8 ranks), which
+// halves the number of dependent load phases per row. The registers come from not keeping the summed
+// row for the norm pass: the thread reads its own stores back (from sum_out, or from its own copy of
+// the buffer when the sum is pushed), which are in L2.
+template <int NR, bool NORM, bool WIDE>
 __global__ void __launch_bounds__(kArThreads, 3)
 allreduce_kernel(nfk_allreduce_params p) {
-  constexpr int CH = NR >= 8 ? 2 : (NR >= 4 ? 4 : 8);     // vectors per chunk
+  constexpr int CH0 = NR >= 8 ? 2 : (NR >= 4 ? 4 : 8);    // vectors per chunk
+  constexpr int CH = (WIDE && CH0 < 8) ? 2 * CH0 : CH0;
+  constexpr bool REREAD = WIDE && NORM;
   __shared__ float red[8];
   const nfk_comm_ctx& c = p.ctx;
   // src_mode 1: the producer GEMM pushed the partial rows into local slabs and raised the ready flags
@@ -162,7 +169,7 @@ allreduce_kernel(nfk_allreduce_params p) {
   const int owned = (p.rows - c.rank + NR - 1) / NR;       // rows rank, rank+NR, ... (may be <= 0)
   for (int k = blockIdx.x; k < owned; k += gridDim.x) {
     const long long row = c.rank + static_cast<long long>(NR) * k;
-    uint4 packed[kArVec];
+    uint4 packed[REREAD ? 1 : kArVec];
     float ss = 0.f;
 #pragma unroll
     for (int i0 = 0; i0 < kArVec; i0 += CH) {
@@ -215,7 +222,7 @@ allreduce_kernel(nfk_allreduce_params p) {
           o.y = pack_bf16x2(acc[2], acc[3]);
           o.z = pack_bf16x2(acc[4], acc[5]);
           o.w = pack_bf16x2(acc[6], acc[7]);
-          packed[i0 + i] = o;
+          if (!REREAD) packed[i0 + i] = o;
           if (sum_out != nullptr) *reinterpret_cast<uint4*>(sum_out + row * p.sum_ld * 2 + v * 16) = o;
           if (p.push_sum) {
 #pragma unroll
@@ -243,7 +250,16 @@ allreduce_kernel(nfk_allreduce_params p) {
         if (v < nvec) {
           const uint4 ww = wv[v];
           const uint32_t w4[4] = {ww.x, ww.y, ww.z, ww.w};
-          const uint32_t x4[4] = {packed[i].x, packed[i].y, packed[i].z, packed[i].w};
+          uint4 xs;
+          if (REREAD) {
+            // this thread's own store of the summed vector, a few microseconds old
+            xs = sum_out != nullptr
+                     ? *reinterpret_cast<const uint4*>(sum_out + row * p.sum_ld * 2 + v * 16)
+                     : ld_sys_v4(reinterpret_cast<const char*>(c.heap[c.rank]) + p.buf_off + row * row_bytes + v * 16);
+          } else {
+            xs = packed[i];
+          }
+          const uint32_t x4[4] = {xs.x, xs.y, xs.z, xs.w};
           uint32_t ov[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -277,14 +293,23 @@ template <int NR>
 int launch_allreduce(const nfk_allreduce_params* p, int ctas, cudaStream_t stream) {
   static bool once = false;
   if (!once) {
-    prefer_max_shared(allreduce_kernel<NR, true>);
-    prefer_max_shared(allreduce_kernel<NR, false>);
+    prefer_max_shared(allreduce_kernel<NR, true, false>);
+    prefer_max_shared(allreduce_kernel<NR, false, false>);
+    prefer_max_shared(allreduce_kernel<NR, true, true>);
+    prefer_max_shared(allreduce_kernel<NR, false, true>);
     once = true;
   }
-  if (p->norm_w != nullptr)
-    allreduce_kernel<NR, true><<<ctas, kArThreads, 0, stream>>>(*p);
+  // The wide form with a norm reads the sum back, so the sum must have been stored somewhere local.
+  const bool norm = p->norm_w != nullptr;
+  const bool wide = p->wide != 0 && NR >= 8 && (!norm || p->sum_out != nullptr || p->push_sum != 0);
+  if (norm && wide)
+    allreduce_kernel<NR, true, true><<<ctas, kArThreads, 0, stream>>>(*p);
+  else if (norm)
+    allreduce_kernel<NR, true, false><<<ctas, kArThreads, 0, stream>>>(*p);
+  else if (wide)
+    allreduce_kernel<NR, false, true><<<ctas, kArThreads, 0, stream>>>(*p);
   else
-    allreduce_kernel<NR, false><<<ctas, kArThreads, 0, stream>>>(*p);
+    allreduce_kernel<NR, false, false><<<ctas, kArThreads, 0, stream>>>(*p);
   return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
 }
 

@@ -210,6 +210,7 @@ typedef struct nfk_allreduce_params {
                           //    NFK_EPI_REDUCE_SCATTER GEMM: owned row k of rank r's partial sits in the local
                           //    slab at buf_off + (r * slab_rows + k) * ld (no NVLink loads, no ready signal)
   int slab_rows;
+  int wide;               // 1 (8 ranks): twice the loads in flight per phase, the norm pass re-reads the stored sum
 } nfk_allreduce_params;
 int nfk_allreduce(const nfk_allreduce_params* p, cudaStream_t stream);
 

@@ -28,7 +28,8 @@ class AllReduceParams(Structure):
                 ("cols", c_int), ("ld", c_longlong), ("epoch", c_int), ("num_ctas", c_int),
                 ("norm_w", c_void_p), ("norm_out_off", c_longlong), ("norm_ld", c_longlong), ("eps", c_float),
                 ("status", c_void_p), ("push_sum", c_int), ("resid", c_void_p), ("resid_ld", c_longlong),
-                ("sum_out", c_void_p), ("sum_ld", c_longlong), ("src_mode", c_int), ("slab_rows", c_int)]
+                ("sum_out", c_void_p), ("sum_ld", c_longlong), ("src_mode", c_int), ("slab_rows", c_int),
+                ("wide", c_int)]
 
 
 class AllGatherParams(Structure):
@@ -59,6 +60,7 @@ class TpCollectives(CollectiveHooks):
         self.fuse_norm = fuse_norm
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.fake_wire_us_per_row = 0.0     # see all_reduce(): sleep standing in for absent ranks
+        self.wide = False                   # all-reduce with twice the loads in flight per phase (8 ranks)
         self._epoch = 0
         self._adhoc_flags = self.heap.alloc_bytes(FLAG_BYTES)
 
@@ -70,6 +72,7 @@ class TpCollectives(CollectiveHooks):
         self.rank, self.tp, self.device = rank, world, torch.device("cpu")
         self.num_ctas, self.fuse_norm = 16, True
         self.fake_wire_us_per_row = 0.0
+        self.wide = False
         self.status = torch.zeros(1, dtype=torch.int32)
         self._epoch = 0
 
@@ -154,6 +157,7 @@ class TpCollectives(CollectiveHooks):
         if sum_out is not None:
             p.sum_out, p.sum_ld = sum_out.data_ptr() + row0 * sum_out.stride(0) * esz, sum_out.stride(0)
         p.status = (status if status is not None else self.status).data_ptr()
+        p.wide = 1 if self.wide else 0
         idx = g.add(name, p, stream, deps=deps, dyn=[("rows", rows_sym), ("epoch", g.symbol("epoch"))],
                     layer=layer, nano=nano)
         if self.fake_wire_us_per_row > 0 and nano >= 0:
@@ -217,6 +221,7 @@ class TpCollectives(CollectiveHooks):
         if sum_out is not None:
             p.sum_out, p.sum_ld = sum_out.data_ptr(), sum_out.stride(0)
         p.status = self.status.data_ptr()
+        p.wide = 1 if self.wide else 0
         rc = _ops.lib().nfk_allreduce(byref(p), c_void_p(torch.cuda.current_stream().cuda_stream))
         if rc != 0:
             raise RuntimeError(f"nfk_allreduce: {_ops.ERRORS.get(rc, rc)}")

@@ -1,7 +1,7 @@
 """Multi-GPU test worker, one process per GPU:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        --master-port 29511 tests/mp_worker.py {collectives|engine|timeout}
+        --master-port 29511 tests/mp_worker.py {collectives|collectives_wide|fused|engine|timeout}
 
 Prints ``MP_WORKER_OK <case>`` from rank 0 on success; any rank's assertion failure exits non-zero.
 """
@@ -18,8 +18,9 @@ from nanoflow_b200.ops import reference as ref  # noqa: E402
 from nanoflow_b200.parallel.collectives import TpCollectives  # noqa: E402
 
 
-def case_collectives(rank, world, dev):
+def case_collectives(rank, world, dev, wide=False):
     coll = TpCollectives(rank, world, dev, heap_bytes=256 << 20)
+    coll.wide = wide        # 8 ranks: the all-reduce form with twice the loads in flight (same results)
     # exact integer pattern (the reference's comm_test.cu:15 uses (i*rank)%101, exact in fp16; here
     # values < 101 * world stay exact in bf16 only when small, so use (i*(rank+1)) % 13)
     for rows, cols in [(64, 1024), (37, 8192), (1, 256), (0, 512), (300, 4096)]:
@@ -293,7 +294,8 @@ if __name__ == "__main__":
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     try:
-        {"collectives": case_collectives, "engine": case_engine, "timeout": case_timeout, "fused": case_fused}[case](rank, world, dev)
+        {"collectives": case_collectives, "collectives_wide": lambda r, w, d: case_collectives(r, w, d, wide=True),
+         "engine": case_engine, "timeout": case_timeout, "fused": case_fused}[case](rank, world, dev)
     except BaseException:
         import traceback
         print(f"MP_WORKER_FAIL rank {rank}\n" + traceback.format_exc(), flush=True)

@@ -35,6 +35,6 @@ def test_two_gpus(case, port):
 
 
 @pytest.mark.skipif(_ngpu() < 8, reason="needs 8 GPUs")
-@pytest.mark.parametrize("case,port", [("collectives", 29621), ("fused", 29623)])
+@pytest.mark.parametrize("case,port", [("collectives", 29621), ("fused", 29623), ("collectives_wide", 29624)])
 def test_eight_gpus(case, port):
     print(_launch(case, 8, port))
