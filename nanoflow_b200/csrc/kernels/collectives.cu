@@ -295,19 +295,25 @@ int launch_allreduce(const nfk_allreduce_params* p, int ctas, cudaStream_t strea
   if (!once) {
     prefer_max_shared(allreduce_kernel<NR, true, false>);
     prefer_max_shared(allreduce_kernel<NR, false, false>);
-    prefer_max_shared(allreduce_kernel<NR, true, true>);
-    prefer_max_shared(allreduce_kernel<NR, false, true>);
+    if constexpr (NR >= 8) {
+      prefer_max_shared(allreduce_kernel<NR, true, true>);
+      prefer_max_shared(allreduce_kernel<NR, false, true>);
+    }
     once = true;
   }
-  // The wide form with a norm reads the sum back, so the sum must have been stored somewhere local.
   const bool norm = p->norm_w != nullptr;
-  const bool wide = p->wide != 0 && NR >= 8 && (!norm || p->sum_out != nullptr || p->push_sum != 0);
-  if (norm && wide)
-    allreduce_kernel<NR, true, true><<<ctas, kArThreads, 0, stream>>>(*p);
-  else if (norm)
+  if constexpr (NR >= 8) {
+    // The wide form with a norm reads the sum back, so the sum must have been stored somewhere local.
+    if (p->wide != 0 && (!norm || p->sum_out != nullptr || p->push_sum != 0)) {
+      if (norm)
+        allreduce_kernel<NR, true, true><<<ctas, kArThreads, 0, stream>>>(*p);
+      else
+        allreduce_kernel<NR, false, true><<<ctas, kArThreads, 0, stream>>>(*p);
+      return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
+    }
+  }
+  if (norm)
     allreduce_kernel<NR, true, false><<<ctas, kArThreads, 0, stream>>>(*p);
-  else if (wide)
-    allreduce_kernel<NR, false, true><<<ctas, kArThreads, 0, stream>>>(*p);
   else
     allreduce_kernel<NR, false, false><<<ctas, kArThreads, 0, stream>>>(*p);
   return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
