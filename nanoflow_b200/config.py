@@ -139,7 +139,8 @@ class EngineConfig:
     """Everything that is not architecture: batching, nano-batches, SM budgets, serving options."""
     global_batch_size: int = 2048          # dense tokens per iteration
     nanobatch_sizes: List[int] = field(default_factory=list)   # token split of the dense batch
-    attn_groups: int = 4                   # decode-attention groups per dense batch (KQV1..4)
+    attn_groups: int = 4                   # accepted for the reference's configs (its KQV1..4 split); here a finer
+                                           # split of QKV / attention is expressed as more nano-batches
     page_size: int = 16
     num_pages: int = 0                     # KV pages per GPU; 0 = derive from free memory
     max_batch_size: int = 2048             # max concurrent requests in one iteration
