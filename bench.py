@@ -115,6 +115,9 @@ def main():
     ap.add_argument("--no-fuse-norm", action="store_true", help="one GPU: separate RMSNorm launches after O / down")
     ap.add_argument("--serial-attention", action="store_true",
                     help="prefill attention after decode attention on one stream instead of beside it")
+    ap.add_argument("--attn-overlap", action="store_true",
+                    help="tensor-parallel overlapped pipelines: decode attention on its own stream under the GEMMs of "
+                         "the other nano-batches (use with three or four nano-batches, e.g. --nano 2048,2048,2048,2048)")
     ap.add_argument("--ar-wide", action="store_true", help="8 GPUs: all-reduce with twice the loads in flight per phase")
     ap.add_argument("--net-streams", type=int, default=1, choices=[1, 2],
                     help="2: the collectives of odd nano-batches run on a second network stream")
@@ -212,6 +215,7 @@ def main():
     cfg.engine.fuse_gemm_rs = bool(args.fuse_rs)
     cfg.engine.gemm_rs_staged = bool(args.fuse_rs_staged)
     cfg.engine.net_streams = args.net_streams
+    cfg.engine.attn_overlap = bool(args.attn_overlap)
     cfg.engine.fuse_gemm_norm = not args.no_fuse_norm
     cfg.engine.prefill_beside_decode = not args.serial_attention
     if args.layers:
@@ -339,6 +343,7 @@ def main():
                        "collective_ctas": cfg.engine.sm_budget.get("comm", 0) if tp > 1 else 0,
                        "prefill_beside_decode": bool(cfg.engine.prefill_beside_decode),
                        "decode_tail": args.decode_tail, "net_streams": cfg.engine.net_streams,
+                       "attn_overlap": bool(cfg.engine.attn_overlap),
                        "kv_pages": eng.num_pages, "tokens_per_step": round(tokens_dev / args.steps, 1),
                        "l2": "inputs larger than L2 (weights per GPU >> 126 MB); no flush",
                        "steady_state": f"{args.skip_cycles} scheduler-only cycles before warm-up",

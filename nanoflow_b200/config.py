@@ -158,6 +158,7 @@ class EngineConfig:
     debug_guards: bool = False             # guard words around activation buffers, checked with the status word
     decode_tail_fraction: float = 0.0      # share of the decode context scheduled into the last nano-batch
     net_streams: int = 1                   # 2: collectives of odd nano-batches get a second network stream
+    attn_overlap: bool = False             # TP: decode attention on its own stream under the other nano-batches' GEMMs
     gemm_shapes: Dict[str, Dict[str, int]] = field(default_factory=dict)   # "<op>.nb<k>" -> pinned launcher arguments
     decode_chunk_pages: int = 0            # 0 = choose per iteration
     use_cuda_graph: bool = False
@@ -244,6 +245,7 @@ def parse_config(raw: Dict[str, Any], *, tp: Optional[int] = None) -> NanoflowCo
         debug_guards=bool(pc.get("debug_guards", False)),
         decode_tail_fraction=float(pc.get("decode_tail_fraction", 0.0)),
         net_streams=int(pc.get("net_streams", 1)),
+        attn_overlap=bool(pc.get("attn_overlap", False)),
         model_id=sc.get("model", ""),
         weight_path=sc.get("weight_path", ""),
         hf_path=sc.get("hf_path", ""),

@@ -30,7 +30,7 @@ from ..models.llama import RankWeights
 from ..ops import reference as ref
 from ..serving.scheduler import BatchPlan
 from .graph import OpGraph, PyExecutor
-from .pipeline import GEMM_SMEM_KB_SHARED_SM, Buffers, CollectiveHooks, IoSpec, build_graph
+from .pipeline import Buffers, CollectiveHooks, IoSpec, build_graph, gemm_smem_budget_kb
 
 RING = 3                       # host staging slots (iterations in flight + one being formed)
 DECODE_MAX_CHUNKS = 16
@@ -194,7 +194,7 @@ class Engine:
                     done[(key, M)] = autotune.tune_gemm(
                         a[:M], ws, out[:M], weights_up=ups, residual=None if resid is None else resid[:M],
                         bias=bias, num_ctas=budget, workspace=b.gemm_ws,
-                        smem_budget_kb=GEMM_SMEM_KB_SHARED_SM if (e.overlap and w.tp > 1) else 0)
+                        smem_budget_kb=gemm_smem_budget_kb(e, w.tp))
                 r = done[(key, M)]
                 e.gemm_shapes[name] = dict(r["best"])
                 self.gemm_tuning[name] = dict(M=M, best=r["best"], us=r["us"], auto_us=r["auto_us"])

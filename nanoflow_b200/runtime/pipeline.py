@@ -95,6 +95,15 @@ class IoSpec:
 # Shared memory a GEMM CTA may take when a collective's CTAs are meant to run beside it on the same
 # SM: the SM has 228 KB and every resident CTA reserves 1 KB plus its own static allocation.
 GEMM_SMEM_KB_SHARED_SM = 200
+# ... and when a decode-attention CTA (96 KB) is meant to sit on the same SM as well (attn_overlap).
+GEMM_SMEM_KB_BESIDE_ATTENTION = 130
+
+
+def gemm_smem_budget_kb(eng: EngineConfig, tp: int) -> int:
+    """Shared memory a GEMM CTA may take in this pipeline (0 = all of it)."""
+    if not (eng.overlap and tp > 1):
+        return 0
+    return GEMM_SMEM_KB_BESIDE_ATTENTION if eng.attn_overlap else GEMM_SMEM_KB_SHARED_SM
 
 
 def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buffers,
@@ -115,6 +124,12 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
     # (LOCAL pipelines) they get their own stream and fill SMs as GEMM CTAs retire.
     if not overlap:
         S = lambda cls: "gemm"
+    elif tp > 1 and eng.attn_overlap:
+        # Decode attention (memory-bound) on its own stream under the GEMMs (compute-bound) of the other
+        # nano-batches: one decode CTA per SM fits beside a GEMM CTA that keeps to 130 KB of shared memory
+        # (and a collective's CTA: 21.1 K + 21.5 K + 21.5 K registers). The O projections are issued after
+        # all nano-batches' front-ends so that the compute stream does not wait behind an attention kernel.
+        S = lambda cls: cls if cls in ("net", "attn") else "gemm"
     elif tp > 1:
         S = lambda cls: "net" if cls == "net" else "gemm"
     else:
@@ -197,7 +212,7 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
             p.tile_m, p.tile_n, p.cta_group = shape["tile_m"], shape["tile_n"], shape["cta_group"]
             p.split_k, p.stream_k = shape["split_k"], shape["stream_k"]
         p.num_ctas = budget.get("gemm", 0)
-        p.smem_budget_kb = GEMM_SMEM_KB_SHARED_SM if (overlap and tp > 1) else 0
+        p.smem_budget_kb = gemm_smem_budget_kb(eng, tp)
         p.status = _ptr(st)
         if bufs.gemm_ws is not None:
             p.workspace = _ptr(bufs.gemm_ws)
@@ -248,6 +263,8 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         straddle = [rope_of[(l, k - 1)]] if k > 0 else []
         dp = attn_params()
         dp.num_ctas = budget.get("attn_decode", 0)
+        if tp > 1 and overlap and eng.attn_overlap and dp.num_ctas == 0:
+            dp.num_ctas = 148        # one CTA per SM: the second would not fit beside a GEMM CTA
         dp.workspace = _ptr(bufs.decode_ws)
         dec = g.add(f"L{l}.nb{k}.attn_decode", dp, S("attn"), deps=[ro], kernel="nfk_attn_decode",
                     dyn=[("req_begin", nb_dec0[k]), ("req_count", nb_decn[k]), ("chunk_pages", chunk_pages),
@@ -367,9 +384,14 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
             # ffn_k beside ffn_{k+1} or the next layer's front-end: no GEMM waits on a collective
             # that started right before it.
             n2s = []
-            for k in range(nn):
-                dec, pre = attn_front(l, k, lw, pool)
-                n2s.append(o_proj(l, k, lw, dec, pre))
+            if tp > 1 and eng.attn_overlap:
+                fronts = [attn_front(l, k, lw, pool) for k in range(nn)]
+                for k in range(nn):
+                    n2s.append(o_proj(l, k, lw, *fronts[k]))
+            else:
+                for k in range(nn):
+                    dec, pre = attn_front(l, k, lw, pool)
+                    n2s.append(o_proj(l, k, lw, dec, pre))
             for k in range(nn):
                 ffn(l, k, lw, n2s[k])
         else:

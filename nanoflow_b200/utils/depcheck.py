@@ -59,6 +59,16 @@ def graph_access(graph: OpGraph, nano_starts: List[int], nano_sizes: List[int], 
 
     total = sum(nano_sizes)
     out: Dict[int, Tuple[List[Range], List[Range]]] = {}
+    # KV pages belong to requests, and a request's tokens of one iteration sit in one nano-batch (a
+    # decode token) or in consecutive ones (a prompt chunk that straddles a cut). The RoPE / append op
+    # of nano-batch k therefore writes pages that only the attention of nano-batch k, and the prefill
+    # attention of later nano-batches, read. The check stands for that with one slice of the pool's
+    # address range per nano-batch.
+    nn = max(1, len(nano_sizes))
+
+    def pool_slice(base: int, k0: int, k1: int) -> Range:
+        sub = kv_pool_bytes // nn
+        return (base + k0 * sub, base + (k1 + 1) * sub if k1 + 1 < nn else base + kv_pool_bytes)
 
     def rng(ptr, rows, ld_elems, cols, esz=2):
         if not ptr or rows <= 0:
@@ -97,7 +107,9 @@ def graph_access(graph: OpGraph, nano_starts: List[int], nano_sizes: List[int], 
             add(writes, rng(p.q_out, cap, p.q_heads * p.head_dim, p.q_heads * p.head_dim))
             add(reads, rng(p.cos_sin, cap, p.head_dim, p.head_dim, 4))
             if kv_pool_bytes:
-                add(writes, (int(p.kv_pool), int(p.kv_pool) + kv_pool_bytes))
+                k = op.nano if op.nano >= 0 else 0
+                add(writes, pool_slice(int(p.kv_pool), k, k) if op.nano >= 0 else
+                    (int(p.kv_pool), int(p.kv_pool) + kv_pool_bytes))
         elif isinstance(p, G.RopeTableParams):
             add(writes, rng(p.cos_sin, total, 2 * p.half, 2 * p.half, 4))
         elif isinstance(p, G.AttnParams):
@@ -115,7 +127,12 @@ def graph_access(graph: OpGraph, nano_starts: List[int], nano_sizes: List[int], 
             else:
                 add(writes, rng(p.out + (r0 + half) * w * 2, cap - half, w, w))
             if kv_pool_bytes:
-                add(reads, (int(p.kv_pool), int(p.kv_pool) + kv_pool_bytes))
+                if op.nano < 0:
+                    add(reads, (int(p.kv_pool), int(p.kv_pool) + kv_pool_bytes))
+                elif op.kernel == "nfk_attn_decode":
+                    add(reads, pool_slice(int(p.kv_pool), op.nano, op.nano))
+                else:       # prefill: its own nano-batch's appends and, for a straddling prompt, earlier ones'
+                    add(reads, pool_slice(int(p.kv_pool), 0, op.nano))
         elif isinstance(p, AllReduceParams):
             base = heap_base + p.buf_off
             if p.src_mode == 1:

@@ -90,7 +90,7 @@ def scale_durations(graph: OpGraph, durations: Sequence[float], rules: Dict[str,
 
 
 def structural_graph(tp: int, nano: Sequence[int], layers: int, pipeline_type: str = "", net_streams: int = 1,
-                     prefill_beside_decode: bool = True) -> OpGraph:
+                     prefill_beside_decode: bool = True, attn_overlap: bool = False) -> OpGraph:
     """The op graph of a pipeline with the tiny model's tensors on the CPU: op names, streams and
     dependencies are those of any model with the same layer count, tensor-parallel degree and
     nano-batch count."""
@@ -109,6 +109,7 @@ def structural_graph(tp: int, nano: Sequence[int], layers: int, pipeline_type: s
                          nanobatch_sizes=sizes if len(nano) > 1 else None, run_layer=layers)
     m, e = cfg.model, cfg.engine
     e.max_batch_size, e.net_streams, e.prefill_beside_decode = gbs, net_streams, prefill_beside_decode
+    e.attn_overlap = attn_overlap
     w = shard_weights(random_full_weights(m, seed=0), m, 0, tp, dtype=torch.bfloat16)
     coll = TpCollectives.for_analysis(0, tp) if tp > 1 else None
     bf = torch.bfloat16
@@ -144,6 +145,7 @@ def main(argv=None) -> int:
     ap.add_argument("--pipeline", default="")
     ap.add_argument("--net-streams", type=int, default=1)
     ap.add_argument("--serial-attention", action="store_true")
+    ap.add_argument("--attn-overlap", action="store_true")
     ap.add_argument("--launch-gap", type=float, default=2.7, help="microseconds between launches on a stream")
     ap.add_argument("--scale", nargs="*", default=[], help="<kind>[.nb<k>]=<factor | +us | -us>")
     ap.add_argument("--pid", type=int, default=0)
@@ -152,7 +154,7 @@ def main(argv=None) -> int:
         d = json.load(f)
     events = [e for e in (d["traceEvents"] if isinstance(d, dict) else d) if e.get("pid", 0) == a.pid]
     nano = [int(x) for x in a.nano.split(",")]
-    g = structural_graph(a.tp, nano, a.layers, a.pipeline, a.net_streams, not a.serial_attention)
+    g = structural_graph(a.tp, nano, a.layers, a.pipeline, a.net_streams, not a.serial_attention, a.attn_overlap)
     dur = durations_from_timeline(g, events, launch_gap_us=a.launch_gap)
     rules = dict(r.split("=", 1) for r in a.scale)
     dur = scale_durations(g, dur, rules)

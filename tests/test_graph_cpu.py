@@ -10,11 +10,12 @@ from nanoflow_b200.runtime.pipeline import Buffers, IoSpec, build_graph
 from nanoflow_b200.utils import depcheck
 
 
-def _host_graph(pipeline_type, tp, nano, gbs=48, fuse_rs=False, net_streams=1, fake_wire=0.0):
+def _host_graph(pipeline_type, tp, nano, gbs=48, fuse_rs=False, net_streams=1, fake_wire=0.0, attn_overlap=False):
     cfg = builtin_config("tiny", gpu_num=tp, global_batch_size=gbs, pipeline_type=pipeline_type, nanobatch_sizes=nano)
     m, e = cfg.model, cfg.engine
     e.fuse_gemm_rs = fuse_rs
     e.net_streams = net_streams
+    e.attn_overlap = attn_overlap
     e.max_batch_size = gbs
     fw = random_full_weights(m, seed=0)
     w = shard_weights(fw, m, 0, tp, dtype=torch.bfloat16)
@@ -334,3 +335,48 @@ def test_sleep_ops_stand_in_for_the_wire_time_of_absent_ranks():
     for w in wires:
         micros = ctypes.c_int.from_buffer_copy(launches[w][5][:4]).value
         assert micros == (123 if g.ops[w].nano == 0 else 456)
+
+
+@pytest.mark.parametrize("nano", [[16, 32], [16, 16, 16], [16, 16, 16, 16]])
+def test_decode_attention_on_its_own_stream_under_tensor_parallelism(nano):
+    """attn_overlap: decode attention leaves the compute stream, all front-ends of a layer are issued
+    before the first O projection, GEMMs keep to the shared-memory budget that leaves room for an
+    attention CTA, and every buffer hazard (KV pool slices per nano-batch included) stays ordered."""
+    from nanoflow_b200.runtime.native import NativeExecutor
+    from nanoflow_b200.runtime.pipeline import GEMM_SMEM_KB_BESIDE_ATTENTION
+
+    g, acc, keep = _host_graph("PLLM", 2, nano, gbs=sum(nano), attn_overlap=True)
+    assert not depcheck.check(g, acc)
+    names = [op.name for op in g.ops]
+    dec = [i for i, op in enumerate(g.ops) if op.kernel == "nfk_attn_decode"]
+    assert dec and all(g.ops[i].stream == "attn" and g.ops[i].params.num_ctas == 148 for i in dec)
+    gemms = [op for op in g.ops if op.kernel == "nfk_gemm_bf16" and op.layer >= 0]
+    assert all(op.params.smem_budget_kb == GEMM_SMEM_KB_BESIDE_ATTENTION for op in gemms)
+    last_front = max(names.index(f"L0.nb{k}.rope_append") for k in range(len(nano)))
+    assert all(names.index(f"L0.nb{k}.o") > last_front for k in range(len(nano)))
+    hb = g.happens_before()
+    # the decode kernel of nano-batch 0 is unordered with the QKV GEMM and the KV append of nano-batch 1 ...
+    d0, q1, r1 = names.index("L0.nb0.attn_decode"), names.index("L0.nb1.qkv"), names.index("L0.nb1.rope_append")
+    assert d0 not in hb[q1] and q1 not in hb[d0] and d0 not in hb[r1] and r1 not in hb[d0]
+    # ... but a KV append is ordered with every attention that may read the pages it writes
+    p1 = names.index("L0.nb1.attn_prefill")
+    assert names.index("L0.nb0.rope_append") in hb[p1] and r1 in hb[p1]
+    plain, acc_plain, keep2 = _host_graph("PLLM", 2, nano, gbs=sum(nano))
+    assert all(op.stream != "attn" for op in plain.ops) and not depcheck.check(plain, acc_plain)
+    ex = NativeExecutor(g, None, single_stream=False, host_only=True)
+    ex.mod.host_log_clear()
+    ex.wait(ex.submit(_symbols(g, 0)))
+    log = ex.mod.host_log()
+    ex.close()
+    anc = _ancestors(log)
+    launches = [i for i, r in enumerate(log) if r[0] == LAUNCH]
+    for j, op in enumerate(g.ops):
+        for d in op.deps:
+            assert anc[launches[j]] >> launches[d] & 1
+
+
+def test_checker_still_sees_a_missing_append_dependency():
+    g, acc, keep = _host_graph("PLLM", 2, [16, 32], attn_overlap=True)
+    victim = next(i for i, op in enumerate(g.ops) if op.name == "L1.nb0.attn_decode")
+    g.ops[victim].deps = []          # the decode kernel no longer waits for its own nano-batch's KV append
+    assert depcheck.check(g, acc)
