@@ -126,9 +126,10 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         S = lambda cls: "gemm"
     elif tp > 1 and eng.attn_overlap:
         # Decode attention (memory-bound) on its own stream under the GEMMs (compute-bound) of the other
-        # nano-batches: one decode CTA per SM fits beside a GEMM CTA that keeps to 130 KB of shared memory
-        # (and a collective's CTA: 21.1 K + 21.5 K + 21.5 K registers). The O projections are issued after
-        # all nano-batches' front-ends so that the compute stream does not wait behind an attention kernel.
+        # nano-batches: one decode CTA (96 KB) per SM fits beside a GEMM CTA that keeps to 130 KB of shared
+        # memory (with the 1 KB reserved per CTA that is the whole SM, so a collective's CTA joins only
+        # once the decode CTA has left). The O projections are issued after all nano-batches' front-ends
+        # so that the compute stream does not wait behind an attention kernel.
         S = lambda cls: cls if cls in ("net", "attn") else "gemm"
     elif tp > 1:
         S = lambda cls: "net" if cls == "net" else "gemm"
