@@ -118,6 +118,8 @@ def main():
     ap.add_argument("--attn-overlap", action="store_true",
                     help="tensor-parallel overlapped pipelines: decode attention on its own stream under the GEMMs of "
                          "the other nano-batches (use with three or four nano-batches, e.g. --nano 2048,2048,2048,2048)")
+    ap.add_argument("--decode-stages", type=int, default=0, choices=[0, 2, 3],
+                    help="decode attention pages in flight per warp (0: 3, or 2 with --attn-overlap)")
     ap.add_argument("--ar-wide", action="store_true", help="8 GPUs: all-reduce with twice the loads in flight per phase")
     ap.add_argument("--net-streams", type=int, default=1, choices=[1, 2],
                     help="2: the collectives of odd nano-batches run on a second network stream")
@@ -216,6 +218,7 @@ def main():
     cfg.engine.gemm_rs_staged = bool(args.fuse_rs_staged)
     cfg.engine.net_streams = args.net_streams
     cfg.engine.attn_overlap = bool(args.attn_overlap)
+    cfg.engine.decode_stages = args.decode_stages
     cfg.engine.fuse_gemm_norm = not args.no_fuse_norm
     cfg.engine.prefill_beside_decode = not args.serial_attention
     if args.layers:

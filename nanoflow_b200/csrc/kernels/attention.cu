@@ -130,22 +130,25 @@ __device__ __forceinline__ void pv_16tok(float (&o)[HD / 8][4], const uint32_t (
 // Decode
 // ================================================================================================
 constexpr int kDecThreads = 128;
-constexpr int kDecStages = 3;
 
-template <int HD>
+// ST = pages in flight per warp (pipeline stages). 3 is the default (96 KB per CTA at head_dim 128, two
+// CTAs per SM); 2 (64 KB) is for the case where a decode CTA shares an SM with a GEMM CTA and a
+// collective's CTA (130 KB + 64 KB + the per-CTA reserve leave room, 130 KB + 96 KB do not).
+template <int HD, int ST>
 struct DecCfg {
   static constexpr int PAGE_BYTES = kPage * HD * 2;            // one head's K (or V) page
   static constexpr int STAGE_BYTES = 2 * PAGE_BYTES;           // K + V
-  static constexpr int WARP_BYTES = kDecStages * STAGE_BYTES;
+  static constexpr int WARP_BYTES = ST * STAGE_BYTES;
   static constexpr int PIPE_BYTES = 4 * WARP_BYTES;
   static constexpr int MERGE_BYTES = 4 * (16 * HD * 4 + 16 * 2 * 4);
   static constexpr int SMEM_BYTES = PIPE_BYTES > MERGE_BYTES ? PIPE_BYTES : MERGE_BYTES;
 };
 
-template <int HD>
+template <int HD, int ST>
 __global__ void __launch_bounds__(kDecThreads, 3)
 attn_decode_kernel(nfk_attn_params p) {
-  using Cfg = DecCfg<HD>;
+  using Cfg = DecCfg<HD, ST>;
+  constexpr int kDecStages = ST;
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int group = p.q_heads / p.kv_heads;
@@ -525,12 +528,12 @@ int check_common(const nfk_attn_params* p) {
   return NF_OK;
 }
 
-template <int HD>
-int launch_decode(const nfk_attn_params* p, cudaStream_t stream) {
-  using Cfg = DecCfg<HD>;
+template <int HD, int ST>
+int launch_decode_st(const nfk_attn_params* p, cudaStream_t stream) {
+  using Cfg = DecCfg<HD, ST>;
   static bool attr = false;
   if (!attr) {
-    if (cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(attn_decode_kernel<HD, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg::SMEM_BYTES) != cudaSuccess)
       return NF_ERR_CUDA;
     attr = true;
@@ -539,13 +542,18 @@ int launch_decode(const nfk_attn_params* p, cudaStream_t stream) {
   const long long total = static_cast<long long>(p->req_count) * p->kv_heads * max_chunks;
   long long ctas = p->num_ctas > 0 ? p->num_ctas : 2LL * sm_count_attn();
   if (ctas > total) ctas = total;
-  attn_decode_kernel<HD><<<static_cast<int>(ctas), kDecThreads, Cfg::SMEM_BYTES, stream>>>(*p);
+  attn_decode_kernel<HD, ST><<<static_cast<int>(ctas), kDecThreads, Cfg::SMEM_BYTES, stream>>>(*p);
   if (cudaGetLastError() != cudaSuccess) return NF_ERR_CUDA;
   if (p->chunk_pages > 0 && max_chunks > 1) {
     attn_decode_merge_kernel<HD><<<p->req_count * p->q_heads, HD, 0, stream>>>(*p);
     if (cudaGetLastError() != cudaSuccess) return NF_ERR_CUDA;
   }
   return NF_OK;
+}
+
+template <int HD>
+int launch_decode(const nfk_attn_params* p, cudaStream_t stream) {
+  return p->decode_stages == 2 ? launch_decode_st<HD, 2>(p, stream) : launch_decode_st<HD, 3>(p, stream);
 }
 
 template <int HD>
@@ -576,6 +584,7 @@ extern "C" int nfk_attn_decode(const nfk_attn_params* p, cudaStream_t stream) {
   if (p->req_count < 0 || p->req_begin < 0) return NF_ERR_BAD_ARG;
   if (p->chunk_pages < 0 || (p->chunk_pages > 0 && (p->max_chunks < 1 || p->workspace == nullptr)))
     return NF_ERR_BAD_ARG;
+  if (p->decode_stages != 0 && p->decode_stages != 2 && p->decode_stages != 3) return NF_ERR_BAD_ARG;
   return p->head_dim == 128 ? launch_decode<128>(p, stream) : launch_decode<64>(p, stream);
 }
 

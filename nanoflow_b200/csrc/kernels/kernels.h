@@ -165,6 +165,7 @@ typedef struct nfk_attn_params {
   const int* items;        // [num_items,3]
   int num_items;
   unsigned int* status;
+  int decode_stages;       // decode: pages in flight per warp, 3 (0 means 3) or 2 (less shared memory per CTA)
 } nfk_attn_params;
 int nfk_attn_decode(const nfk_attn_params* p, cudaStream_t stream);
 int nfk_attn_prefill(const nfk_attn_params* p, cudaStream_t stream);

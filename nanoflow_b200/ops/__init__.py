@@ -67,7 +67,7 @@ class AttnParams(Structure):
                 ("page_size", c_int), ("num_pages", c_int), ("sm_scale", c_float),
                 ("num_ctas", c_int), ("req_begin", c_int), ("req_count", c_int),
                 ("chunk_pages", c_int), ("workspace", c_void_p), ("max_chunks", c_int),
-                ("items", c_void_p), ("num_items", c_int), ("status", c_void_p)]
+                ("items", c_void_p), ("num_items", c_int), ("status", c_void_p), ("decode_stages", c_int)]
 
 
 def library_path() -> Path:
@@ -437,10 +437,12 @@ def _attn_common(q, out, kv_pool, qo_indptr, kv_indptr, kv_indices, kv_last_page
 def attn_decode(q, out, kv_pool, qo_indptr, kv_indptr, kv_indices, kv_last_page_len, *,
                 q_heads: int, req_begin: int, req_count: int, sm_scale: Optional[float] = None,
                 num_ctas: int = 0, chunk_pages: int = 0, workspace: Optional[torch.Tensor] = None,
-                max_chunks: int = 1, status: Optional[torch.Tensor] = None):
-    """Single-query attention for requests [req_begin, req_begin+req_count) over the paged pool."""
+                max_chunks: int = 1, status: Optional[torch.Tensor] = None, stages: int = 0):
+    """Single-query attention for requests [req_begin, req_begin+req_count) over the paged pool.
+    ``stages``: pages in flight per warp, 3 (default) or 2 (64 KB of shared memory per CTA instead of 96)."""
     p = _attn_common(q, out, kv_pool, qo_indptr, kv_indptr, kv_indices, kv_last_page_len, q_heads,
                      sm_scale, num_ctas, status)
+    p.decode_stages = stages
     p.req_begin, p.req_count = req_begin, req_count
     p.chunk_pages, p.max_chunks = chunk_pages, max_chunks
     p.workspace = _p(workspace)

@@ -264,8 +264,12 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         straddle = [rope_of[(l, k - 1)]] if k > 0 else []
         dp = attn_params()
         dp.num_ctas = budget.get("attn_decode", 0)
-        if tp > 1 and overlap and eng.attn_overlap and dp.num_ctas == 0:
-            dp.num_ctas = 148        # one CTA per SM: the second would not fit beside a GEMM CTA
+        dp.decode_stages = eng.decode_stages
+        if tp > 1 and overlap and eng.attn_overlap:
+            if dp.num_ctas == 0:
+                dp.num_ctas = 148    # one CTA per SM: the second would not fit beside a GEMM CTA
+            if dp.decode_stages == 0:
+                dp.decode_stages = 2 # 64 KB: leaves room for a collective's CTA beside GEMM + decode
         dp.workspace = _ptr(bufs.decode_ws)
         dec = g.add(f"L{l}.nb{k}.attn_decode", dp, S("attn"), deps=[ro], kernel="nfk_attn_decode",
                     dyn=[("req_begin", nb_dec0[k]), ("req_count", nb_decn[k]), ("chunk_pages", chunk_pages),

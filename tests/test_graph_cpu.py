@@ -350,6 +350,7 @@ def test_decode_attention_on_its_own_stream_under_tensor_parallelism(nano):
     names = [op.name for op in g.ops]
     dec = [i for i, op in enumerate(g.ops) if op.kernel == "nfk_attn_decode"]
     assert dec and all(g.ops[i].stream == "attn" and g.ops[i].params.num_ctas == 148 for i in dec)
+    assert all(g.ops[i].params.decode_stages == 2 for i in dec)     # 64 KB per CTA: a collective's CTA still fits
     gemms = [op for op in g.ops if op.kernel == "nfk_gemm_bf16" and op.layer >= 0]
     assert all(op.params.smem_budget_kb == GEMM_SMEM_KB_BESIDE_ATTENTION for op in gemms)
     last_front = max(names.index(f"L0.nb{k}.rope_append") for k in range(len(nano)))
@@ -363,6 +364,7 @@ def test_decode_attention_on_its_own_stream_under_tensor_parallelism(nano):
     assert names.index("L0.nb0.rope_append") in hb[p1] and r1 in hb[p1]
     plain, acc_plain, keep2 = _host_graph("PLLM", 2, nano, gbs=sum(nano))
     assert all(op.stream != "attn" for op in plain.ops) and not depcheck.check(plain, acc_plain)
+    assert all(op.params.decode_stages == 0 for op in plain.ops if op.kernel == "nfk_attn_decode")
     ex = NativeExecutor(g, None, single_stream=False, host_only=True)
     ex.mod.host_log_clear()
     ex.wait(ex.submit(_symbols(g, 0)))

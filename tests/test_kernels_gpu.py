@@ -393,6 +393,36 @@ def test_attn_decode_split_kv(chunk_pages):
     _close(out, want, atol=1e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("kv_heads,group,hd,split", [(1, 8, 128, 0), (8, 8, 128, 0), (2, 2, 64, 0), (2, 8, 128, 9)])
+def test_attn_decode_two_pages_in_flight(kv_heads, group, hd, split):
+    """The two-stage form of the decode kernel (64 KB of shared memory per CTA instead of 96, for SMs it
+    shares with a GEMM CTA and a collective's CTA): same results as the three-stage default."""
+    batch = 23
+    q_heads = kv_heads * group
+    lens = torch.randint(1, 900, (batch,)).tolist()
+    lens[0], lens[1], lens[2], lens[3] = 1, 16, 17, 33
+    pool, qo, kvp, kvi, last = _make_paged(lens, [1] * batch, kv_heads, hd)
+    q = torch.randn(batch, q_heads * hd, device="cuda", dtype=torch.bfloat16)
+    outs = []
+    for stages in (3, 2):
+        out = torch.zeros_like(q)
+        st = ops.new_status()
+        kw = {}
+        if split:
+            mc = (57 + split - 1) // split
+            kw = dict(chunk_pages=split, max_chunks=mc,
+                      workspace=torch.empty(batch * q_heads * mc * (hd + 2), device="cuda", dtype=torch.float32))
+        ops.attn_decode(q, out, pool, qo, kvp, kvi, last, q_heads=q_heads, req_begin=0, req_count=batch,
+                        num_ctas=37, status=st, stages=stages, **kw)
+        ops.check_status(st, "attn_decode")
+        outs.append(out)
+    want = ref.paged_attention(q, pool, qo.cpu(), kvp.cpu(), kvi, last.cpu(), q_heads=q_heads)
+    _close(outs[0], want, atol=1e-2, rtol=2e-2)
+    _close(outs[1], want, atol=1e-2, rtol=2e-2)
+    with pytest.raises(RuntimeError):
+        ops.attn_decode(q, outs[0], pool, qo, kvp, kvi, last, q_heads=q_heads, req_begin=0, req_count=batch, stages=4)
+
+
 def test_attn_decode_request_window():
     """Decode over a sub-range of requests (one attention group of a nano-batch)."""
     kv_heads, group, hd, batch = 1, 8, 128, 20
