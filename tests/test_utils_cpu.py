@@ -169,7 +169,20 @@ def test_parameter_search_finds_the_best_point_and_writes_a_loadable_config(tmp_
     assert cfg.engine.resolved_nanobatches() == [3712, 4480] and cfg.engine.sm_budget["comm"] == 96
     assert cfg.engine.decode_tail_fraction == 0.25 and cfg.engine.pipeline_type == "PLLM"
     rows = open(files[1]).read().strip().splitlines()
-    assert rows[0] == "nano_0,nano_1,comm_ctas,decode_tail,tokens_per_s" and len(rows) == len(log) + 1
+    assert rows[0] == "nanobatches,comm_ctas,decode_tail,switches,tokens_per_s" and len(rows) == len(log) + 1
+    # more nano-batches and bench switches as further axes
+    assert S.split_sizes(8192, 0.25, count=4) == [2048, 2048, 2048, 2048] and sum(S.split_sizes(8192, 0.3, count=3)) == 8192
+
+    def runner2(pt):      # best: four nano-batches with the attention overlap on, two network streams
+        v = 40000.0 + (3000 if (len(pt["nano"]) == 4 and pt["switches"]["attn-overlap"]) else 0)
+        return v + (500 if pt["switches"]["net-streams"] == 2 else 0) - 1e-3 * abs(pt["nano"][0] - 8192 // len(pt["nano"]))
+
+    best2, v2, log2 = S.search(8192, [0.45, 0.5, 0.55], [96], [0.0], runner2, rounds=3, nano_counts=[2, 4],
+                               switches={"attn-overlap": [False, True], "net-streams": [1, 2]})
+    assert best2["nano"] == [2048] * 4 and best2["switches"] == {"attn-overlap": True, "net-streams": 2}
+    files2 = S.write_results(str(tmp_path / "b"), "llama2-70B", 8, 8192, "PLLM", best2, v2, log2)
+    cfg2 = load_config(files2[0], tp=8)
+    assert cfg2.engine.attn_overlap and cfg2.engine.net_streams == 2 and cfg2.engine.resolved_nanobatches() == [2048] * 4
 
 
 def test_whatif_replay_of_an_op_graph():
