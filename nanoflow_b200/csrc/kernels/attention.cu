@@ -623,6 +623,7 @@ extern "C" int nfk_attn_decode_static(const nfk_attn_params* p, cudaStream_t str
   if (rc != NF_OK) return rc;
   if (p->req_count == 0) return NF_OK;
   if (p->req_count < 0 || p->req_begin < 0 || p->chunk_pages < 0) return NF_ERR_BAD_ARG;
+  if (p->decode_stages != 0 && p->decode_stages != 2 && p->decode_stages != 3) return NF_ERR_BAD_ARG;
   nfk_attn_params q = *p;
   q.workspace = nullptr;
   if (q.chunk_pages > 0) {
