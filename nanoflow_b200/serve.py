@@ -138,6 +138,12 @@ def main(argv=None) -> int:
         from .parallel.health import Heartbeat
 
         health = Heartbeat(_get_default_store(), rank, world)
+    if args.online and world > 1:
+        # all ranks release requests by rank 0's clock, so that the replicated schedulers stay identical
+        from torch.distributed.distributed_c10d import _get_default_store
+        from .serving.frontend import SharedReleaseClock
+
+        rm.release_clock = SharedReleaseClock(_get_default_store(), rank)
     loop = ServingLoop(engine, sch, rm, simulated_time=not args.online, est_cycle_time=args.est_cycle_time,
                        offload=offload, health=health, trace_phases=args.profile_mode)
     log = None

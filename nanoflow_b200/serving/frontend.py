@@ -19,8 +19,12 @@ from .request import NewRequestInfo, NewRequestQueue
 
 class RequestManager:
     def __init__(self, filename: Optional[str] = None, *, vocab_size: int = 32000, random_ids: bool = False,
-                 seed: int = 0, tokenizer: Optional[Callable[[str], "np.ndarray"]] = None):
+                 seed: int = 0, tokenizer: Optional[Callable[[str], "np.ndarray"]] = None,
+                 clock: Callable[[], float] = time.perf_counter):
         self.filename = filename
+        self._clock = clock                  # wall clock of this process (tests inject skewed ones)
+        self.release_clock = None            # SharedReleaseClock under tensor parallelism (see issue())
+        self._issue_cycle = 0
         self.avaliable_request_queue = NewRequestQueue()   # spelling kept from the reference API
         self.full_request_queue = NewRequestQueue()
         self.start_time = 0.0
@@ -103,7 +107,7 @@ class RequestManager:
         return int(2048 // (1 + self.pdr))
 
     def start_processing(self) -> None:
-        self.start_time = time.perf_counter()
+        self.start_time = self._clock()
         if self.avaliable_request_queue.size > 0:
             self.start_idx = self.avaliable_request_queue.peek().req_idx
         elif self.full_request_queue.size > 0:
@@ -116,7 +120,7 @@ class RequestManager:
         becomes the wall-clock release time (latencies are measured from it), as in the reference."""
         while self.full_request_queue.size > 0 and self.full_request_queue.peek().start_time <= self.passed_time:
             r = self.full_request_queue.get()
-            r.start_time = time.perf_counter()
+            r.start_time = self._clock()
             self.avaliable_request_queue.put(r)
 
     def simulate_issue(self, estimate_cycle_time: float = 0.175) -> None:
@@ -124,10 +128,43 @@ class RequestManager:
         self.release_request()
 
     def issue(self) -> None:
-        t = time.perf_counter()
+        """Release by wall clock. Every tensor-parallel rank runs its own copy of the scheduler and all
+        copies must admit the same requests in the same cycle (the collectives move rows whose count
+        each rank derives from its own plan), but no two processes read the same wall clock. With a
+        ``release_clock`` the elapsed time that rank 0 measured for this cycle is the one every rank
+        uses, so the copies stay identical; without one (a single rank) the local clock decides."""
+        t = self._clock()
         self.passed_time += t - self.start_time
         self.start_time = t
+        if self.release_clock is not None:
+            self.passed_time = self.release_clock.passed(self._issue_cycle, self.passed_time)
+        self._issue_cycle += 1
         self.release_request()
+
+
+class SharedReleaseClock:
+    """Rank 0's elapsed time, cycle by cycle, through the job's key-value store.
+
+    Rank 0 publishes the elapsed serving time it measured at the top of cycle ``c`` under one key per
+    cycle; the other ranks block on that key (the store's ``get`` waits until the key exists) and use
+    the value instead of their own clock. Keys older than ``keep`` cycles are deleted by rank 0: ranks
+    are never further apart than the iterations in flight, because every iteration's collectives wait
+    for all of them. The reference runs one scheduler in one process for all GPUs
+    (pipeline/utils/serve_8B.py:687-696) and so never meets the problem."""
+
+    def __init__(self, store, rank: int, prefix: str = "nf_release", keep: int = 64):
+        self.store, self.rank, self.prefix, self.keep = store, rank, prefix, keep
+
+    def passed(self, cycle: int, local_passed: float) -> float:
+        import struct
+
+        key = f"{self.prefix}/{cycle}"
+        if self.rank == 0:
+            self.store.set(key, struct.pack("<d", float(local_passed)))
+            if cycle >= self.keep:
+                self.store.delete_key(f"{self.prefix}/{cycle - self.keep}")
+            return float(local_passed)
+        return struct.unpack("<d", bytes(self.store.get(key)))[0]
 
 
 def _lazy_hf_tokenizer(name: str):

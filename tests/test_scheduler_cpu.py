@@ -214,3 +214,58 @@ def test_decode_tail_puts_a_share_of_the_decode_context_into_the_last_nanobatch(
                 tail_sum, total = ctx[Dh:].sum(), ctx.sum()
                 assert tail_sum >= frac * total > tail_sum - ctx[Dh]
     assert mixed > 5 or frac == 1.0
+
+
+def test_online_release_is_identical_on_ranks_with_skewed_clocks():
+    """Two replicas of request manager + scheduler (two tensor-parallel ranks) whose wall clocks run at
+    different speeds admit the same requests in the same cycle once both release by rank 0's clock."""
+    import threading
+
+    import torch.distributed as dist
+
+    from nanoflow_b200.serving.frontend import SharedReleaseClock
+
+    store = dist.HashStore()
+    store.set_timeout(__import__("datetime").timedelta(seconds=20))
+    arrivals = np.cumsum(np.random.default_rng(3).exponential(0.05, size=60))
+    cycles = 80
+    results = {}
+
+    def replica(rank, tick):
+        now = [0.0]
+
+        def clock():              # every read advances this rank's private clock
+            now[0] += tick
+            return now[0]
+
+        rm = RequestManager(vocab_size=1000, random_ids=True, seed=0, clock=clock)
+        for a in arrivals:
+            rm.add_request(40, 6, float(a))
+        rm.finalize_stats()
+        rm.release_clock = SharedReleaseClock(store, rank, keep=8)
+        pool = DistKVPool(2, 2, 64, 400, 16)
+        s = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=64, nanobatch_sizes=[32, 32],
+                      average_prefill_length=40, average_decode_length=6, group_size=2)
+        rm.start_processing()
+        sig, prev = [], None
+        for _ in range(cycles):
+            rm.issue()
+            p = s.schedule()
+            if prev is not None:
+                s.process_outputs(prev, np.zeros(len(prev.sample_reqs), dtype=np.int32))
+            prev = p
+            sig.append(None if p is None else
+                       (p.num_tokens, p.num_decode, tuple((r.req_idx, a, n) for r, a, n in p.prefill),
+                        tuple(nb.token_count for nb in p.nano), p.kv_indices.tolist()))
+        results[rank] = sig
+
+    threads = [threading.Thread(target=replica, args=(0, 0.011)), threading.Thread(target=replica, args=(1, 0.017))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(60)
+    assert set(results) == {0, 1}
+    assert results[0] == results[1]
+    assert sum(1 for x in results[0] if x is not None) > 10       # the trace was actually served
+    # without the shared clock the same two replicas drift apart (this is the failure being guarded)
+    assert store.num_keys() <= 8 + 2                               # old keys are deleted
