@@ -23,6 +23,8 @@
 #include "kernels.h"
 #include "attn_decode_static.h"
 
+#include <mutex>
+
 namespace nf {
 namespace {
 
@@ -170,9 +172,11 @@ attn_decode_kernel(nfk_attn_params p) {
     const int last_len = p.kv_last_page_len[req];
     int c_begin = 0, c_end = np, n_chunks = 1;
     if (p.chunk_pages > 0) {
+      // A context longer than chunk_pages * max_chunks pages still has only max_chunks work items:
+      // the last one takes all remaining pages, and the merge below counts the same number of chunks.
       c_begin = chunk * p.chunk_pages;
-      c_end = min(np, c_begin + p.chunk_pages);
-      n_chunks = (np + p.chunk_pages - 1) / p.chunk_pages;
+      c_end = (chunk == max_chunks - 1) ? np : min(np, c_begin + p.chunk_pages);
+      n_chunks = min(max_chunks, (np + p.chunk_pages - 1) / p.chunk_pages);
     }
     if (c_begin >= c_end) continue;  // uniform across the CTA
     const int tok = p.qo_indptr[req];
@@ -316,7 +320,7 @@ __global__ void attn_decode_merge_kernel(nfk_attn_params p) {
   const int bl = blockIdx.x / p.q_heads, head = blockIdx.x % p.q_heads;
   const int req = p.req_begin + bl;
   const int np = p.kv_indptr[req + 1] - p.kv_indptr[req];
-  const int n_chunks = (np + p.chunk_pages - 1) / p.chunk_pages;
+  const int n_chunks = min(p.max_chunks, (np + p.chunk_pages - 1) / p.chunk_pages);   // as in the decode kernel
   if (n_chunks <= 1) return;  // the decode kernel already wrote the final rows
   const float* ws = p.workspace + (static_cast<long long>(bl) * p.q_heads + head) * p.max_chunks * (HD + 2);
   float mm = -INFINITY;
@@ -605,6 +609,9 @@ float* g_static_scratch_ptr[kMaxDevices] = {nullptr};
 int static_scratch_for_current_device(float** out) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return NF_ERR_CUDA;
+  // first calls from several host threads: one of them asks, the others wait for its answer
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
   if (g_static_scratch_ptr[dev] == nullptr) {
     void* ptr = nullptr;
     if (cudaGetSymbolAddress(&ptr, g_decode_static_scratch) != cudaSuccess || ptr == nullptr)

@@ -18,7 +18,10 @@
 //   * the function itself allocates nothing (no cudaMalloc / cudaFree, no allocating library call).
 //     The first call on each device looks up the array's device address
 //     (cudaGetSymbolAddress, with that device current) and caches it; make that first call
-//     before starting any stream capture;
+//     before starting any stream capture. The look-up is guarded by a mutex, so first calls from
+//     several host threads are safe;
+//   * a request with more than chunk_pages * max_chunks pages is still computed in full: its last
+//     chunk takes all remaining pages;
 //   * all calls on a device share the one array. Nothing in it needs to start at zero: every chunk
 //     slot that the merge step reads has been written by the same call. But two calls that overlap
 //     on the GPU (different streams) would overwrite each other's partials, so keep calls that use

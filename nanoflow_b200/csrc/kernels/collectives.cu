@@ -54,12 +54,17 @@ __device__ __forceinline__ void st_sys_v4(void* p, const uint4& v) {
                : "memory");
 }
 
-// Bounded wait until *flag has reached `epoch` (wrap-safe). Returns false on timeout.
-__device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int epoch) {
+// Bounded wait until *flag has reached `epoch` (wrap-safe). Returns false on timeout, and also as
+// soon as the status word is set: once one wait of an iteration has run out (a peer is gone), the
+// later collectives of that iteration give up at their first poll round instead of each spending its
+// own two seconds, so a dead peer costs one time limit, not one per collective.
+__device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int epoch,
+                                          const unsigned int* status = nullptr) {
   uint64_t t0 = 0;
   for (unsigned int it = 0;; ++it) {
     if (static_cast<int>(ld_acquire_sys(flag) - epoch) >= 0) return true;
     if ((it & 63u) == 63u) {
+      if (status != nullptr && *reinterpret_cast<const volatile unsigned int*>(status) != 0u) return false;
       uint64_t now;
       asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
       if (t0 == 0) t0 = now;
@@ -86,7 +91,7 @@ __device__ __forceinline__ void comm_enter(const nfk_comm_ctx& c, long long flag
   if (signal && blockIdx.x == 0 && threadIdx.x < c.nranks)
     st_release_sys(&flags_of(c, threadIdx.x, flag_off)->ready[c.rank], epoch);
   if (threadIdx.x < c.nranks) {
-    if (!wait_flag(&flags_of(c, c.rank, flag_off)->ready[threadIdx.x], epoch))
+    if (!wait_flag(&flags_of(c, c.rank, flag_off)->ready[threadIdx.x], epoch, status))
       report_status(status, NF_ST_TIMEOUT_PEER_FLAG);
   }
   __syncthreads();
@@ -110,7 +115,7 @@ __device__ __forceinline__ void comm_exit(const nfk_comm_ctx& c, long long flag_
   __threadfence_system();
   if (threadIdx.x < c.nranks) {
     st_release_sys(&flags_of(c, threadIdx.x, flag_off)->done[c.rank], epoch);
-    if (!wait_flag(&mine->done[threadIdx.x], epoch)) report_status(status, NF_ST_TIMEOUT_PEER_FLAG);
+    if (!wait_flag(&mine->done[threadIdx.x], epoch, status)) report_status(status, NF_ST_TIMEOUT_PEER_FLAG);
   }
 }
 
@@ -342,7 +347,7 @@ allgather_kernel(nfk_allgather_params p) {
 __global__ void comm_barrier_kernel(nfk_comm_ctx c, long long flag_off, int epoch, unsigned int* status) {
   if (threadIdx.x < c.nranks) {
     st_release_sys(&flags_of(c, threadIdx.x, flag_off)->ready[c.rank], static_cast<unsigned int>(epoch));
-    if (!wait_flag(&flags_of(c, c.rank, flag_off)->ready[threadIdx.x], static_cast<unsigned int>(epoch)))
+    if (!wait_flag(&flags_of(c, c.rank, flag_off)->ready[threadIdx.x], static_cast<unsigned int>(epoch), status))
       report_status(status, NF_ST_TIMEOUT_PEER_FLAG);
   }
 }

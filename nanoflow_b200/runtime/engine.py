@@ -152,6 +152,8 @@ class Engine:
         self.graph: OpGraph = build_graph(m, e, weights, self.bufs, self.coll, io)
         self.tokens_host = [torch.zeros(B, dtype=torch.int32).pin_memory() for _ in range(RING)]
         self.tokens_np = [t.numpy() for t in self.tokens_host]
+        self.status_host = [torch.zeros(1, dtype=torch.int32).pin_memory() for _ in range(RING)]
+        self.status_np = [t.numpy() for t in self.status_host]
         self.stream = torch.cuda.Stream(device=dev)
         self.done_events = [torch.cuda.Event() for _ in range(RING)]
         self._staged: Optional[dict] = None
@@ -301,6 +303,7 @@ class Engine:
         sym["kv_src"] = self.meta_host[slot].data_ptr() + 4 * lay.off["kv_indices"]
         sym["kv_words"] = st["kv_words"]
         sym["tokens_dst"] = self.tokens_host[slot].data_ptr()
+        sym["status_dst"] = self.status_host[slot].data_ptr()
         sym["epoch"] = self._iter + 1      # collective flag epoch: same on every rank, never reset
         if self.native is not None:
             st["ticket"] = self.native.submit(sym, timed)
@@ -310,7 +313,7 @@ class Engine:
                 self.py_exec.run(sym, main_stream=self.stream)
                 self.done_events[slot].record(self.stream)
         self.h2d_bytes_last = 4 * (lay.fixed_words + st["kv_words"])
-        self.d2h_bytes_last = 4 * st["n_sample"] + st.get("n_offload", 0) * self.page_bytes_layer * self.model.run_layers
+        self.d2h_bytes_last = 4 * st["n_sample"] + 4 + st.get("n_offload", 0) * self.page_bytes_layer * self.model.run_layers
         self._inflight.append(st)
         self._staged = None
         self._iter += 1
@@ -325,6 +328,14 @@ class Engine:
             self.done_events[st["slot"]].synchronize()
         self._last_tokens = self.tokens_np[st["slot"]][:st["n_sample"]].copy()
         self.last_offload = (st["slot"], st.get("n_offload", 0))
+        code = int(self.status_np[st["slot"]][0]) & 0xFFFFFFFF
+        if code:
+            # a bounded wait ran out (peer gone) or an index was out of range in this iteration: its
+            # tokens cannot be trusted, so stop here rather than at the end of serving
+            self.status_np[st["slot"]][0] = 0
+            self.bufs.status.zero_()
+            raise RuntimeError(f"engine iteration {self._iter - len(self._inflight) - 1}: device status 0x{code:x} "
+                               f"({ops.STATUS_CODES.get(code & 0xF00, '?')})")
         return self._last_tokens
 
     def offloaded_pages(self) -> Optional[torch.Tensor]:

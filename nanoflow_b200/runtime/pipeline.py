@@ -441,6 +441,10 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         last = g.add("argmax_combine", cp, S("net"), deps=[agc if agc is not None else am])
     if io is not None:
         c3 = MemcpyParams(dst=c_void_p(0), src=_ptr(bufs.sampled), elem_bytes=4, count=0)
-        g.add("tokens_d2h", c3, g.ops[last].stream, deps=[last],
-              dyn=[("dst", g.symbol("tokens_dst")), ("count", n_sample)])
+        td = g.add("tokens_d2h", c3, g.ops[last].stream, deps=[last],
+                   dyn=[("dst", g.symbol("tokens_dst")), ("count", n_sample)])
+        # the status word travels with the tokens, so the host sees a timeout or a bad index in the
+        # iteration that had it, not at the end of serving
+        c4 = MemcpyParams(dst=c_void_p(0), src=_ptr(st), elem_bytes=4, count=1)
+        g.add("status_d2h", c4, g.ops[last].stream, deps=[td], dyn=[("dst", g.symbol("status_dst"))])
     return g

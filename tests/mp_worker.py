@@ -271,9 +271,17 @@ def case_timeout(rank, world, dev):
     buf = coll.alloc((8, 256), torch.bfloat16)
     spare = coll.new_flags()
     torch.cuda.synchronize(); dist.barrier()
+    spare2 = coll.new_flags()
     if rank == 0:
         coll.all_reduce_(buf, flag_off=spare, epoch=1)
+        # a second collective behind the one that timed out gives up at once: the status word is already
+        # set, so a dead peer costs one time limit per iteration, not one per collective
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        coll.all_reduce_(buf, flag_off=spare2, epoch=1)
+        e1.record()
         torch.cuda.synchronize()
+        assert e0.elapsed_time(e1) < 500.0, f"second collective waited {e0.elapsed_time(e1):.0f} ms"
         try:
             coll.check_status()
             raise AssertionError("expected a peer-flag timeout")

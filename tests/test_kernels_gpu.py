@@ -393,6 +393,26 @@ def test_attn_decode_split_kv(chunk_pages):
     _close(out, want, atol=1e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("chunk_pages,max_chunks", [(8, 4), (16, 1), (5, 3)])
+def test_attn_decode_split_kv_context_longer_than_the_chunks_cover(chunk_pages, max_chunks):
+    """A request with more pages than chunk_pages * max_chunks: the last chunk takes the remaining pages
+    (no page is dropped, the merge stays inside the request's workspace slots)."""
+    kv_heads, group, hd, batch = 2, 8, 128, 4
+    q_heads = kv_heads * group
+    lens = [2000, 31, 1500, 640]                 # 125, 2, 94, 40 pages
+    pool, qo, kvp, kvi, last = _make_paged(lens, [1] * batch, kv_heads, hd)
+    q = torch.randn(batch, q_heads * hd, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros_like(q)
+    ws = torch.full((batch * q_heads * max_chunks * (hd + 2) + 64,), float("nan"), device="cuda", dtype=torch.float32)
+    st = ops.new_status()
+    ops.attn_decode(q, out, pool, qo, kvp, kvi, last, q_heads=q_heads, req_begin=0, req_count=batch,
+                    chunk_pages=chunk_pages, workspace=ws, max_chunks=max_chunks, status=st)
+    ops.check_status(st, "attn_decode split, long context")
+    want = ref.paged_attention(q, pool, qo.cpu(), kvp.cpu(), kvi, last.cpu(), q_heads=q_heads)
+    _close(out, want, atol=1e-2, rtol=2e-2)
+    assert torch.isnan(ws[-64:]).all()          # nothing was written past the workspace
+
+
 @pytest.mark.parametrize("kv_heads,group,hd,split", [(1, 8, 128, 0), (8, 8, 128, 0), (2, 2, 64, 0), (2, 8, 128, 9)])
 def test_attn_decode_two_pages_in_flight(kv_heads, group, hd, split):
     """The two-stage form of the decode kernel (64 KB of shared memory per CTA instead of 96, for SMs it

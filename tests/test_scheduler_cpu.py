@@ -267,5 +267,4 @@ def test_online_release_is_identical_on_ranks_with_skewed_clocks():
     assert set(results) == {0, 1}
     assert results[0] == results[1]
     assert sum(1 for x in results[0] if x is not None) > 10       # the trace was actually served
-    # without the shared clock the same two replicas drift apart (this is the failure being guarded)
     assert store.num_keys() <= 8 + 2                               # old keys are deleted

@@ -69,6 +69,25 @@ def test_static_scratch_decode_matches_workspace_decode_twice():
         assert bool(((got.float() - oracle).abs() <= 1e-2 + 2e-2 * oracle.abs()).all())
 
 
+def test_static_scratch_context_longer_than_the_chunks_cover():
+    """More pages than chunk_pages * max_chunks: the last chunk absorbs the rest, as in the workspace entry."""
+    lib = ops.lib()
+    fn = lib.nfk_attn_decode_static
+    fn.restype = ctypes.c_int
+    stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+    kv_heads, group, hd = 2, 8, 128
+    q_heads = kv_heads * group
+    lens = [2000, 31, 1500]
+    pool, q, qo, kvp, kvi, last = _problem(len(lens), kv_heads, group, hd, lens, 5)
+    got = torch.zeros_like(q)
+    rc = fn(byref(_params(q, got, pool, qo, kvp, kvi, last, q_heads, 8, 4, None)), stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    from nanoflow_b200.ops import reference as ref
+    oracle = ref.paged_attention(q, pool, qo.cpu(), kvp.cpu(), kvi, last.cpu(), q_heads=q_heads)
+    assert bool(((got.float() - oracle).abs() <= 1e-2 + 2e-2 * oracle.abs()).all())
+
+
 def test_static_scratch_rejects_oversized_request():
     lib = ops.lib()
     fn = lib.nfk_attn_decode_static
