@@ -291,6 +291,8 @@ _LLAMA31_SCALING = {"factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4
 
 MODEL_ARCHS: Dict[str, Dict[str, Any]] = {
     "tiny": _hf(256, 688, 2, 4, 2, 1024, 10000.0),
+    # the same with 8 KV heads, so that it can be sharded over 8 ranks (head-parallel attention)
+    "tiny8": _hf(1024, 2816, 2, 16, 8, 1024, 10000.0),
     "llama2-70B": _hf(8192, 28672, 80, 64, 8, 32000, 10000.0),
     "llama3-70B": _hf(8192, 28672, 80, 64, 8, 128256, 500000.0, max_pos=8192, eos=128001, bos=128000),
     "llama3.1-70B": _hf(8192, 28672, 80, 64, 8, 128256, 500000.0, max_pos=131072, scaling=_LLAMA31_SCALING,
@@ -312,7 +314,7 @@ MODEL_IDS = {
     "llama3.1-70B": "meta-llama/Meta-Llama-3.1-70B-Instruct", "llama3-8B": "meta-llama/Meta-Llama-3-8B-Instruct",
     "llama3.1-8B": "meta-llama/Meta-Llama-3.1-8B-Instruct", "qwen2-72B": "Qwen/Qwen2-72B-Instruct",
     "deepseek-67B": "deepseek-ai/deepseek-llm-67b-chat", "mixtral-8-7B": "mistralai/Mixtral-8x7B-Instruct-v0.1",
-    "tiny": "nanoflow/tiny-llama-test",
+    "tiny": "nanoflow/tiny-llama-test", "tiny8": "nanoflow/tiny8-llama-test",
 }
 
 
@@ -419,7 +421,7 @@ def write_shipped_configs(root: Optional[Path] = None) -> List[Path]:
     root = root or CONFIG_DIR
     written = []
     for model in MODEL_ARCHS:
-        if model == "tiny":
+        if model.startswith("tiny"):
             continue
         for name, raw in shipped_variants(model).items():
             path = root / model / f"{name}.json"

@@ -284,6 +284,112 @@ allreduce_kernel(nfk_allreduce_params p) {
   comm_exit(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status);
 }
 
+// ---- in-switch (NVLS) form -------------------------------------------------------------------------
+// With the heaps bound to one NVLink multicast object, a load from the multicast address of a word is
+// answered by the NVSwitch with the sum of that word over all ranks (multimem.ld_reduce, bf16 inputs
+// added in fp32), and a store to it lands in every rank's copy (multimem.st). The owner of a row then
+// needs one 16-byte load per 8 columns instead of one per rank, and one store instead of one per rank:
+// an eighth of the instructions in flight for the same bytes of result, and about two thirds of the bytes
+// on this GPU's links (its own partial rows still leave once, the normed rows of the others still arrive).
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_v4(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// One row per CTA pass, the whole row in flight at once (8 multimem loads + 8 residual loads per thread);
+// rows r, r + nranks, ... of the buffer belong to rank r as in allreduce_kernel. The switch returns the
+// ranks' sum already rounded to bf16; the residual is added to that in fp32 and the result rounded once
+// more, so sums can differ from allreduce_kernel's (one rounding) in the last bf16 bit.
+template <bool NORM>
+__global__ void __launch_bounds__(kArThreads, 3)
+allreduce_mc_kernel(nfk_allreduce_params p) {
+  __shared__ float red[8];
+  const nfk_comm_ctx& c = p.ctx;
+  comm_enter(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status, true);
+  const int NR = c.nranks;
+  const int nvec = p.cols >> 3;
+  const long long row_bytes = p.ld * 2;
+  const uint4* wv = NORM ? reinterpret_cast<const uint4*>(p.norm_w) : nullptr;
+  char* mc = reinterpret_cast<char*>(p.mc_heap);
+  const char* resid = reinterpret_cast<const char*>(p.resid);
+  char* sum_out = reinterpret_cast<char*>(p.sum_out);
+  const int owned = (p.rows - c.rank + NR - 1) / NR;
+  for (int k = blockIdx.x; k < owned; k += gridDim.x) {
+    const long long row = c.rank + static_cast<long long>(NR) * k;
+    uint4 in[kArVec], rs[kArVec];
+#pragma unroll
+    for (int i = 0; i < kArVec; ++i) {
+      const int v = threadIdx.x + i * kArThreads;
+      if (v < nvec) {
+        in[i] = multimem_ld_reduce_bf16x8(mc + p.buf_off + row * row_bytes + v * 16);
+        if (resid != nullptr) rs[i] = *reinterpret_cast<const uint4*>(resid + row * p.resid_ld * 2 + v * 16);
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < kArVec; ++i) {
+      const int v = threadIdx.x + i * kArThreads;
+      if (v < nvec) {
+        uint4 o = in[i];
+        if (resid != nullptr) {
+          const uint32_t a4[4] = {in[i].x, in[i].y, in[i].z, in[i].w};
+          const uint32_t b4[4] = {rs[i].x, rs[i].y, rs[i].z, rs[i].w};
+          uint32_t o4[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 a = unpack_bf16x2(a4[e]), b = unpack_bf16x2(b4[e]);
+            o4[e] = pack_bf16x2(a.x + b.x, a.y + b.y);
+          }
+          o = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+        }
+        in[i] = o;
+        if (sum_out != nullptr) *reinterpret_cast<uint4*>(sum_out + row * p.sum_ld * 2 + v * 16) = o;
+        if (p.push_sum) multimem_st_v4(mc + p.buf_off + row * row_bytes + v * 16, o);
+        if (NORM) {
+          const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack_bf16x2(ow[e]);
+            ss += f.x * f.x + f.y * f.y;
+          }
+        }
+      }
+    }
+    if (NORM) {
+      const float tot = block_sum_ar(ss, red);
+      const float inv = rsqrtf(tot / static_cast<float>(p.cols) + p.eps);
+#pragma unroll
+      for (int i = 0; i < kArVec; ++i) {
+        const int v = threadIdx.x + i * kArThreads;
+        if (v < nvec) {
+          const uint4 ww = wv[v];
+          const uint32_t w4[4] = {ww.x, ww.y, ww.z, ww.w};
+          const uint32_t x4[4] = {in[i].x, in[i].y, in[i].z, in[i].w};
+          uint32_t ov[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 g = unpack_bf16x2(w4[e]);
+            const float2 f = unpack_bf16x2(x4[e]);
+            ov[e] = pack_bf16x2(f.x * inv * g.x, f.y * inv * g.y);
+          }
+          multimem_st_v4(mc + p.norm_out_off + row * static_cast<long long>(p.norm_ld) * 2 + v * 16,
+                         make_uint4(ov[0], ov[1], ov[2], ov[3]));
+        }
+      }
+    }
+  }
+  comm_exit(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status);
+}
+
 // A collective's CTAs are meant to share SMs with the CTAs of a GEMM that is launched after it. An SM
 // changes its L1 / shared-memory split only while idle, so a kernel that asks for no shared memory
 // would leave its SMs configured with too little for a GEMM CTA until it exits. Asking for the
@@ -307,6 +413,19 @@ int launch_allreduce(const nfk_allreduce_params* p, int ctas, cudaStream_t strea
     once = true;
   }
   const bool norm = p->norm_w != nullptr;
+  if (p->mc_heap != nullptr && p->src_mode == 0 && NR > 1) {
+    static bool once_mc = false;
+    if (!once_mc) {
+      prefer_max_shared(allreduce_mc_kernel<true>);
+      prefer_max_shared(allreduce_mc_kernel<false>);
+      once_mc = true;
+    }
+    if (norm)
+      allreduce_mc_kernel<true><<<ctas, kArThreads, 0, stream>>>(*p);
+    else
+      allreduce_mc_kernel<false><<<ctas, kArThreads, 0, stream>>>(*p);
+    return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
+  }
   if constexpr (NR >= 8) {
     // The wide form with a norm reads the sum back, so the sum must have been stored somewhere local.
     if (p->wide != 0 && (!norm || p->sum_out != nullptr || p->push_sum != 0)) {
@@ -375,6 +494,7 @@ extern "C" int nfk_allreduce(const nfk_allreduce_params* p, cudaStream_t stream)
     return NF_ERR_BAD_ARG;
   if (p->src_mode != 0 && (p->src_mode != 1 || p->push_sum != 0 || p->slab_rows * p->ctx.nranks < p->rows))
     return NF_ERR_BAD_ARG;   // slab input: the sum cannot be pushed back into a per-rank buffer
+  if (p->mc_heap != nullptr && (reinterpret_cast<uintptr_t>(p->mc_heap) & 15) != 0) return NF_ERR_BAD_ARG;
   // Even an empty buffer takes part in the handshakes so that all ranks stay in step.
   const int nr = p->ctx.nranks;
   const int owned = (p->rows + nr - 1) / nr;

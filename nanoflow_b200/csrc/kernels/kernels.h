@@ -212,6 +212,9 @@ typedef struct nfk_allreduce_params {
                           //    slab at buf_off + (r * slab_rows + k) * ld (no NVLink loads, no ready signal)
   int slab_rows;
   int wide;               // 1 (8 ranks): twice the loads in flight per phase, the norm pass re-reads the stored sum
+  void* mc_heap;          // optional: the heaps' NVLink multicast mapping (one address that stands for the same
+                          //    offset on every rank). Non-null selects the in-switch form: owned rows are summed by
+                          //    multimem.ld_reduce and results are written to all ranks by multimem.st (src_mode 0 only)
 } nfk_allreduce_params;
 int nfk_allreduce(const nfk_allreduce_params* p, cudaStream_t stream);
 

@@ -29,7 +29,7 @@ class AllReduceParams(Structure):
                 ("norm_w", c_void_p), ("norm_out_off", c_longlong), ("norm_ld", c_longlong), ("eps", c_float),
                 ("status", c_void_p), ("push_sum", c_int), ("resid", c_void_p), ("resid_ld", c_longlong),
                 ("sum_out", c_void_p), ("sum_ld", c_longlong), ("src_mode", c_int), ("slab_rows", c_int),
-                ("wide", c_int)]
+                ("wide", c_int), ("mc_heap", c_void_p)]
 
 
 class AllGatherParams(Structure):
@@ -51,11 +51,13 @@ FLAG_BYTES = 128
 
 class TpCollectives(CollectiveHooks):
     def __init__(self, rank: int, world: int, device: torch.device, heap_bytes: int = 1 << 30,
-                 num_ctas: int = 148, fuse_norm: bool = True):
+                 num_ctas: int = 148, fuse_norm: bool = True, backend: str = ""):
         if world > 8:
             raise ValueError("at most 8 ranks (one NVSwitch domain)")
         self.rank, self.tp, self.device = rank, world, device
-        self.heap = SymmetricHeap(rank, world, device, heap_bytes)
+        self.heap = SymmetricHeap(rank, world, device, heap_bytes, backend=backend)
+        # all-reduces go through the NVSwitch (multimem) whenever the heap has a multicast mapping
+        self.use_multimem = self.heap.mc_base != 0
         self.num_ctas = num_ctas
         self.fuse_norm = fuse_norm
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
@@ -71,6 +73,7 @@ class TpCollectives(CollectiveHooks):
         self = cls.__new__(cls)
         self.rank, self.tp, self.device = rank, world, torch.device("cpu")
         self.num_ctas, self.fuse_norm = 16, True
+        self.use_multimem = False
         self.fake_wire_us_per_row = 0.0
         self.wide = False
         self.status = torch.zeros(1, dtype=torch.int32)
@@ -158,6 +161,8 @@ class TpCollectives(CollectiveHooks):
             p.sum_out, p.sum_ld = sum_out.data_ptr() + row0 * sum_out.stride(0) * esz, sum_out.stride(0)
         p.status = (status if status is not None else self.status).data_ptr()
         p.wide = 1 if self.wide else 0
+        if self.use_multimem and slab is None:
+            p.mc_heap = self.heap.mc_base
         idx = g.add(name, p, stream, deps=deps, dyn=[("rows", rows_sym), ("epoch", g.symbol("epoch"))],
                     layer=layer, nano=nano)
         if self.fake_wire_us_per_row > 0 and nano >= 0:
@@ -222,6 +227,8 @@ class TpCollectives(CollectiveHooks):
             p.sum_out, p.sum_ld = sum_out.data_ptr(), sum_out.stride(0)
         p.status = self.status.data_ptr()
         p.wide = 1 if self.wide else 0
+        if self.use_multimem:
+            p.mc_heap = self.heap.mc_base
         rc = _ops.lib().nfk_allreduce(byref(p), c_void_p(torch.cuda.current_stream().cuda_stream))
         if rc != 0:
             raise RuntimeError(f"nfk_allreduce: {_ops.ERRORS.get(rc, rc)}")

@@ -1,7 +1,7 @@
 """Multi-GPU test worker, one process per GPU:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        --master-port 29511 tests/mp_worker.py {collectives|collectives_wide|fused|engine|timeout}
+        --master-port 29511 tests/mp_worker.py {collectives|collectives_wide|collectives_nvls|fused|engine|engine_nvls|timeout}
 
 Prints ``MP_WORKER_OK <case>`` from rank 0 on success; any rank's assertion failure exits non-zero.
 """
@@ -18,8 +18,12 @@ from nanoflow_b200.ops import reference as ref  # noqa: E402
 from nanoflow_b200.parallel.collectives import TpCollectives  # noqa: E402
 
 
-def case_collectives(rank, world, dev, wide=False):
-    coll = TpCollectives(rank, world, dev, heap_bytes=256 << 20)
+def case_collectives(rank, world, dev, wide=False, backend="ipc"):
+    coll = TpCollectives(rank, world, dev, heap_bytes=512 << 20, backend=backend)
+    if backend == "nvls":
+        assert coll.use_multimem and coll.heap.mc_base != 0, "NVLS heap without a multicast address"
+    if rank == 0:
+        print(f"symmetric heap: {coll.heap.backend}, all-reduce through the switch: {coll.use_multimem}", flush=True)
     coll.wide = wide        # 8 ranks: the all-reduce form with twice the loads in flight (same results)
     # exact integer pattern (the reference's comm_test.cu:15 uses (i*rank)%101, exact in fp16; here
     # values < 101 * world stay exact in bf16 only when small, so use (i*(rank+1)) % 13)
@@ -150,6 +154,31 @@ def case_collectives(rank, world, dev, wide=False):
             nbytes = rows * cols * 2
             busbw = 2 * (world - 1) / world * nbytes / (t.item() * 1e-3) / 1e9
             print(f"allreduce {rows}x{cols} bf16 ctas={ctas}: {t.item()*1e3:.1f} us, bus bw {busbw:.0f} GB/s", flush=True)
+    # the form the engine uses: owners keep the sum (+ residual) locally and push only the normed rows
+    rows, cols = 4096, 8192
+    buf = coll.alloc((rows, cols), torch.bfloat16)
+    hout = coll.alloc((rows, cols), torch.bfloat16)
+    x_loc = torch.zeros(rows, cols, dtype=torch.bfloat16, device=dev)
+    wn = torch.ones(cols, dtype=torch.bfloat16, device=dev)
+    buf.normal_()
+    for ctas in (32, 64, 96, 148):
+        for _ in range(3):
+            coll.all_reduce_(buf, norm_w=wn, norm_out=hout, resid=x_loc, sum_out=x_loc, push_sum=False, num_ctas=ctas)
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            coll.all_reduce_(buf, norm_w=wn, norm_out=hout, resid=x_loc, sum_out=x_loc, push_sum=False, num_ctas=ctas)
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / 10], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            # bytes one GPU must receive: the other ranks' partial rows of the rows it owns (pull form), or
+            # the switch's sums of them (in-switch form); and, either way, the other owners' normed rows
+            own = rows // world * cols * 2
+            wire = (own + (world - 1) * own) if coll.use_multimem else 2 * (world - 1) * own
+            print(f"allreduce+norm {rows}x{cols} bf16 ctas={ctas}: {t.item()*1e3:.1f} us "
+                  f"({wire / 770e9 * 1e6:.0f} us at 770 GB/s per direction)", flush=True)
     coll.check_status()
     coll.close()
 
@@ -211,7 +240,7 @@ def case_fused(rank, world, dev):
     coll.close()
 
 
-def case_engine(rank, world, dev):
+def case_engine(rank, world, dev, backend="ipc"):
     from nanoflow_b200.config import builtin_config
     from nanoflow_b200.models import ReferenceLlama, random_full_weights, shard_weights
     from nanoflow_b200.runtime.engine import Engine
@@ -221,7 +250,9 @@ def case_engine(rank, world, dev):
     for ptype, nano, fuse in (("NON_OVERLAP", None, False), ("PLLM", [16, 32], False), ("PLLM", [16, 32], True),
                               ("NON_OVERLAP", None, True)):
         gbs = 48
-        cfg = builtin_config("tiny", gpu_num=world, global_batch_size=gbs, pipeline_type=ptype, nanobatch_sizes=nano)
+        # two KV heads shard over two ranks; more ranks take the variant with eight KV heads
+        arch = "tiny" if world <= 2 else "tiny8"
+        cfg = builtin_config(arch, gpu_num=world, global_batch_size=gbs, pipeline_type=ptype, nanobatch_sizes=nano)
         cfg.engine.max_batch_size = gbs
         cfg.engine.fuse_gemm_rs = fuse
         fw = random_full_weights(cfg.model, seed=0, std=0.05)
@@ -230,18 +261,18 @@ def case_engine(rank, world, dev):
                 if v is not None:
                     setattr(lay, k, v.bfloat16().float())
         fw.embed, fw.norm, fw.lm_head = fw.embed.bfloat16().float(), fw.norm.bfloat16().float(), fw.lm_head.bfloat16().float()
-        oracle = ReferenceLlama(builtin_config("tiny").model, fw)
+        oracle = ReferenceLlama(builtin_config(arch).model, fw)
         rng = np.random.default_rng(0)
         prompts = [rng.integers(0, 1024, size=32, dtype=np.int32) for _ in range(4)]
         rm = RequestManager(vocab_size=1024)
         for p in prompts:
             rm.add_request(32, 16, 0.0, prompt=p)
         rm.finalize_stats()
-        pool = DistKVPool(2, 2, 64, 64, 16, world)
+        pool = DistKVPool(2, cfg.model.num_kv_heads, 64, 64, 16, world)
         sch = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=gbs,
                         nanobatch_sizes=cfg.engine.resolved_nanobatches(), average_prefill_length=32,
                         average_decode_length=16, group_size=2)
-        coll = TpCollectives(rank, world, dev, heap_bytes=64 << 20)
+        coll = TpCollectives(rank, world, dev, heap_bytes=64 << 20, backend=backend)
         eng = Engine(cfg, shard_weights(fw, cfg.model, rank, world, device=dev), device=dev, collectives=coll,
                      num_pages=64)
         st = ServingLoop(eng, sch, rm, est_cycle_time=1.0).run()
@@ -267,7 +298,7 @@ def case_engine(rank, world, dev):
 def case_timeout(rank, world, dev):
     """A collective whose peers never arrive ends by itself with a status code; the context stays usable.
     Rank 0 alone calls the all-reduce (nobody else signals), then everyone proves the GPU still works."""
-    coll = TpCollectives(rank, world, dev, heap_bytes=16 << 20)
+    coll = TpCollectives(rank, world, dev, heap_bytes=16 << 20, backend="ipc")   # nothing bound in the switch
     buf = coll.alloc((8, 256), torch.bfloat16)
     spare = coll.new_flags()
     torch.cuda.synchronize(); dist.barrier()
@@ -303,7 +334,9 @@ if __name__ == "__main__":
     dist.init_process_group("nccl", device_id=dev)
     try:
         {"collectives": case_collectives, "collectives_wide": lambda r, w, d: case_collectives(r, w, d, wide=True),
-         "engine": case_engine, "timeout": case_timeout, "fused": case_fused}[case](rank, world, dev)
+         "collectives_nvls": lambda r, w, d: case_collectives(r, w, d, backend="nvls"),
+         "engine": case_engine, "engine_nvls": lambda r, w, d: case_engine(r, w, d, backend="nvls"),
+         "timeout": case_timeout, "fused": case_fused}[case](rank, world, dev)
     except BaseException:
         import traceback
         print(f"MP_WORKER_FAIL rank {rank}\n" + traceback.format_exc(), flush=True)

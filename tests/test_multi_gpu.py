@@ -18,7 +18,11 @@ def _ngpu():
 
 
 def _launch(case, n, port):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    # Heaps are plain CUDA IPC mappings unless the case is about the in-switch path, and NCCL keeps NVLS
+    # off in every case that a rank may leave early.
+    env = dict(os.environ, NANOFLOW_SYMM_BACKEND="ipc")
+    if not case.endswith("_nvls"):
+        env["NCCL_NVLS_ENABLE"] = "0"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "mp_worker.py"), case]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
@@ -29,12 +33,14 @@ def _launch(case, n, port):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("case,port", [("collectives", 29611), ("fused", 29614), ("engine", 29612), ("timeout", 29613)])
+@pytest.mark.parametrize("case,port", [("collectives", 29611), ("fused", 29614), ("engine", 29612), ("timeout", 29613),
+                                       ("collectives_nvls", 29615), ("engine_nvls", 29616)])
 def test_two_gpus(case, port):
     print(_launch(case, 2, port))
 
 
 @pytest.mark.skipif(_ngpu() < 8, reason="needs 8 GPUs")
-@pytest.mark.parametrize("case,port", [("collectives", 29621), ("fused", 29623), ("collectives_wide", 29624)])
+@pytest.mark.parametrize("case,port", [("collectives", 29621), ("fused", 29623), ("collectives_wide", 29624),
+                                       ("engine", 29625), ("collectives_nvls", 29626), ("engine_nvls", 29627)])
 def test_eight_gpus(case, port):
     print(_launch(case, 8, port))
