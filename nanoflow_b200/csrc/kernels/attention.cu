@@ -508,16 +508,7 @@ attn_prefill_kernel(nfk_attn_params p) {
   }
 }
 
-int sm_count_attn() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
+inline int sm_count_attn() { return device_sm_count(); }
 
 int check_common(const nfk_attn_params* p) {
   if (p == nullptr) return NF_ERR_BAD_ARG;
@@ -535,7 +526,8 @@ int check_common(const nfk_attn_params* p) {
 template <int HD, int ST>
 int launch_decode_st(const nfk_attn_params* p, cudaStream_t stream) {
   using Cfg = DecCfg<HD, ST>;
-  static bool attr = false;
+  static bool attr_dev[kMaxDevices] = {false};   // the attribute is per device
+  bool& attr = attr_dev[device_slot()];
   if (!attr) {
     if (cudaFuncSetAttribute(attn_decode_kernel<HD, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg::SMEM_BYTES) != cudaSuccess)
@@ -563,7 +555,8 @@ int launch_decode(const nfk_attn_params* p, cudaStream_t stream) {
 template <int HD>
 int launch_prefill(const nfk_attn_params* p, cudaStream_t stream) {
   using Cfg = PreCfg<HD>;
-  static bool attr = false;
+  static bool attr_dev[kMaxDevices] = {false};   // the attribute is per device
+  bool& attr = attr_dev[device_slot()];
   if (!attr) {
     if (cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg::SMEM_BYTES) != cudaSuccess)
@@ -600,7 +593,6 @@ static __device__ __align__(256) float g_decode_static_scratch[NFK_ATTN_DECODE_S
 
 namespace nf {
 namespace {
-constexpr int kMaxDevices = 64;
 float* g_static_scratch_ptr[kMaxDevices] = {nullptr};
 
 // Device address of the scratch array on the current device. In host code the array's name is only

@@ -345,16 +345,7 @@ attn_prefill_tc_kernel(nfk_attn_params p) {
   }
 }
 
-int sm_count_tc() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
+inline int sm_count_tc() { return device_sm_count(); }
 
 }  // namespace
 }  // namespace nf
@@ -369,7 +360,8 @@ extern "C" int nfk_attn_prefill_tc(const nfk_attn_params* p, cudaStream_t stream
   if (p->head_dim != HD || p->page_size != kPage || group > 16 || (16 % group) != 0) return NF_ERR_UNSUPPORTED;
   if (p->num_items == 0) return NF_OK;
   if (p->num_items < 0 || p->items == nullptr) return NF_ERR_BAD_ARG;
-  static bool attr = false;
+  static bool attr_dev[kMaxDevices] = {false};   // the attribute is per device
+  bool& attr = attr_dev[device_slot()];
   if (!attr) {
     if (cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
         cudaSuccess)

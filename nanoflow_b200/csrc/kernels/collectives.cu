@@ -402,7 +402,8 @@ void prefer_max_shared(K kernel) {
 
 template <int NR>
 int launch_allreduce(const nfk_allreduce_params* p, int ctas, cudaStream_t stream) {
-  static bool once = false;
+  static bool once_dev[kMaxDevices] = {false};   // the attribute is per device
+  bool& once = once_dev[device_slot()];
   if (!once) {
     prefer_max_shared(allreduce_kernel<NR, true, false>);
     prefer_max_shared(allreduce_kernel<NR, false, false>);
@@ -414,7 +415,8 @@ int launch_allreduce(const nfk_allreduce_params* p, int ctas, cudaStream_t strea
   }
   const bool norm = p->norm_w != nullptr;
   if (p->mc_heap != nullptr && p->src_mode == 0 && NR > 1) {
-    static bool once_mc = false;
+    static bool once_mc_dev[kMaxDevices] = {false};
+    bool& once_mc = once_mc_dev[device_slot()];
     if (!once_mc) {
       prefer_max_shared(allreduce_mc_kernel<true>);
       prefer_max_shared(allreduce_mc_kernel<false>);
@@ -498,7 +500,7 @@ extern "C" int nfk_allreduce(const nfk_allreduce_params* p, cudaStream_t stream)
   // Even an empty buffer takes part in the handshakes so that all ranks stay in step.
   const int nr = p->ctx.nranks;
   const int owned = (p->rows + nr - 1) / nr;
-  int ctas = p->num_ctas > 0 ? p->num_ctas : 148;
+  int ctas = p->num_ctas > 0 ? p->num_ctas : device_sm_count();
   if (ctas > owned) ctas = owned > 0 ? owned : 1;
   switch (nr) {
     case 1: return launch_allreduce<1>(p, ctas, stream);
@@ -520,7 +522,8 @@ extern "C" int nfk_allgather(const nfk_allgather_params* p, cudaStream_t stream)
   long long ctas = p->num_ctas > 0 ? p->num_ctas : 16;
   const long long need = ((p->shard_bytes >> 4) * (p->rows > 1 ? p->rows : 1) + kCommThreads - 1) / kCommThreads;
   if (ctas > need) ctas = need > 0 ? need : 1;
-  static bool once = false;
+  static bool once_dev[kMaxDevices] = {false};   // the attribute is per device
+  bool& once = once_dev[device_slot()];
   if (!once) {
     prefer_max_shared(allgather_kernel);
     once = true;
@@ -532,7 +535,8 @@ extern "C" int nfk_allgather(const nfk_allgather_params* p, cudaStream_t stream)
 extern "C" int nfk_comm_barrier(const nfk_comm_barrier_params* p, cudaStream_t stream) {
   using namespace nf;
   if (!p || !ctx_ok(p->ctx) || p->flag_off % 16 != 0) return NF_ERR_BAD_ARG;
-  static bool once = false;
+  static bool once_dev[kMaxDevices] = {false};   // the attribute is per device
+  bool& once = once_dev[device_slot()];
   if (!once) {
     prefer_max_shared(comm_barrier_kernel);
     once = true;

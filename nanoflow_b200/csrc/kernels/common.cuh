@@ -290,6 +290,14 @@ NF_DEVICE float2 unpack_bf16x2(uint32_t u) {
 
 #endif  // __CUDACC__
 
+// ---- host: facts about the current device, asked once per device ----------------------------------
+// Number of SMs of the current device (grids are sized from it). Falls back to a B200's 148 when no
+// device can be asked (planning calls on a machine without a GPU).
+int device_sm_count();
+// Slot of the current device in per-device caches (0 when there is no device); kMaxDevices slots.
+constexpr int kMaxDevices = 64;
+int device_slot();
+
 // ---- host: driver entry point for tensor-map encoding (no link-time libcuda dependency) -----------
 typedef CUresult (*nf_encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                        const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,

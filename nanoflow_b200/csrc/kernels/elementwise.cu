@@ -286,7 +286,10 @@ __global__ void flag_wait_kernel(const unsigned int* flag, unsigned int target, 
   report_status(status, NF_ST_TIMEOUT_PEER_FLAG);
 }
 
-inline int grid_for(int rows) { return rows < 148 * 16 ? (rows > 0 ? rows : 1) : 148 * 16; }
+inline int grid_for(int rows) {
+  const int cap = device_sm_count() * 16;
+  return rows < cap ? (rows > 0 ? rows : 1) : cap;
+}
 inline int ok_or_cuda() { return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA; }
 inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -352,7 +355,7 @@ extern "C" int nfk_silu_mul(void* out, const void* gate, const void* up, long lo
     return NF_ERR_BAD_ARG;
   const long long nvec = n / 8;
   long long blocks = (nvec + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > device_sm_count() * 8) blocks = device_sm_count() * 8;
   silu_mul_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>((uint4*)out, (const uint4*)gate,
                                                                 (const uint4*)up, nvec);
   return ok_or_cuda();

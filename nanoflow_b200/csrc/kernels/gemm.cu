@@ -40,6 +40,29 @@ nf_encode_tiled_fn get_encode_tiled() {
   return fn;
 }
 
+int device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return (dev >= 0 && dev < kMaxDevices) ? dev : 0;
+}
+
+int device_sm_count() {
+  static int cached[kMaxDevices] = {0};
+  const int slot = device_slot();
+  int n = cached[slot];
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, slot) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      return 148;
+    }
+    cached[slot] = n;   // the same value from whichever thread gets here first
+  }
+  return n;
+}
+
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                       uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
   nf_encode_tiled_fn enc = get_encode_tiled();
@@ -675,16 +698,7 @@ __global__ void rs_signal_only_kernel(DevParams p) {
   }
 }
 
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
+inline int sm_count() { return device_sm_count(); }
 
 // Split-K second pass: D = sum_s partial[s] (+ bias) (+ beta * C), fp32 -> bf16.
 __global__ void __launch_bounds__(256)
@@ -944,8 +958,11 @@ int launch(const nfk_gemm_params& g, int bn, int split_k, bool stream_k, cudaStr
   } else {
     tmB1 = tmB0;
   }
-  static bool attr_set = false;
-  static int max_workers = 0;    // CTAs (or CTA pairs) that can be resident at once
+  // function attributes and occupancy are per device: one slot per device this process drives
+  static bool attr_set_dev[kMaxDevices] = {false};
+  static int max_workers_dev[kMaxDevices] = {0};    // CTAs (or CTA pairs) that can be resident at once
+  bool& attr_set = attr_set_dev[device_slot()];
+  int& max_workers = max_workers_dev[device_slot()];
   if (!attr_set) {
     if (cudaFuncSetAttribute(gemm_tcgen05_kernel<MT, EPI, CG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kSmemMax) != cudaSuccess)

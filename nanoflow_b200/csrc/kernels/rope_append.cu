@@ -178,7 +178,7 @@ extern "C" int nfk_rope_table(const nfk_rope_table_params* p, cudaStream_t strea
     return NF_ERR_BAD_ARG;
   const long long total = static_cast<long long>(p->T) * p->half;
   long long blocks = (total + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > device_sm_count() * 8) blocks = device_sm_count() * 8;
   rope_table_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(*p);
   return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
 }
@@ -200,12 +200,12 @@ extern "C" int nfk_rope_append(const nfk_rope_append_params* p, cudaStream_t str
     if (reinterpret_cast<uintptr_t>(p->cos_sin) & 15) return NF_ERR_BAD_ARG;
     const long long total = static_cast<long long>(p->T) * units;
     long long nb = (total + 255) / 256;
-    if (nb > 148 * 16) nb = 148 * 16;
+    if (nb > device_sm_count() * 16) nb = device_sm_count() * 16;
     rope_append_table_kernel<<<static_cast<int>(nb), 256, 0, stream>>>(*p);
     return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
   }
   int threads = units < 64 ? 64 : (units < 128 ? 128 : 256);
-  int blocks = p->T < 148 * 8 ? p->T : 148 * 8;
+  int blocks = p->T < device_sm_count() * 8 ? p->T : device_sm_count() * 8;
   rope_append_kernel<<<blocks, threads, 0, stream>>>(*p);
   return cudaGetLastError() == cudaSuccess ? NF_OK : NF_ERR_CUDA;
 }

@@ -113,6 +113,17 @@ def new_status(device=None) -> torch.Tensor:
     return torch.zeros(1, dtype=torch.int32, device=device or "cuda")
 
 
+def sm_count(device=None) -> int:
+    """SMs of ``device`` (the current CUDA device by default); a B200's 148 on a machine without a GPU,
+    where graphs are only built for analysis."""
+    if not torch.cuda.is_available():
+        return 148
+    if device is not None and torch.device(device).type != "cuda":
+        return 148
+    return int(torch.cuda.get_device_properties(device if device is not None else torch.cuda.current_device())
+               .multi_processor_count)
+
+
 def check_status(status: torch.Tensor, what: str = "kernel") -> None:
     """Read a device status word (synchronises) and raise if a kernel reported a problem."""
     code = int(status.item()) & 0xFFFFFFFF

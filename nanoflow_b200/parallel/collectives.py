@@ -51,14 +51,14 @@ FLAG_BYTES = 128
 
 class TpCollectives(CollectiveHooks):
     def __init__(self, rank: int, world: int, device: torch.device, heap_bytes: int = 1 << 30,
-                 num_ctas: int = 148, fuse_norm: bool = True, backend: str = ""):
+                 num_ctas: int = 0, fuse_norm: bool = True, backend: str = ""):
         if world > 8:
             raise ValueError("at most 8 ranks (one NVSwitch domain)")
         self.rank, self.tp, self.device = rank, world, device
         self.heap = SymmetricHeap(rank, world, device, heap_bytes, backend=backend)
         # all-reduces go through the NVSwitch (multimem) whenever the heap has a multicast mapping
         self.use_multimem = self.heap.mc_base != 0
-        self.num_ctas = num_ctas
+        self.num_ctas = num_ctas or _ops.sm_count(device)
         self.fuse_norm = fuse_norm
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.fake_wire_us_per_row = 0.0     # see all_reduce(): sleep standing in for absent ranks

@@ -279,7 +279,7 @@ class Engine:
             cp = self.eng.decode_chunk_pages
         else:
             items = plan.num_decode * self.model.kv_heads_local
-            target = 2 * 148 * 2
+            target = 2 * ops.sm_count(self.device) * 2      # two rounds of two CTAs per SM
             if items == 0 or items >= target or plan.max_kv_pages <= 16:
                 return 0, 1
             want = min(DECODE_MAX_CHUNKS, math.ceil(target / items))

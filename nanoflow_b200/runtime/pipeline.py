@@ -30,6 +30,7 @@ from typing import Callable, Dict, List, Optional
 
 import torch
 
+from .. import ops as _ops
 from ..config import EngineConfig, ModelConfig
 from ..models.llama import RankWeights
 from .graph import (ArgmaxCombineParams, ArgmaxParams, AttnParams, EmbeddingParams, GatherParams, GemmParams, RopeTableParams,
@@ -267,7 +268,7 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         dp.decode_stages = eng.decode_stages
         if tp > 1 and overlap and eng.attn_overlap:
             if dp.num_ctas == 0:
-                dp.num_ctas = 148    # one CTA per SM: the second would not fit beside a GEMM CTA
+                dp.num_ctas = _ops.sm_count(st.device)   # one CTA per SM: a second would not fit beside a GEMM CTA
             if dp.decode_stages == 0:
                 dp.decode_stages = 2 # 64 KB: leaves room for a collective's CTA beside GEMM + decode
         dp.workspace = _ptr(bufs.decode_ws)

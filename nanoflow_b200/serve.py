@@ -143,7 +143,7 @@ def main(argv=None) -> int:
         from torch.distributed.distributed_c10d import _get_default_store
         from .serving.frontend import SharedReleaseClock
 
-        rm.release_clock = SharedReleaseClock(_get_default_store(), rank)
+        rm.release_clock = SharedReleaseClock(_get_default_store(), rank, world)
     loop = ServingLoop(engine, sch, rm, simulated_time=not args.online, est_cycle_time=args.est_cycle_time,
                        offload=offload, health=health, trace_phases=args.profile_mode)
     log = None

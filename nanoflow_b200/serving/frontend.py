@@ -147,13 +147,17 @@ class SharedReleaseClock:
 
     Rank 0 publishes the elapsed serving time it measured at the top of cycle ``c`` under one key per
     cycle; the other ranks block on that key (the store's ``get`` waits until the key exists) and use
-    the value instead of their own clock. Keys older than ``keep`` cycles are deleted by rank 0: ranks
-    are never further apart than the iterations in flight, because every iteration's collectives wait
-    for all of them. The reference runs one scheduler in one process for all GPUs
-    (pipeline/utils/serve_8B.py:687-696) and so never meets the problem."""
+    the value instead of their own clock. Every follower counts the cycles it has consumed in a counter
+    key; every ``keep`` cycles rank 0 reads those counters and deletes the keys that all followers are
+    past (while the engine is busy the ranks are at most the iterations in flight apart, but in an idle
+    stretch nothing else holds rank 0 back). The reference runs one scheduler in one process for all
+    GPUs (pipeline/utils/serve_8B.py:687-696) and so never meets the problem."""
 
-    def __init__(self, store, rank: int, prefix: str = "nf_release", keep: int = 64):
-        self.store, self.rank, self.prefix, self.keep = store, rank, prefix, keep
+    def __init__(self, store, rank: int, world: int = 2, prefix: str = "nf_release", keep: int = 64):
+        self.store, self.rank, self.world, self.prefix, self.keep = store, rank, world, prefix, max(1, keep)
+        self._deleted = 0          # rank 0: keys of cycles [0, _deleted) are gone
+        if rank != 0:
+            self.store.add(f"{prefix}/ack/{rank}", 0)
 
     def passed(self, cycle: int, local_passed: float) -> float:
         import struct
@@ -161,10 +165,16 @@ class SharedReleaseClock:
         key = f"{self.prefix}/{cycle}"
         if self.rank == 0:
             self.store.set(key, struct.pack("<d", float(local_passed)))
-            if cycle >= self.keep:
-                self.store.delete_key(f"{self.prefix}/{cycle - self.keep}")
+            if cycle - self._deleted >= 2 * self.keep:
+                seen = min((int(self.store.add(f"{self.prefix}/ack/{r}", 0)) for r in range(1, self.world)),
+                           default=cycle)
+                for c in range(self._deleted, min(seen, cycle)):
+                    self.store.delete_key(f"{self.prefix}/{c}")
+                self._deleted = max(self._deleted, min(seen, cycle))
             return float(local_passed)
-        return struct.unpack("<d", bytes(self.store.get(key)))[0]
+        value = struct.unpack("<d", bytes(self.store.get(key)))[0]
+        self.store.add(f"{self.prefix}/ack/{self.rank}", 1)
+        return value
 
 
 def _lazy_hf_tokenizer(name: str):

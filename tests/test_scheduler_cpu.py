@@ -242,7 +242,7 @@ def test_online_release_is_identical_on_ranks_with_skewed_clocks():
         for a in arrivals:
             rm.add_request(40, 6, float(a))
         rm.finalize_stats()
-        rm.release_clock = SharedReleaseClock(store, rank, keep=8)
+        rm.release_clock = SharedReleaseClock(store, rank, 2, keep=8)
         pool = DistKVPool(2, 2, 64, 400, 16)
         s = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=64, nanobatch_sizes=[32, 32],
                       average_prefill_length=40, average_decode_length=6, group_size=2)
@@ -267,4 +267,4 @@ def test_online_release_is_identical_on_ranks_with_skewed_clocks():
     assert set(results) == {0, 1}
     assert results[0] == results[1]
     assert sum(1 for x in results[0] if x is not None) > 10       # the trace was actually served
-    assert store.num_keys() <= 8 + 2                               # old keys are deleted
+    assert store.num_keys() < cycles                               # keys that both ranks are past get deleted
