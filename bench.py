@@ -118,6 +118,11 @@ def main():
     ap.add_argument("--attn-overlap", action="store_true",
                     help="tensor-parallel overlapped pipelines: decode attention on its own stream under the GEMMs of "
                          "the other nano-batches (use with three or four nano-batches, e.g. --nano 2048,2048,2048,2048)")
+    ap.add_argument("--cross-layer", action="store_true",
+                    help="overlapped pipelines: software pipeline across layers (a nano-batch's attention of layer l+1 "
+                         "under the other nano-batches' O / FFN GEMMs of layer l)")
+    ap.add_argument("--prefill-impl", default="", choices=["", "ws", "tc", "mma"], help="prefill attention kernel")
+    ap.add_argument("--decode-ctas", type=int, default=0, help="CTA budget of the decode attention kernel (0 = default)")
     ap.add_argument("--decode-stages", type=int, default=0, choices=[0, 2, 3],
                     help="decode attention pages in flight per warp (0: 3, or 2 with --attn-overlap)")
     ap.add_argument("--ar-wide", action="store_true", help="8 GPUs: all-reduce with twice the loads in flight per phase")
@@ -224,6 +229,10 @@ def main():
     cfg.engine.gemm_rs_staged = bool(args.fuse_rs_staged)
     cfg.engine.net_streams = args.net_streams
     cfg.engine.attn_overlap = bool(args.attn_overlap)
+    cfg.engine.cross_layer_pipeline = bool(args.cross_layer)
+    cfg.engine.prefill_impl = args.prefill_impl
+    if args.decode_ctas:
+        cfg.engine.sm_budget["attn_decode"] = args.decode_ctas
     cfg.engine.decode_stages = args.decode_stages
     cfg.engine.fuse_gemm_norm = not args.no_fuse_norm
     cfg.engine.prefill_beside_decode = not args.serial_attention
@@ -356,6 +365,8 @@ def main():
                        "prefill_beside_decode": bool(cfg.engine.prefill_beside_decode),
                        "decode_tail": args.decode_tail, "net_streams": cfg.engine.net_streams,
                        "attn_overlap": bool(cfg.engine.attn_overlap),
+                       "cross_layer_pipeline": bool(cfg.engine.cross_layer_pipeline),
+                       "prefill_impl": cfg.engine.prefill_impl or "default",
                        "symm_heap": getattr(getattr(coll, "heap", None), "backend", "none") if world > 1 else "none",
                        "all_reduce": ("in-switch (multimem)" if getattr(coll, "use_multimem", False) else
                                       "peer loads") if world > 1 else "none",

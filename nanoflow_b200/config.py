@@ -159,6 +159,10 @@ class EngineConfig:
     decode_tail_fraction: float = 0.0      # share of the decode context scheduled into the last nano-batch
     net_streams: int = 1                   # 2: collectives of odd nano-batches get a second network stream
     attn_overlap: bool = False             # TP: decode attention on its own stream under the other nano-batches' GEMMs
+    cross_layer_pipeline: bool = False     # overlapped pipelines: the QKV / RoPE of layer l+1 of a nano-batch is issued
+                                           # right behind its FFN of layer l, so its attention runs under the other
+                                           # nano-batches' O / FFN GEMMs (software pipeline across layers)
+    prefill_impl: str = ""                 # "" = choose (ws for head_dim 128), "ws", "tc", "mma"
     decode_stages: int = 0                 # decode attention pages in flight per warp: 0 = 3 (2 under attn_overlap), 2, 3
     gemm_shapes: Dict[str, Dict[str, int]] = field(default_factory=dict)   # "<op>.nb<k>" -> pinned launcher arguments
     decode_chunk_pages: int = 0            # 0 = choose per iteration
@@ -247,6 +251,8 @@ def parse_config(raw: Dict[str, Any], *, tp: Optional[int] = None) -> NanoflowCo
         decode_tail_fraction=float(pc.get("decode_tail_fraction", 0.0)),
         net_streams=int(pc.get("net_streams", 1)),
         attn_overlap=bool(pc.get("attn_overlap", False)),
+        cross_layer_pipeline=bool(pc.get("cross_layer_pipeline", False)),
+        prefill_impl=str(pc.get("prefill_impl", "")),
         decode_stages=int(pc.get("decode_stages", 0)),
         model_id=sc.get("model", ""),
         weight_path=sc.get("weight_path", ""),

@@ -305,10 +305,12 @@ __device__ __forceinline__ void multimem_st_v4(void* mc, const uint4& v) {
                : "memory");
 }
 
-// One row per CTA pass, the whole row in flight at once (8 multimem loads + 8 residual loads per thread);
-// rows r, r + nranks, ... of the buffer belong to rank r as in allreduce_kernel. The switch returns the
-// ranks' sum already rounded to bf16; the residual is added to that in fp32 and the result rounded once
-// more, so sums can differ from allreduce_kernel's (one rounding) in the last bf16 bit.
+// One row per CTA pass with the whole row in flight at once (8 multimem loads + 8 residual loads per
+// thread), and the next row's loads issued before the current row is summed, normalised and stored, so
+// that a CTA always has a row on the wire; rows r, r + nranks, ... of the buffer belong to rank r as in
+// allreduce_kernel. The switch returns the ranks' sum already rounded to bf16; the residual is added to
+// that in fp32 and the result rounded once more, so sums can differ from allreduce_kernel's (one
+// rounding) in the last bf16 bit.
 template <bool NORM>
 __global__ void __launch_bounds__(kArThreads, 3)
 allreduce_mc_kernel(nfk_allreduce_params p) {
@@ -323,17 +325,24 @@ allreduce_mc_kernel(nfk_allreduce_params p) {
   const char* resid = reinterpret_cast<const char*>(p.resid);
   char* sum_out = reinterpret_cast<char*>(p.sum_out);
   const int owned = (p.rows - c.rank + NR - 1) / NR;
-  for (int k = blockIdx.x; k < owned; k += gridDim.x) {
+  uint4 in[kArVec], rs[kArVec], in_nx[kArVec], rs_nx[kArVec];
+  auto fetch = [&](int k, uint4 (&a)[kArVec], uint4 (&b)[kArVec]) {
     const long long row = c.rank + static_cast<long long>(NR) * k;
-    uint4 in[kArVec], rs[kArVec];
 #pragma unroll
     for (int i = 0; i < kArVec; ++i) {
       const int v = threadIdx.x + i * kArThreads;
       if (v < nvec) {
-        in[i] = multimem_ld_reduce_bf16x8(mc + p.buf_off + row * row_bytes + v * 16);
-        if (resid != nullptr) rs[i] = *reinterpret_cast<const uint4*>(resid + row * p.resid_ld * 2 + v * 16);
+        a[i] = multimem_ld_reduce_bf16x8(mc + p.buf_off + row * row_bytes + v * 16);
+        if (resid != nullptr) b[i] = *reinterpret_cast<const uint4*>(resid + row * p.resid_ld * 2 + v * 16);
       }
     }
+  };
+  int k = blockIdx.x;
+  if (k < owned) fetch(k, in, rs);
+  for (; k < owned; k += gridDim.x) {
+    const long long row = c.rank + static_cast<long long>(NR) * k;
+    const int k_next = k + gridDim.x;
+    if (k_next < owned) fetch(k_next, in_nx, rs_nx);
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < kArVec; ++i) {
@@ -385,6 +394,11 @@ allreduce_mc_kernel(nfk_allreduce_params p) {
                          make_uint4(ov[0], ov[1], ov[2], ov[3]));
         }
       }
+    }
+#pragma unroll
+    for (int i = 0; i < kArVec; ++i) {
+      in[i] = in_nx[i];
+      rs[i] = rs_nx[i];
     }
   }
   comm_exit(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status);

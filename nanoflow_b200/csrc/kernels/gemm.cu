@@ -551,6 +551,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               // sends the row's run to the owner's slab. A lane only ever reads back what it wrote, so
               // the generic -> async proxy fence is all the ordering the copy needs.
               uint8_t* stage_row = smem + STAGES * STAGE_BYTES + (q * 32 + lane) * kRsRowPitch;
+              // the bulk copy of the previous run reads this row: it must be done reading before the first
+              // write of a new run (waiting here, not right after the copy, lets the copy run under the
+              // accumulator loads in between)
+              if ((c & 3) == 0) tma_store_wait_read<0>();
 #pragma unroll
               for (int g8 = 0; g8 < 4; ++g8) {
                 if (g8 * 8 < nval) {
@@ -576,7 +580,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                   bulk_store_1d(srow + run_col0, stage_row, static_cast<uint32_t>(run_end - run_col0) * 2u);
                 }
                 tma_store_commit();
-                tma_store_wait_read<0>();   // the staging row may be rewritten
               }
               continue;
             }

@@ -171,6 +171,9 @@ int nfk_attn_decode(const nfk_attn_params* p, cudaStream_t stream);
 int nfk_attn_prefill(const nfk_attn_params* p, cudaStream_t stream);
 // Same contract as nfk_attn_prefill for head_dim 128, on tcgen05 tensor cores (attention_tc.cu).
 int nfk_attn_prefill_tc(const nfk_attn_params* p, cudaStream_t stream);
+// The same on a warp-specialised pipeline: a TMA load warp (whole pages, no transposes), an MMA warp that
+// issues the next tile's scores under this tile's softmax, four softmax warps (attention_ws.cu).
+int nfk_attn_prefill_ws(const nfk_attn_params* p, cudaStream_t stream);
 
 // ------------------------------------------------------------------------------------------------
 // KV offload (kv_offload.cu): gather / scatter whole pages between the pool and a staging buffer

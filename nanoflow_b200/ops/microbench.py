@@ -1,4 +1,4 @@
-"""Per-kernel micro-benchmarks: ``python -m nanoflow_b200.ops.microbench [gemm|swiglu|smallm|decode|prefill|norm|hostlink|all]``
+"""Per-kernel micro-benchmarks: ``python -m nanoflow_b200.ops.microbench [gemm|swiglu|smallm|decode|prefill|norm|hostlink|budget|all]``
 (JSON lines; ``... table rows.jsonl`` turns them into a markdown table).
 
 Each case is timed with CUDA events on the launching stream after warm-up, with an L2 flush (a
@@ -132,12 +132,85 @@ def bench_prefill():
         items = torch.tensor([[b, b * ctx + t, min(tq, ctx - t)] for b in range(batch)
                               for t in range(0, ctx, tq)], dtype=torch.int32, device="cuda")
         flops = 4.0 * batch * q_heads * hd * ctx * ctx / 2
-        for impl in ("tc", "mma"):
+        for impl in ("ws", "tc", "mma"):
             fn = lambda: ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, items, q_heads=q_heads, impl=impl)
             med, best = time_ms(fn)
             print(json.dumps(dict(op="attn_prefill_" + impl, batch=batch, ctx=ctx, kv_heads=kv_heads, group=group,
                                   ms=round(med, 4), tflops=round(flops / med / 1e9, 1),
                                   frac_of_peak=round(flops / med / 1e9 / tf_peak, 3), peak=how)), flush=True)
+
+
+def bench_budget():
+    """Decode attention against its CTA budget, alone and beside back-to-back GEMMs on a second stream:
+    the table an SM-budget search needs (the reference sweeps ``sm_blk`` the same way,
+    gemv/src/bench_batch_decode.cu:222-249, and ships only the chosen numbers in its configs).
+
+    Shapes are one GPU's share of Llama-2-70B at TP8 in the 1024/512 steady state: 2731 decode requests x
+    one KV head, ~1280 tokens of context; the GEMM is the gate/up projection of a 2048-row nano-batch."""
+    bw_peak, tf_peak, how = peaks()
+    batch, ctx, kv_heads, group, hd = 2731, 1280, 1, 8, 128
+    q_heads = kv_heads * group
+    pool, qo, kvp, kvi, last = _paged(batch, ctx, kv_heads, hd)
+    q = torch.randn(batch, q_heads * hd, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    nbytes = batch * ctx * kv_heads * hd * 2 * 2 + 2 * q.numel() * 2
+    M, F, K = 2048, 3584, 8192
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    wg = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.02
+    wu = torch.randn(F, K, device="cuda", dtype=torch.bfloat16) * 0.02
+    act = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
+    ws = torch.zeros(160 << 20, dtype=torch.uint8, device="cuda")
+    gflop = 4.0 * M * F * K
+    s_a, s_g = torch.cuda.Stream(), torch.cuda.Stream()
+    n_gemm = 3
+
+    def run(ctas, stages, smem_kb, mode):
+        """mode: 'decode', 'gemm' or 'both'. Returns (decode us, gemm us per launch, span us), best of 5."""
+        best = None
+        for it in range(7):
+            flush_l2()
+            torch.cuda.synchronize()
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+            e[0].record()
+            s_a.wait_event(e[0]); s_g.wait_event(e[0])
+            if mode in ("gemm", "both"):
+                with torch.cuda.stream(s_g):
+                    e[1].record()
+                    for _ in range(n_gemm):
+                        ops.gemm_swiglu(a, wg, wu, out=act, workspace=ws, smem_budget_kb=smem_kb)
+                    e[2].record()
+            if mode in ("decode", "both"):
+                with torch.cuda.stream(s_a):
+                    e[3].record()
+                    ops.attn_decode(q, out, pool, qo, kvp, kvi, last, q_heads=q_heads, req_begin=0, req_count=batch,
+                                    num_ctas=ctas, stages=stages)
+                    e[4].record()
+            torch.cuda.current_stream().wait_stream(s_a)
+            torch.cuda.current_stream().wait_stream(s_g)
+            e[5].record()
+            torch.cuda.synchronize()
+            row = (e[3].elapsed_time(e[4]) * 1e3 if mode != "gemm" else 0.0,
+                   e[1].elapsed_time(e[2]) * 1e3 / n_gemm if mode != "decode" else 0.0,
+                   e[0].elapsed_time(e[5]) * 1e3)
+            if it >= 2 and (best is None or row[2] < best[2]):
+                best = row
+        return best
+
+    for smem_kb in (0, 200, 130):
+        _, g_us, _ = run(0, 0, smem_kb, "gemm")
+        print(json.dumps(dict(op="budget_gemm_alone", M=M, F=F, K=K, smem_kb=smem_kb, us=round(g_us, 1),
+                              tflops=round(gflop / g_us / 1e6, 1), peak=how)), flush=True)
+    for stages in (3, 2):
+        for ctas in (16, 32, 48, 64, 96, 148, 296):
+            d_us, _, _ = run(ctas, stages, 0, "decode")
+            row = dict(op="budget_decode", num_ctas=ctas, stages=stages, alone_us=round(d_us, 1),
+                       alone_frac_of_peak=round(nbytes / d_us / 1e3 / bw_peak, 3), peak=how)
+            if ctas <= 148:
+                smem_kb = 130 if stages == 3 else 160       # what is left of the SM beside a decode CTA
+                d2, g2, span = run(ctas, stages, smem_kb, "both")
+                row.update(beside_gemm_smem_kb=smem_kb, beside_us=round(d2, 1), gemm_beside_us=round(g2, 1),
+                           span_us=round(span, 1))
+            print(json.dumps(row), flush=True)
 
 
 def bench_norm():
@@ -296,6 +369,8 @@ def main(argv):
         bench_decode()
     if what in ("prefill", "all"):
         bench_prefill()
+    if what == "budget":
+        bench_budget()
     if what in ("norm", "all"):
         bench_norm()
     if what in ("hostlink", "all"):

@@ -279,7 +279,10 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         pp.num_ctas = budget.get("attn_prefill", 0)
         pp.items = _ptr(bufs.nano_items[k])
         # head_dim 128: the tcgen05 kernel; other head sizes: the warp-level mma.sync kernel
-        pre_kernel = "nfk_attn_prefill_tc" if (hd == 128 and eng.prefill_tc) else "nfk_attn_prefill"
+        impl = eng.prefill_impl or ("tc" if (hd == 128 and eng.prefill_tc) else "mma")
+        if hd != 128:
+            impl = "mma"
+        pre_kernel = {"ws": "nfk_attn_prefill_ws", "tc": "nfk_attn_prefill_tc", "mma": "nfk_attn_prefill"}[impl]
         pre = g.add(f"L{l}.nb{k}.attn_prefill", pp, prefill_stream, deps=[ro] + straddle, kernel=pre_kernel,
                     dyn=[("num_items", nb_items[k])], layer=l, nano=k)
         rope_of[(l, k)] = ro
@@ -383,7 +386,20 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         pool = bufs.kv_pool[l]
         if eng.offload and io is not None and io.offload_staging is not None:
             offload_layer(l, pool, len(g.ops) - 1)
-        if overlap and nn > 1:
+        if overlap and nn > 1 and eng.cross_layer_pipeline:
+            # Software pipeline across layers (the reference's one-GPU schedule,
+            # pipeline/src/pipeline_local.cu:353-431): per nano-batch the compute stream gets
+            # O / FFN of layer l followed at once by QKV / RoPE of layer l+1, so the attention of that
+            # nano-batch for layer l+1 (attention stream) runs under the O / FFN / QKV GEMMs of the other
+            # nano-batches, and is done when its own O projection comes round again.
+            if l == 0:
+                sw_fronts = [attn_front(0, k, lw, pool) for k in range(nn)]
+            nxt_l = l + 1
+            for k in range(nn):
+                ffn(l, k, lw, o_proj(l, k, lw, *sw_fronts[k]))
+                if nxt_l < model.run_layers:
+                    sw_fronts[k] = attn_front(nxt_l, k, w.layers[nxt_l % model.num_layers], bufs.kv_pool[nxt_l])
+        elif overlap and nn > 1:
             # Issue order per layer: (front_k, o_k) for every nano-batch, then ffn_k for every
             # nano-batch. The all-reduce after o_k then runs (on the net stream, its CTAs sharing SMs
             # with the GEMM CTAs) beside the attention front-end of nano-batch k+1, the one after

@@ -12,13 +12,14 @@ from nanoflow_b200.serving import DistKVPool, RequestManager, Scheduler
 from nanoflow_b200.serving.loop import ServingLoop
 
 
-def _run(pipeline_type, nano, executor, gbs=48, guards=False, tail=0.0):
+def _run(pipeline_type, nano, executor, gbs=48, guards=False, tail=0.0, cross_layer=False):
     from nanoflow_b200.runtime.engine import Engine
 
     cfg = builtin_config("tiny", gpu_num=1, global_batch_size=gbs, pipeline_type=pipeline_type,
                          nanobatch_sizes=nano)
     cfg.engine.max_batch_size = gbs
     cfg.engine.debug_guards = guards
+    cfg.engine.cross_layer_pipeline = cross_layer
     fw = random_full_weights(cfg.model, seed=0, std=0.05)
     # the oracle sees the same bf16-rounded weights; only activation rounding differs
     for lay in fw.layers:
@@ -82,6 +83,13 @@ def test_engine_with_decode_requests_at_both_ends_of_the_batch():
     """Part of the decode requests scheduled behind the prompt chunks, into the last nano-batch: the
     decode kernel of that nano-batch starts at a request index past the prompts."""
     _run("LOCAL", [16, 32], "native", tail=0.5)
+
+
+@pytest.mark.parametrize("nano,tail,executor", [([16, 32], 0.0, "native"), ([16, 16, 16], 0.5, "native"), ([24, 24], 0.5, "graph")])
+def test_engine_cross_layer_software_pipeline(nano, tail, executor):
+    """QKV / RoPE of layer l+1 issued behind the same nano-batch's FFN of layer l (attention under the other
+    nano-batches' GEMMs): same tokens as the oracle."""
+    _run("LOCAL", nano, executor, cross_layer=True, tail=tail)
 
 
 def test_engine_matches_oracle_native_executor():

@@ -10,12 +10,14 @@ from nanoflow_b200.runtime.pipeline import Buffers, IoSpec, build_graph
 from nanoflow_b200.utils import depcheck
 
 
-def _host_graph(pipeline_type, tp, nano, gbs=48, fuse_rs=False, net_streams=1, fake_wire=0.0, attn_overlap=False):
+def _host_graph(pipeline_type, tp, nano, gbs=48, fuse_rs=False, net_streams=1, fake_wire=0.0, attn_overlap=False,
+                cross_layer=False):
     cfg = builtin_config("tiny", gpu_num=tp, global_batch_size=gbs, pipeline_type=pipeline_type, nanobatch_sizes=nano)
     m, e = cfg.model, cfg.engine
     e.fuse_gemm_rs = fuse_rs
     e.net_streams = net_streams
     e.attn_overlap = attn_overlap
+    e.cross_layer_pipeline = cross_layer
     e.max_batch_size = gbs
     fw = random_full_weights(m, seed=0)
     w = shard_weights(fw, m, 0, tp, dtype=torch.bfloat16)
@@ -365,6 +367,39 @@ def test_decode_attention_on_its_own_stream_under_tensor_parallelism(nano):
     plain, acc_plain, keep2 = _host_graph("PLLM", 2, nano, gbs=sum(nano))
     assert all(op.stream != "attn" for op in plain.ops) and not depcheck.check(plain, acc_plain)
     assert all(op.params.decode_stages == 0 for op in plain.ops if op.kernel == "nfk_attn_decode")
+    ex = NativeExecutor(g, None, single_stream=False, host_only=True)
+    ex.mod.host_log_clear()
+    ex.wait(ex.submit(_symbols(g, 0)))
+    log = ex.mod.host_log()
+    ex.close()
+    anc = _ancestors(log)
+    launches = [i for i, r in enumerate(log) if r[0] == LAUNCH]
+    for j, op in enumerate(g.ops):
+        for d in op.deps:
+            assert anc[launches[j]] >> launches[d] & 1
+
+
+@pytest.mark.parametrize("pipeline_type,tp,nano,attn_overlap", [("LOCAL", 1, [16, 32], False), ("LOCAL", 1, [16, 16, 16], False),
+                                                                 ("PLLM", 2, [16, 32], True), ("PLLM", 2, [16, 16, 16], True)])
+def test_cross_layer_software_pipeline_order(pipeline_type, tp, nano, attn_overlap):
+    """cross_layer_pipeline: a nano-batch's QKV / RoPE of layer l+1 follows its FFN of layer l on the compute
+    stream, ahead of the next nano-batch's O projection of layer l, so its attention (own stream) is unordered
+    with those GEMMs; all buffer hazards stay ordered and the executor wires every dependency."""
+    from nanoflow_b200.runtime.native import NativeExecutor
+
+    g, acc, keep = _host_graph(pipeline_type, tp, nano, gbs=sum(nano), attn_overlap=attn_overlap, cross_layer=True)
+    assert not depcheck.check(g, acc)
+    names = [op.name for op in g.ops]
+    for i, op in enumerate(g.ops):
+        assert all(d < i for d in op.deps + op.after_start)
+    assert names.index("L0.nb0.down") < names.index("L1.nb0.qkv") < names.index("L0.nb1.o")
+    hb = g.happens_before()
+    a1, o1, gu1 = names.index("L1.nb0.attn_decode"), names.index("L0.nb1.o"), names.index("L0.nb1.gate_up")
+    assert g.ops[a1].stream == "attn"
+    assert a1 not in hb[o1] and o1 not in hb[a1] and a1 not in hb[gu1] and gu1 not in hb[a1]
+    # same ops as the per-layer order, only issued differently
+    plain, _, keep2 = _host_graph(pipeline_type, tp, nano, gbs=sum(nano), attn_overlap=attn_overlap)
+    assert sorted(names) == sorted(op.name for op in plain.ops)
     ex = NativeExecutor(g, None, single_stream=False, host_only=True)
     ex.mod.host_log_clear()
     ex.wait(ex.submit(_symbols(g, 0)))

@@ -472,9 +472,9 @@ def _prefill_items(qo_indptr, group, reqs=None):
 
 @pytest.mark.parametrize("kv_heads,group,hd", [(1, 8, 128), (8, 8, 128), (4, 4, 128), (2, 1, 128), (2, 2, 64)])
 @pytest.mark.parametrize("case", ["short", "long", "chunked", "mixed"])
-@pytest.mark.parametrize("impl", ["mma", "tc"])
+@pytest.mark.parametrize("impl", ["mma", "tc", "ws"])
 def test_attn_prefill(kv_heads, group, hd, case, impl):
-    if impl == "tc" and hd != 128:
+    if impl in ("tc", "ws") and hd != 128:
         pytest.skip("the tcgen05 prefill kernel is built for head_dim 128")
     q_heads = kv_heads * group
     if case == "short":
