@@ -141,6 +141,11 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
     # the SMs that round leaves idle. The O projection, next on the GEMM stream, waits for both, so no
     # GEMM is ever queued beside the pair.
     prefill_stream = "attn2" if eng.prefill_beside_decode else S("attn")
+    if overlap and tp > 1 and eng.attn_overlap and eng.cross_layer_pipeline:
+        # Skewed schedule (below): only the decode kernel is small enough to sit on an SM beside a GEMM CTA;
+        # a prefill CTA (98-113 KB) would have to wait for a GEMM CTA to leave and then hold the next
+        # GEMM's CTA off that SM, so prefill attention stays in line on the compute stream.
+        prefill_stream = "gemm"
     # Collectives of one nano-batch never depend on those of another, and each is bound by the latency of
     # its peer loads rather than by the links; with two network streams the collective of an odd
     # nano-batch starts when its GEMM is done instead of queueing behind the previous one.
@@ -339,8 +344,13 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
 
     def ffn(l, k, lw, n2):
         """gate/up SwiGLU -> down -> reduce (+ residual, + fused next-layer attention norm)."""
-        gu = gemm(f"L{l}.nb{k}.gate_up", bufs.h, lw.wg, bufs.act, k, swiglu_up=lw.wu, deps=[n2], layer=l,
-                  tile_key="gate_up")
+        ffn_down(l, k, lw, ffn_gate_up(l, k, lw, n2))
+
+    def ffn_gate_up(l, k, lw, n2):
+        return gemm(f"L{l}.nb{k}.gate_up", bufs.h, lw.wg, bufs.act, k, swiglu_up=lw.wu, deps=[n2], layer=l,
+                    tile_key="gate_up")
+
+    def ffn_down(l, k, lw, gu):
         if tp == 1:
             # the next layer's attention norm comes out of the same call (not after the last layer:
             # the final norm runs on the sampled rows only)
@@ -386,7 +396,51 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         pool = bufs.kv_pool[l]
         if eng.offload and io is not None and io.offload_staging is not None:
             offload_layer(l, pool, len(g.ops) - 1)
-        if overlap and nn > 1 and eng.cross_layer_pipeline:
+        if overlap and nn > 1 and eng.cross_layer_pipeline and tp > 1:
+            # Skewed schedule under tensor parallelism: behind the O projection of nano-batch k the compute
+            # stream gets the front-end (QKV, RoPE / append) of the nano-batch whose O projection comes
+            # next (k+1 of this layer, or nano-batch 0 of the next layer), then k's FFN. With
+            # attn_overlap the decode attention of that next nano-batch then runs on its own stream under
+            # k's gate/up and down GEMMs, the all-reduce of k's O output hides under the front-end GEMM,
+            # and the one after k's down projection under the next O projection.
+            if nn == 2:
+                # Two nano-batches A, B, with B one phase behind A. Per period p the compute stream gets
+                #   o(B,p-1)  F(A,p)  gate_up(B,p-1)  o(A,p)  down(B,p-1)  gate_up(A,p)  F(B,p)  down(A,p)
+                # (F = QKV + RoPE / append). Every op that has to wait for something off the compute stream
+                # has a GEMM of the other nano-batch issued in between: decode attention of A under B's
+                # gate/up, the all-reduce of A's O output under B's down projection, the all-reduce after
+                # A's down projection under B's O projection, and the same for B a phase later. Of all
+                # interleavings of the two chains this one leaves the compute stream idle the least when
+                # replayed with measured op durations.
+                def lw_of(layer):
+                    return w.layers[layer % model.num_layers]
+
+                if l == 0:
+                    sw_state = {}
+                else:
+                    sw_state["n2B"] = o_proj(l - 1, 1, lw_of(l - 1), *sw_state.pop("frontB"))
+                sw_state["frontA"] = attn_front(l, 0, lw, pool)
+                if l > 0:
+                    sw_state["guB"] = ffn_gate_up(l - 1, 1, lw_of(l - 1), sw_state.pop("n2B"))
+                n2a = o_proj(l, 0, lw, *sw_state.pop("frontA"))
+                if l > 0:
+                    ffn_down(l - 1, 1, lw_of(l - 1), sw_state.pop("guB"))
+                gua = ffn_gate_up(l, 0, lw, n2a)
+                sw_state["frontB"] = attn_front(l, 1, lw, pool)
+                ffn_down(l, 0, lw, gua)
+                if l + 1 == model.run_layers:
+                    ffn(l, 1, lw, o_proj(l, 1, lw, *sw_state.pop("frontB")))
+                continue
+            if l == 0:
+                sw_fronts = {0: attn_front(0, 0, lw, pool)}
+            for k in range(nn):
+                n2 = o_proj(l, k, lw, *sw_fronts.pop(k))
+                if k + 1 < nn:
+                    sw_fronts[k + 1] = attn_front(l, k + 1, lw, pool)
+                elif l + 1 < model.run_layers:
+                    sw_fronts[0] = attn_front(l + 1, 0, w.layers[(l + 1) % model.num_layers], bufs.kv_pool[l + 1])
+                ffn(l, k, lw, n2)
+        elif overlap and nn > 1 and eng.cross_layer_pipeline:
             # Software pipeline across layers (the reference's one-GPU schedule,
             # pipeline/src/pipeline_local.cu:353-431): per nano-batch the compute stream gets
             # O / FFN of layer l followed at once by QKV / RoPE of layer l+1, so the attention of that

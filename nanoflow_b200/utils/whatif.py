@@ -9,7 +9,7 @@ what it is given. Its use is to take the durations measured in one timeline
 second network stream, decode requests spread over the nano-batches, another nano-batch split.
 
     python -m nanoflow_b200.utils.whatif tl8.json --tp 8 --nano 4096,4096 [--net-streams 2]
-        [--scale attn_decode.nb0=0.5 attn_decode.nb1=+167]
+        [--attn-overlap] [--cross-layer] [--scale attn_decode.nb0=0.5 attn_decode.nb1=+167]
 
 The reference's only schedule tooling plots per-cycle batch sizes after the fact
 (pipeline/utils/plotSchedule.py:1-52); it has no model of the per-layer op schedule.
@@ -90,7 +90,8 @@ def scale_durations(graph: OpGraph, durations: Sequence[float], rules: Dict[str,
 
 
 def structural_graph(tp: int, nano: Sequence[int], layers: int, pipeline_type: str = "", net_streams: int = 1,
-                     prefill_beside_decode: bool = True, attn_overlap: bool = False) -> OpGraph:
+                     prefill_beside_decode: bool = True, attn_overlap: bool = False,
+                     cross_layer: bool = False) -> OpGraph:
     """The op graph of a pipeline with the tiny model's tensors on the CPU: op names, streams and
     dependencies are those of any model with the same layer count, tensor-parallel degree and
     nano-batch count."""
@@ -110,6 +111,7 @@ def structural_graph(tp: int, nano: Sequence[int], layers: int, pipeline_type: s
     m, e = cfg.model, cfg.engine
     e.max_batch_size, e.net_streams, e.prefill_beside_decode = gbs, net_streams, prefill_beside_decode
     e.attn_overlap = attn_overlap
+    e.cross_layer_pipeline = cross_layer
     w = shard_weights(random_full_weights(m, seed=0), m, 0, tp, dtype=torch.bfloat16)
     coll = TpCollectives.for_analysis(0, tp) if tp > 1 else None
     bf = torch.bfloat16
@@ -146,6 +148,7 @@ def main(argv=None) -> int:
     ap.add_argument("--net-streams", type=int, default=1)
     ap.add_argument("--serial-attention", action="store_true")
     ap.add_argument("--attn-overlap", action="store_true")
+    ap.add_argument("--cross-layer", action="store_true", help="software pipeline across layers (skewed under TP)")
     ap.add_argument("--launch-gap", type=float, default=2.7, help="microseconds between launches on a stream")
     ap.add_argument("--scale", nargs="*", default=[], help="<kind>[.nb<k>]=<factor | +us | -us>")
     ap.add_argument("--pid", type=int, default=0)
@@ -154,7 +157,8 @@ def main(argv=None) -> int:
         d = json.load(f)
     events = [e for e in (d["traceEvents"] if isinstance(d, dict) else d) if e.get("pid", 0) == a.pid]
     nano = [int(x) for x in a.nano.split(",")]
-    g = structural_graph(a.tp, nano, a.layers, a.pipeline, a.net_streams, not a.serial_attention, a.attn_overlap)
+    g = structural_graph(a.tp, nano, a.layers, a.pipeline, a.net_streams, not a.serial_attention, a.attn_overlap,
+                         a.cross_layer)
     dur = durations_from_timeline(g, events, launch_gap_us=a.launch_gap)
     rules = dict(r.split("=", 1) for r in a.scale)
     dur = scale_durations(g, dur, rules)
