@@ -123,7 +123,9 @@ def main():
                          "under the other nano-batches' O / FFN GEMMs of layer l)")
     ap.add_argument("--prefill-impl", default="", choices=["", "ws", "tc", "mma"], help="prefill attention kernel")
     ap.add_argument("--decode-ctas", type=int, default=0, help="CTA budget of the decode attention kernel (0 = default)")
-    ap.add_argument("--decode-stages", type=int, default=0, choices=[0, 2, 3],
+    ap.add_argument("--decode-impl", default="", choices=["", "tma"], help="decode attention kernel (tma: producer warp)")
+    ap.add_argument("--gemm-smem-kb", type=int, default=0, help="with --attn-overlap: shared memory a GEMM CTA keeps")
+    ap.add_argument("--decode-stages", type=int, default=0, choices=[0, 2, 3, 4],
                     help="decode attention pages in flight per warp (0: 3, or 2 with --attn-overlap)")
     ap.add_argument("--ar-wide", action="store_true", help="8 GPUs: all-reduce with twice the loads in flight per phase")
     ap.add_argument("--symm-backend", default="", choices=["", "auto", "ipc", "nvls"],
@@ -231,6 +233,10 @@ def main():
     cfg.engine.attn_overlap = bool(args.attn_overlap)
     cfg.engine.cross_layer_pipeline = bool(args.cross_layer)
     cfg.engine.prefill_impl = args.prefill_impl
+    cfg.engine.decode_impl = args.decode_impl
+    if args.gemm_smem_kb:
+        from nanoflow_b200.runtime import pipeline as _pl
+        _pl.GEMM_SMEM_KB_BESIDE_ATTENTION = args.gemm_smem_kb
     if args.decode_ctas:
         cfg.engine.sm_budget["attn_decode"] = args.decode_ctas
     cfg.engine.decode_stages = args.decode_stages
@@ -367,6 +373,7 @@ def main():
                        "attn_overlap": bool(cfg.engine.attn_overlap),
                        "cross_layer_pipeline": bool(cfg.engine.cross_layer_pipeline),
                        "prefill_impl": cfg.engine.prefill_impl or "default",
+                       "decode_impl": cfg.engine.decode_impl or "default",
                        "symm_heap": getattr(getattr(coll, "heap", None), "backend", "none") if world > 1 else "none",
                        "all_reduce": ("in-switch (multimem)" if getattr(coll, "use_multimem", False) else
                                       "peer loads") if world > 1 else "none",

@@ -163,6 +163,7 @@ class EngineConfig:
                                            # right behind its FFN of layer l, so its attention runs under the other
                                            # nano-batches' O / FFN GEMMs (software pipeline across layers)
     prefill_impl: str = ""                 # "" = choose (ws for head_dim 128), "ws", "tc", "mma"
+    decode_impl: str = ""                  # "" = per-warp cp.async rings, "tma" = TMA producer warp (head_dim 128)
     decode_stages: int = 0                 # decode attention pages in flight per warp: 0 = 3 (2 under attn_overlap), 2, 3
     gemm_shapes: Dict[str, Dict[str, int]] = field(default_factory=dict)   # "<op>.nb<k>" -> pinned launcher arguments
     decode_chunk_pages: int = 0            # 0 = choose per iteration
@@ -253,6 +254,7 @@ def parse_config(raw: Dict[str, Any], *, tp: Optional[int] = None) -> NanoflowCo
         attn_overlap=bool(pc.get("attn_overlap", False)),
         cross_layer_pipeline=bool(pc.get("cross_layer_pipeline", False)),
         prefill_impl=str(pc.get("prefill_impl", "")),
+        decode_impl=str(pc.get("decode_impl", "")),
         decode_stages=int(pc.get("decode_stages", 0)),
         model_id=sc.get("model", ""),
         weight_path=sc.get("weight_path", ""),

@@ -168,6 +168,10 @@ typedef struct nfk_attn_params {
   int decode_stages;       // decode: pages in flight per warp, 3 (0 means 3) or 2 (less shared memory per CTA)
 } nfk_attn_params;
 int nfk_attn_decode(const nfk_attn_params* p, cudaStream_t stream);
+// The same with the pages copied by a TMA producer warp into a ring of decode_stages (2, 3 or 4) pages per
+// consumer warp, one work item per warp (attention_dec.cu): full bandwidth from one CTA per SM, for sharing
+// SMs with GEMM CTAs. head_dim 128; calls with chunk_pages > 0 are forwarded to nfk_attn_decode.
+int nfk_attn_decode_tma(const nfk_attn_params* p, cudaStream_t stream);
 int nfk_attn_prefill(const nfk_attn_params* p, cudaStream_t stream);
 // Same contract as nfk_attn_prefill for head_dim 128, on tcgen05 tensor cores (attention_tc.cu).
 int nfk_attn_prefill_tc(const nfk_attn_params* p, cudaStream_t stream);

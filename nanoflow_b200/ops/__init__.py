@@ -448,9 +448,11 @@ def _attn_common(q, out, kv_pool, qo_indptr, kv_indptr, kv_indices, kv_last_page
 def attn_decode(q, out, kv_pool, qo_indptr, kv_indptr, kv_indices, kv_last_page_len, *,
                 q_heads: int, req_begin: int, req_count: int, sm_scale: Optional[float] = None,
                 num_ctas: int = 0, chunk_pages: int = 0, workspace: Optional[torch.Tensor] = None,
-                max_chunks: int = 1, status: Optional[torch.Tensor] = None, stages: int = 0):
+                max_chunks: int = 1, status: Optional[torch.Tensor] = None, stages: int = 0, impl: str = ""):
     """Single-query attention for requests [req_begin, req_begin+req_count) over the paged pool.
-    ``stages``: pages in flight per warp, 3 (default) or 2 (64 KB of shared memory per CTA instead of 96)."""
+    ``stages``: pages in flight per warp, 3 (default) or 2 (64 KB of shared memory per CTA instead of 96).
+    ``impl``: "" = per-warp cp.async rings, "tma" = pages copied by a TMA producer warp (head_dim 128;
+    ``stages`` may then also be 4)."""
     p = _attn_common(q, out, kv_pool, qo_indptr, kv_indptr, kv_indices, kv_last_page_len, q_heads,
                      sm_scale, num_ctas, status)
     p.decode_stages = stages
@@ -462,7 +464,10 @@ def attn_decode(q, out, kv_pool, qo_indptr, kv_indptr, kv_indices, kv_last_page_
         if workspace is None or workspace.dtype != torch.float32 or workspace.numel() < need:
             raise RuntimeError("attn_decode: split-KV needs an fp32 workspace of "
                                f"{need} elements")
-    _check(lib().nfk_attn_decode(byref(p), _stream()), "nfk_attn_decode")
+    if impl == "tma":
+        _check(lib().nfk_attn_decode_tma(byref(p), _stream()), "nfk_attn_decode_tma")
+    else:
+        _check(lib().nfk_attn_decode(byref(p), _stream()), "nfk_attn_decode")
     return out
 
 

@@ -164,7 +164,7 @@ def bench_budget():
     s_a, s_g = torch.cuda.Stream(), torch.cuda.Stream()
     n_gemm = 3
 
-    def run(ctas, stages, smem_kb, mode):
+    def run(ctas, stages, smem_kb, mode, impl=""):
         """mode: 'decode', 'gemm' or 'both'. Returns (decode us, gemm us per launch, span us), best of 5."""
         best = None
         for it in range(7):
@@ -183,7 +183,7 @@ def bench_budget():
                 with torch.cuda.stream(s_a):
                     e[3].record()
                     ops.attn_decode(q, out, pool, qo, kvp, kvi, last, q_heads=q_heads, req_begin=0, req_count=batch,
-                                    num_ctas=ctas, stages=stages)
+                                    num_ctas=ctas, stages=stages, impl=impl)
                     e[4].record()
             torch.cuda.current_stream().wait_stream(s_a)
             torch.cuda.current_stream().wait_stream(s_g)
@@ -196,18 +196,20 @@ def bench_budget():
                 best = row
         return best
 
-    for smem_kb in (0, 200, 130):
+    for smem_kb in (0, 200, 160, 130, 128, 96):
         _, g_us, _ = run(0, 0, smem_kb, "gemm")
         print(json.dumps(dict(op="budget_gemm_alone", M=M, F=F, K=K, smem_kb=smem_kb, us=round(g_us, 1),
                               tflops=round(gflop / g_us / 1e6, 1), peak=how)), flush=True)
-    for stages in (3, 2):
+    # (kernel, pages in flight per warp, shared memory a GEMM CTA may keep beside one such CTA)
+    for impl, stages, smem_kb in (("", 3, 128), ("", 2, 160), ("tma", 2, 160), ("tma", 3, 128), ("tma", 4, 96)):
         for ctas in (16, 32, 48, 64, 96, 148, 296):
-            d_us, _, _ = run(ctas, stages, 0, "decode")
-            row = dict(op="budget_decode", num_ctas=ctas, stages=stages, alone_us=round(d_us, 1),
+            if ctas > 148 and stages == 4:
+                continue
+            d_us, _, _ = run(ctas, stages, 0, "decode", impl)
+            row = dict(op="budget_decode", impl=impl or "cp.async", num_ctas=ctas, stages=stages, alone_us=round(d_us, 1),
                        alone_frac_of_peak=round(nbytes / d_us / 1e3 / bw_peak, 3), peak=how)
             if ctas <= 148:
-                smem_kb = 130 if stages == 3 else 160       # what is left of the SM beside a decode CTA
-                d2, g2, span = run(ctas, stages, smem_kb, "both")
+                d2, g2, span = run(ctas, stages, smem_kb, "both", impl)
                 row.update(beside_gemm_smem_kb=smem_kb, beside_us=round(d2, 1), gemm_beside_us=round(g2, 1),
                            span_us=round(span, 1))
             print(json.dumps(row), flush=True)

@@ -277,7 +277,8 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
             if dp.decode_stages == 0:
                 dp.decode_stages = 2 # 64 KB: leaves room for a collective's CTA beside GEMM + decode
         dp.workspace = _ptr(bufs.decode_ws)
-        dec = g.add(f"L{l}.nb{k}.attn_decode", dp, S("attn"), deps=[ro], kernel="nfk_attn_decode",
+        dec_kernel = "nfk_attn_decode_tma" if (eng.decode_impl == "tma" and hd == 128) else "nfk_attn_decode"
+        dec = g.add(f"L{l}.nb{k}.attn_decode", dp, S("attn"), deps=[ro], kernel=dec_kernel,
                     dyn=[("req_begin", nb_dec0[k]), ("req_count", nb_decn[k]), ("chunk_pages", chunk_pages),
                          ("max_chunks", max_chunks)], layer=l, nano=k)
         pp = attn_params()

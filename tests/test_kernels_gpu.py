@@ -355,6 +355,51 @@ def _make_paged(batch_lens, qo_lens, kv_heads, hd, page=16, extra_pages=5, shuff
     return pool, dev(qo_indptr), dev(kv_indptr), kv_indices.cuda(), dev(last)
 
 
+@pytest.mark.parametrize("batch", [1, 7, 37, 61, 300])
+@pytest.mark.parametrize("kv_heads,group", [(8, 8), (1, 8), (4, 4), (2, 1), (1, 16)])
+@pytest.mark.parametrize("num_ctas,stages", [(0, 0), (7, 2), (30, 4), (3, 3)])
+def test_attn_decode_tma_producer(batch, kv_heads, group, num_ctas, stages):
+    """The decode kernel with a TMA producer warp (one work item per consumer warp, pages through an mbarrier
+    ring): same results as the fp32 restatement for every ring depth and CTA budget."""
+    hd = 128
+    q_heads = kv_heads * group
+    lens = torch.randint(1, 700, (batch,)).tolist()
+    lens[0] = 1
+    if batch > 2:
+        lens[1], lens[2] = 16, 17
+    pool, qo, kvp, kvi, last = _make_paged(lens, [1] * batch, kv_heads, hd)
+    q = torch.randn(batch, q_heads * hd, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros_like(q)
+    st = ops.new_status()
+    ops.attn_decode(q, out, pool, qo, kvp, kvi, last, q_heads=q_heads, req_begin=0, req_count=batch,
+                    num_ctas=num_ctas, status=st, stages=stages, impl="tma")
+    ops.check_status(st, "attn_decode tma")
+    want = ref.paged_attention(q, pool, qo.cpu(), kvp.cpu(), kvi, last.cpu(), q_heads=q_heads)
+    _close(out, want, atol=1e-2, rtol=2e-2)
+
+
+def test_attn_decode_tma_forwards_split_kv_and_request_ranges():
+    """chunk_pages > 0 goes to the kernel with the merge pass; req_begin selects a range of requests."""
+    kv_heads, group, hd, batch = 2, 8, 128, 9
+    q_heads = kv_heads * group
+    lens = [2000, 31, 4096, 640, 1, 99, 100, 515, 16]
+    pool, qo, kvp, kvi, last = _make_paged(lens, [1] * batch, kv_heads, hd)
+    q = torch.randn(batch, q_heads * hd, device="cuda", dtype=torch.bfloat16)
+    want = ref.paged_attention(q, pool, qo.cpu(), kvp.cpu(), kvi, last.cpu(), q_heads=q_heads)
+    out = torch.zeros_like(q)
+    ws = torch.empty(batch * q_heads * 16 * (hd + 2), device="cuda", dtype=torch.float32)
+    st = ops.new_status()
+    ops.attn_decode(q, out, pool, qo, kvp, kvi, last, q_heads=q_heads, req_begin=0, req_count=batch,
+                    chunk_pages=16, workspace=ws, max_chunks=16, status=st, impl="tma")
+    ops.check_status(st, "attn_decode tma split")
+    _close(out, want, atol=1e-2, rtol=2e-2)
+    out2 = torch.zeros_like(q)
+    ops.attn_decode(q, out2, pool, qo, kvp, kvi, last, q_heads=q_heads, req_begin=3, req_count=4, status=st, impl="tma")
+    ops.check_status(st, "attn_decode tma range")
+    _close(out2[3:7], want[3:7], atol=1e-2, rtol=2e-2)
+    assert bool((out2[:3] == 0).all()) and bool((out2[7:] == 0).all())
+
+
 @pytest.mark.parametrize("batch", [1, 7, 37, 61])
 @pytest.mark.parametrize("kv_heads,group,hd", [(8, 8, 128), (1, 8, 128), (4, 4, 128), (2, 1, 128), (2, 2, 64)])
 @pytest.mark.parametrize("num_ctas", [0, 7, 30])
