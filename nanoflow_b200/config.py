@@ -139,8 +139,6 @@ class EngineConfig:
     """Everything that is not architecture: batching, nano-batches, SM budgets, serving options."""
     global_batch_size: int = 2048          # dense tokens per iteration
     nanobatch_sizes: List[int] = field(default_factory=list)   # token split of the dense batch
-    attn_groups: int = 4                   # accepted for the reference's configs (its KQV1..4 split); here a finer
-                                           # split of QKV / attention is expressed as more nano-batches
     page_size: int = 16
     num_pages: int = 0                     # KV pages per GPU; 0 = derive from free memory
     max_batch_size: int = 2048             # max concurrent requests in one iteration
@@ -231,7 +229,6 @@ def parse_config(raw: Dict[str, Any], *, tp: Optional[int] = None) -> NanoflowCo
     eng = EngineConfig(
         global_batch_size=gbs,
         nanobatch_sizes=list(nano or []),
-        attn_groups=int(pc.get("attn_groups", 4)),
         page_size=page,
         num_pages=num_pages,
         max_batch_size=int(mc.get("max_batch_size", 2048)),
@@ -358,7 +355,7 @@ def make_config(model: str, *, gpu_num: int = 1, global_batch_size: int = 2048,
         "pipeline_configs": {
             "gemm_op_tag": [], "global_batch_size": global_batch_size,
             "nanobatch_1_size": nano[0], "nanobatch_sizes": nano,
-            "kqv1_size": 0, "kqv3_size": 0, "attn_groups": 4,
+            "kqv1_size": 0, "kqv3_size": 0,
             "sm_budget": {"gemm": 0, "attn_decode": 0, "attn_prefill": 0, "comm": 96, "offload": 8},
             "decode_chunk_pages": 0,
         },
