@@ -267,6 +267,20 @@ def small_case(which: str):
                              dtype=torch.int32, device="cuda")
         for _ in range(3):
             ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, items, q_heads=64, impl="tc")
+    elif which == "prefill_ws":
+        pool, qo, kvp, kvi, last = _paged(4, 1024, 8, 128, qo_len=1024)
+        q = torch.randn(4096, 64 * 128, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        items = torch.tensor([[b, b * 1024 + t, 16] for b in range(4) for t in range(0, 1024, 16)],
+                             dtype=torch.int32, device="cuda")
+        for _ in range(3):
+            ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, items, q_heads=64, impl="ws")
+    elif which == "decode_tma":
+        pool, qo, kvp, kvi, last = _paged(512, 1280, 8, 128)
+        q = torch.randn(512, 64 * 128, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        for _ in range(4):
+            ops.attn_decode(q, out, pool, qo, kvp, kvi, last, q_heads=64, req_begin=0, req_count=512, impl="tma")
     elif which == "prefill":
         pool, qo, kvp, kvi, last = _paged(4, 1024, 8, 128, qo_len=1024)
         q = torch.randn(4096, 64 * 128, device="cuda", dtype=torch.bfloat16)

@@ -54,6 +54,7 @@ class ServingLoop:
         self.offload = offload
         self.health = health      # parallel.health.Heartbeat: peers are checked before every launch
         self._prev: Optional[BatchPlan] = None
+        self.failed: Optional[Exception] = None     # set by _abandon when a peer failure stopped the loop
         self.stats = LoopStats()
 
     def _release(self) -> None:
@@ -86,7 +87,11 @@ class ServingLoop:
             plan = self.scheduler.schedule()
         if self.health is not None:
             self.health.beat()
-            self.health.check()    # raises PeerFailure before anything that waits on a peer is launched
+            try:
+                self.health.check()    # raises PeerFailure before anything that waits on a peer is launched
+            except Exception as failure:
+                self._abandon(plan, failure)
+                raise
         if plan is not None:
             with phase("update"):
                 self.engine.update(plan)
@@ -107,6 +112,23 @@ class ServingLoop:
         self.stats.cycles += 1
         self.stats.retired.extend(self.scheduler.drain_retired())
         return plan
+
+    def _abandon(self, plan: Optional[BatchPlan], failure: Exception) -> None:
+        """A peer is gone: nothing new is launched. The iteration still in flight is waited for (its device
+        waits are bounded, so this returns) and its tokens are dropped, every running request gives its
+        pages back and returns to the head of the request queue (``Scheduler.requeue_running``), and the
+        failure carries what was saved (``failure.requeued``, ``failure.retired``) to the caller, who can
+        serve the queue again with a re-formed group. The plan scheduled in this cycle was never launched."""
+        if self._prev is not None:
+            try:
+                self.engine.run_async_wait()
+            except RuntimeError:
+                pass          # a bounded device wait ran out on the way: expected when the peer died mid-iteration
+            self._prev = None
+        failure.requeued = self.scheduler.requeue_running()
+        self.stats.retired.extend(self.scheduler.drain_retired())
+        failure.retired = len(self.stats.retired)
+        self.failed = failure
 
     def drain(self) -> None:
         if self._prev is not None:

@@ -240,6 +240,39 @@ class Scheduler:
                 keep.append((it, req))
         self._held_pages = keep
 
+    def requeue_running(self) -> int:
+        """Give up every request that is in flight: free its pages and put it back at the head of the
+        request queue with the tokens it has produced so far folded into its prompt, so that whoever
+        serves the queue next (this engine after the failure has been dealt with, or a new one at a
+        smaller tensor-parallel degree) recomputes its KV and carries on where it stopped. Requests that
+        had already stopped and were only waiting for their last tokens are retired with what they have.
+        Returns the number of re-queued requests. Tokens of iterations still in flight are dropped."""
+        redo_list = []
+        for ws in (self._decode_workset, self._prefill_workset):
+            for r in list(ws._set):
+                if r.preempted:
+                    continue
+                r.preempted = True
+                r.kv_cache.release()
+                redo = NewRequestInfo()
+                redo.req_idx = r.req_idx
+                redo.prompt = np.concatenate([r.prompt, np.asarray(r.output, dtype=np.int32)])
+                redo.output_len = r.output_len - len(r.output)
+                redo.start_time = r.request_comein_time
+                if redo.output_len > 0:
+                    redo_list.append(redo)
+                else:
+                    self._retire(r)
+            ws._set.clear()
+        for r in self._draining:
+            r.pending = 0
+            self._retire(r)
+        self._draining = []
+        self.release_held_pages(self.iteration)
+        for redo in sorted(redo_list, key=lambda q: q.req_idx, reverse=True):
+            self._request_queue._queue.appendleft(redo)
+        return len(redo_list)
+
     # ---- main entry -----------------------------------------------------------------------------
     @property
     def has_work(self) -> bool:

@@ -89,3 +89,66 @@ def test_rank_that_never_joins_is_detected():
     assert res[2][0] == "absent"
     for r in (0, 1):
         assert res[r][0] == "peer_failure" and res[r][1] == 2 and res[r][2] == 0
+
+
+def test_serving_loop_gives_pages_back_and_requeues_requests_when_a_peer_is_gone():
+    """The loop's reaction to a peer failure, on the CPU backend: nothing more is launched, the iteration in
+    flight is waited for, every running request returns its KV pages and goes back to the head of the queue
+    with its generated tokens folded into its prompt, and a fresh loop over the same queue serves them to
+    the end (what a group re-formed without the dead rank would do)."""
+    import numpy as np
+    import torch
+
+    from nanoflow_b200.config import builtin_config
+    from nanoflow_b200.models import random_full_weights, shard_weights
+    from nanoflow_b200.runtime.cpu_backend import CpuEngine
+    from nanoflow_b200.serving import DistKVPool, RequestManager, Scheduler
+    from nanoflow_b200.serving.loop import ServingLoop
+
+    class FailingHealth:
+        def __init__(self, fail_at):
+            self.step, self.fail_at = 0, fail_at
+
+        def beat(self):
+            self.step += 1
+
+        def check(self):
+            if self.step >= self.fail_at:
+                raise PeerFailure(1, self.fail_at - 1, self.step)
+
+    cfg = builtin_config("tiny", gpu_num=1, global_batch_size=48, pipeline_type="NON_OVERLAP_LOCAL")
+    cfg.engine.max_batch_size = 48
+    fw = random_full_weights(cfg.model, seed=0)
+    shards = [shard_weights(fw, cfg.model, 0, 1, dtype=torch.float32)]
+    rm = RequestManager(vocab_size=1024, random_ids=True, seed=1)
+    for _ in range(6):
+        rm.add_request(24, 10, 0.0)
+    rm.finalize_stats()
+    pool = DistKVPool(2, 2, 64, 64, 16, 1)
+    free0 = pool.num_free_pages if hasattr(pool, "num_free_pages") else None
+
+    def make(health):
+        sch = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=48, average_prefill_length=24,
+                        average_decode_length=10, group_size=2)
+        return ServingLoop(CpuEngine(cfg, shards, num_pages=64), sch, rm, est_cycle_time=1.0, health=health), sch
+
+    loop, sch = make(FailingHealth(fail_at=6))
+    with pytest.raises(PeerFailure) as info:
+        loop.run()
+    failure = info.value
+    assert loop.failed is failure and failure.requeued > 0
+    assert sch.in_flight == 0 and not sch._draining and not sch._held_pages
+    if free0 is not None:
+        assert pool.num_free_pages == free0                      # every page came back
+    queued = list(rm.avaliable_request_queue._queue)
+    assert len(queued) + failure.retired == 6
+    assert [q.req_idx for q in queued] == sorted(q.req_idx for q in queued)
+    partial = [q for q in queued if q.prompt.size > 24]
+    assert partial and all(q.prompt.size + q.output_len == 24 + 10 for q in queued)
+    done_before = {r.req_idx: len(r.output) for r in loop.stats.retired}
+    # a second loop (the re-formed group) serves what was re-queued
+    loop2, sch2 = make(None)
+    st2 = loop2.run()
+    assert len(st2.retired) == len(queued)
+    assert all(len(r.output) + (r.input_len - 24) == 10 for r in st2.retired)
+    assert set(done_before) | {r.req_idx for r in st2.retired} == set(range(6))
