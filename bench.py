@@ -118,6 +118,9 @@ def main():
     ap.add_argument("--attn-overlap", action="store_true",
                     help="tensor-parallel overlapped pipelines: decode attention on its own stream under the GEMMs of "
                          "the other nano-batches (use with three or four nano-batches, e.g. --nano 2048,2048,2048,2048)")
+    ap.add_argument("--gate-gemm", action="store_true",
+                    help="tensor parallel: the GEMM behind an all-reduce + norm starts with the collective and waits per "
+                         "128-row block for its input rows")
     ap.add_argument("--cross-layer", action="store_true",
                     help="overlapped pipelines: software pipeline across layers (a nano-batch's attention of layer l+1 "
                          "under the other nano-batches' O / FFN GEMMs of layer l)")
@@ -232,6 +235,7 @@ def main():
     cfg.engine.net_streams = args.net_streams
     cfg.engine.attn_overlap = bool(args.attn_overlap)
     cfg.engine.cross_layer_pipeline = bool(args.cross_layer)
+    cfg.engine.gate_gemm = bool(args.gate_gemm)
     cfg.engine.prefill_impl = args.prefill_impl
     cfg.engine.decode_impl = args.decode_impl
     if args.gemm_smem_kb:
@@ -372,6 +376,7 @@ def main():
                        "decode_tail": args.decode_tail, "net_streams": cfg.engine.net_streams,
                        "attn_overlap": bool(cfg.engine.attn_overlap),
                        "cross_layer_pipeline": bool(cfg.engine.cross_layer_pipeline),
+                       "gated_gemm_behind_all_reduce": bool(cfg.engine.gate_gemm and tp > 1),
                        "prefill_impl": cfg.engine.prefill_impl or "default",
                        "decode_impl": cfg.engine.decode_impl or "default",
                        "symm_heap": getattr(getattr(coll, "heap", None), "backend", "none") if world > 1 else "none",

@@ -160,6 +160,8 @@ class EngineConfig:
     cross_layer_pipeline: bool = False     # overlapped pipelines: the QKV / RoPE of layer l+1 of a nano-batch is issued
                                            # right behind its FFN of layer l, so its attention runs under the other
                                            # nano-batches' O / FFN GEMMs (software pipeline across layers)
+    gate_gemm: bool = False                # TP: the GEMM behind an all-reduce + norm starts with the collective and waits
+                                           # per 128-row block for the rows it reads (all-gather -> GEMM in one pipeline)
     prefill_impl: str = ""                 # "" = choose (ws for head_dim 128), "ws", "tc", "mma"
     decode_impl: str = ""                  # "" = per-warp cp.async rings, "tma" = TMA producer warp (head_dim 128)
     decode_stages: int = 0                 # decode attention pages in flight per warp: 0 = 3 (2 under attn_overlap), 2, 3
@@ -251,6 +253,7 @@ def parse_config(raw: Dict[str, Any], *, tp: Optional[int] = None) -> NanoflowCo
         attn_overlap=bool(pc.get("attn_overlap", False)),
         cross_layer_pipeline=bool(pc.get("cross_layer_pipeline", False)),
         prefill_impl=str(pc.get("prefill_impl", "")),
+        gate_gemm=bool(pc.get("gate_gemm", False)),
         decode_impl=str(pc.get("decode_impl", "")),
         decode_stages=int(pc.get("decode_stages", 0)),
         model_id=sc.get("model", ""),

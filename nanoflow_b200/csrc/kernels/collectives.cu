@@ -131,6 +131,47 @@ __device__ __forceinline__ float block_sum_comm(float v, float* red) {
 }
 
 constexpr int kArThreads = 128;
+constexpr int kGateRows = 128;       // rows per gate flag block (one M tile of the consumer GEMM)
+
+// Owned rows (k indices: row = rank + nranks * k) of this rank inside gate block b of a `rows`-row buffer.
+__device__ __forceinline__ int gate_owned_in_block(int b, int rows, int rank, int nranks) {
+  const int lo_row = b * kGateRows, hi_row = min(rows, lo_row + kGateRows);
+  const int lo = lo_row <= rank ? 0 : (lo_row - rank + nranks - 1) / nranks;
+  const int hi = hi_row <= rank ? 0 : (hi_row - rank + nranks - 1) / nranks;
+  return hi > lo ? hi - lo : 0;
+}
+__device__ __forceinline__ void gate_publish(const nfk_allreduce_params& p, int b) {
+  for (int r = 0; r < p.ctx.nranks; ++r) {
+    unsigned int* f = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(p.ctx.heap[r]) + p.gate_off) +
+                      static_cast<long long>(b) * 8 + p.ctx.rank;
+    st_release_sys(f, static_cast<unsigned int>(p.epoch));
+  }
+}
+// Blocks in which this rank owns no row have nothing to wait for: publish them up front (one CTA).
+__device__ __forceinline__ void gate_publish_empty_blocks(const nfk_allreduce_params& p) {
+  if (p.gate_cnt == nullptr || blockIdx.x != 0) return;
+  const int blocks = (p.rows + kGateRows - 1) / kGateRows;
+  for (int b = threadIdx.x; b < blocks; b += blockDim.x)
+    if (gate_owned_in_block(b, p.rows, p.ctx.rank, p.ctx.nranks) == 0) gate_publish(p, b);
+}
+// Called by the whole CTA after it has pushed the normed row `row`: the CTA that completes this rank's
+// share of the row's block tells every rank. The system-scope fence of every thread orders its pushes
+// before the count; the publishing thread's release store orders the counts it has seen before the flag.
+__device__ __forceinline__ void gate_row_done(const nfk_allreduce_params& p, long long row) {
+  if (p.gate_cnt == nullptr) return;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int b = static_cast<int>(row / kGateRows);
+    const unsigned int want = static_cast<unsigned int>(gate_owned_in_block(b, p.rows, p.ctx.rank, p.ctx.nranks));
+    const unsigned int prev = atomicAdd(&p.gate_cnt[b], 1u);
+    if (prev + 1 == want) {
+      p.gate_cnt[b] = 0;
+      __threadfence_system();
+      gate_publish(p, b);
+    }
+  }
+}
 constexpr int kArVec = 8;                                  // 16-byte vectors per thread per row
 constexpr int kMaxCols = kArVec * 8 * kArThreads;          // 8192 columns
 
@@ -164,6 +205,7 @@ allreduce_kernel(nfk_allreduce_params p) {
   const nfk_comm_ctx& c = p.ctx;
   // src_mode 1: the producer GEMM pushed the partial rows into local slabs and raised the ready flags
   comm_enter(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status, p.src_mode == 0);
+  gate_publish_empty_blocks(p);
 
   const int nvec = p.cols >> 3;
   const long long row_bytes = p.ld * 2;
@@ -279,6 +321,7 @@ allreduce_kernel(nfk_allreduce_params p) {
                           row * static_cast<long long>(p.norm_ld) * 2 + v * 16, o);
         }
       }
+      gate_row_done(p, row);
     }
   }
   comm_exit(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status);
@@ -317,6 +360,7 @@ allreduce_mc_kernel(nfk_allreduce_params p) {
   __shared__ float red[8];
   const nfk_comm_ctx& c = p.ctx;
   comm_enter(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status, true);
+  gate_publish_empty_blocks(p);
   const int NR = c.nranks;
   const int nvec = p.cols >> 3;
   const long long row_bytes = p.ld * 2;
@@ -394,6 +438,7 @@ allreduce_mc_kernel(nfk_allreduce_params p) {
                          make_uint4(ov[0], ov[1], ov[2], ov[3]));
         }
       }
+      gate_row_done(p, row);
     }
 #pragma unroll
     for (int i = 0; i < kArVec; ++i) {
@@ -511,6 +556,7 @@ extern "C" int nfk_allreduce(const nfk_allreduce_params* p, cudaStream_t stream)
   if (p->src_mode != 0 && (p->src_mode != 1 || p->push_sum != 0 || p->slab_rows * p->ctx.nranks < p->rows))
     return NF_ERR_BAD_ARG;   // slab input: the sum cannot be pushed back into a per-rank buffer
   if (p->mc_heap != nullptr && (reinterpret_cast<uintptr_t>(p->mc_heap) & 15) != 0) return NF_ERR_BAD_ARG;
+  if (p->gate_cnt != nullptr && (p->norm_w == nullptr || p->gate_off % 16 != 0)) return NF_ERR_BAD_ARG;
   // Even an empty buffer takes part in the handshakes so that all ranks stay in step.
   const int nr = p->ctx.nranks;
   const int owned = (p->rows + nr - 1) / nr;

@@ -144,7 +144,50 @@ struct DevParams {
   int rs_rank, rs_nranks, rs_rows_cap, rs_epoch;
   long long rs_slab_off, rs_flag_off;
   int rs_staged;     // partial rows leave through shared memory and bulk copies instead of 16-byte stores
+  // gated input: see nfk_gemm_params::gate_flags
+  const unsigned int* gate_flags;
+  int gate_epoch, gate_nranks;
 };
+
+// Tile index -> (m group, n block). Normally m groups vary fastest, so CTAs that run together share
+// weight panels in L2; with a gated input n blocks vary fastest, so the first wave of tiles needs only the
+// first rows of A.
+__device__ __forceinline__ void tile_coords(const DevParams& p, int tile, int m_groups, int n_blocks, int& m_grp,
+                                            int& n_blk) {
+  if (p.gate_flags != nullptr) {
+    m_grp = tile / n_blocks;
+    n_blk = tile - m_grp * n_blocks;
+  } else {
+    m_grp = tile % m_groups;
+    n_blk = tile / m_groups;
+  }
+}
+
+// Bounded wait until every rank has delivered its rows of 128-row block `m_tile` of A. The flags are
+// written by remote stores (st.release.sys); the loads that follow are TMA copies (async proxy), hence
+// the proxy fence after the acquire.
+__device__ __forceinline__ bool wait_gate(const DevParams& p, int m_tile, volatile int* abort_flag) {
+  const unsigned int* f = p.gate_flags + static_cast<long long>(m_tile) * 8;
+  uint64_t t0 = 0;
+  for (int r = 0; r < p.gate_nranks; ++r) {
+    for (uint32_t it = 0;; ++it) {
+      unsigned int v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f + r) : "memory");
+      if (static_cast<int>(v - static_cast<unsigned int>(p.gate_epoch)) >= 0) break;
+      if ((it & 63u) == 63u) {
+        if (*abort_flag) return false;
+        if (p.status != nullptr && *reinterpret_cast<volatile unsigned int*>(p.status) != 0u) return false;
+        uint64_t now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        if (t0 == 0) t0 = now;
+        if (now - t0 > 2000000000ull) return false;   // 2 s
+        __nanosleep(64);
+      }
+    }
+  }
+  asm volatile("fence.proxy.async;" ::: "memory");
+  return true;
+}
 
 // Wait helper shared by all roles: bounded by wall clock (globaltimer) and by the CTA abort flag.
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
@@ -319,9 +362,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     bool ok = true;
     Walk walk(worker, workers, tiles, num_kb, sk, p.sk_tiles_dp, p.sk_q);
     Segment sg;
+    int gate_seen = -1;     // M tiles up to this one have been seen complete (tiles are walked in row order)
     while (ok && walk.next(sg)) {
-      const int m_grp = sg.tile % m_groups, n_blk = sg.tile / m_groups;
+      int m_grp, n_blk;
+      tile_coords(p, sg.tile, m_groups, n_blocks, m_grp, n_blk);
       const int mt_valid = min(MT, m_tiles - m_grp * MT);
+      if (p.gate_flags != nullptr) {
+        // last 128-row block of A that this CTA loads for the tile
+        const int need = (CG == 2) ? min(m_tiles - 1, m_grp * 2 + static_cast<int>(rank)) : m_grp * MT + mt_valid - 1;
+        const int first = (CG == 2) ? need : m_grp * MT;
+        for (int mt_i = max(first, gate_seen + 1); mt_i <= need && ok; ++mt_i) {
+          if (!wait_gate(p, mt_i, abort_flag)) {
+            report_status(p.status, NF_ST_TIMEOUT_PEER_FLAG);
+            raise_abort();
+            ok = false;
+          }
+        }
+        if (!ok) break;
+        if (need > gate_seen) gate_seen = need;
+      }
       for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0)) {
         if (!wait_or_abort(&empty_bar[s], ph ^ 1, abort_flag)) {
           report_status(p.status, NF_ST_TIMEOUT_SMEM_EMPTY);
@@ -392,7 +451,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     Walk walk(worker, workers, tiles, num_kb, sk, p.sk_tiles_dp, p.sk_q);
     Segment sg;
     while (ok && walk.next(sg)) {
-      const int m_grp = sg.tile % m_groups;
+      int m_grp, n_blk_unused;
+      tile_coords(p, sg.tile, m_groups, n_blocks, m_grp, n_blk_unused);
       const int mt_valid = (CG == 2) ? 1 : min(MT, m_tiles - m_grp * MT);
       const uint32_t acc = (ACC_BUFS == 2) ? (tcount & 1) : 0;
       const uint32_t acc_ph = (ACC_BUFS == 2) ? ((tcount >> 1) & 1) : (tcount & 1);
@@ -448,7 +508,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     Walk walk(worker, workers, tiles, num_kb, sk, p.sk_tiles_dp, p.sk_q);
     Segment sg;
     while (walk.next(sg)) {
-      const int m_grp = sg.tile % m_groups, n_blk = sg.tile / m_groups;
+      int m_grp, n_blk;
+      tile_coords(p, sg.tile, m_groups, n_blocks, m_grp, n_blk);
       const int m_first = (m_grp * CG + static_cast<int>(rank)) * MT;   // first M tile this CTA drains
       const int mt_valid = min(MT, m_tiles - m_first);                  // <= 0: tile past the last row
       const uint32_t acc = (ACC_BUFS == 2) ? (tcount & 1) : 0;
@@ -1043,6 +1104,9 @@ int launch(const nfk_gemm_params& g, int bn, int split_k, bool stream_k, cudaStr
   p.rs_slab_off = g.rs_slab_off;
   p.rs_flag_off = g.rs_flag_off;
   p.rs_staged = rs_staged ? 1 : 0;
+  p.gate_flags = g.gate_flags;
+  p.gate_epoch = g.gate_epoch;
+  p.gate_nranks = g.gate_nranks;
   if (CG == 2) {
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(ctas);
@@ -1197,6 +1261,10 @@ int resolve_shape(const nfk_gemm_params& gp, bool swiglu, bool rs, Shape& s) {
   const nfk_gemm_params* g = &gp;
   s = choose_shape(*g, swiglu);
   if (rs) s.split_k = 1;   // partial tiles go straight to their owners: no K split
+  if (g->gate_flags != nullptr) {
+    s.split_k = 1;         // gated input: whole tiles in row order only
+    s.stream_k = false;
+  }
   if (g->tile_n != 0 || g->tile_m != 0) {
     // pinned tile shape: fill in the other dimension with its default, split only on request
     s.bn = g->tile_n != 0 ? g->tile_n : 256;
@@ -1206,9 +1274,9 @@ int resolve_shape(const nfk_gemm_params& gp, bool swiglu, bool rs, Shape& s) {
     s.stream_k = false;
   }
   if (g->stream_k == 1) s.stream_k = true;
-  if (g->stream_k == 2 || s.split_k != 1) s.stream_k = false;
+  if (g->stream_k == 2 || s.split_k != 1 || g->gate_flags != nullptr) s.stream_k = false;
   if (s.cg == 2 && s.mt != 1) return NF_ERR_UNSUPPORTED;
-  if (g->split_k != 0) s.split_k = g->split_k;
+  if (g->split_k != 0 && g->gate_flags == nullptr) s.split_k = g->split_k;
   if (s.split_k < 1 || s.split_k > 16) return NF_ERR_BAD_ARG;
   if (s.split_k > 1) {
     if (swiglu || g->workspace == nullptr ||
@@ -1296,6 +1364,9 @@ extern "C" int nfk_gemm_bf16(const nfk_gemm_params* g, cudaStream_t stream) {
   const bool swiglu = g->epilogue == NFK_EPI_SWIGLU;
   if (swiglu && g->B2 == nullptr) return NF_ERR_BAD_ARG;
   const bool rs = g->epilogue == NFK_EPI_REDUCE_SCATTER;
+  if (g->gate_flags != nullptr &&
+      (rs || g->gate_nranks < 1 || g->gate_nranks > 8 || (reinterpret_cast<uintptr_t>(g->gate_flags) & 3) != 0))
+    return NF_ERR_BAD_ARG;
   if (rs) {
     if (g->rs_nranks < 1 || g->rs_nranks > 8 || g->rs_rank < 0 || g->rs_rank >= g->rs_nranks ||
         g->rs_rows_cap * g->rs_nranks < g->M || g->rs_slab_off % 16 != 0 || g->rs_flag_off % 16 != 0 ||

@@ -57,6 +57,16 @@ typedef struct nfk_gemm_params {
   // Reduce-scatter epilogue: 1 = rows leave through a shared-memory staging piece and one bulk copy per
   // row and 128 columns (256-byte NVLink writes); 0 = 16-byte stores straight from registers.
   int rs_staged;
+  // Gated input (all-gather -> GEMM in one pipeline): the rows of A are still being delivered by a
+  // collective when the GEMM starts. gate_flags points to this GPU's copy of the collective's row-block
+  // flags, [ceil(M/128)][8] words: word [b][r] reaches gate_epoch once rank r has delivered all of its rows
+  // of block b (rows 128b .. 128b+127). The TMA producer of a CTA waits (bounded) for the gate_nranks words
+  // of an M tile before its first load of that tile, and tiles are walked row block by row block (all
+  // column blocks of the first rows first), so the main loops of the first tiles run while the collective
+  // is still delivering the later rows. Null = A is complete before the launch. Linear and SwiGLU
+  // epilogues; no split-K and no stream-K tail in this mode.
+  const unsigned int* gate_flags;
+  int gate_epoch, gate_nranks;
 } nfk_gemm_params;
 
 int nfk_gemm_bf16(const nfk_gemm_params* p, cudaStream_t stream);
@@ -219,6 +229,13 @@ typedef struct nfk_allreduce_params {
                           //    slab at buf_off + (r * slab_rows + k) * ld (no NVLink loads, no ready signal)
   int slab_rows;
   int wide;               // 1 (8 ranks): twice the loads in flight per phase, the norm pass re-reads the stored sum
+  // Optional row-block flags for a consumer that starts before this collective has finished (see
+  // nfk_gemm_params::gate_flags): gate_off is the heap offset of [ceil(rows/128)][8] words (same offset on
+  // every rank), gate_cnt a local array of ceil(rows/128) zero-initialised words (this rank's rows done per
+  // block; reset by the kernel). Once a rank has pushed all the normed rows it owns inside block b it writes
+  // `epoch` into word [b][rank] on every rank. Needs norm_w / norm_out (the pushed rows are what is gated).
+  long long gate_off;
+  unsigned int* gate_cnt;
   void* mc_heap;          // optional: the heaps' NVLink multicast mapping (one address that stands for the same
                           //    offset on every rank). Non-null selects the in-switch form: owned rows are summed by
                           //    multimem.ld_reduce and results are written to all ranks by multimem.st (src_mode 0 only)

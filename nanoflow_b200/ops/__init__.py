@@ -41,7 +41,7 @@ class GemmParams(Structure):
                 ("rs_rows_cap", c_int), ("rs_flag_off", c_longlong), ("rs_epoch", c_int), ("smem_budget_kb", c_int),
                 ("cta_group", c_int), ("stream_k", c_int),
                 ("norm_w", c_void_p), ("norm_out", c_void_p), ("norm_ld", c_longlong), ("norm_eps", c_float),
-                ("rs_staged", c_int)]
+                ("rs_staged", c_int), ("gate_flags", c_void_p), ("gate_epoch", c_int), ("gate_nranks", c_int)]
 
 
 class RopeAppendParams(Structure):
@@ -139,14 +139,18 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
          status: Optional[torch.Tensor] = None, tile_m: int = 0, split_k: int = 0,
          workspace: Optional[torch.Tensor] = None, smem_budget_kb: int = 0,
          cta_group: int = 0, stream_k: int = 0, norm_w: Optional[torch.Tensor] = None,
-         norm_out: Optional[torch.Tensor] = None, norm_eps: float = 1e-5) -> torch.Tensor:
+         norm_out: Optional[torch.Tensor] = None, norm_eps: float = 1e-5,
+         gate_flags: Optional[torch.Tensor] = None, gate_epoch: int = 0, gate_nranks: int = 1) -> torch.Tensor:
     """out[M,N] = a[M,K] @ w[N,K]^T (+ bias) (+ beta * residual). Rows may be strided.
 
     With ``norm_w`` / ``norm_out`` the call also leaves ``norm_out = RMSNorm(out) * norm_w`` (from the
     split-K reduce pass when K is split, by a norm launch otherwise).
 
     ``tile_n`` / ``tile_m`` / ``split_k`` pin the kernel shape (0 = let the launcher's cost model
-    choose); split-K needs ``workspace`` (any dtype, >= split_k*M*N*4 bytes)."""
+    choose); split-K needs ``workspace`` (any dtype, >= split_k*M*N*4 bytes).
+
+    ``gate_flags`` (int32 [ceil(M/128), 8]): rows of ``a`` are still arriving; the kernel waits, per
+    128-row block, until words [block, 0:gate_nranks] have reached ``gate_epoch``."""
     _bf16(a, "a"); _bf16(w, "w")
     M, K = a.shape
     N, K2 = w.shape
@@ -182,8 +186,18 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None
     if norm_w is not None:
         _bf16(norm_w, "norm_w"); _bf16(norm_out, "norm_out")
         p.norm_w, p.norm_out, p.norm_ld, p.norm_eps = _p(norm_w), _p(norm_out), norm_out.stride(0), norm_eps
+    _set_gate(p, gate_flags, gate_epoch, gate_nranks, M)
     _check(lib().nfk_gemm_bf16(byref(p), _stream()), "nfk_gemm_bf16")
     return out
+
+
+def _set_gate(p: "GemmParams", flags: Optional[torch.Tensor], epoch: int, nranks: int, M: int) -> None:
+    if flags is None:
+        return
+    _i32(flags, "gate_flags")
+    if not flags.is_contiguous() or flags.numel() < (M + 127) // 128 * 8:
+        raise RuntimeError("gemm: gate_flags must be a contiguous int32 [ceil(M/128), 8] tensor")
+    p.gate_flags, p.gate_epoch, p.gate_nranks = _p(flags), epoch, nranks
 
 
 class GemmPlan(Structure):
@@ -214,8 +228,10 @@ def gemm_swiglu(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, *,
                 out: Optional[torch.Tensor] = None, tile_n: int = 0, num_ctas: int = 0,
                 status: Optional[torch.Tensor] = None, tile_m: int = 0, split_k: int = 0,
                 workspace: Optional[torch.Tensor] = None, cta_group: int = 0,
-                stream_k: int = 0, smem_budget_kb: int = 0) -> torch.Tensor:
-    """out[M,F] = silu(a @ w_gate^T) * (a @ w_up^T), gate and up products fused in one kernel."""
+                stream_k: int = 0, smem_budget_kb: int = 0, gate_flags: Optional[torch.Tensor] = None,
+                gate_epoch: int = 0, gate_nranks: int = 1) -> torch.Tensor:
+    """out[M,F] = silu(a @ w_gate^T) * (a @ w_up^T), gate and up products fused in one kernel.
+    ``gate_flags``: as in :func:`gemm`."""
     _bf16(a, "a"); _bf16(w_gate, "w_gate"); _bf16(w_up, "w_up")
     M, K = a.shape
     F, K2 = w_gate.shape
@@ -238,6 +254,7 @@ def gemm_swiglu(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, *,
     p.cta_group = cta_group
     p.stream_k = stream_k
     p.smem_budget_kb = smem_budget_kb
+    _set_gate(p, gate_flags, gate_epoch, gate_nranks, M)
     _check(lib().nfk_gemm_bf16(byref(p), _stream()), "nfk_gemm_bf16(swiglu)")
     return out
 

@@ -237,6 +237,15 @@ def small_case(which: str):
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         for _ in range(4):
             ops.gemm(a, w, out=out)
+    elif which == "gemm_m256":
+        # the one-GPU dense batch: every weight byte is streamed once per call (134 MB, larger than L2)
+        M, N, K = 256, 8192, 8192
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ws = torch.zeros(160 << 20, dtype=torch.uint8, device="cuda")
+        for _ in range(4):
+            ops.gemm(a, w, out=out, workspace=ws)
     elif which == "gemm_shapes":
         # one launch per kernel shape: CTA pair 256 wide, CTA pair 128 wide, single CTA 256 wide
         M, N, K = 4096, 8192, 8192

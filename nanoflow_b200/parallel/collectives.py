@@ -29,7 +29,7 @@ class AllReduceParams(Structure):
                 ("norm_w", c_void_p), ("norm_out_off", c_longlong), ("norm_ld", c_longlong), ("eps", c_float),
                 ("status", c_void_p), ("push_sum", c_int), ("resid", c_void_p), ("resid_ld", c_longlong),
                 ("sum_out", c_void_p), ("sum_ld", c_longlong), ("src_mode", c_int), ("slab_rows", c_int),
-                ("wide", c_int), ("mc_heap", c_void_p)]
+                ("wide", c_int), ("gate_off", c_longlong), ("gate_cnt", c_void_p), ("mc_heap", c_void_p)]
 
 
 class AllGatherParams(Structure):
@@ -57,7 +57,9 @@ class TpCollectives(CollectiveHooks):
         self.rank, self.tp, self.device = rank, world, device
         self.heap = SymmetricHeap(rank, world, device, heap_bytes, backend=backend)
         # all-reduces go through the NVSwitch (multimem) whenever the heap has a multicast mapping
-        self.use_multimem = self.heap.mc_base != 0
+        # (from four ranks on: with two, half of a row's partial sums are local and the peer-load form is as fast)
+        self.use_multimem = self.heap.mc_base != 0 and world >= 4
+        self.last_gate = None
         self.num_ctas = num_ctas or _ops.sm_count(device)
         self.fuse_norm = fuse_norm
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
@@ -74,6 +76,7 @@ class TpCollectives(CollectiveHooks):
         self.rank, self.tp, self.device = rank, world, torch.device("cpu")
         self.num_ctas, self.fuse_norm = 16, True
         self.use_multimem = False
+        self.last_gate = None
         self.fake_wire_us_per_row = 0.0
         self.wide = False
         self.status = torch.zeros(1, dtype=torch.int32)
@@ -129,8 +132,11 @@ class TpCollectives(CollectiveHooks):
                    deps, layer: int, nano: int, stream: str = "net", norm_w: Optional[torch.Tensor] = None,
                    norm_out: Optional[torch.Tensor] = None, eps: float = 1e-5, status=None, num_ctas: int = 0,
                    resid: Optional[torch.Tensor] = None, sum_out: Optional[torch.Tensor] = None,
-                   push_sum: bool = True, slab: Optional[dict] = None):
+                   push_sum: bool = True, slab: Optional[dict] = None, gate_rows_cap: int = 0):
         """Append a reduction of ``buf`` rows [row0, row0+rows) over all ranks.
+
+        ``gate_rows_cap`` > 0 (with a fused norm): the op also raises row-block flags as it pushes the
+        normed rows; ``self.last_gate`` then holds what the consumer GEMM needs (see GemmParams.gate_flags).
 
         With ``slab`` (from :meth:`rs_slot`) the partial rows were pushed into local slabs by a GEMM
         with the reduce-scatter epilogue: the op then reads locally and shares the GEMM's flag block.
@@ -163,6 +169,14 @@ class TpCollectives(CollectiveHooks):
         p.wide = 1 if self.wide else 0
         if self.use_multimem and slab is None:
             p.mc_heap = self.heap.mc_base
+        self.last_gate = None
+        if gate_rows_cap > 0 and fused and self.fake_wire_us_per_row <= 0:
+            blocks = (gate_rows_cap + 127) // 128
+            p.gate_off = self.heap.alloc_bytes(blocks * 8 * 4)
+            cnt = torch.zeros(blocks, dtype=torch.int32, device=self.device)
+            self._gate_keep = getattr(self, "_gate_keep", []) + [cnt]
+            p.gate_cnt = cnt.data_ptr()
+            self.last_gate = {"flags": self.heap.base + p.gate_off, "nranks": self.tp}
         idx = g.add(name, p, stream, deps=deps, dyn=[("rows", rows_sym), ("epoch", g.symbol("epoch"))],
                     layer=layer, nano=nano)
         if self.fake_wire_us_per_row > 0 and nano >= 0:

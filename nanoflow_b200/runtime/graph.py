@@ -94,6 +94,9 @@ class Op:
     stream: str
     deps: List[int] = field(default_factory=list)         # wait for completion of these ops
     after_start: List[int] = field(default_factory=list)  # wait for the start of these ops
+    gated: List[int] = field(default_factory=list)        # ops whose output this op consumes row block by row block
+                                                          # behind device-side flags: launched once they have started
+                                                          # (also listed in after_start), done only after they are done
     dyn: List[Tuple[str, str]] = field(default_factory=list)  # (int field of params, symbol name)
     layer: int = -1
     nano: int = -1
@@ -111,7 +114,8 @@ class OpGraph:
 
     def add(self, name: str, params: Structure, stream: str, deps: Sequence[Optional[int]] = (),
             dyn: Sequence[Tuple[str, str]] = (), kernel: Optional[str] = None,
-            after_start: Sequence[Optional[int]] = (), layer: int = -1, nano: int = -1) -> int:
+            after_start: Sequence[Optional[int]] = (), layer: int = -1, nano: int = -1,
+            gated: Sequence[Optional[int]] = ()) -> int:
         if stream not in STREAM_CLASSES:
             raise ValueError(f"unknown stream class {stream}")
         kernel = kernel or KERNEL_OF[type(params)]
@@ -119,10 +123,11 @@ class OpGraph:
             self.symbol(s)
             if not hasattr(params, f):
                 raise AttributeError(f"{type(params).__name__} has no field {f}")
+        gated = sorted({d for d in gated if d is not None})
         op = Op(name=name, kernel=kernel, params=params, stream=stream,
                 deps=sorted({d for d in deps if d is not None}),
-                after_start=sorted({d for d in after_start if d is not None}), dyn=list(dyn),
-                layer=layer, nano=nano)
+                after_start=sorted({d for d in after_start if d is not None} | set(gated)), dyn=list(dyn),
+                layer=layer, nano=nano, gated=gated)
         for d in op.deps + op.after_start:
             if not (0 <= d < len(self.ops)):
                 raise ValueError(f"op {name}: dependency {d} is not an earlier op")
@@ -137,7 +142,9 @@ class OpGraph:
         hb: List[set] = []
         for i, op in enumerate(self.ops):
             s = set()
-            preds = list(op.deps)
+            # a gated op cannot finish before the ops that feed it row block by row block have delivered
+            # every block, so for the data those ops write the edge orders like a dependency
+            preds = list(op.deps) + list(op.gated)
             if op.stream in last_on_stream:
                 preds.append(last_on_stream[op.stream])
             for p in preds:

@@ -187,7 +187,7 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
     cur = 0                                             # which residual buffer holds x
 
     def gemm(name, a, wt, out, k, *, residual=None, beta=1.0, bias=None, swiglu_up=None, deps=(), layer=-1,
-             tile_key=None, rs=None, norm=None):
+             tile_key=None, rs=None, norm=None, gate=None):
         p = GemmParams()
         r0 = starts[k]
         p.A, p.B, p.D = _ptr(a, r0), _ptr(wt), (_ptr(out, r0) if out is not None else c_void_p(0))
@@ -213,18 +213,27 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
             dyn.append(("rs_epoch", g.symbol("epoch")))
         key = tile_key or name.split(".")[-1]
         p.tile_n = eng.gemm_tile_n.get(key, 0)
+        gated = ()
+        if gate is not None:
+            # rows of `a` arrive block by block from the collective `gate["op"]`: launch with it, wait per M tile
+            p.gate_flags, p.gate_nranks = gate["flags"], gate["nranks"]
+            dyn.append(("gate_epoch", g.symbol("epoch")))
+            gated = [gate["op"]]
+            deps = [d for d in deps if d != gate["op"]]
         shape = eng.gemm_shapes.get(f"{key}.nb{k}") if rs is None else None
         if shape is not None and p.tile_n == 0:
             # measured at start-up (ops/autotune.py)
             p.tile_m, p.tile_n, p.cta_group = shape["tile_m"], shape["tile_n"], shape["cta_group"]
             p.split_k, p.stream_k = shape["split_k"], shape["stream_k"]
+            if gate is not None:
+                p.split_k, p.stream_k = 1, 2      # whole tiles in row order (the launcher enforces it as well)
         p.num_ctas = budget.get("gemm", 0)
         p.smem_budget_kb = gemm_smem_budget_kb(eng, tp)
         p.status = _ptr(st)
         if bufs.gemm_ws is not None:
             p.workspace = _ptr(bufs.gemm_ws)
             p.workspace_bytes = bufs.gemm_ws.numel() * bufs.gemm_ws.element_size()
-        return g.add(name, p, "gemm", deps=deps, dyn=dyn, layer=layer, nano=k)
+        return g.add(name, p, "gemm", deps=deps, dyn=dyn, layer=layer, nano=k, gated=gated)
 
     def norm(name, x, wt, out, k, deps, layer, resid=None):
         r0 = starts[k]
@@ -235,12 +244,15 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
     def attn_front(l, k, lw, pool):
         """norm -> QKV -> RoPE/append -> attention for nano-batch k of layer l."""
         xin = bufs.x[cur]
+        gate = None
         if h_normed[k] is not None:
             n1 = h_normed[k]          # the previous all-reduce already wrote the normed rows into h
             h_normed[k] = None
+            gate, h_gate[k] = h_gate[k], None
         else:
             n1 = norm(f"L{l}.nb{k}.ln_attn", xin, lw.ln_attn, bufs.h, k, [last_x_writer[k]], l)
-        q = gemm(f"L{l}.nb{k}.qkv", bufs.h, lw.wqkv, bufs.qkv, k, bias=lw.bqkv, deps=[n1], layer=l, tile_key="qkv")
+        q = gemm(f"L{l}.nb{k}.qkv", bufs.h, lw.wqkv, bufs.qkv, k, bias=lw.bqkv, deps=[n1], layer=l, tile_key="qkv",
+                 gate=gate)
         r0 = starts[k]
         rp = RopeAppendParams()
         rp.qkv, rp.ld_qkv = _ptr(bufs.qkv, r0), bufs.qkv.stride(0)
@@ -340,7 +352,8 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         ar1, _ = coll.all_reduce(g, f"L{l}.nb{k}.ar_o", part, starts[k], nb_T[k], hidden, [o], l, k,
                                  stream=net_of(k), norm_w=lw.ln_ffn, norm_out=bufs.h, eps=model.rms_norm_eps,
                                  status=st, num_ctas=comm_ctas, resid=x_res, sum_out=x_res, push_sum=False,
-                                 slab=slab)
+                                 slab=slab, **gate_kw(k))
+        ffn_gate[k] = take_gate(ar1)
         return ar1
 
     def ffn(l, k, lw, n2):
@@ -348,8 +361,9 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         ffn_down(l, k, lw, ffn_gate_up(l, k, lw, n2))
 
     def ffn_gate_up(l, k, lw, n2):
+        gate, ffn_gate[k] = ffn_gate[k], None
         return gemm(f"L{l}.nb{k}.gate_up", bufs.h, lw.wg, bufs.act, k, swiglu_up=lw.wu, deps=[n2], layer=l,
-                    tile_key="gate_up")
+                    tile_key="gate_up", gate=gate)
 
     def ffn_down(l, k, lw, gu):
         if tp == 1:
@@ -372,9 +386,10 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         ar2, fused2 = coll.all_reduce(g, f"L{l}.nb{k}.ar_d", part, starts[k], nb_T[k], hidden, [d], l, k,
                                       stream=net_of(k), norm_w=nxt, norm_out=None if last else bufs.h,
                                       eps=model.rms_norm_eps, status=st, num_ctas=comm_ctas, resid=x_res,
-                                      sum_out=x_res, push_sum=last, slab=slab)
+                                      sum_out=x_res, push_sum=last, slab=slab, **({} if last else gate_kw(k)))
         last_x_writer[k] = ar2
         h_normed[k] = ar2 if fused2 else None
+        h_gate[k] = take_gate(ar2) if fused2 else None
 
     def offload_layer(l, pool, pace_dep):
         """Layer-by-layer KV offload of retired requests: gather their pages of layer l into a
@@ -392,6 +407,19 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
 
     rope_of: Dict = {}
     h_normed: List[Optional[int]] = [None] * nn     # op that already wrote normed rows of nano-batch k into h
+    # gate_gemm: the GEMM that reads the normed rows starts together with the all-reduce that delivers them
+    # and waits per 128-row block (flags raised by the collective as it pushes): all-gather -> GEMM in one
+    # pipeline instead of two kernels in sequence
+    use_gate = tp > 1 and eng.gate_gemm and hasattr(coll, "last_gate") and not fuse_rs
+    h_gate: List[Optional[dict]] = [None] * nn      # gate of the rows in h that the next QKV GEMM reads
+    ffn_gate: List[Optional[dict]] = [None] * nn    # ... that the next gate/up GEMM reads
+
+    def gate_kw(k):
+        return {"gate_rows_cap": sizes[k]} if use_gate else {}
+
+    def take_gate(op_idx):
+        gt = getattr(coll, "last_gate", None) if use_gate else None
+        return dict(gt, op=op_idx) if (gt is not None and op_idx is not None) else None
     for l in range(model.run_layers):
         lw = w.layers[l % model.num_layers]
         pool = bufs.kv_pool[l]

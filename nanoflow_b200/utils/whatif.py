@@ -43,7 +43,11 @@ def simulate(graph: OpGraph, durations: Sequence[float], single_stream: bool = F
         for d in op.after_start:
             if start[d] > t:
                 t, src = start[d], d
-        start[i], end[i], why[i] = t, t + float(durations[i]), src
+        e = t + float(durations[i])
+        for d in getattr(op, "gated", ()):        # fed row block by row block: done no earlier than its feeder
+            if end[d] > e:
+                e = end[d]
+        start[i], end[i], why[i] = t, e, src
         free[s] = (end[i], i)
     last = max(range(n), key=lambda i: end[i]) if n else None
     path = []

@@ -1,7 +1,7 @@
 """Multi-GPU test worker, one process per GPU:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        --master-port 29511 tests/mp_worker.py {collectives|collectives_wide|collectives_nvls|fused|engine|engine_nvls|timeout}
+        --master-port 29511 tests/mp_worker.py {collectives|collectives_wide|collectives_nvls|fused|engine|engine_nvls|engine_gate|engine_gate_nvls|timeout}
 
 Prints ``MP_WORKER_OK <case>`` from rank 0 on success; any rank's assertion failure exits non-zero.
 """
@@ -21,7 +21,8 @@ from nanoflow_b200.parallel.collectives import TpCollectives  # noqa: E402
 def case_collectives(rank, world, dev, wide=False, backend="ipc"):
     coll = TpCollectives(rank, world, dev, heap_bytes=512 << 20, backend=backend)
     if backend == "nvls":
-        assert coll.use_multimem and coll.heap.mc_base != 0, "NVLS heap without a multicast address"
+        assert coll.heap.mc_base != 0, "NVLS heap without a multicast address"
+        coll.use_multimem = True            # also with two ranks, where the engine would keep the peer-load form
     if rank == 0:
         print(f"symmetric heap: {coll.heap.backend}, all-reduce through the switch: {coll.use_multimem}", flush=True)
     coll.wide = wide        # 8 ranks: the all-reduce form with twice the loads in flight (same results)
@@ -240,7 +241,7 @@ def case_fused(rank, world, dev):
     coll.close()
 
 
-def case_engine(rank, world, dev, backend="ipc"):
+def case_engine(rank, world, dev, backend="ipc", gate=False):
     from nanoflow_b200.config import builtin_config
     from nanoflow_b200.models import ReferenceLlama, random_full_weights, shard_weights
     from nanoflow_b200.runtime.engine import Engine
@@ -255,6 +256,7 @@ def case_engine(rank, world, dev, backend="ipc"):
         cfg = builtin_config(arch, gpu_num=world, global_batch_size=gbs, pipeline_type=ptype, nanobatch_sizes=nano)
         cfg.engine.max_batch_size = gbs
         cfg.engine.fuse_gemm_rs = fuse
+        cfg.engine.gate_gemm = gate and not fuse     # QKV / gate-up start with the all-reduce that feeds them
         fw = random_full_weights(cfg.model, seed=0, std=0.05)
         for lay in fw.layers:
             for k, v in vars(lay).items():
@@ -273,6 +275,8 @@ def case_engine(rank, world, dev, backend="ipc"):
                         nanobatch_sizes=cfg.engine.resolved_nanobatches(), average_prefill_length=32,
                         average_decode_length=16, group_size=2)
         coll = TpCollectives(rank, world, dev, heap_bytes=64 << 20, backend=backend)
+        if backend == "nvls":
+            coll.use_multimem = True
         eng = Engine(cfg, shard_weights(fw, cfg.model, rank, world, device=dev), device=dev, collectives=coll,
                      num_pages=64)
         st = ServingLoop(eng, sch, rm, est_cycle_time=1.0).run()
@@ -336,6 +340,8 @@ if __name__ == "__main__":
         {"collectives": case_collectives, "collectives_wide": lambda r, w, d: case_collectives(r, w, d, wide=True),
          "collectives_nvls": lambda r, w, d: case_collectives(r, w, d, backend="nvls"),
          "engine": case_engine, "engine_nvls": lambda r, w, d: case_engine(r, w, d, backend="nvls"),
+         "engine_gate": lambda r, w, d: case_engine(r, w, d, gate=True),
+         "engine_gate_nvls": lambda r, w, d: case_engine(r, w, d, backend="nvls", gate=True),
          "timeout": case_timeout, "fused": case_fused}[case](rank, world, dev)
     except BaseException:
         import traceback

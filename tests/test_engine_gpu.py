@@ -131,6 +131,43 @@ def test_virtual_tensor_parallel_rank_runs_alone():
     assert all(0 <= t < 1024 for r in st.retired for t in r.output)
 
 
+def test_gated_gemms_behind_the_all_reduce_give_the_same_tokens():
+    """gate_gemm: QKV and gate/up start together with the all-reduce + norm that delivers their input rows
+    and wait per 128-row block. One GPU runs rank 0's share of a two-way job (collectives reduced to their
+    local part, as above): the flag protocol between the collective and the GEMM runs for real, and the
+    sampled tokens equal those of the ungated pipeline."""
+    from nanoflow_b200.parallel.collectives import TpCollectives
+    from nanoflow_b200.runtime.engine import Engine
+
+    def serve(gate, ptype, nano):
+        gbs = 384
+        cfg = builtin_config("tiny", gpu_num=2, global_batch_size=gbs, pipeline_type=ptype, nanobatch_sizes=nano)
+        cfg.engine.max_batch_size = gbs
+        cfg.engine.gate_gemm = gate
+        fw = random_full_weights(cfg.model, seed=0, std=0.05)
+        coll = TpCollectives(0, 1, torch.device("cuda", 0), heap_bytes=64 << 20)
+        eng = Engine(cfg, shard_weights(fw, cfg.model, 0, 2, device="cuda"), collectives=coll, num_pages=256)
+        gated = [op for op in eng.graph.ops if op.gated]
+        assert bool(gated) == gate
+        rm = RequestManager(vocab_size=1024, random_ids=True, seed=3)
+        for _ in range(6):
+            rm.add_request(150, 6, 0.0)
+        rm.finalize_stats()
+        pool = DistKVPool(2, 2, 64, 256, 16, 2)
+        sch = Scheduler(pool, rm.avaliable_request_queue, global_batch_size=gbs,
+                        nanobatch_sizes=cfg.engine.resolved_nanobatches(), average_prefill_length=150,
+                        average_decode_length=6, group_size=2)
+        st = ServingLoop(eng, sch, rm, est_cycle_time=1.0).run()
+        eng.check_status()
+        coll.check_status()
+        eng.finalize()
+        assert len(st.retired) == 6
+        return {r.req_idx: list(r.output) for r in st.retired}
+
+    for ptype, nano in (("NON_OVERLAP", None), ("PLLM", [128, 256])):
+        assert serve(True, ptype, nano) == serve(False, ptype, nano)
+
+
 def test_kv_offload_and_restore():
     """PLLM_OFFLOAD: pages of retired requests reach pinned host memory layer by layer, match the
     oracle's rotated K / V, and can be scattered back into fresh pages."""

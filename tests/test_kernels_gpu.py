@@ -438,6 +438,50 @@ def test_attn_decode_split_kv(chunk_pages):
     _close(out, want, atol=1e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 512, 256), (1000, 1024, 1024), (2048, 1280, 512), (77, 256, 128)])
+@pytest.mark.parametrize("tile_m,tile_n,cta_group", [(0, 0, 0), (1, 256, 2), (2, 128, 1), (1, 64, 1)])
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_gemm_gated_input_with_flags_already_raised(M, N, K, tile_m, tile_n, cta_group, swiglu):
+    """Gated input (row-block flags, tiles walked row block by row block): with every flag at the epoch the
+    result is the ungated one bit for bit, for single CTAs, CTA pairs, several M tiles per CTA and SwiGLU;
+    ranks beyond gate_nranks are not looked at."""
+    if cta_group == 2 and M <= 128:
+        pytest.skip("a pair covers two M tiles")
+    g = torch.Generator(device="cpu").manual_seed(5)
+    a = torch.randn(M, K, generator=g).bfloat16().cuda()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().cuda()
+    w2 = (torch.randn(N, K, generator=g) * 0.05).bfloat16().cuda()
+    blocks = (M + 127) // 128
+    flags = torch.zeros(blocks, 8, dtype=torch.int32, device="cuda")
+    flags[:, :3] = 7
+    flags[:, 0] = 9          # later epochs count as raised
+    st = ops.new_status()
+    kw = dict(tile_m=tile_m, tile_n=tile_n, cta_group=cta_group, status=st)
+    if swiglu:
+        want = ops.gemm_swiglu(a, w, w2, **kw)
+        got = ops.gemm_swiglu(a, w, w2, gate_flags=flags, gate_epoch=7, gate_nranks=3, **kw)
+    else:
+        want = ops.gemm(a, w, **kw)
+        got = ops.gemm(a, w, gate_flags=flags, gate_epoch=7, gate_nranks=3, **kw)
+    ops.check_status(st, "gated gemm")
+    assert torch.equal(got, want)
+
+
+def test_gemm_gated_input_times_out_when_a_flag_never_comes():
+    """A row block whose flag is never raised: the producer's bounded wait runs out, the kernel unwinds and
+    reports a peer-flag timeout; the context stays usable."""
+    a = torch.randn(256, 128, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(256, 128, device="cuda", dtype=torch.bfloat16)
+    flags = torch.full((2, 8), 3, dtype=torch.int32, device="cuda")
+    flags[1, 1] = 2                      # rank 1 never delivers block 1 for epoch 3
+    st = ops.new_status()
+    ops.gemm(a, w, gate_flags=flags, gate_epoch=3, gate_nranks=2, status=st, tile_m=1, tile_n=128, cta_group=1)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="0x500"):
+        ops.check_status(st, "gated gemm")
+    assert torch.equal(ops.gemm(a, w), ops.gemm(a, w))
+
+
 @pytest.mark.parametrize("chunk_pages,max_chunks", [(8, 4), (16, 1), (5, 3)])
 def test_attn_decode_split_kv_context_longer_than_the_chunks_cover(chunk_pages, max_chunks):
     """A request with more pages than chunk_pages * max_chunks: the last chunk takes the remaining pages
