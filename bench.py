@@ -137,8 +137,9 @@ def main():
     ap.add_argument("--no-multimem", action="store_true", help="keep the peer-load all-reduce even on an nvls heap")
     ap.add_argument("--net-streams", type=int, default=1, choices=[1, 2],
                     help="2: the collectives of odd nano-batches run on a second network stream")
-    ap.add_argument("--decode-tail", type=float, default=0.0,
-                    help="share of the decode requests' context scheduled into the last nano-batch (0 = all first)")
+    ap.add_argument("--decode-tail", type=float, default=-1.0,
+                    help="share of the decode requests' context scheduled into the last nano-batch (0 = all first; "
+                         "default: 0.5 for the overlapped tensor-parallel pipeline, else 0)")
     ap.add_argument("--virtual-tp", type=int, default=0,
                     help="one GPU runs rank 0's share of a tensor-parallel job of this degree, collectives reduced "
                          "to their local part (development aid; the JSON line is marked invalid)")
@@ -220,6 +221,9 @@ def main():
     # Measured on B200: with two ranks the all-reduces are short and splitting the batch costs more GEMM
     # efficiency than the overlap returns; from four ranks on the overlapped pipeline wins.
     ptype = args.pipeline or ("NON_OVERLAP_LOCAL" if tp == 1 else "NON_OVERLAP" if tp == 2 else "PLLM")
+    if args.decode_tail < 0:
+        # both nano-batches get decode requests, so that each attention front-end covers the other's all-reduce
+        args.decode_tail = 0.5 if (tp > 2 and not ptype.startswith("NON")) else 0.0
     nano = None
     if args.nano:
         nano = [int(x) for x in args.nano.split(",")]

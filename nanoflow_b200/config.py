@@ -162,7 +162,7 @@ class EngineConfig:
                                            # nano-batches' O / FFN GEMMs (software pipeline across layers)
     gate_gemm: bool = False                # TP: the GEMM behind an all-reduce + norm starts with the collective and waits
                                            # per 128-row block for the rows it reads (all-gather -> GEMM in one pipeline)
-    prefill_impl: str = ""                 # "" = choose (ws for head_dim 128), "ws", "tc", "mma"
+    prefill_impl: str = ""                 # "" = choose (ws for head_dim 128, mma otherwise or with prefill_tc off), "ws", "tc", "mma"
     decode_impl: str = ""                  # "" = per-warp cp.async rings, "tma" = TMA producer warp (head_dim 128)
     decode_stages: int = 0                 # decode attention pages in flight per warp: 0 = 3 (2 under attn_overlap), 2, 3
     gemm_shapes: Dict[str, Dict[str, int]] = field(default_factory=dict)   # "<op>.nb<k>" -> pinned launcher arguments

@@ -494,14 +494,14 @@ def attn_prefill(q, out, kv_pool, qo_indptr, kv_indptr, kv_indices, kv_last_page
     """Causal attention for work items [(request, first token, token count)] over the paged pool.
 
     ``impl``: "ws" = warp-specialised tcgen05 kernel (head_dim 128), "tc" = the earlier tcgen05 kernel,
-    "mma" = warp-level mma.sync kernel, "auto" = tc when the head size allows."""
+    "mma" = warp-level mma.sync kernel, "auto" = ws when the head size allows."""
     p = _attn_common(q, out, kv_pool, qo_indptr, kv_indptr, kv_indices, kv_last_page_len, q_heads,
                      sm_scale, num_ctas, status)
     _i32(items, "items")
     p.items, p.num_items = _p(items), items.shape[0]
-    if impl == "ws":
+    if impl == "ws" or (impl == "auto" and kv_pool.shape[-1] == 128):
         _check(lib().nfk_attn_prefill_ws(byref(p), _stream()), "nfk_attn_prefill_ws")
-    elif impl == "tc" or (impl == "auto" and kv_pool.shape[-1] == 128):
+    elif impl == "tc":
         _check(lib().nfk_attn_prefill_tc(byref(p), _stream()), "nfk_attn_prefill_tc")
     else:
         _check(lib().nfk_attn_prefill(byref(p), _stream()), "nfk_attn_prefill")

@@ -297,7 +297,7 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         pp.num_ctas = budget.get("attn_prefill", 0)
         pp.items = _ptr(bufs.nano_items[k])
         # head_dim 128: the tcgen05 kernel; other head sizes: the warp-level mma.sync kernel
-        impl = eng.prefill_impl or ("tc" if (hd == 128 and eng.prefill_tc) else "mma")
+        impl = eng.prefill_impl or ("ws" if (hd == 128 and eng.prefill_tc) else "mma")
         if hd != 128:
             impl = "mma"
         pre_kernel = {"ws": "nfk_attn_prefill_ws", "tc": "nfk_attn_prefill_tc", "mma": "nfk_attn_prefill"}[impl]
