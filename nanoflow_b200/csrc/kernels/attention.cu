@@ -24,6 +24,7 @@
 #include "attn_decode_static.h"
 #include "attn_mma.cuh"
 
+#include <atomic>
 #include <mutex>
 
 namespace nf {
@@ -86,9 +87,16 @@ struct DecCfg {
   static constexpr int SMEM_BYTES = PIPE_BYTES > MERGE_BYTES ? PIPE_BYTES : MERGE_BYTES;
 };
 
+// Work items are handed out through a counter: a CTA takes its first item by its index and every further
+// one with an atomic increment, so CTAs that run slower (an SM shared with another kernel's CTA, a long
+// context) take fewer items instead of holding up the launch. One counter pair per launch slot; launches
+// cycle through the slots, and the last CTA of a launch to finish resets its slot.
+constexpr int kDecodeCounterSlots = 64;
+__device__ unsigned int g_decode_counters[kDecodeCounterSlots][2];
+
 template <int HD, int ST>
 __global__ void __launch_bounds__(kDecThreads, 3)
-attn_decode_kernel(nfk_attn_params p) {
+attn_decode_kernel(nfk_attn_params p, int slot) {
   using Cfg = DecCfg<HD, ST>;
   constexpr int kDecStages = ST;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -102,7 +110,14 @@ attn_decode_kernel(nfk_attn_params p) {
   const float scale = p.sm_scale * kLog2e;
   const uint32_t warp_smem = smem_u32(smem) + warp * Cfg::WARP_BYTES;
 
-  for (long long item = blockIdx.x; item < total; item += gridDim.x) {
+  unsigned int* counters = g_decode_counters[slot];
+  long long item = blockIdx.x;
+  while (item < total) {
+    // the index of the item after this one is fetched now (thread 0 keeps it) and handed to the CTA through
+    // the first word of the pipeline buffers once this item no longer needs them
+    long long fetched = 0;
+    if (threadIdx.x == 0) fetched = static_cast<long long>(gridDim.x) + atomicAdd(&counters[0], 1u);
+    do {
     const int chunk = static_cast<int>(item % max_chunks);
     const int kvh = static_cast<int>((item / max_chunks) % p.kv_heads);
     const int bl = static_cast<int>(item / (static_cast<long long>(max_chunks) * p.kv_heads));
@@ -118,7 +133,7 @@ attn_decode_kernel(nfk_attn_params p) {
       c_end = (chunk == max_chunks - 1) ? np : min(np, c_begin + p.chunk_pages);
       n_chunks = min(max_chunks, (np + p.chunk_pages - 1) / p.chunk_pages);
     }
-    if (c_begin >= c_end) continue;  // uniform across the CTA
+    if (c_begin >= c_end) break;  // uniform across the CTA: on to the next item
     const int tok = p.qo_indptr[req];
 
     uint32_t qa[HD / 16][4];
@@ -251,7 +266,19 @@ attn_decode_kernel(nfk_attn_params p) {
         if (c == 0) ws[HD] = L > 0.f ? mm + log2f(L) : -INFINITY;
       }
     }
-    __syncthreads();  // smem is reused by the next item's loads
+    } while (false);
+    __syncthreads();  // every warp is done with the pipeline buffers and the merge area
+    if (threadIdx.x == 0) *reinterpret_cast<long long*>(smem) = fetched;
+    __syncthreads();
+    item = *reinterpret_cast<const long long*>(smem);
+    __syncthreads();  // ... before the next item's loads overwrite the word
+  }
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(&counters[1], 1u);
+    if (prev == gridDim.x - 1) {      // every CTA has taken its last item: the slot is free again
+      counters[0] = 0;
+      counters[1] = 0;
+    }
   }
 }
 
@@ -478,7 +505,9 @@ int launch_decode_st(const nfk_attn_params* p, cudaStream_t stream) {
   const long long total = static_cast<long long>(p->req_count) * p->kv_heads * max_chunks;
   long long ctas = p->num_ctas > 0 ? p->num_ctas : 2LL * sm_count_attn();
   if (ctas > total) ctas = total;
-  attn_decode_kernel<HD, ST><<<static_cast<int>(ctas), kDecThreads, Cfg::SMEM_BYTES, stream>>>(*p);
+  static std::atomic<unsigned int> launch_seq{0};
+  const int slot = static_cast<int>(launch_seq.fetch_add(1u) % kDecodeCounterSlots);
+  attn_decode_kernel<HD, ST><<<static_cast<int>(ctas), kDecThreads, Cfg::SMEM_BYTES, stream>>>(*p, slot);
   if (cudaGetLastError() != cudaSuccess) return NF_ERR_CUDA;
   if (p->chunk_pages > 0 && max_chunks > 1) {
     attn_decode_merge_kernel<HD><<<p->req_count * p->q_heads, HD, 0, stream>>>(*p);
