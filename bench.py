@@ -375,7 +375,8 @@ def main():
                        "input_len": args.input_len, "output_len": args.output_len,
                        "parallelism": f"tp{world}", "pipeline_type": ptype, "layers": model.run_layers,
                        "nanobatches": cfg.engine.resolved_nanobatches(), "fused_gemm_reduce_scatter": bool(cfg.engine.fuse_gemm_rs and tp > 1),
-                       "collective_ctas": cfg.engine.sm_budget.get("comm", 0) if tp > 1 else 0,
+                       "collective_ctas": (next((op.params.num_ctas for op in eng.graph.ops
+                                                 if op.kernel == "nfk_allreduce" and op.layer >= 0), 0) if tp > 1 else 0),
                        "prefill_beside_decode": bool(cfg.engine.prefill_beside_decode),
                        "decode_tail": args.decode_tail, "net_streams": cfg.engine.net_streams,
                        "attn_overlap": bool(cfg.engine.attn_overlap),

@@ -147,7 +147,7 @@ class EngineConfig:
     actual_gpu_num: int = 1
     gpu_num: int = 1
     # sm_100a tuning fields
-    sm_budget: Dict[str, int] = field(default_factory=lambda: {"gemm": 0, "attn_decode": 0, "attn_prefill": 0, "comm": 96, "offload": 8})
+    sm_budget: Dict[str, int] = field(default_factory=lambda: {"gemm": 0, "attn_decode": 0, "attn_prefill": 0, "comm": 0, "offload": 8})
     gemm_tile_n: Dict[str, int] = field(default_factory=dict)
     autotune_gemm: bool = True             # time candidate GEMM shapes at start-up and pin the fastest per op
     prefill_tc: bool = True                # head_dim 128: prefill attention on tcgen05 (else the mma.sync kernel)
@@ -359,7 +359,7 @@ def make_config(model: str, *, gpu_num: int = 1, global_batch_size: int = 2048,
             "gemm_op_tag": [], "global_batch_size": global_batch_size,
             "nanobatch_1_size": nano[0], "nanobatch_sizes": nano,
             "kqv1_size": 0, "kqv3_size": 0,
-            "sm_budget": {"gemm": 0, "attn_decode": 0, "attn_prefill": 0, "comm": 96, "offload": 8},
+            "sm_budget": {"gemm": 0, "attn_decode": 0, "attn_prefill": 0, "comm": 0, "offload": 8},
             "decode_chunk_pages": 0,
         },
         "serve_configs": {

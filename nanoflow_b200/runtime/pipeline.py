@@ -100,6 +100,17 @@ GEMM_SMEM_KB_SHARED_SM = 200
 GEMM_SMEM_KB_BESIDE_ATTENTION = 130
 
 
+def default_comm_ctas(tp: int, in_switch: bool) -> int:
+    """CTAs of a collective that runs beside other kernels (overlapped pipelines). A collective's CTAs slow
+    whatever shares their SMs (eight GPUs, in-switch all-reduce: 161.0 / 161.1 / 164.6 / 166.3 ms per
+    iteration with 16 / 32 / 96 / 148 CTAs), while the in-switch all-reduce alone is as fast with 32 CTAs as
+    with 96 at eight ranks (a rank then owns 512 of a nano-batch's 4096 rows, 16 per CTA). So: about 16 owned
+    rows per CTA for the in-switch form; the peer-load form needs its loads in flight and keeps 96."""
+    if not in_switch:
+        return 96
+    return max(16, min(96, 256 // max(1, tp)))
+
+
 def gemm_smem_budget_kb(eng: EngineConfig, tp: int) -> int:
     """Shared memory a GEMM CTA may take in this pipeline (0 = all of it)."""
     if not (eng.overlap and tp > 1):
@@ -307,6 +318,8 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         return dec, pre
 
     comm_ctas = budget.get("comm", 0)
+    if overlap and tp > 1 and comm_ctas == 0:
+        comm_ctas = default_comm_ctas(tp, bool(getattr(coll, "use_multimem", False)))
 
     # Residual stream under tensor parallelism: x is a local buffer in which a rank keeps only the
     # rows it owns (row i belongs to rank i % tp) up to date; the K-split GEMMs write their partial
