@@ -433,3 +433,16 @@ def test_checker_still_sees_a_missing_append_dependency():
     victim = next(i for i, op in enumerate(g.ops) if op.name == "L1.nb0.attn_decode")
     g.ops[victim].deps = []          # the decode kernel no longer waits for its own nano-batch's KV append
     assert depcheck.check(g, acc)
+
+
+def test_collectives_beside_other_kernels_get_a_cta_budget_by_form_and_rank_count():
+    from nanoflow_b200.runtime.pipeline import default_comm_ctas
+
+    assert default_comm_ctas(8, True) == 32 and default_comm_ctas(4, True) == 64     # ~16 owned rows per CTA
+    assert default_comm_ctas(2, True) == 96 and default_comm_ctas(8, False) == 96
+    g, acc, keep = _host_graph("PLLM", 2, [16, 32])            # peer-load form (the analysis heap has no multicast mapping)
+    ars = [op for op in g.ops if op.kernel == "nfk_allreduce" and op.layer >= 0]
+    assert ars and all(op.params.num_ctas == 96 for op in ars)
+    g1, _, keep1 = _host_graph("NON_OVERLAP", 2, None)         # nothing runs beside: the collective's own default (all SMs)
+    coll = keep1[2]
+    assert all(op.params.num_ctas == coll.num_ctas for op in g1.ops if op.kernel == "nfk_allreduce" and op.layer >= 0)
