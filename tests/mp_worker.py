@@ -174,10 +174,12 @@ def case_collectives(rank, world, dev, wide=False, backend="ipc"):
         t = torch.tensor([e0.elapsed_time(e1) / 10], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         if rank == 0:
-            # bytes one GPU must receive: the other ranks' partial rows of the rows it owns (pull form), or
-            # the switch's sums of them (in-switch form); and, either way, the other owners' normed rows
+            # Bytes on one GPU's links, busier direction. Pull form: in = the other ranks' partial rows of the
+            # rows it owns + the other owners' normed rows (out is the mirror image). In-switch form: out =
+            # its partial rows of ALL rows (the switch reads every rank's copy of every row) + its normed
+            # rows once; in = the sums of its rows + the other owners' normed rows.
             own = rows // world * cols * 2
-            wire = (own + (world - 1) * own) if coll.use_multimem else 2 * (world - 1) * own
+            wire = (world * own + own) if coll.use_multimem else 2 * (world - 1) * own
             print(f"allreduce+norm {rows}x{cols} bf16 ctas={ctas}: {t.item()*1e3:.1f} us "
                   f"({wire / 770e9 * 1e6:.0f} us at 770 GB/s per direction)", flush=True)
     coll.check_status()
