@@ -134,6 +134,9 @@ def main():
     ap.add_argument("--symm-backend", default="", choices=["", "auto", "ipc", "nvls"],
                     help="symmetric heap: nvls binds the ranks' heaps to an NVLink multicast object (all-reduce "
                          "through the switch), ipc is plain peer mappings; default auto (nvls when available)")
+    ap.add_argument("--push-by-copy", action="store_true",
+                    help="all-reduce + norm: the normed rows reach the peers by copy-engine copies instead of stores "
+                         "from the kernel")
     ap.add_argument("--no-multimem", action="store_true", help="keep the peer-load all-reduce even on an nvls heap")
     ap.add_argument("--net-streams", type=int, default=1, choices=[1, 2],
                     help="2: the collectives of odd nano-batches run on a second network stream")
@@ -188,6 +191,7 @@ def main():
         coll.wide = bool(args.ar_wide)
         if args.no_multimem:
             coll.use_multimem = False
+        coll.push_by_copy = bool(args.push_by_copy)
 
     def barrier():
         if world > 1:
@@ -384,6 +388,7 @@ def main():
                        "gated_gemm_behind_all_reduce": bool(cfg.engine.gate_gemm and tp > 1),
                        "prefill_impl": cfg.engine.prefill_impl or "default",
                        "decode_impl": cfg.engine.decode_impl or "default",
+                       "normed_rows_pushed_by": ("copy engines" if getattr(coll, "push_by_copy", False) else "kernel") if world > 1 else "none",
                        "symm_heap": getattr(getattr(coll, "heap", None), "backend", "none") if world > 1 else "none",
                        "all_reduce": ("in-switch (multimem)" if getattr(coll, "use_multimem", False) else
                                       "peer loads") if world > 1 else "none",

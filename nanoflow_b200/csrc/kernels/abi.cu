@@ -40,6 +40,15 @@ extern "C" int nfk_memcpy_p(const nfk_memcpy_params* p, cudaStream_t s) {
   return cudaMemcpyAsync(p->dst, p->src, static_cast<size_t>(bytes), cudaMemcpyDefault, s) == cudaSuccess
              ? NF_OK : NF_ERR_CUDA;
 }
+extern "C" int nfk_memcpy2d_p(const nfk_memcpy2d_params* p, cudaStream_t s) {
+  if (!p || p->height < 0 || p->width < 0 || p->dpitch < p->width || p->spitch < p->width) return NF_ERR_BAD_ARG;
+  if (p->height == 0 || p->width == 0) return NF_OK;
+  if (!p->dst || !p->src) return NF_ERR_BAD_ARG;
+  return cudaMemcpy2DAsync(p->dst, static_cast<size_t>(p->dpitch), p->src, static_cast<size_t>(p->spitch),
+                           static_cast<size_t>(p->width), static_cast<size_t>(p->height), cudaMemcpyDefault,
+                           s) == cudaSuccess
+             ? NF_OK : NF_ERR_CUDA;
+}
 extern "C" int nfk_sleep_p(const nfk_sleep_params* p, cudaStream_t s) {
   if (!p) return NF_ERR_BAD_ARG;
   return p->micros == 0 ? NF_OK : nfk_sleep(p->micros, s);

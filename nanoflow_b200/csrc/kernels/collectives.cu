@@ -315,15 +315,21 @@ allreduce_kernel(nfk_allreduce_params p) {
             ov[e] = pack_bf16x2(f.x * inv * g.x, f.y * inv * g.y);
           }
           const uint4 o = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+          if (p.push_mode == 1) {
+            *reinterpret_cast<uint4*>(reinterpret_cast<char*>(c.heap[c.rank]) + p.norm_out_off +
+                                      row * static_cast<long long>(p.norm_ld) * 2 + v * 16) = o;
+          } else {
 #pragma unroll
-          for (int r = 0; r < NR; ++r)
-            st_sys_v4(reinterpret_cast<char*>(c.heap[r]) + p.norm_out_off +
-                          row * static_cast<long long>(p.norm_ld) * 2 + v * 16, o);
+            for (int r = 0; r < NR; ++r)
+              st_sys_v4(reinterpret_cast<char*>(c.heap[r]) + p.norm_out_off +
+                            row * static_cast<long long>(p.norm_ld) * 2 + v * 16, o);
+          }
         }
       }
       gate_row_done(p, row);
     }
   }
+  if (p.push_mode == 1) return;     // the caller's copies and barrier follow on the stream
   comm_exit(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status);
 }
 
@@ -434,8 +440,12 @@ allreduce_mc_kernel(nfk_allreduce_params p) {
             const float2 f = unpack_bf16x2(x4[e]);
             ov[e] = pack_bf16x2(f.x * inv * g.x, f.y * inv * g.y);
           }
-          multimem_st_v4(mc + p.norm_out_off + row * static_cast<long long>(p.norm_ld) * 2 + v * 16,
-                         make_uint4(ov[0], ov[1], ov[2], ov[3]));
+          const uint4 o = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+          if (p.push_mode == 1)
+            *reinterpret_cast<uint4*>(reinterpret_cast<char*>(c.heap[c.rank]) + p.norm_out_off +
+                                      row * static_cast<long long>(p.norm_ld) * 2 + v * 16) = o;
+          else
+            multimem_st_v4(mc + p.norm_out_off + row * static_cast<long long>(p.norm_ld) * 2 + v * 16, o);
         }
       }
       gate_row_done(p, row);
@@ -446,6 +456,7 @@ allreduce_mc_kernel(nfk_allreduce_params p) {
       rs[i] = rs_nx[i];
     }
   }
+  if (p.push_mode == 1) return;     // the caller's copies and barrier follow on the stream
   comm_exit(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status);
 }
 
@@ -557,6 +568,8 @@ extern "C" int nfk_allreduce(const nfk_allreduce_params* p, cudaStream_t stream)
     return NF_ERR_BAD_ARG;   // slab input: the sum cannot be pushed back into a per-rank buffer
   if (p->mc_heap != nullptr && (reinterpret_cast<uintptr_t>(p->mc_heap) & 15) != 0) return NF_ERR_BAD_ARG;
   if (p->gate_cnt != nullptr && (p->norm_w == nullptr || p->gate_off % 16 != 0)) return NF_ERR_BAD_ARG;
+  if (p->push_mode != 0 && (p->push_mode != 1 || p->norm_w == nullptr || p->gate_cnt != nullptr || p->push_sum != 0))
+    return NF_ERR_BAD_ARG;
   // Even an empty buffer takes part in the handshakes so that all ranks stay in step.
   const int nr = p->ctx.nranks;
   const int owned = (p->rows + nr - 1) / nr;

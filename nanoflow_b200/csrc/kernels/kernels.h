@@ -236,6 +236,10 @@ typedef struct nfk_allreduce_params {
   // `epoch` into word [b][rank] on every rank. Needs norm_w / norm_out (the pushed rows are what is gated).
   long long gate_off;
   unsigned int* gate_cnt;
+  // 1: the normed rows this rank owns are stored into its OWN copy of norm_out only and the kernel ends
+  // without the exit handshake: the caller delivers them to the peers with copy-engine copies (no SM
+  // involved, see parallel/collectives.py) and closes with nfk_comm_barrier. Needs norm_w; no gate flags.
+  int push_mode;
   void* mc_heap;          // optional: the heaps' NVLink multicast mapping (one address that stands for the same
                           //    offset on every rank). Non-null selects the in-switch form: owned rows are summed by
                           //    multimem.ld_reduce and results are written to all ranks by multimem.st (src_mode 0 only)
@@ -299,6 +303,9 @@ typedef struct nfk_copy_cols_params {
 typedef struct nfk_memcpy_params {   // plain async copy (any direction); elem_bytes * count bytes
   void* dst; const void* src; long long elem_bytes; int count;
 } nfk_memcpy_params;
+typedef struct nfk_memcpy2d_params {  // strided async copy: `height` rows of `width` bytes, row pitches in bytes
+  void* dst; const void* src; long long dpitch, spitch, width; int height;
+} nfk_memcpy2d_params;
 typedef struct nfk_kv_move_params {
   void* pool; void* staging; const int* page_ids; int n_pages; long long page_bytes; int num_pages;
   int direction; int num_ctas; unsigned int* status;

@@ -29,7 +29,8 @@ class AllReduceParams(Structure):
                 ("norm_w", c_void_p), ("norm_out_off", c_longlong), ("norm_ld", c_longlong), ("eps", c_float),
                 ("status", c_void_p), ("push_sum", c_int), ("resid", c_void_p), ("resid_ld", c_longlong),
                 ("sum_out", c_void_p), ("sum_ld", c_longlong), ("src_mode", c_int), ("slab_rows", c_int),
-                ("wide", c_int), ("gate_off", c_longlong), ("gate_cnt", c_void_p), ("mc_heap", c_void_p)]
+                ("wide", c_int), ("gate_off", c_longlong), ("gate_cnt", c_void_p), ("push_mode", c_int),
+                ("mc_heap", c_void_p)]
 
 
 class AllGatherParams(Structure):
@@ -65,6 +66,7 @@ class TpCollectives(CollectiveHooks):
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.fake_wire_us_per_row = 0.0     # see all_reduce(): sleep standing in for absent ranks
         self.wide = False                   # all-reduce with twice the loads in flight per phase (8 ranks)
+        self.push_by_copy = False           # normed rows reach the peers by copy-engine copies (see all_reduce)
         self._epoch = 0
         self._adhoc_flags = self.heap.alloc_bytes(FLAG_BYTES)
 
@@ -77,6 +79,7 @@ class TpCollectives(CollectiveHooks):
         self.num_ctas, self.fuse_norm = 16, True
         self.use_multimem = False
         self.last_gate = None
+        self.push_by_copy = False
         self.fake_wire_us_per_row = 0.0
         self.wide = False
         self.status = torch.zeros(1, dtype=torch.int32)
@@ -177,8 +180,34 @@ class TpCollectives(CollectiveHooks):
             self._gate_keep = getattr(self, "_gate_keep", []) + [cnt]
             p.gate_cnt = cnt.data_ptr()
             self.last_gate = {"flags": self.heap.base + p.gate_off, "nranks": self.tp}
+        by_copy = (self.push_by_copy and fused and self.tp > 1 and slab is None and not push_sum
+                   and self.last_gate is None and nano >= 0)
+        if by_copy:
+            p.push_mode = 1
         idx = g.add(name, p, stream, deps=deps, dyn=[("rows", rows_sym), ("epoch", g.symbol("epoch"))],
                     layer=layer, nano=nano)
+        if by_copy:
+            # The kernel has left this rank's normed rows (rows rank, rank + tp, ...) in its own copy of
+            # norm_out. The copy engines deliver them: one strided copy per peer (each row is contiguous, the
+            # rows are tp rows apart), behind the kernel on the same stream, so no SM is involved in the
+            # half of the collective that moves the most bytes into a GPU; a barrier then tells every rank
+            # that its copy of norm_out is complete. The row count is the symbol nb<k>_own_rows.
+            from ..runtime.graph import Memcpy2DParams
+            row_bytes = norm_out.stride(0) * esz
+            first = p.norm_out_off + self.rank * row_bytes
+            for step in range(1, self.tp):
+                peer = (self.rank + step) % self.tp
+                c = Memcpy2DParams()
+                c.dst, c.src = self.heap.peer_base[peer] + first, self.heap.base + first
+                c.dpitch = c.spitch = self.tp * row_bytes
+                c.width, c.height = cols * esz, 0
+                idx = g.add(f"{name}.push{peer}", c, stream, deps=[idx],
+                            dyn=[("height", g.symbol(f"nb{nano}_own_rows"))], layer=layer, nano=nano)
+            b = BarrierParams()
+            b.ctx, b.flag_off, b.epoch = self.ctx(), self.new_flags(), 0
+            b.status = p.status
+            idx = g.add(f"{name}.done", b, stream, deps=[idx], dyn=[("epoch", g.symbol("epoch"))],
+                        layer=layer, nano=nano)
         if self.fake_wire_us_per_row > 0 and nano >= 0:
             # Stand-in for the time on the wire when the other ranks are not there (virtual tensor
             # parallelism on one GPU): a one-thread sleep on the collective's stream, as long as the

@@ -258,6 +258,9 @@ class Engine:
             put(f"items{k}", nb.items.reshape(-1))
             sym[f"nb{k}_T"], sym[f"nb{k}_items"] = nb.token_count, int(nb.items.shape[0])
             sym[f"nb{k}_dec_begin"], sym[f"nb{k}_dec_count"] = nb.dec_begin, nb.dec_count
+            if f"nb{k}_own_rows" in self.graph.symbols:     # rows of the nano-batch this rank owns (row i: rank i % tp)
+                tp_, rk = self.w.tp, getattr(self.coll, "rank", 0)
+                sym[f"nb{k}_own_rows"] = max(0, (nb.token_count - rk + tp_ - 1) // tp_)
             if f"nb{k}_wire_us" in self.graph.symbols:       # sleeps standing in for absent ranks (virtual TP)
                 sym[f"nb{k}_wire_us"] = int(nb.token_count * getattr(self.coll, "fake_wire_us_per_row", 0.0))
         n_off = 0

@@ -62,6 +62,11 @@ class MemcpyParams(Structure):
     _fields_ = [("dst", c_void_p), ("src", c_void_p), ("elem_bytes", c_longlong), ("count", c_int)]
 
 
+class Memcpy2DParams(Structure):
+    _fields_ = [("dst", c_void_p), ("src", c_void_p), ("dpitch", c_longlong), ("spitch", c_longlong),
+                ("width", c_longlong), ("height", c_int)]
+
+
 class SleepParams(Structure):
     _fields_ = [("micros", c_int)]
 
@@ -82,7 +87,7 @@ KERNEL_OF = {
     NormParams: "nfk_norm_p",
     EmbeddingParams: "nfk_embedding_p", GatherParams: "nfk_gather_p", ArgmaxParams: "nfk_argmax_p",
     ArgmaxCombineParams: "nfk_argmax_combine_p", CopyColsParams: "nfk_copy_cols_p",
-    MemcpyParams: "nfk_memcpy_p", KvMoveParams: "nfk_kv_move_p", SleepParams: "nfk_sleep_p",
+    MemcpyParams: "nfk_memcpy_p", Memcpy2DParams: "nfk_memcpy2d_p", KvMoveParams: "nfk_kv_move_p", SleepParams: "nfk_sleep_p",
 }
 
 

@@ -1,7 +1,7 @@
 """Multi-GPU test worker, one process per GPU:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        --master-port 29511 tests/mp_worker.py {collectives|collectives_wide|collectives_nvls|fused|engine|engine_nvls|engine_gate|engine_gate_nvls|timeout}
+        --master-port 29511 tests/mp_worker.py {collectives|collectives_wide|collectives_nvls|fused|engine|engine_nvls|engine_gate|engine_gate_nvls|engine_copy|engine_copy_nvls|timeout}
 
 Prints ``MP_WORKER_OK <case>`` from rank 0 on success; any rank's assertion failure exits non-zero.
 """
@@ -243,7 +243,7 @@ def case_fused(rank, world, dev):
     coll.close()
 
 
-def case_engine(rank, world, dev, backend="ipc", gate=False):
+def case_engine(rank, world, dev, backend="ipc", gate=False, by_copy=False):
     from nanoflow_b200.config import builtin_config
     from nanoflow_b200.models import ReferenceLlama, random_full_weights, shard_weights
     from nanoflow_b200.runtime.engine import Engine
@@ -279,6 +279,7 @@ def case_engine(rank, world, dev, backend="ipc", gate=False):
         coll = TpCollectives(rank, world, dev, heap_bytes=64 << 20, backend=backend)
         if backend == "nvls":
             coll.use_multimem = True
+        coll.push_by_copy = by_copy          # normed rows delivered by copy-engine copies + a closing barrier
         eng = Engine(cfg, shard_weights(fw, cfg.model, rank, world, device=dev), device=dev, collectives=coll,
                      num_pages=64)
         st = ServingLoop(eng, sch, rm, est_cycle_time=1.0).run()
@@ -342,6 +343,8 @@ if __name__ == "__main__":
         {"collectives": case_collectives, "collectives_wide": lambda r, w, d: case_collectives(r, w, d, wide=True),
          "collectives_nvls": lambda r, w, d: case_collectives(r, w, d, backend="nvls"),
          "engine": case_engine, "engine_nvls": lambda r, w, d: case_engine(r, w, d, backend="nvls"),
+         "engine_copy": lambda r, w, d: case_engine(r, w, d, by_copy=True),
+         "engine_copy_nvls": lambda r, w, d: case_engine(r, w, d, backend="nvls", by_copy=True),
          "engine_gate": lambda r, w, d: case_engine(r, w, d, gate=True),
          "engine_gate_nvls": lambda r, w, d: case_engine(r, w, d, backend="nvls", gate=True),
          "timeout": case_timeout, "fused": case_fused}[case](rank, world, dev)
