@@ -708,3 +708,30 @@ def test_gemm_reduce_scatter_epilogue_staged_equals_direct(M, N, K, tile_n, cta_
         untouched[rank, :rows.numel()] = False
         assert bool((slabs.view(torch.int16)[untouched] == 0x7F7F).all())
         assert bool((staged[base + 256 + world * cap * N * 2:base + region] == 0x7F).all())
+
+
+def test_strided_copy_op_moves_every_nth_row():
+    """nfk_memcpy2d_p (the op that delivers a rank's normed rows to a peer through the copy engines):
+    rows r, r + n, r + 2n, ... of one buffer land in the same rows of another, nothing else is touched."""
+    from ctypes import byref, c_void_p
+
+    from nanoflow_b200.runtime.graph import Memcpy2DParams
+
+    rows, cols, n, r = 37, 512, 8, 3
+    src = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
+    dst = torch.full_like(src, -1.0)
+    own = (rows - r + n - 1) // n
+    p = Memcpy2DParams()
+    row_bytes = cols * 2
+    p.dst, p.src = dst.data_ptr() + r * row_bytes, src.data_ptr() + r * row_bytes
+    p.dpitch = p.spitch = n * row_bytes
+    p.width, p.height = row_bytes, own
+    rc = ops.lib().nfk_memcpy2d_p(byref(p), c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    mine = torch.arange(r, rows, n, device="cuda")
+    assert torch.equal(dst[mine], src[mine])
+    others = torch.tensor([i for i in range(rows) if i % n != r], device="cuda")
+    assert bool((dst[others] == -1.0).all())
+    p.height = 0
+    assert ops.lib().nfk_memcpy2d_p(byref(p), c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
