@@ -121,6 +121,9 @@ def main():
     ap.add_argument("--gate-gemm", action="store_true",
                     help="tensor parallel: the GEMM behind an all-reduce + norm starts with the collective and waits per "
                          "128-row block for its input rows")
+    ap.add_argument("--o-allgather", default="",
+                    help="tensor parallel: comma-separated nano-batches whose O projection takes the all-gather form "
+                         "(attention output gathered column-wise, N-split weight) instead of K-split weight + all-reduce")
     ap.add_argument("--cross-layer", action="store_true",
                     help="overlapped pipelines: software pipeline across layers (a nano-batch's attention of layer l+1 "
                          "under the other nano-batches' O / FFN GEMMs of layer l)")
@@ -244,6 +247,7 @@ def main():
     cfg.engine.attn_overlap = bool(args.attn_overlap)
     cfg.engine.cross_layer_pipeline = bool(args.cross_layer)
     cfg.engine.gate_gemm = bool(args.gate_gemm)
+    cfg.engine.o_allgather_nanos = [int(k) for k in args.o_allgather.split(",") if k != ""] if tp > 1 else []
     cfg.engine.prefill_impl = args.prefill_impl
     cfg.engine.decode_impl = args.decode_impl
     if args.gemm_smem_kb:
@@ -262,7 +266,8 @@ def main():
     model = cfg.model
 
     t_load = time.perf_counter()
-    weights = random_rank_weights(model, 0 if args.virtual_tp > 1 else rank, tp, dev, seed=0)
+    weights = random_rank_weights(model, 0 if args.virtual_tp > 1 else rank, tp, dev, seed=0,
+                                  o1=bool(cfg.engine.o_allgather_nanos))
     torch.cuda.synchronize()
     # One GPU: iterations go out as CUDA graphs (measured 45.5 against 47.1 ms per iteration); with
     # several ranks the launch gaps already hide under the other streams and plain launches are kept.
@@ -386,6 +391,7 @@ def main():
                        "attn_overlap": bool(cfg.engine.attn_overlap),
                        "cross_layer_pipeline": bool(cfg.engine.cross_layer_pipeline),
                        "gated_gemm_behind_all_reduce": bool(cfg.engine.gate_gemm and tp > 1),
+                       "o_projection_all_gather_form_nanobatches": list(cfg.engine.o_allgather_nanos),
                        "prefill_impl": cfg.engine.prefill_impl or "default",
                        "decode_impl": cfg.engine.decode_impl or "default",
                        "normed_rows_pushed_by": ("copy engines" if getattr(coll, "push_by_copy", False) else "kernel") if world > 1 else "none",

@@ -162,6 +162,10 @@ class EngineConfig:
                                            # nano-batches' O / FFN GEMMs (software pipeline across layers)
     gate_gemm: bool = False                # TP: the GEMM behind an all-reduce + norm starts with the collective and waits
                                            # per 128-row block for the rows it reads (all-gather -> GEMM in one pipeline)
+    o_allgather_nanos: List[int] = field(default_factory=list)   # TP: nano-batches whose O projection takes the
+                                           # all-gather form (attention output gathered column-wise, N-split
+                                           # weight, column blocks of the result gathered by the row owners)
+                                           # instead of K-split weight + all-reduce
     prefill_impl: str = ""                 # "" = choose (ws for head_dim 128, mma otherwise or with prefill_tc off), "ws", "tc", "mma"
     decode_impl: str = ""                  # "" = per-warp cp.async rings, "tma" = TMA producer warp (head_dim 128)
     decode_stages: int = 0                 # decode attention pages in flight per warp: 0 = 3 (2 under attn_overlap), 2, 3
@@ -254,6 +258,7 @@ def parse_config(raw: Dict[str, Any], *, tp: Optional[int] = None) -> NanoflowCo
         cross_layer_pipeline=bool(pc.get("cross_layer_pipeline", False)),
         prefill_impl=str(pc.get("prefill_impl", "")),
         gate_gemm=bool(pc.get("gate_gemm", False)),
+        o_allgather_nanos=[int(k) for k in pc.get("o_allgather_nanos", [])],
         decode_impl=str(pc.get("decode_impl", "")),
         decode_stages=int(pc.get("decode_stages", 0)),
         model_id=sc.get("model", ""),

@@ -204,7 +204,7 @@ allreduce_kernel(nfk_allreduce_params p) {
   __shared__ float red[8];
   const nfk_comm_ctx& c = p.ctx;
   // src_mode 1: the producer GEMM pushed the partial rows into local slabs and raised the ready flags
-  comm_enter(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status, p.src_mode == 0);
+  comm_enter(c, p.flag_off, static_cast<unsigned int>(p.epoch), p.status, p.src_mode != 1);
   gate_publish_empty_blocks(p);
 
   const int nvec = p.cols >> 3;
@@ -230,6 +230,17 @@ allreduce_kernel(nfk_allreduce_params p) {
 #pragma unroll
             for (int r = 0; r < NR; ++r)
               in[i][r] = ld_sys_v4(reinterpret_cast<const char*>(c.heap[r]) + p.buf_off + row * row_bytes + v * 16);
+          } else if (p.src_mode == 2) {
+            // column blocks: rank r produced columns [r * cols / NR, (r + 1) * cols / NR) of every row (an
+            // N-split GEMM), so the row is gathered, one load per vector, instead of summed
+            const int src = (v << 3) / (p.cols / NR);
+            const char* base = reinterpret_cast<const char*>(c.heap[0]);
+#pragma unroll
+            for (int r = 1; r < NR; ++r)      // a chain of selects: no indexed read of the parameter block
+              if (r == src) base = reinterpret_cast<const char*>(c.heap[r]);
+            in[i][0] = ld_sys_v4(base + p.buf_off + row * row_bytes + v * 16);
+#pragma unroll
+            for (int r = 1; r < NR; ++r) in[i][r] = make_uint4(0u, 0u, 0u, 0u);
           } else {
 #pragma unroll
             for (int r = 0; r < NR; ++r)
@@ -564,8 +575,10 @@ extern "C" int nfk_allreduce(const nfk_allreduce_params* p, cudaStream_t stream)
     return NF_ERR_BAD_ARG;
   if (p->sum_out != nullptr && ((reinterpret_cast<uintptr_t>(p->sum_out) & 15) || p->sum_ld % 8 != 0))
     return NF_ERR_BAD_ARG;
-  if (p->src_mode != 0 && (p->src_mode != 1 || p->push_sum != 0 || p->slab_rows * p->ctx.nranks < p->rows))
+  if (p->src_mode == 1 && (p->push_sum != 0 || p->slab_rows * p->ctx.nranks < p->rows))
     return NF_ERR_BAD_ARG;   // slab input: the sum cannot be pushed back into a per-rank buffer
+  if (p->src_mode == 2 && p->cols % (8 * p->ctx.nranks) != 0) return NF_ERR_BAD_ARG;   // whole vectors per block
+  if (p->src_mode < 0 || p->src_mode > 2) return NF_ERR_BAD_ARG;
   if (p->mc_heap != nullptr && (reinterpret_cast<uintptr_t>(p->mc_heap) & 15) != 0) return NF_ERR_BAD_ARG;
   if (p->gate_cnt != nullptr && (p->norm_w == nullptr || p->gate_off % 16 != 0)) return NF_ERR_BAD_ARG;
   if (p->push_mode != 0 && (p->push_mode != 1 || p->norm_w == nullptr || p->gate_cnt != nullptr || p->push_sum != 0))

@@ -227,6 +227,9 @@ typedef struct nfk_allreduce_params {
   int src_mode;           // 0: pull row i from every rank's buffer. 1: the partials were pushed here by a
                           //    NFK_EPI_REDUCE_SCATTER GEMM: owned row k of rank r's partial sits in the local
                           //    slab at buf_off + (r * slab_rows + k) * ld (no NVLink loads, no ready signal)
+                          //    2: rank r's buffer holds columns [r*cols/nranks, (r+1)*cols/nranks) of every row (the
+                          //    output of an N-split GEMM): an owned row is gathered from the ranks' column blocks
+                          //    instead of summed, then residual / norm / pushes as in mode 0
   int slab_rows;
   int wide;               // 1 (8 ranks): twice the loads in flight per phase, the norm pass re-reads the stored sum
   // Optional row-block flags for a consumer that starts before this collective has finished (see

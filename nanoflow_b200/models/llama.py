@@ -56,6 +56,10 @@ class LayerWeights:
     ln_attn: torch.Tensor
     ln_ffn: torch.Tensor
     bqkv: Optional[torch.Tensor] = None
+    # N-split form of the O projection, [hidden / tp, q_size]: rows rank*hidden/tp ... of the full matrix, for
+    # nano-batches that all-gather the attention output instead of all-reducing the projection (the
+    # reference's O1 weights, pipeline/src/vortexData.cu; only kept when a pipeline asks for it)
+    wo1: Optional[torch.Tensor] = None
 
 
 @dataclass
@@ -71,12 +75,12 @@ class RankWeights:
         mv = lambda t: None if t is None else t.to(device=device, dtype=dtype)
         return RankWeights(mv(self.embed), mv(self.norm), mv(self.lm_head),
                            [LayerWeights(mv(l.wqkv), mv(l.wo), mv(l.wg), mv(l.wu), mv(l.wd), mv(l.ln_attn),
-                                         mv(l.ln_ffn), mv(l.bqkv)) for l in self.layers], self.rank, self.tp)
+                                         mv(l.ln_ffn), mv(l.bqkv), mv(l.wo1)) for l in self.layers], self.rank, self.tp)
 
     def nbytes(self) -> int:
         n = sum(t.numel() * t.element_size() for t in (self.embed, self.norm, self.lm_head))
         for l in self.layers:
-            for t in (l.wqkv, l.wo, l.wg, l.wu, l.wd, l.ln_attn, l.ln_ffn, l.bqkv):
+            for t in (l.wqkv, l.wo, l.wg, l.wu, l.wd, l.ln_attn, l.ln_ffn, l.bqkv, l.wo1):
                 if t is not None:
                     n += t.numel() * t.element_size()
         return n
@@ -100,9 +104,9 @@ def random_full_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.02, dtyp
 
 
 def shard_weights(fw: FullWeights, cfg: ModelConfig, rank: int, tp: int, dtype=torch.bfloat16,
-                  device="cpu") -> RankWeights:
+                  device="cpu", o1: bool = False) -> RankWeights:
     """Slice the full model for one tensor-parallel rank (head-parallel attention, N-split gate/up,
-    K-split O and down, vocab-split LM head)."""
+    K-split O and down, vocab-split LM head). ``o1`` adds the N-split form of the O projection."""
     hd = cfg.head_dim
     ql, kl, fl = cfg.num_q_heads // tp * hd, cfg.num_kv_heads // tp * hd, cfg.intermediate_size // tp
     vl = ((cfg.vocab_size + tp - 1) // tp + 7) // 8 * 8
@@ -112,6 +116,7 @@ def shard_weights(fw: FullWeights, cfg: ModelConfig, rank: int, tp: int, dtype=t
     if hi > lo:
         head[:hi - lo] = fw.lm_head[lo:hi]
     layers = []
+    hs = cfg.hidden_size // tp
     for l in fw.layers:
         qs, ks = slice(rank * ql, (rank + 1) * ql), slice(rank * kl, (rank + 1) * kl)
         wqkv = torch.cat([l.wk[ks], l.wv[ks], l.wq[qs]], dim=0)
@@ -119,12 +124,13 @@ def shard_weights(fw: FullWeights, cfg: ModelConfig, rank: int, tp: int, dtype=t
         fs = slice(rank * fl, (rank + 1) * fl)
         layers.append(LayerWeights(wqkv=mv(wqkv), wo=mv(l.wo[:, qs]), wg=mv(l.wg[fs]), wu=mv(l.wu[fs]),
                                    wd=mv(l.wd[:, fs]), ln_attn=mv(l.ln_attn), ln_ffn=mv(l.ln_ffn),
-                                   bqkv=None if bqkv is None else mv(bqkv)))
+                                   bqkv=None if bqkv is None else mv(bqkv),
+                                   wo1=mv(l.wo[rank * hs:(rank + 1) * hs]) if (o1 and tp > 1) else None))
     return RankWeights(embed=mv(fw.embed), norm=mv(fw.norm), lm_head=mv(head), layers=layers, rank=rank, tp=tp)
 
 
 def random_rank_weights(cfg: ModelConfig, rank: int, tp: int, device, dtype=torch.bfloat16, seed: int = 0,
-                        std: float = 0.02) -> RankWeights:
+                        std: float = 0.02, o1: bool = False) -> RankWeights:
     """Random-init shard generated directly on ``device`` (never materialises the full model):
     the ``--empty_weight`` path of the reference (pipeline/src/vortexData.cu:386-406) with defined
     values instead of uninitialised memory."""
@@ -153,7 +159,8 @@ def random_rank_weights(cfg: ModelConfig, rank: int, tp: int, device, dtype=torc
         ln_f = torch.empty(h, dtype=dtype, device=device).normal_(0.0, std, generator=g_shared) + 1
         layers.append(LayerWeights(wqkv=rn(ql + 2 * kl, h), wo=rn(h, ql), wg=rn(fl, h), wu=rn(fl, h),
                                    wd=rn(h, fl), ln_attn=ln_a, ln_ffn=ln_f,
-                                   bqkv=rn(ql + 2 * kl) if cfg.qkv_bias else None))
+                                   bqkv=rn(ql + 2 * kl) if cfg.qkv_bias else None,
+                                   wo1=rn(h // tp, cfg.num_q_heads * hd) if (o1 and tp > 1) else None))
     return RankWeights(embed=embed, norm=norm, lm_head=rn(vl, h), layers=layers, rank=rank, tp=tp)
 
 

@@ -121,8 +121,10 @@ def _num_layers(sd: Dict[str, torch.Tensor]) -> int:
 
 
 def rank_weights_from_state(sd: Dict[str, torch.Tensor], cfg: ModelConfig, rank: int, tp: int,
-                            device="cpu", dtype=torch.bfloat16, has_bias: Optional[bool] = None) -> RankWeights:
-    """One rank's file contents -> kernel layout ([N, K]; vocab-sharded LM head)."""
+                            device="cpu", dtype=torch.bfloat16, has_bias: Optional[bool] = None,
+                            o1: bool = False) -> RankWeights:
+    """One rank's file contents -> kernel layout ([N, K]; vocab-sharded LM head). ``o1`` also keeps the
+    N-split O projection (``O1_<l>``) for pipelines that all-gather the attention output."""
     mv = lambda t: t.to(device=device, dtype=dtype).contiguous()
     L = _num_layers(sd)
     vl = cfg.vocab_local if cfg.tp == tp else ((cfg.vocab_size + tp - 1) // tp + 7) // 8 * 8
@@ -138,18 +140,19 @@ def rank_weights_from_state(sd: Dict[str, torch.Tensor], cfg: ModelConfig, rank:
         layers.append(LayerWeights(
             wqkv=mv(sd[f"KQV_{l}"].t()), wo=mv(sd[f"O2_{l}"].t()), wg=mv(sd[f"G_{l}"].t()), wu=mv(sd[f"U_{l}"].t()),
             wd=mv(sd[f"D_{l}"].t()), ln_attn=mv(sd[f"LNATT_{l}"]), ln_ffn=mv(sd[f"LNFFN_{l}"]),
-            bqkv=mv(bias.reshape(-1)) if use_bias else None))
+            bqkv=mv(bias.reshape(-1)) if use_bias else None,
+            wo1=mv(sd[f"O1_{l}"].t()) if (o1 and tp > 1) else None))
     return RankWeights(embed=mv(sd["Embed"]), norm=mv(sd["ModelNorm"]), lm_head=mv(head), layers=layers,
                        rank=rank, tp=tp)
 
 
 def load_rank_weights(weight_dir: str, cfg: ModelConfig, rank: int, tp: int, device="cpu",
-                      dtype=torch.bfloat16) -> RankWeights:
+                      dtype=torch.bfloat16, o1: bool = False) -> RankWeights:
     path = os.path.join(weight_dir, f"weight_rank_{rank}.pt")
     if not os.path.exists(path):
         raise FileNotFoundError(f"{path} not found: run save_weights first (or use random weights)")
     sd = torch.load(path, map_location="cpu")
-    return rank_weights_from_state(sd, cfg, rank, tp, device=device, dtype=dtype)
+    return rank_weights_from_state(sd, cfg, rank, tp, device=device, dtype=dtype, o1=o1)
 
 
 def load_weights(nranks: int, weight_dir: str, cfg: ModelConfig, device="cpu", dtype=torch.bfloat16):

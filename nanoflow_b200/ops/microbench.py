@@ -1,4 +1,4 @@
-"""Per-kernel micro-benchmarks: ``python -m nanoflow_b200.ops.microbench [gemm|swiglu|smallm|decode|prefill|norm|hostlink|budget|all]``
+"""Per-kernel micro-benchmarks: ``python -m nanoflow_b200.ops.microbench [gemm|swiglu|smallm|decode|prefill|norm|hostlink|budget|library|all]``
 (JSON lines; ``... table rows.jsonl`` turns them into a markdown table).
 
 Each case is timed with CUDA events on the launching stream after warm-up, with an L2 flush (a
@@ -138,6 +138,125 @@ def bench_prefill():
             print(json.dumps(dict(op="attn_prefill_" + impl, batch=batch, ctx=ctx, kv_heads=kv_heads, group=group,
                                   ms=round(med, 4), tflops=round(flops / med / 1e9, 1),
                                   frac_of_peak=round(flops / med / 1e9 / tf_peak, 3), peak=how)), flush=True)
+
+
+def bench_library_attention():
+    """Same-box comparison rows: this package's decode / prefill attention kernels and the installed
+    ``flashinfer`` library's on the same paged KV pool (HND layout, page 16, bf16, head_dim 128). A comparator
+    only: nothing on the serving path calls the library. Its kernels are compiled on first use (or found in
+    its cache directory, FLASHINFER_WORKSPACE_BASE); a form that cannot be built or run here gives a row with
+    ``unavailable`` and the first line of the reason. The reference links a FlashInfer fork for the same two
+    kernels (gemv/include/attention/decode.cuh, prefill.cuh)."""
+    bw_peak, tf_peak, how = peaks()
+    hd, page = 128, 16
+
+    def row(**kw):
+        print(json.dumps(kw), flush=True)
+
+    def guarded(op, shape, make, rate):
+        try:
+            fn = make()
+            med, _ = time_ms(fn)
+            row(op=op, **shape, ms=round(med, 4), **rate(med), peak=how)
+        except Exception as e:      # a missing compiler, cache or kernel image is a result here, not an error
+            row(op=op, **shape, unavailable=(str(e).strip().splitlines() or [type(e).__name__])[0][:200])
+
+    try:
+        import flashinfer
+    except Exception as e:
+        row(op="flashinfer", unavailable=str(e)[:200])
+        return
+    fws = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
+    for (batch, ctx, kv_heads, group) in [(2731, 1280, 1, 8), (683, 1280, 1, 8), (256, 1280, 8, 8)]:
+        q_heads = kv_heads * group
+        pool, qo, kvp, kvi, last = _paged(batch, ctx, kv_heads, hd)
+        q = torch.randn(batch, q_heads * hd, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        shape = dict(batch=batch, ctx=ctx, kv_heads=kv_heads, group=group)
+        nbytes = batch * ctx * kv_heads * hd * 2 * 2 + 2 * q.numel() * 2
+        rate = lambda med: dict(gbs=round(nbytes / med / 1e6, 1), frac_of_peak=round(nbytes / med / 1e6 / bw_peak, 3))
+        guarded("attn_decode", shape, lambda: (lambda: ops.attn_decode(
+            q, out, pool, qo, kvp, kvi, last, q_heads=q_heads, req_begin=0, req_count=batch)), rate)
+
+        def fa2():
+            w = flashinfer.BatchDecodeWithPagedKVCacheWrapper(fws, "HND", use_tensor_cores=True)
+            w.plan(kvp, kvi, last, q_heads, kv_heads, hd, page, q_data_type=torch.bfloat16,
+                   kv_data_type=torch.bfloat16)
+            q3 = q.view(batch, q_heads, hd)
+            o3 = w.run(q3, pool)
+            want = torch.empty_like(q)
+            ops.attn_decode(q, want, pool, qo, kvp, kvi, last, q_heads=q_heads, req_begin=0, req_count=batch)
+            torch.cuda.synchronize()
+            err = (o3.reshape(batch, -1).float() - want.float()).abs().max().item()
+            if err > 0.05:
+                raise RuntimeError(f"library result differs from this package's by {err:.3f}")
+            return lambda: w.run(q3, pool)
+        guarded("attn_decode_flashinfer_fa2", shape, fa2, rate)
+
+        def trtllm():
+            npages = (ctx + page - 1) // page
+            tables = kvi.view(batch, npages).contiguous()
+            lens = torch.full((batch,), ctx, dtype=torch.int32, device="cuda")
+            ws = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
+            q3 = q.view(batch, q_heads, hd)
+            call = lambda: flashinfer.decode.trtllm_batch_decode_with_kv_cache(
+                q3, pool, ws, tables, lens, ctx, hd ** -0.5, 1.0, kv_layout="HND")
+            o3 = call()
+            want = torch.empty_like(q)
+            ops.attn_decode(q, want, pool, qo, kvp, kvi, last, q_heads=q_heads, req_begin=0, req_count=batch)
+            torch.cuda.synchronize()
+            err = (o3.reshape(batch, -1).float() - want.float()).abs().max().item()
+            if err > 0.05:
+                raise RuntimeError(f"library result differs from this package's by {err:.3f}")
+            return call
+        guarded("attn_decode_flashinfer_trtllm_gen", shape, trtllm, rate)
+        del pool
+
+    for (batch, ctx, kv_heads, group) in [(4, 1024, 1, 8), (8, 1024, 8, 4), (1, 4096, 8, 8)]:
+        q_heads = kv_heads * group
+        pool, qo, kvp, kvi, last = _paged(batch, ctx, kv_heads, hd, qo_len=ctx)
+        q = torch.randn(batch * ctx, q_heads * hd, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        tq = 128 // group
+        items = torch.tensor([[b, b * ctx + t, min(tq, ctx - t)] for b in range(batch)
+                              for t in range(0, ctx, tq)], dtype=torch.int32, device="cuda")
+        flops = 4.0 * batch * q_heads * hd * ctx * ctx / 2
+        shape = dict(batch=batch, ctx=ctx, kv_heads=kv_heads, group=group)
+        rate = lambda med: dict(tflops=round(flops / med / 1e9, 1), frac_of_peak=round(flops / med / 1e9 / tf_peak, 3))
+        guarded("attn_prefill_ws", shape, lambda: (lambda: ops.attn_prefill(
+            q, out, pool, qo, kvp, kvi, last, items, q_heads=q_heads, impl="ws")), rate)
+
+        def fa2p():
+            w = flashinfer.BatchPrefillWithPagedKVCacheWrapper(fws, "HND")
+            w.plan(qo, kvp, kvi, last, q_heads, kv_heads, hd, page, causal=True, q_data_type=torch.bfloat16,
+                   kv_data_type=torch.bfloat16)
+            q3 = q.view(batch * ctx, q_heads, hd)
+            o3 = w.run(q3, pool)
+            ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, items, q_heads=q_heads, impl="ws")
+            torch.cuda.synchronize()
+            err = (o3.reshape(batch * ctx, -1).float() - out.float()).abs().max().item()
+            if err > 0.05:
+                raise RuntimeError(f"library result differs from this package's by {err:.3f}")
+            return lambda: w.run(q3, pool)
+        guarded("attn_prefill_flashinfer_fa2", shape, fa2p, rate)
+
+        def trtllm_p():
+            npages = (ctx + page - 1) // page
+            tables = kvi.view(batch, npages).contiguous()
+            lens = torch.full((batch,), ctx, dtype=torch.int32, device="cuda")
+            ws = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
+            q3 = q.view(batch * ctx, q_heads, hd)
+            call = lambda: flashinfer.prefill.trtllm_batch_context_with_kv_cache(
+                q3, pool, ws, tables, lens, ctx, ctx, hd ** -0.5, 1.0, batch, qo, qo, kv_layout="HND")
+            o3 = call()
+            ops.attn_prefill(q, out, pool, qo, kvp, kvi, last, items, q_heads=q_heads, impl="ws")
+            torch.cuda.synchronize()
+            err = (o3.reshape(batch * ctx, -1).float() - out.float()).abs().max().item()
+            if err > 0.05:
+                raise RuntimeError(f"library result differs from this package's by {err:.3f}")
+            return call
+        guarded("attn_prefill_flashinfer_trtllm_gen", shape, trtllm_p, rate)
+        del pool
 
 
 def bench_budget():
@@ -396,6 +515,8 @@ def main(argv):
         bench_prefill()
     if what == "budget":
         bench_budget()
+    if what == "library":
+        bench_library_attention()
     if what in ("norm", "all"):
         bench_norm()
     if what in ("hostlink", "all"):

@@ -135,8 +135,13 @@ class TpCollectives(CollectiveHooks):
                    deps, layer: int, nano: int, stream: str = "net", norm_w: Optional[torch.Tensor] = None,
                    norm_out: Optional[torch.Tensor] = None, eps: float = 1e-5, status=None, num_ctas: int = 0,
                    resid: Optional[torch.Tensor] = None, sum_out: Optional[torch.Tensor] = None,
-                   push_sum: bool = True, slab: Optional[dict] = None, gate_rows_cap: int = 0):
+                   push_sum: bool = True, slab: Optional[dict] = None, gate_rows_cap: int = 0,
+                   gather_cols: bool = False):
         """Append a reduction of ``buf`` rows [row0, row0+rows) over all ranks.
+
+        ``gather_cols``: rank r's ``buf`` holds columns [r*cols/tp, (r+1)*cols/tp) of the rows (an N-split
+        GEMM wrote them); the row owners gather the blocks instead of summing (kernel src_mode 2), the rest
+        (residual, stored sum, norm, pushes) is the same.
 
         ``gate_rows_cap`` > 0 (with a fused norm): the op also raises row-block flags as it pushes the
         normed rows; ``self.last_gate`` then holds what the consumer GEMM needs (see GemmParams.gate_flags).
@@ -156,6 +161,8 @@ class TpCollectives(CollectiveHooks):
         else:
             p.buf_off = self.heap.offset_of(buf) + row0 * buf.stride(0) * esz
             p.flag_off = self.new_flags()
+            if gather_cols:
+                p.src_mode = 2
         p.rows, p.cols, p.ld = 0, cols, buf.stride(0)
         p.epoch, p.num_ctas = 0, num_ctas or self.num_ctas
         fused = norm_w is not None and norm_out is not None
@@ -170,7 +177,7 @@ class TpCollectives(CollectiveHooks):
             p.sum_out, p.sum_ld = sum_out.data_ptr() + row0 * sum_out.stride(0) * esz, sum_out.stride(0)
         p.status = (status if status is not None else self.status).data_ptr()
         p.wide = 1 if self.wide else 0
-        if self.use_multimem and slab is None:
+        if self.use_multimem and slab is None and not gather_cols:
             p.mc_heap = self.heap.mc_base
         self.last_gate = None
         if gate_rows_cap > 0 and fused and self.fake_wire_us_per_row <= 0:
@@ -217,6 +224,39 @@ class TpCollectives(CollectiveHooks):
             idx = g.add(name + ".wire", SleepParams(0), stream, deps=[idx],
                         dyn=[("micros", g.symbol(f"nb{nano}_wire_us"))], layer=layer, nano=nano)
         return idx, fused
+
+    def all_gather_columns(self, g: OpGraph, name: str, src: torch.Tensor, dst: torch.Tensor, row0: int,
+                           rows_sym: str, deps, layer: int, nano: int, stream: str = "net", status=None):
+        """Append a column-wise all-gather done by the copy engines: rows [row0, row0 + rows) of the local
+        ``src`` [T, w] become column block ``rank`` of the same rows of the symmetric ``dst`` [T, tp * w] on
+        every rank (one strided copy per rank, own copy included), closed by a barrier; no SM moves data. The
+        reference gathers the attention output this way in front of its N-split O projection
+        (pipeline/src/pipeline.cu:671-677, ``AG1_GEMV``).
+
+        A peer may still be reading its ``dst`` rows from the previous use when this rank's copy arrives
+        unless the caller orders them: in the pipelines every use of ``dst`` is followed by a collective with
+        an entry handshake that this rank's next attention depends on, which gives that order."""
+        from ..runtime.graph import Memcpy2DParams
+        esz = src.element_size()
+        w_bytes = src.shape[1] * esz
+        if dst.shape[1] % src.shape[1] != 0 or dst.shape[1] < self.tp * src.shape[1] or dst.stride(1) != 1 \
+                or src.stride(1) != 1:
+            raise ValueError("column-wise all-gather: dst must be [rows, tp * w] for src [rows, w]")
+        dst_off = self.heap.offset_of(dst) + row0 * dst.stride(0) * esz + self.rank * w_bytes
+        idx = None
+        for step in range(self.tp):
+            peer = (self.rank + step) % self.tp
+            c = Memcpy2DParams()
+            c.dst, c.src = self.heap.peer_base[peer] + dst_off, src.data_ptr() + row0 * src.stride(0) * esz
+            c.dpitch, c.spitch = dst.stride(0) * esz, src.stride(0) * esz
+            c.width, c.height = w_bytes, 0
+            idx = g.add(f"{name}.copy{peer}", c, stream, deps=list(deps) if idx is None else [idx],
+                        dyn=[("height", rows_sym)], layer=layer, nano=nano)
+        b = BarrierParams()
+        b.ctx, b.flag_off, b.epoch = self.ctx(), self.new_flags(), 0
+        b.status = (status if status is not None else self.status).data_ptr()
+        return g.add(f"{name}.done", b, stream, deps=[idx], dyn=[("epoch", g.symbol("epoch"))],
+                     layer=layer, nano=nano)
 
     def rs_slot(self, part: torch.Tensor, slab_row0: int, rows_cap: int) -> dict:
         """Slab + flag block for one fused GEMM -> reduce-scatter: ``part`` rows

@@ -138,7 +138,8 @@ class Engine:
                                   device=dev),
             meta=meta, nano_items=nano_items,
             gemm_ws=torch.zeros(GEMM_WS_BYTES // 4, dtype=torch.float32, device=dev),
-            rope_table=torch.zeros(T, m.head_dim // 2, 2, dtype=torch.float32, device=dev))
+            rope_table=torch.zeros(T, m.head_dim // 2, 2, dtype=torch.float32, device=dev),
+            attn_full=alloc(T, m.q_size_local * weights.tp) if (weights.tp > 1 and e.o_allgather_nanos) else None)
         io = IoSpec(self.meta_dev, layout.fixed_words, layout.off["kv_indices"])
         self.offload_host = None
         if self.offload_cap:
@@ -182,6 +183,12 @@ class Engine:
                  ("o", b.attn_out, [l.wo for l in L], None, x_out, x_out if tp1 else None, None),
                  ("gate_up", b.h, [l.wg for l in L], [l.wu for l in L], b.act, None, None),
                  ("down", b.act, [l.wd for l in L], None, x_out, x_out if tp1 else None, None)]
+        o1_nanos = set(e.o_allgather_nanos) if (b.attn_full is not None) else set()
+        if o1_nanos:
+            hs = m.hidden_size // w.tp
+            specs.append(("o1", b.attn_full, [l.wo1 for l in L], None, x_out[:, w.rank * hs:(w.rank + 1) * hs],
+                          None, None))
+            b.attn_full.normal_()
         for t in (b.h, b.attn_out, b.act):
             t.normal_()
         done: Dict[tuple, dict] = {}
@@ -192,6 +199,8 @@ class Engine:
                 name = f"{key}.nb{k}"
                 if name in e.gemm_shapes or key in e.gemm_tile_n:
                     continue
+                if (key == "o1") != (k in o1_nanos) and key in ("o", "o1"):
+                    continue
                 if (key, M) not in done:
                     done[(key, M)] = autotune.tune_gemm(
                         a[:M], ws, out[:M], weights_up=ups, residual=None if resid is None else resid[:M],
@@ -201,8 +210,9 @@ class Engine:
                 e.gemm_shapes[name] = dict(r["best"])
                 self.gemm_tuning[name] = dict(M=M, best=r["best"], us=r["us"], auto_us=r["auto_us"])
         torch.cuda.synchronize(self.device)
-        for t in (b.h, b.attn_out, b.act, b.qkv, b.x[0], b.x[1]):
-            t.zero_()
+        for t in (b.h, b.attn_out, b.act, b.qkv, b.x[0], b.x[1], b.attn_full):
+            if t is not None:
+                t.zero_()
 
     # ---- sizing -----------------------------------------------------------------------------------
     def _derive_num_pages(self, T: int, B: int) -> int:
@@ -210,6 +220,8 @@ class Engine:
         free, total = torch.cuda.mem_get_info(self.device)
         act = 2 * T * (3 * m.hidden_size + m.qkv_size_local + 2 * m.q_size_local + m.ffn_local)
         act += 2 * B * (2 * m.hidden_size + self.w.lm_head.shape[0]) + (256 << 20)
+        if e.o_allgather_nanos and self.w.tp > 1:
+            act += 2 * T * m.q_size_local * self.w.tp
         budget = free - (total * (1.0 - e.gpu_mem_fraction)) - act
         page_bytes = 2 * m.kv_heads_local * e.page_size * m.head_dim * 2 * m.run_layers
         n = int(budget // page_bytes)

@@ -65,6 +65,8 @@ class Buffers:
     meta: Dict[str, torch.Tensor]    # int32 views into the metadata block (see engine.MetaLayout)
     nano_items: List[torch.Tensor]   # per nano-batch [cap,3] int32 views
     gemm_ws: Optional[torch.Tensor] = None   # split-K partial sums (fp32); all GEMMs share one stream
+    attn_full: Optional[torch.Tensor] = None  # [T, q_size] symmetric: all ranks' attention outputs side by side
+                                              # (only with nano-batches whose O projection takes the all-gather form)
     rope_table: Optional[torch.Tensor] = None  # [T, head_dim/2, 2] fp32 angles of the iteration's tokens
 
 
@@ -80,6 +82,10 @@ class CollectiveHooks:
         return None, False
 
     def all_gather_candidates(self, g: OpGraph, bufs: Buffers, rows_sym: str, deps) -> Optional[int]:
+        return None
+
+    def all_gather_columns(self, g: OpGraph, name: str, src: torch.Tensor, dst: torch.Tensor, row0: int,
+                           rows_sym: str, deps, layer: int, nano: int, stream: str = "net", status=None):
         return None
 
 
@@ -343,6 +349,14 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
         if row0 > part.shape[0]:
             raise ValueError("partial-product buffer too small for the reduce-scatter slabs")
 
+    # nano-batches whose O projection takes the all-gather form
+    o1_nanos = set(k for k in eng.o_allgather_nanos if 0 <= k < nn) if tp > 1 else set()
+    if o1_nanos:
+        if bufs.attn_full is None or any(lw_.wo1 is None for lw_ in w.layers):
+            raise ValueError("o_allgather_nanos needs the N-split O weights (wo1) and the attn_full buffer")
+        if hidden % (8 * tp) != 0:
+            raise ValueError("o_allgather_nanos: hidden size must split into whole 16-byte vectors per rank")
+
     def rs_slot(k):
         # the slab region of a nano-batch is reused by every fused GEMM of that nano-batch (they are
         # ordered by their collectives' exit handshakes); the flag block is private to each GEMM +
@@ -359,6 +373,24 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
             # the FFN's input norm comes out of the same call (fused into the split-K reduce when K is split)
             return gemm(f"L{l}.nb{k}.o", bufs.attn_out, lw.wo, x_res, k, residual=x_res, beta=1.0, deps=[dec, pre],
                         layer=l, tile_key="o", norm=(lw.ln_ffn, bufs.h))
+        if k in o1_nanos:
+            # All-gather form (the reference's first O-projection scheme, pipeline/src/pipeline.cu:671-682:
+            # AG1_GEMV -> O1 -> AG_O1): the ranks' attention outputs are gathered column-wise, the N-split
+            # weight gives every rank complete sums for its hidden / tp columns of all rows, and the row owners
+            # gather those column blocks (one load per vector instead of one per rank), add the residual,
+            # norm and push as after the K-split form. Same bytes on the links as the all-reduce, moved in two
+            # steps of which the first is done by the copy engines.
+            hs = hidden // tp
+            ag = coll.all_gather_columns(g, f"L{l}.nb{k}.ag_attn", bufs.attn_out, bufs.attn_full, starts[k],
+                                         nb_T[k], [dec, pre], l, k, stream=net_of(k), status=st)
+            o = gemm(f"L{l}.nb{k}.o1", bufs.attn_full, lw.wo1, part[:, w.rank * hs:(w.rank + 1) * hs], k,
+                     deps=[ag, last_x_writer[k]], layer=l, tile_key="o1")
+            ar1, _ = coll.all_reduce(g, f"L{l}.nb{k}.ag_o", part, starts[k], nb_T[k], hidden, [o], l, k,
+                                     stream=net_of(k), norm_w=lw.ln_ffn, norm_out=bufs.h, eps=model.rms_norm_eps,
+                                     status=st, num_ctas=comm_ctas, resid=x_res, sum_out=x_res, push_sum=False,
+                                     gather_cols=True, **gate_kw(k))
+            ffn_gate[k] = take_gate(ar1)
+            return ar1
         slab = rs_slot(k) if fuse_rs else None
         o = gemm(f"L{l}.nb{k}.o", bufs.attn_out, lw.wo, None if fuse_rs else part, k,
                  deps=[dec, pre, last_x_writer[k]], layer=l, tile_key="o", rs=slab)

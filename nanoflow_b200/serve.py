@@ -101,9 +101,10 @@ def main(argv=None) -> int:
                 torch.distributed.barrier()
             have_files = ensure_converted(eng_cfg.weight_path, "", max(1, world))
         if not have_files:
-            weights = random_rank_weights(model, rank, max(1, world), dev)
+            weights = random_rank_weights(model, rank, max(1, world), dev, o1=bool(eng_cfg.o_allgather_nanos))
         else:
-            weights = load_rank_weights(eng_cfg.weight_path, model, rank, max(1, world), device=dev)
+            weights = load_rank_weights(eng_cfg.weight_path, model, rank, max(1, world), device=dev,
+                                        o1=bool(eng_cfg.o_allgather_nanos))
         engine = Engine(cfg, weights, device=dev, collectives=coll, num_pages=args.allocate_page_num or None)
         num_pages = engine.num_pages
     else:

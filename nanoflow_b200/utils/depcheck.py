@@ -51,9 +51,13 @@ def check(graph: OpGraph, access: Dict[int, Tuple[List[Range], List[Range]]]) ->
 
 # ---- access extraction from parameter blocks ------------------------------------------------------
 def graph_access(graph: OpGraph, nano_starts: List[int], nano_sizes: List[int], heap_base: int = 0,
-                 kv_pool_bytes: int = 0) -> Dict[int, Tuple[List[Range], List[Range]]]:
+                 kv_pool_bytes: int = 0, peer_bases: List[int] = ()) -> Dict[int, Tuple[List[Range], List[Range]]]:
     """Read / write byte ranges of every op, from its parameter block. Row counts that are dynamic
-    (symbols) are replaced by the capacity of the op's nano-batch (or ``sum(nano_sizes)``)."""
+    (symbols) are replaced by the capacity of the op's nano-batch (or ``sum(nano_sizes)``).
+
+    ``peer_bases``: where the ranks' symmetric heaps are mapped. A strided copy into a peer's heap stands
+    for the copy that the peer issues into this rank's heap at the same moment, so its target is taken at the
+    same offset of this rank's heap."""
     from ..parallel.collectives import AllGatherParams, AllReduceParams
     from ..runtime import graph as G
 
@@ -146,6 +150,17 @@ def graph_access(graph: OpGraph, nano_starts: List[int], nano_sizes: List[int], 
             add(writes, rng(p.sum_out, cap, p.sum_ld, p.cols))
             if p.norm_w:
                 add(writes, rng(heap_base + p.norm_out_off, cap, p.norm_ld, p.cols))
+        elif isinstance(p, G.Memcpy2DParams):
+            rows = cap
+            if any(f == "height" and sym.endswith("_own_rows") for f, sym in op.dyn) and peer_bases:
+                rows = (cap + len(peer_bases) - 1) // len(peer_bases)      # every tp-th row of the nano-batch
+            span = lambda ptr, pitch: (int(ptr), int(ptr) + (max(rows, 1) - 1) * int(pitch) + int(p.width))
+            add(reads, span(p.src, p.spitch))
+            dst = int(p.dst)
+            below = [b for b in peer_bases if b and b <= dst]
+            if below and heap_base:
+                dst = heap_base + (dst - max(below))
+            add(writes, span(dst, p.dpitch))
         elif isinstance(p, G.GatherParams):
             add(reads, rng(p.inp, p.in_rows, p.ld_in, p.cols))
             add(writes, rng(p.out, total, p.cols, p.cols))

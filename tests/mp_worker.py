@@ -1,7 +1,7 @@
 """Multi-GPU test worker, one process per GPU:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        --master-port 29511 tests/mp_worker.py {collectives|collectives_wide|collectives_nvls|fused|engine|engine_nvls|engine_gate|engine_gate_nvls|engine_copy|engine_copy_nvls|timeout}
+        --master-port 29511 tests/mp_worker.py {collectives|collectives_wide|collectives_nvls|fused|engine|engine_nvls|engine_gate|engine_gate_nvls|engine_copy|engine_copy_nvls|engine_o1|engine_o1_nvls|timeout}
 
 Prints ``MP_WORKER_OK <case>`` from rank 0 on success; any rank's assertion failure exits non-zero.
 """
@@ -243,7 +243,7 @@ def case_fused(rank, world, dev):
     coll.close()
 
 
-def case_engine(rank, world, dev, backend="ipc", gate=False, by_copy=False):
+def case_engine(rank, world, dev, backend="ipc", gate=False, by_copy=False, o1=False):
     from nanoflow_b200.config import builtin_config
     from nanoflow_b200.models import ReferenceLlama, random_full_weights, shard_weights
     from nanoflow_b200.runtime.engine import Engine
@@ -259,6 +259,12 @@ def case_engine(rank, world, dev, backend="ipc", gate=False, by_copy=False):
         cfg.engine.max_batch_size = gbs
         cfg.engine.fuse_gemm_rs = fuse
         cfg.engine.gate_gemm = gate and not fuse     # QKV / gate-up start with the all-reduce that feeds them
+        if o1:
+            if fuse:
+                continue
+            # the all-gather form of the O projection: for the first nano-batch beside the all-reduce form of the
+            # second (the reference's mix), and for the only nano-batch of the in-line pipeline
+            cfg.engine.o_allgather_nanos = [0]
         fw = random_full_weights(cfg.model, seed=0, std=0.05)
         for lay in fw.layers:
             for k, v in vars(lay).items():
@@ -280,8 +286,10 @@ def case_engine(rank, world, dev, backend="ipc", gate=False, by_copy=False):
         if backend == "nvls":
             coll.use_multimem = True
         coll.push_by_copy = by_copy          # normed rows delivered by copy-engine copies + a closing barrier
-        eng = Engine(cfg, shard_weights(fw, cfg.model, rank, world, device=dev), device=dev, collectives=coll,
+        eng = Engine(cfg, shard_weights(fw, cfg.model, rank, world, device=dev, o1=o1), device=dev, collectives=coll,
                      num_pages=64)
+        if o1:
+            assert any(op.name.endswith(".o1") for op in eng.graph.ops)
         st = ServingLoop(eng, sch, rm, est_cycle_time=1.0).run()
         eng.check_status(); coll.check_status()
         eng.finalize()
@@ -345,6 +353,8 @@ if __name__ == "__main__":
          "engine": case_engine, "engine_nvls": lambda r, w, d: case_engine(r, w, d, backend="nvls"),
          "engine_copy": lambda r, w, d: case_engine(r, w, d, by_copy=True),
          "engine_copy_nvls": lambda r, w, d: case_engine(r, w, d, backend="nvls", by_copy=True),
+         "engine_o1": lambda r, w, d: case_engine(r, w, d, o1=True),
+         "engine_o1_nvls": lambda r, w, d: case_engine(r, w, d, backend="nvls", o1=True),
          "engine_gate": lambda r, w, d: case_engine(r, w, d, gate=True),
          "engine_gate_nvls": lambda r, w, d: case_engine(r, w, d, backend="nvls", gate=True),
          "timeout": case_timeout, "fused": case_fused}[case](rank, world, dev)

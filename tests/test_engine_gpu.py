@@ -103,19 +103,24 @@ def test_engine_cuda_graph_executor(pipeline_type, nano):
     _run(pipeline_type, nano, "graph")
 
 
-def test_virtual_tensor_parallel_rank_runs_alone():
+@pytest.mark.parametrize("o1", [False, True])
+def test_virtual_tensor_parallel_rank_runs_alone(o1):
     """One GPU runs rank 0's share of a two-way tensor-parallel job with the collectives reduced to
     their local part (the reference's vnranks aid): shapes, nano-batch overlap and the fused
-    all-reduce + norm path are exercised without a second GPU; tokens are not meaningful."""
+    all-reduce + norm path are exercised without a second GPU; tokens are not meaningful.
+    ``o1``: the first nano-batch's O projection in its all-gather form (strided copies, N-split weight,
+    column-block gather)."""
     from nanoflow_b200.parallel.collectives import TpCollectives
     from nanoflow_b200.runtime.engine import Engine
 
     gbs = 48
     cfg = builtin_config("tiny", gpu_num=2, global_batch_size=gbs, pipeline_type="PLLM", nanobatch_sizes=[16, 32])
     cfg.engine.max_batch_size = gbs
+    cfg.engine.o_allgather_nanos = [0] if o1 else []
     fw = random_full_weights(cfg.model, seed=0, std=0.05)
     coll = TpCollectives(0, 1, torch.device("cuda", 0), heap_bytes=64 << 20)
-    eng = Engine(cfg, shard_weights(fw, cfg.model, 0, 2, device="cuda"), collectives=coll, num_pages=64)
+    eng = Engine(cfg, shard_weights(fw, cfg.model, 0, 2, device="cuda", o1=o1), collectives=coll, num_pages=64)
+    assert any(op.name.endswith(".o1") for op in eng.graph.ops) == o1
     rm = RequestManager(vocab_size=1024, random_ids=True)
     for _ in range(4):
         rm.add_request(32, 8, 0.0)

@@ -11,19 +11,21 @@ from nanoflow_b200.utils import depcheck
 
 
 def _host_graph(pipeline_type, tp, nano, gbs=48, fuse_rs=False, net_streams=1, fake_wire=0.0, attn_overlap=False,
-                cross_layer=False):
+                cross_layer=False, o_allgather=(), by_copy=False):
     cfg = builtin_config("tiny", gpu_num=tp, global_batch_size=gbs, pipeline_type=pipeline_type, nanobatch_sizes=nano)
     m, e = cfg.model, cfg.engine
     e.fuse_gemm_rs = fuse_rs
     e.net_streams = net_streams
     e.attn_overlap = attn_overlap
     e.cross_layer_pipeline = cross_layer
+    e.o_allgather_nanos = list(o_allgather)
     e.max_batch_size = gbs
     fw = random_full_weights(m, seed=0)
-    w = shard_weights(fw, m, 0, tp, dtype=torch.bfloat16)
+    w = shard_weights(fw, m, 0, tp, dtype=torch.bfloat16, o1=bool(o_allgather))
     coll = TpCollectives.for_analysis(0, tp) if tp > 1 else None
     if coll is not None:
         coll.fake_wire_us_per_row = fake_wire
+        coll.push_by_copy = by_copy
     bf = torch.bfloat16
     z = lambda *s, dtype=bf: torch.zeros(*s, dtype=dtype)
     sym = (lambda *s, dtype=bf: coll.alloc(s, dtype)) if coll else z
@@ -43,12 +45,14 @@ def _host_graph(pipeline_type, tp, nano, gbs=48, fuse_rs=False, net_streams=1, f
                    inv_freq=torch.zeros(m.head_dim // 2), status=torch.zeros(1, dtype=torch.int32),
                    decode_ws=torch.zeros(1024), meta=meta,
                    nano_items=[torch.zeros(s + 2, 3, dtype=torch.int32) for s in sizes],
-                   gemm_ws=torch.zeros(1 << 16))
+                   gemm_ws=torch.zeros(1 << 16),
+                   attn_full=sym(T, m.q_size_local * tp) if (o_allgather and tp > 1) else None)
     io = IoSpec(meta_dev, 4 * T, 8 * T)
     g = build_graph(m, e, w, bufs, coll, io)
     starts = [sum(sizes[:k]) for k in range(len(sizes))]
     pool_bytes = pools[0].numel() * 2
-    acc = depcheck.graph_access(g, starts, sizes, heap_base=coll.heap.base if coll else 0, kv_pool_bytes=pool_bytes)
+    acc = depcheck.graph_access(g, starts, sizes, heap_base=coll.heap.base if coll else 0, kv_pool_bytes=pool_bytes,
+                                peer_bases=list(coll.heap.peer_base) if coll else ())
     return g, acc, (bufs, w, coll, meta_dev)
 
 
@@ -78,6 +82,42 @@ def test_fused_reduce_scatter_ops_are_in_the_tp_graph():
     # flags carry only the iteration's epoch, so no two collectives of one iteration may share a block
     offs = [op.params.flag_off for op in g.ops if op.kernel in ("nfk_allreduce", "nfk_allgather")]
     assert len(offs) == len(set(offs))
+
+
+@pytest.mark.parametrize("nanos", [(0,), (0, 1)])
+def test_all_gather_form_of_the_o_projection(nanos):
+    """o_allgather_nanos: for those nano-batches the attention output is gathered column-wise by strided
+    copies + a barrier, the O projection runs on the N-split weight into this rank's column block of the
+    symmetric buffer, and the row owners gather the blocks (src_mode 2) with residual + norm as usual."""
+    g, acc, (bufs, w, coll, _) = _host_graph("PLLM", 2, [16, 32], o_allgather=nanos)
+    assert not depcheck.check(g, acc)
+    m_layers = 2
+    for k in (0, 1):
+        o1 = [op for op in g.ops if op.name.endswith(f"nb{k}.o1")]
+        o2 = [op for op in g.ops if op.name.endswith(f"nb{k}.o")]
+        gath = [op for op in g.ops if op.name.endswith(f"nb{k}.ag_o")]
+        if k in nanos:
+            assert len(o1) == m_layers and not o2 and len(gath) == m_layers
+            for op in o1:
+                assert op.params.N == bufs.x[1].shape[1] // 2 and op.params.K == bufs.attn_full.shape[1]
+                assert op.params.ldd == bufs.x[1].stride(0)       # a column block of the symmetric buffer
+                assert op.params.A == bufs.attn_full.data_ptr() + (0 if k == 0 else 16) * bufs.attn_full.stride(0) * 2
+            assert all(op.params.src_mode == 2 and op.params.norm_w for op in gath)
+            copies = [op for op in g.ops if f"nb{k}.ag_attn.copy" in op.name]
+            assert len(copies) == 2 * m_layers and all(op.kernel == "nfk_memcpy2d_p" for op in copies)
+            assert all(op.params.width == bufs.attn_out.shape[1] * 2 for op in copies)
+        else:
+            assert len(o2) == m_layers and not o1 and not gath
+    # dropping the barrier's edge into the GEMM must be seen: the GEMM reads what the peers' copies write
+    o1_idx = next(i for i, op in enumerate(g.ops) if op.name.endswith("nb0.o1"))
+    g.ops[o1_idx].deps = [d for d in g.ops[o1_idx].deps if not g.ops[d].name.endswith("ag_attn.done")]
+    assert depcheck.check(g, acc)
+
+
+def test_copy_engine_push_is_ordered_before_its_consumers():
+    g, acc, _ = _host_graph("PLLM", 2, [16, 32], by_copy=True)
+    assert any(".push" in op.name for op in g.ops)
+    assert not depcheck.check(g, acc)
 
 
 def test_checker_sees_a_missing_dependency():

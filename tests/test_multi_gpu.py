@@ -35,7 +35,8 @@ def _launch(case, n, port):
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("case,port", [("collectives", 29611), ("fused", 29614), ("engine", 29612), ("timeout", 29613),
                                        ("collectives_nvls", 29615), ("engine_nvls", 29616), ("engine_gate", 29617),
-                                       ("engine_gate_nvls", 29618), ("engine_copy", 29619), ("engine_copy_nvls", 29620)])
+                                       ("engine_gate_nvls", 29618), ("engine_copy", 29619), ("engine_copy_nvls", 29620),
+                                       ("engine_o1", 29630), ("engine_o1_nvls", 29631)])
 def test_two_gpus(case, port):
     print(_launch(case, 2, port))
 
@@ -43,6 +44,7 @@ def test_two_gpus(case, port):
 @pytest.mark.skipif(_ngpu() < 8, reason="needs 8 GPUs")
 @pytest.mark.parametrize("case,port", [("collectives", 29621), ("fused", 29623), ("collectives_wide", 29624),
                                        ("engine", 29625), ("collectives_nvls", 29626), ("engine_nvls", 29627),
-                                       ("engine_gate_nvls", 29628), ("engine_copy_nvls", 29629)])
+                                       ("engine_gate_nvls", 29628), ("engine_copy_nvls", 29629),
+                                       ("engine_o1", 29632)])
 def test_eight_gpus(case, port):
     print(_launch(case, 8, port))
