@@ -1066,6 +1066,14 @@ int launch(const nfk_gemm_params& g, int bn, int split_k, bool stream_k, cudaStr
   int workers = (g.num_ctas > 0 ? g.num_ctas : sm_count()) / CG;
   if (workers > max_workers) workers = max_workers;
   if (workers < 1) workers = 1;
+  // stream_k 3: one work unit per CTA (or CTA pair), more CTAs than fit at once; the hardware block
+  // scheduler deals the units out as CTAs retire, so an SM that another kernel's CTAs slow down takes
+  // fewer of them instead of holding the launch back (no CTA of this kernel waits for another one)
+  const bool hw_dealt = g.stream_k == 3 && g.gate_flags == nullptr;
+  if (hw_dealt) {
+    workers = units;
+    stream_k = false;
+  }
   SkPlan sk{m_groups * n_blocks, 0, 0, 0};
   if (stream_k && split_k == 1 && EPI != 2 && g.workspace != nullptr) {
     sk = plan_stream_k(m_groups * n_blocks, workers, (g.K + BK - 1) / BK);
@@ -1229,7 +1237,7 @@ Shape choose_shape(const nfk_gemm_params& g, bool swiglu) {
       }
       // the same shape with a stream-K tail: full waves as above, then one round of k ranges whose
       // pieces are written out as fp32 and summed by the last piece of each tile
-      if (sk == 1 && g.stream_k != 2 && g.workspace != nullptr && g.epilogue != NFK_EPI_REDUCE_SCATTER) {
+      if (sk == 1 && g.stream_k < 2 && g.workspace != nullptr && g.epilogue != NFK_EPI_REDUCE_SCATTER) {
         const SkPlan pl = plan_stream_k(tiles, workers, num_kb);
         const long long need = static_cast<long long>(pl.rest) * pl.max_pieces * cg * mt * BM * bn * 4;
         if (pl.q > 0 && need <= g.workspace_bytes) {
@@ -1274,7 +1282,7 @@ int resolve_shape(const nfk_gemm_params& gp, bool swiglu, bool rs, Shape& s) {
     s.stream_k = false;
   }
   if (g->stream_k == 1) s.stream_k = true;
-  if (g->stream_k == 2 || s.split_k != 1 || g->gate_flags != nullptr) s.stream_k = false;
+  if (g->stream_k >= 2 || s.split_k != 1 || g->gate_flags != nullptr) s.stream_k = false;
   if (s.cg == 2 && s.mt != 1) return NF_ERR_UNSUPPORTED;
   if (g->split_k != 0 && g->gate_flags == nullptr) s.split_k = g->split_k;
   if (s.split_k < 1 || s.split_k > 16) return NF_ERR_BAD_ARG;

@@ -46,7 +46,9 @@ typedef struct nfk_gemm_params {
   int rs_epoch;
   int smem_budget_kb;  // 0 = all 227 KB; smaller leaves shared memory for a kernel meant to share the SM
   int cta_group;       // 0 = let the cost model decide; 1 = one CTA per tile; 2 = a CTA pair per 256-row tile
-  int stream_k;        // tail wave cut into k ranges: 0 = cost model (off when the tile shape is pinned), 1 = on, 2 = off
+  int stream_k;        // tail wave cut into k ranges: 0 = cost model (off when the tile shape is pinned), 1 = on, 2 = off,
+                       // 3 = off and one work unit per CTA, dealt out by the hardware block scheduler (for a GEMM
+                       // that shares SMs with another stream's kernel)
   // Optional RMSNorm of the result rows: norm_out[M, N] = RMSNorm(D) * norm_w (what the next layer's
   // first GEMM reads). With split-K the reduce pass produces it from the rows it already holds;
   // otherwise the launcher adds a norm launch after the GEMM. Linear epilogue only.

@@ -1,4 +1,4 @@
-"""Per-kernel micro-benchmarks: ``python -m nanoflow_b200.ops.microbench [gemm|swiglu|smallm|decode|prefill|norm|hostlink|budget|library|all]``
+"""Per-kernel micro-benchmarks: ``python -m nanoflow_b200.ops.microbench [gemm|swiglu|smallm|decode|prefill|norm|hostlink|budget|library|interference|all]``
 (JSON lines; ``... table rows.jsonl`` turns them into a markdown table).
 
 Each case is timed with CUDA events on the launching stream after warm-up, with an L2 flush (a
@@ -259,6 +259,81 @@ def bench_library_attention():
         del pool
 
 
+def bench_interference():
+    """A GEMM beside a collective kernel that moves local data only: the all-reduce + residual + RMSNorm kernel
+    with one rank (every load and store local, 268 MB through HBM per call) on a second stream beside the TP8
+    per-GPU GEMMs of Llama-2-70B at M = 4096, for several CTA counts of the collective; then pinned tile shapes
+    with the tiles dealt statically to persistent CTAs (stream_k = 2) and one work unit per CTA dealt by the
+    hardware block scheduler (stream_k = 3). Separates what sharing SMs with a collective's CTAs costs from
+    what the collective's NVLink traffic costs (which needs the other GPUs: ``parallel/overlap_bench.py``)."""
+    from nanoflow_b200.parallel.collectives import TpCollectives
+    dev = torch.device("cuda", torch.cuda.current_device())
+    coll = TpCollectives(0, 1, dev, heap_bytes=768 << 20)
+    rows, hidden = 4096, 8192
+    buf = coll.alloc((rows, hidden), torch.bfloat16)
+    buf.normal_()
+    hout = coll.alloc((rows, hidden), torch.bfloat16)
+    resid = torch.randn(rows, hidden, device=dev, dtype=torch.bfloat16)
+    xout = torch.empty_like(resid)
+    wn = torch.ones(hidden, device=dev, dtype=torch.bfloat16)
+    ws = torch.zeros(160 << 20, dtype=torch.uint8, device=dev)
+    s_g, s_c = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def timed(fn_g, fn_c=None, reps_c=1, iters=8):
+        ts = []
+        for _ in range(3 + iters):
+            flush_l2()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if fn_c is not None:
+                with torch.cuda.stream(s_c):
+                    c0.record()
+                    for _ in range(reps_c):
+                        fn_c()
+                    c1.record()
+            with torch.cuda.stream(s_g):
+                e0.record()
+                fn_g()
+                e1.record()
+            torch.cuda.synchronize()
+            ts.append((e0.elapsed_time(e1) * 1e3, c0.elapsed_time(c1) * 1e3 if fn_c is not None else 0.0))
+        ts = sorted(ts[3:])
+        return ts[len(ts) // 2]
+
+    def collective(ctas):
+        return lambda: coll.all_reduce_(buf, norm_w=wn, norm_out=hout, num_ctas=ctas, resid=resid, sum_out=xout,
+                                        push_sum=False)
+
+    for name, M, N, K in [("qkv", 4096, 1280, 8192), ("o", 4096, 8192, 1024), ("down", 4096, 8192, 3584)]:
+        a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        g = lambda: ops.gemm(a, w, out=out, workspace=ws, smem_budget_kb=200)
+        alone = timed(g)[0]
+        for ctas in (16, 32, 96, 148):
+            ar_alone = timed(collective(ctas))[0]
+            both = timed(g, collective(ctas), reps_c=2)     # two calls, so that the collective outlasts the GEMM
+            print(json.dumps(dict(op="gemm_beside_local_collective", gemm=name, gemm_alone_us=round(alone, 1),
+                                  ar_ctas=ctas, ar_alone_us=round(ar_alone, 1), gemm_beside_us=round(both[0], 1),
+                                  two_ars_beside_us=round(both[1], 1))), flush=True)
+        for tn, cg, sk in [(256, 2, 0), (128, 2, 0), (256, 1, 0), (128, 1, 0), (256, 2, 2), (128, 2, 2)]:
+            try:
+                for mode in (2, 3):
+                    gg = lambda: ops.gemm(a, w, out=out, workspace=ws, smem_budget_kb=200, tile_n=tn, cta_group=cg,
+                                          split_k=sk, stream_k=mode)
+                    al = timed(gg)[0]
+                    both = timed(gg, collective(32), reps_c=2)
+                    print(json.dumps(dict(op="gemm_tile_deal", gemm=name, tile_n=tn, cta_group=cg, split_k=sk,
+                                          stream_k=mode, alone_us=round(al, 1), beside_us=round(both[0], 1),
+                                          two_ars_us=round(both[1], 1))), flush=True)
+            except RuntimeError as e:       # e.g. split-K partial sums larger than the workspace
+                print(json.dumps(dict(op="gemm_tile_deal", gemm=name, tile_n=tn, cta_group=cg, split_k=sk,
+                                      error=str(e)[:100])), flush=True)
+    coll.check_status()
+    coll.close()
+
+
 def bench_budget():
     """Decode attention against its CTA budget, alone and beside back-to-back GEMMs on a second stream:
     the table an SM-budget search needs (the reference sweeps ``sm_blk`` the same way,
@@ -517,6 +592,8 @@ def main(argv):
         bench_budget()
     if what == "library":
         bench_library_attention()
+    if what == "interference":
+        bench_interference()
     if what in ("norm", "all"):
         bench_norm()
     if what in ("hostlink", "all"):

@@ -57,9 +57,11 @@ class TpCollectives(CollectiveHooks):
             raise ValueError("at most 8 ranks (one NVSwitch domain)")
         self.rank, self.tp, self.device = rank, world, device
         self.heap = SymmetricHeap(rank, world, device, heap_bytes, backend=backend)
-        # all-reduces go through the NVSwitch (multimem) whenever the heap has a multicast mapping
-        # (from four ranks on: with two, half of a row's partial sums are local and the peer-load form is as fast)
-        self.use_multimem = self.heap.mc_base != 0 and world >= 4
+        # all-reduces go through the NVSwitch (multimem) when the heap has a multicast mapping and there are
+        # eight ranks: that is where it was timed (168 against 210-228 us alone). With two ranks half of a
+        # row's partial sums are local and the peer-load form is as fast; four ranks keep the peer-load form,
+        # which is the one that has run there (set use_multimem to try the other).
+        self.use_multimem = self.heap.mc_base != 0 and world >= 8
         self.last_gate = None
         self.num_ctas = num_ctas or _ops.sm_count(device)
         self.fuse_norm = fuse_norm

@@ -188,9 +188,18 @@ def main(argv=None) -> int:
     if log is not None:
         log.info("done: %d cycles, %d requests retired, %.1f tokens/s, %.2f ms per cycle", st.cycles, summary.retired,
                  summary.token_per_second, summary.cycle_time * 1e3)
+    if offload is not None:
+        off_line = (f"KV offload: {offload.total_requests} requests, {offload.total_pages} pages, "
+                    f"{offload.total_bytes / 1e6:.1f} MB per GPU to pinned host memory "
+                    f"({offload.total_bytes / 1e6 / max(wall, 1e-9):.1f} MB/s per GPU), "
+                    f"{offload.dropped_requests} requests beyond the per-iteration staging")
+        if log is not None:
+            log.info(off_line)
     if rank == 0:
         print(f"cycles {st.cycles}  retired {summary.retired}  tokens/s {summary.token_per_second:.1f} "
               f"(per GPU {summary.token_per_second_per_gpu:.1f})  cycle {summary.cycle_time * 1e3:.2f} ms")
+        if offload is not None:
+            print(off_line)
         if args.output_prefix:
             os.makedirs(os.path.dirname(os.path.abspath(args.output_prefix)) or ".", exist_ok=True)
             write_outputs(args.output_prefix, summary, st.retired, sch.schedule_log, output_idx=args.output_idx,

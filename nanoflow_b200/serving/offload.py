@@ -38,6 +38,11 @@ class KVOffloadManager:
         self.max_host_bytes = max_host_bytes
         self.store: Dict[int, StoredKV] = {}
         self.bytes = 0
+        # totals since start (what left the GPU, whether or not the host store still keeps it)
+        self.total_requests = 0
+        self.total_pages = 0
+        self.total_bytes = 0
+        self.dropped_requests = 0               # retired beyond the per-iteration staging capacity
         self._pending: Dict[int, List] = {}     # iteration -> [(req, n_pages)] in page order
 
     # ---- hooks called by the serving loop --------------------------------------------------------
@@ -49,6 +54,7 @@ class KVOffloadManager:
         for req in plan.retired_reqs:
             n = req.kv_cache.num_pages
             if used + n > cap:
+                self.dropped_requests += len(plan.retired_reqs) - len(lst)
                 break                              # beyond the per-iteration staging: dropped, not offloaded
             lst.append((req, used, n, req.kv_cache.seqlen))
             used += n
@@ -66,6 +72,9 @@ class KVOffloadManager:
                     self.bytes -= old.data.numel() * old.data.element_size()
                 self.store[req.req_idx] = StoredKV(req.req_idx, seqlen, data)
                 self.bytes += nbytes
+                self.total_requests += 1
+                self.total_pages += n
+                self.total_bytes += nbytes
                 req.offloaded = True
         scheduler.release_held_pages(plan.iteration)
 

@@ -148,6 +148,36 @@ def test_gemm_cta_pair(M, N, K, tile_n, split_k, num_ctas):
     _close(out, ref.gemm(a, w, res, 0.5, bias), atol=3e-2 * math.sqrt(K / 64), rtol=2e-2)
 
 
+@pytest.mark.parametrize("M,N,K", [(4096, 1280, 1024), (1000, 1000, 512), (3712, 8192, 256), (130, 40, 64)])
+@pytest.mark.parametrize("tile_m,tile_n,cta_group,split_k", [(0, 0, 0, 0), (1, 256, 2, 1), (1, 128, 2, 2), (1, 128, 1, 1),
+                                                             (2, 96, 1, 3)])
+def test_gemm_work_units_dealt_by_the_block_scheduler(M, N, K, tile_m, tile_n, cta_group, split_k):
+    """stream_k = 3: one work unit per CTA (or CTA pair) and more CTAs than fit on the GPU at once; the result is
+    that of the persistent launch."""
+    if split_k > 1 and K // 64 < split_k:
+        pytest.skip("fewer k-blocks than splits")
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    ws = torch.zeros(max(64 << 20, max(split_k, 1) * M * N), device="cuda", dtype=torch.float32)
+    st = ops.new_status()
+    kw = dict(residual=res, beta=0.5, bias=bias, tile_m=tile_m, tile_n=tile_n, split_k=split_k, workspace=ws,
+              cta_group=cta_group, status=st)
+    out = ops.gemm(a, w, stream_k=3, **kw)
+    ops.check_status(st, "gemm")
+    _close(out, ref.gemm(a, w, res, 0.5, bias), atol=3e-2 * math.sqrt(K / 64), rtol=2e-2)
+    assert torch.equal(out, ops.gemm(a, w, stream_k=2, **kw))
+    f = 1792
+    wg = torch.randn(f, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    wu = torch.randn(f, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    if split_k <= 1:
+        act = ops.gemm_swiglu(a, wg, wu, tile_m=tile_m, tile_n=tile_n, cta_group=cta_group, stream_k=3, workspace=ws, status=st)
+        ops.check_status(st, "gemm_swiglu")
+        assert torch.equal(act, ops.gemm_swiglu(a, wg, wu, tile_m=tile_m, tile_n=tile_n, cta_group=cta_group, stream_k=2,
+                                                workspace=ws, status=st))
+
+
 @pytest.mark.parametrize("M,F,K", [(256, 128, 64), (300, 3584, 1024), (1408, 1792, 2048), (129, 264, 136)])
 @pytest.mark.parametrize("tile_n", [128, 192, 224, 256])
 def test_gemm_swiglu_cta_pair(M, F, K, tile_n):
