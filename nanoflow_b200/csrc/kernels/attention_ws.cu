@@ -10,12 +10,18 @@
 //   warp 5, one thread   tcgen05.mma: S(t+1) = Q K(t+1)^T is issued before P(t) is waited for, into the
 //                        other of two S accumulators in TMEM, so the tensor cores work on the next tile's
 //                        scores while the softmax warps are still busy with this tile; then
-//                        O += P(t) V(t), with V read token-major (MN-major B operand: no transpose pass)
+//                        O += P(t) V(t) with P read from TMEM (A operand in tensor memory) and V read
+//                        token-major from shared memory (MN-major B operand: no transpose pass)
 //   warps 0-3            softmax: one thread per query row reads its 64 scores from TMEM, keeps the
-//                        running maximum and sum, writes P (bf16) to shared memory as the next A operand
+//                        running maximum and sum, and writes P (bf16, two per column) back over the first 32
+//                        columns of the S accumulator it came from: P never passes through shared memory
+//
+// S(t+2) goes into the accumulator that held S(t) / P(t), so the MMA thread issues it only once
+// O += P(t) V(t) has completed (products into different accumulators are not ordered against each other's
+// operand reads); S(t+2) is needed a whole softmax pass later, so that wait is off the critical path.
 //
 // O stays in TMEM for the whole item: P is taken relative to a reference maximum that only moves (and O
-// is rescaled in TMEM) when a row's maximum outgrows it by more than 2^8. Two CTAs fit an SM (113 KB of
+// is rescaled in TMEM) when a row's maximum outgrows it by more than 2^8. Two CTAs fit an SM (97 KB of
 // shared memory, 256 TMEM columns each). Every wait is bounded; a wait that runs out sets the status
 // word and all roles leave through the common exit, which frees TMEM.
 //
@@ -38,15 +44,14 @@ constexpr float kRescaleGap = 8.0f;   // log2 of how far a row maximum may outgr
 constexpr int Q_OFF = 0;                       // 2 halves x [128 rows][64 hd]                 32 KB
 constexpr int K_OFF = 32768;                   // 2 stages x 2 halves x [64 tok][64 hd]        32 KB
 constexpr int V_OFF = K_OFF + 32768;           // 2 stages x 2 halves x [64 tok][64 hd]        32 KB
-constexpr int P_OFF = V_OFF + 32768;           // [128 rows][64 tok]                           16 KB
-constexpr int BAR_OFF = P_OFF + 16384;
+constexpr int BAR_OFF = V_OFF + 32768;
 constexpr int kSmemBytes = BAR_OFF + 256;
 constexpr int kStageBytes = 16384;             // one K (or V) tile
 constexpr int kHalfBytes = 8192;               // [64 tok][64 hd]
 
 enum Bar : int {
   Q_FULL = 0, Q_EMPTY, K_FULL0, K_FULL1, K_EMPTY0, K_EMPTY1, V_FULL0, V_FULL1, V_EMPTY0, V_EMPTY1,
-  S_FULL0, S_FULL1, S_EMPTY0, S_EMPTY1, P_FULL, PV_DONE, O_FREE, NUM_BARS
+  S_FULL0, S_FULL1, P_FULL0, P_FULL1, PV_DONE0, PV_DONE1, O_FREE, NUM_BARS
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -56,9 +61,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-__device__ __forceinline__ uint32_t sw128(int row, int chunk) {
-  return static_cast<uint32_t>(row * 128 + ((chunk ^ (row & 7)) << 4));
 }
 // Shared-memory descriptor of an MN-major operand in the 128-byte swizzle: 64 elements along M/N are
 // contiguous (one 128-byte row per k index), `lbo` bytes lead to the next 64 elements along M/N, `sbo`
@@ -113,7 +115,7 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 
   if (threadIdx.x == 0) {
     for (int b = 0; b < NUM_BARS; ++b) {
-      const bool warps4 = b == S_EMPTY0 || b == S_EMPTY1 || b == P_FULL || b == O_FREE;
+      const bool warps4 = b == P_FULL0 || b == P_FULL1 || b == O_FREE;
       mbar_init(&bars[b], warps4 ? 4 : 1);
     }
     *abort_flag = 0;
@@ -123,7 +125,7 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   }
   // Q rows past an item's last token are never loaded; start them (and everything else) from zero so
   // that what the tensor cores read there is always finite
-  for (int i = threadIdx.x; i < P_OFF / 16 + 1024; i += kThreads) st_shared_v4(sb + i * 16, 0u, 0u, 0u, 0u);
+  for (int i = threadIdx.x; i < BAR_OFF / 16; i += kThreads) st_shared_v4(sb + i * 16, 0u, 0u, 0u, 0u);
   fence_proxy_async_smem();
   if (warp == 5) {
     tmem_alloc(tmem_slot, 256);   // S0: columns [0,64), S1: [64,128), O: [128,256)
@@ -215,10 +217,14 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       const uint32_t idesc_s = umma_idesc_bf16(128, kTile);
       const uint32_t idesc_o = umma_idesc_bf16(128, HD) | kIdescBMnMajor;
       uint32_t g = 0, n_item = 0;
-      auto issue_s = [&](uint32_t gt) -> bool {
+      // `pv_issued`: PV products issued so far by this CTA. The S accumulator that S(gt) goes into held P(gt-2),
+      // the A operand of PV(gt-2); products with different accumulators are not ordered against each other's
+      // operand reads, so the latest PV issued (gt-2 inside an item, gt-1 at its start) must have completed.
+      auto issue_s = [&](uint32_t gt, uint32_t pv_issued) -> bool {
         const int s = gt & 1;
         const uint32_t ph = (gt >> 1) & 1;
-        if (!mbar_wait(&bars[K_FULL0 + s], ph) || !mbar_wait(&bars[S_EMPTY0 + s], ph ^ 1)) return false;
+        if (pv_issued > 0 && !mbar_wait(&bars[PV_DONE0 + ((pv_issued - 1) & 1)], ((pv_issued - 1) >> 1) & 1)) return false;
+        if (!mbar_wait(&bars[K_FULL0 + s], ph)) return false;
         tc_fence_after();
         const uint32_t kb = sb + K_OFF + s * kStageBytes;
 #pragma unroll
@@ -236,18 +242,18 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const Item it = read_item(p, w);
         if (!it.valid) continue;
         if (!mbar_wait(&bars[Q_FULL], n_item & 1) || *abort_flag) { fail(NF_ST_TIMEOUT_SMEM_FULL); break; }
-        if (!issue_s(g)) { fail(NF_ST_TIMEOUT_SMEM_FULL); break; }
+        if (!issue_s(g, g)) { fail(NF_ST_TIMEOUT_SMEM_FULL); break; }
         for (int t = 0; t < it.n_tiles; ++t) {
           const uint32_t gt = g + t;
           if (t + 1 < it.n_tiles) {
-            if (!issue_s(gt + 1)) { fail(NF_ST_TIMEOUT_SMEM_FULL); ok = false; break; }
+            if (!issue_s(gt + 1, gt)) { fail(NF_ST_TIMEOUT_SMEM_FULL); ok = false; break; }
           } else {
             umma_commit(&bars[Q_EMPTY]);     // the last S product of the item has been issued
           }
           // the previous item's O must have been read out before this item's first PV overwrites it
           if (t == 0 && !mbar_wait(&bars[O_FREE], (n_item & 1) ^ 1)) { fail(NF_ST_TIMEOUT_TMEM_EMPTY); ok = false; break; }
           const int s = gt & 1;
-          if (!mbar_wait(&bars[P_FULL], gt & 1) || !mbar_wait(&bars[V_FULL0 + s], (gt >> 1) & 1) || *abort_flag) {
+          if (!mbar_wait(&bars[P_FULL0 + s], (gt >> 1) & 1) || !mbar_wait(&bars[V_FULL0 + s], (gt >> 1) & 1) || *abort_flag) {
             fail(NF_ST_TIMEOUT_SMEM_FULL);
             ok = false;
             break;
@@ -256,10 +262,10 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           const uint32_t vb = sb + V_OFF + s * kStageBytes;
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_bf16_ss(tmem + 2 * kTile, umma_desc_k_sw128(sb + P_OFF + k * 32),
+            umma_bf16_ts(tmem + 2 * kTile, tmem + s * kTile + k * 8,      // P(t): 16 tokens = 8 columns per step
                          umma_desc_mn_sw128(vb + k * 2048, kHalfBytes, 1024), idesc_o, (t | k) ? 1u : 0u);
           umma_commit(&bars[V_EMPTY0 + s]);
-          umma_commit(&bars[PV_DONE]);
+          umma_commit(&bars[PV_DONE0 + s]);
         }
         g += it.n_tiles;
         ++n_item;
@@ -289,9 +295,6 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         tmem_ld_32x32b_x32(t_lane + s * kTile, r0);
         tmem_ld_32x32b_x32(t_lane + s * kTile + 32, r1);
         tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[S_EMPTY0 + s]);     // the MMA warp may write this S buffer again
         const int cbase = t * kTile;
         if (cbase + kTile - 1 > pos) {                        // only tiles on the diagonal need the mask
 #pragma unroll
@@ -305,13 +308,17 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         for (int j = 0; j < 32; ++j) mxp = fmaxf(mxp, fmaxf(__uint_as_float(r0[j]), __uint_as_float(r1[j])));
         const float mx = mxp * scale;
         const bool grow = mx > m_ref + kRescaleGap || (m_ref == -INFINITY && mx > -INFINITY);
-        // P(t) overwrites the buffer PV(t-1) reads, and O may only be touched between two PV products
-        if (!mbar_wait(&bars[PV_DONE], (gt & 1) ^ 1) || *abort_flag) { fail(NF_ST_TIMEOUT_TMEM_FULL); ok = false; break; }
         if (t == 0) {
           m_ref = mx;
         } else if (__any_sync(0xffffffffu, grow)) {
           // bring O (in TMEM) and the row sum to the new reference maximum; warp-wide because the TMEM
-          // accesses are, rows that did not grow scale by one
+          // accesses are, rows that did not grow scale by one. O may only be touched between two PV
+          // products: PV(t-1) is the last one issued (PV(t) needs this tile's P), so once it is done O is still
+          if (!mbar_wait(&bars[PV_DONE0 + ((gt - 1) & 1)], ((gt - 1) >> 1) & 1) || *abort_flag) {
+            fail(NF_ST_TIMEOUT_TMEM_FULL);
+            ok = false;
+            break;
+          }
           tc_fence_after();
           const float alpha = grow ? (m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - mx)) : 1.f;
 #pragma unroll 1
@@ -329,31 +336,32 @@ attn_prefill_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
         const float ms = m_ref == -INFINITY ? 0.f : m_ref;
         float rs = 0.f;
-        const uint32_t prow = sb + P_OFF;
+        uint32_t pk[32];                                      // column j: tokens 2j, 2j + 1 of the tile
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint32_t w0[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const uint32_t a = c < 4 ? r0[c * 8 + 2 * e] : r1[(c - 4) * 8 + 2 * e];
-            const uint32_t b = c < 4 ? r0[c * 8 + 2 * e + 1] : r1[(c - 4) * 8 + 2 * e + 1];
-            const float x0 = fast_exp2(fmaf(__uint_as_float(a), scale, -ms));
-            const float x1 = fast_exp2(fmaf(__uint_as_float(b), scale, -ms));
-            rs += x0 + x1;
-            w0[e] = pack_bf16x2(x0, x1);
-          }
-          st_shared_v4(prow + sw128(row, c), w0[0], w0[1], w0[2], w0[3]);     // tokens 8c .. 8c+7 of the tile
+        for (int j = 0; j < 16; ++j) {
+          const float x0 = fast_exp2(fmaf(__uint_as_float(r0[2 * j]), scale, -ms));
+          const float x1 = fast_exp2(fmaf(__uint_as_float(r0[2 * j + 1]), scale, -ms));
+          const float y0 = fast_exp2(fmaf(__uint_as_float(r1[2 * j]), scale, -ms));
+          const float y1 = fast_exp2(fmaf(__uint_as_float(r1[2 * j + 1]), scale, -ms));
+          rs += (x0 + x1) + (y0 + y1);
+          pk[j] = pack_bf16x2(x0, x1);
+          pk[16 + j] = pack_bf16x2(y0, y1);
         }
         l += rs;
+        // P(t) goes over the first half of the S accumulator it was computed from (all 64 scores are in
+        // registers); the other accumulator holds P(t-1) / S(t+1), so nothing has to be waited for
+        tmem_st_32x32b_x32(t_lane + s * kTile, pk);
+        tmem_st_wait();
         tc_fence_before();
-        fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[P_FULL]);
+        if (lane == 0) mbar_arrive(&bars[P_FULL0 + s]);
       }
       if (!ok) break;
       g += it.n_tiles;
       // ---- the item's last PV product, then O / l to global memory ----
-      if (!mbar_wait(&bars[PV_DONE], (g & 1) ^ 1) || *abort_flag) { fail(NF_ST_TIMEOUT_TMEM_FULL); break; }
+      // (one barrier per S accumulator: the softmax warps do not wait for every product, and up to two can be
+      // outstanding here, which a single barrier's phase bit could not tell apart)
+      if (!mbar_wait(&bars[PV_DONE0 + ((g - 1) & 1)], ((g - 1) >> 1) & 1) || *abort_flag) { fail(NF_ST_TIMEOUT_TMEM_FULL); break; }
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* dst = outp + (static_cast<long long>(it.tok0 + tl) * p.q_heads + it.kvh * group + hh) * HD;

@@ -160,7 +160,7 @@ def build_graph(model: ModelConfig, eng: EngineConfig, w: RankWeights, bufs: Buf
     prefill_stream = "attn2" if eng.prefill_beside_decode else S("attn")
     if overlap and tp > 1 and eng.attn_overlap and eng.cross_layer_pipeline:
         # Skewed schedule (below): only the decode kernel is small enough to sit on an SM beside a GEMM CTA;
-        # a prefill CTA (98-113 KB) would have to wait for a GEMM CTA to leave and then hold the next
+        # a prefill CTA (97 KB) would have to wait for a GEMM CTA to leave and then hold the next
         # GEMM's CTA off that SM, so prefill attention stays in line on the compute stream.
         prefill_stream = "gemm"
     # Collectives of one nano-batch never depend on those of another, and each is bound by the latency of
