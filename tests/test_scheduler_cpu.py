@@ -268,3 +268,41 @@ def test_online_release_is_identical_on_ranks_with_skewed_clocks():
     assert results[0] == results[1]
     assert sum(1 for x in results[0] if x is not None) > 10       # the trace was actually served
     assert store.num_keys() < cycles                               # keys that both ranks are past get deleted
+
+
+def test_offload_manager_files_retired_requests_and_counts_what_left_the_gpu():
+    """KVOffloadManager with a stand-in engine: requests retired in an iteration ride on its offload in page
+    order, what does not fit the per-iteration staging is dropped (and counted), the host store evicts beyond
+    its byte limit while the totals keep counting, and held pages are released once the copy has completed."""
+    from types import SimpleNamespace
+    import torch
+    from nanoflow_b200.serving.offload import KVOffloadManager
+
+    layers, cap, page_elems = 2, 8, 16
+    host = torch.arange(layers * cap * page_elems, dtype=torch.float32).view(layers, cap, page_elems)
+    engine = SimpleNamespace(offload_cap=cap, offloaded_pages=lambda: host)
+    released = []
+    sched = SimpleNamespace(release_held_pages=lambda it: released.append(it))
+    page_bytes = layers * page_elems * 4
+    mgr = KVOffloadManager(engine, max_host_bytes=5 * page_bytes)
+
+    def req(idx, pages, seqlen):
+        return SimpleNamespace(req_idx=idx, kv_cache=SimpleNamespace(num_pages=pages, seqlen=seqlen), offloaded=False)
+
+    a, b, c = req(1, 3, 40), req(2, 4, 60), req(3, 2, 20)          # 3 + 4 fit the 8 staging pages, the third does not
+    plan = SimpleNamespace(iteration=7, retired_reqs=[a, b, c])
+    mgr.on_iteration(plan)
+    mgr.on_complete(plan, sched)
+    assert released == [7]
+    assert a.offloaded and b.offloaded and not c.offloaded
+    assert (mgr.total_requests, mgr.total_pages, mgr.dropped_requests) == (2, 7, 1)
+    assert mgr.total_bytes == 7 * page_bytes
+    # request 2's pages are the four staged behind request 1's three
+    assert torch.equal(mgr.store[2].data, host[:, 3:7]) and mgr.store[2].seqlen == 60
+    # the store holds at most five pages' worth: filing request 2 (4 pages) evicted request 1 (3 pages)
+    assert 1 not in mgr.store and mgr.bytes == 4 * page_bytes
+    # an iteration without retired requests still releases what it held
+    empty = SimpleNamespace(iteration=8, retired_reqs=[])
+    mgr.on_iteration(empty)
+    mgr.on_complete(empty, sched)
+    assert released == [7, 8] and mgr.total_requests == 2
