@@ -278,7 +278,11 @@ struct Walk {
 // each stages its own 128 rows of A and BN/2 of the weight rows, the even CTA issues
 // tcgen05.mma.cta_group::2 for both, and each CTA drains its own 128 accumulator rows. Per SM that
 // halves the weight bytes entering shared memory for the same tensor work.
-template <int MT, int EPI, int CG>
+// WIDE (CTA pairs, plain epilogue): a tile of more than 256 columns, computed as two pair MMAs of BN / 2 columns
+// per k step into one accumulator of BN columns. A pair MMA takes half of its weight rows from each CTA, so
+// each CTA stages quarter `rank` of both halves, one behind the other, and the accumulator columns come out in
+// the order of the weight rows. A separate instantiation: the common kernel's instruction stream is untouched.
+template <int MT, int EPI, int CG, bool WIDE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                     const __grid_constant__ CUtensorMap tmB1, DevParams p) {
@@ -298,6 +302,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int lane = threadIdx.x & 31;
 
   static_assert(CG == 1 || MT == 1, "CTA pairs cover one M tile per CTA");
+  static_assert(!WIDE || (CG == 2 && EPI == 0), "wide tiles: CTA pairs, plain epilogue");
   const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;   // position in the CTA pair
   const bool leader = rank == 0;
   const int BN = p.bn;                    // tile width = N of one MMA instruction
@@ -397,7 +402,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if (leader) mbar_expect_tx(&full_bar[s], 2 * (A_TILE_BYTES + B_BYTES));
           if (EPI == 1)
             tma_load_2d_pair(sb, rank == 0 ? &tmB0 : &tmB1, fb, kb * BK, n_blk * OUT_BN);
-          else
+          else if (WIDE) {
+            const int qrows = BN / 4;
+            tma_load_2d_pair(sb, &tmB0, fb, kb * BK, n_blk * BN + static_cast<int>(rank) * qrows);
+            tma_load_2d_pair(sb + qrows * (BK * 2), &tmB0, fb, kb * BK,
+                             n_blk * BN + BN / 2 + static_cast<int>(rank) * qrows);
+          } else
             tma_load_2d_pair(sb, &tmB0, fb, kb * BK, n_blk * BN + static_cast<int>(rank) * (BN / 2));
           tma_load_2d_pair(sa, &tmA, fb, kb * BK, (m_grp * 2 + static_cast<int>(rank)) * BM);
           continue;
@@ -444,7 +454,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else if (warp == 1 && lane == 0 && leader) {
     // ---------------- MMA issuer (the even CTA of a pair issues for both) ----------------
-    const uint32_t idesc = umma_idesc_bf16(BM * CG, BN);
+    const uint32_t idesc = umma_idesc_bf16(BM * CG, WIDE ? BN / 2 : BN);
     uint32_t tcount = 0, ph = 0;
     int s = 0;
     bool ok = true;
@@ -482,6 +492,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               const uint64_t db = umma_desc_k_sw128(b_addr + k * UMMA_K * 2);
               if (CG == 2) umma_bf16_ss_pair(d_tmem, da, db, idesc, (kb != sg.kb0 || k != 0) ? 1u : 0u);
               else umma_bf16_ss(d_tmem + mt * BN, da, db, idesc, (kb != sg.kb0 || k != 0) ? 1u : 0u);
+              if (WIDE)   // second half of the tile: the weight rows staged behind the first quarter
+                umma_bf16_ss_pair(d_tmem + BN / 2, da,
+                                  umma_desc_k_sw128(b_addr + (BN / 4) * (BK * 2) + k * UMMA_K * 2), idesc,
+                                  (kb != sg.kb0 || k != 0) ? 1u : 0u);
             }
           }
         }
@@ -1002,8 +1016,8 @@ inline SkPlan plan_stream_k(int tiles, int workers, int num_kb) {
   return pl;
 }
 
-template <int MT, int EPI, int CG>
-int launch(const nfk_gemm_params& g, int bn, int split_k, bool stream_k, cudaStream_t stream) {
+template <int MT, int EPI, int CG, bool WIDE>
+int launch_impl(const nfk_gemm_params& g, int bn, int split_k, bool stream_k, cudaStream_t stream) {
   int budget = g.smem_budget_kb > 0 ? g.smem_budget_kb * 1024 : kSmemMax;
   if (budget > kSmemMax) budget = kSmemMax;
   const bool rs_staged = EPI == 2 && g.rs_staged != 0;
@@ -1013,7 +1027,8 @@ int launch(const nfk_gemm_params& g, int bn, int split_k, bool stream_k, cudaStr
   int rc = make_tmap_bf16_2d(&tmA, g.A, g.M, g.K, g.lda, BM, BK);
   if (rc != NF_OK) return rc;
   // rows of B that one TMA copy brings in: a whole tile, a SwiGLU half, or a CTA pair's half
-  const int b_box = (EPI == 1) ? geo.out_bn : bn / CG;
+  // (wide tiles: a quarter of the tile per copy, two copies per CTA)
+  const int b_box = (EPI == 1) ? geo.out_bn : (WIDE ? bn / 4 : bn / CG);
   rc = make_tmap_bf16_2d(&tmB0, g.B, g.N, g.K, g.ldb, b_box, BK);
   if (rc != NF_OK) return rc;
   if (EPI == 1) {
@@ -1028,12 +1043,12 @@ int launch(const nfk_gemm_params& g, int bn, int split_k, bool stream_k, cudaStr
   bool& attr_set = attr_set_dev[device_slot()];
   int& max_workers = max_workers_dev[device_slot()];
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<MT, EPI, CG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<MT, EPI, CG, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kSmemMax) != cudaSuccess)
       return NF_ERR_CUDA;
     // Always the largest shared-memory split: with a reduced budget (smem_budget_kb) the SM then
     // keeps room for the CTAs of a kernel that runs beside this one, whichever of the two came first.
-    (void)cudaFuncSetAttribute(gemm_tcgen05_kernel<MT, EPI, CG>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    (void)cudaFuncSetAttribute(gemm_tcgen05_kernel<MT, EPI, CG, WIDE>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                cudaSharedmemCarveoutMaxShared);
     (void)cudaGetLastError();
     max_workers = sm_count() / CG;
@@ -1051,7 +1066,7 @@ int launch(const nfk_gemm_params& g, int bn, int split_k, bool stream_k, cudaStr
       qc.attrs = qa;
       qc.numAttrs = 1;
       int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_kernel<MT, EPI, CG>, &qc) == cudaSuccess && n > 0 &&
+      if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_kernel<MT, EPI, CG, WIDE>, &qc) == cudaSuccess && n > 0 &&
           n < max_workers)
         max_workers = n;
       else
@@ -1128,12 +1143,12 @@ int launch(const nfk_gemm_params& g, int bn, int split_k, bool stream_k, cudaStr
     la[0].val.clusterDim.z = 1;
     lc.attrs = la;
     lc.numAttrs = 1;
-    if (cudaLaunchKernelEx(&lc, gemm_tcgen05_kernel<MT, EPI, CG>, tmA, tmB0, tmB1, p) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&lc, gemm_tcgen05_kernel<MT, EPI, CG, WIDE>, tmA, tmB0, tmB1, p) != cudaSuccess) {
       (void)cudaGetLastError();
       return NF_ERR_CUDA;
     }
   } else {
-    gemm_tcgen05_kernel<MT, EPI, CG><<<ctas, kGemmThreads, geo.smem_bytes, stream>>>(tmA, tmB0, tmB1, p);
+    gemm_tcgen05_kernel<MT, EPI, CG, WIDE><<<ctas, kGemmThreads, geo.smem_bytes, stream>>>(tmA, tmB0, tmB1, p);
     if (cudaGetLastError() != cudaSuccess) return NF_ERR_CUDA;
   }
   if (sk.q > 0 && EPI != 2) {
@@ -1167,6 +1182,15 @@ int launch(const nfk_gemm_params& g, int bn, int split_k, bool stream_k, cudaStr
     return nfk_rmsnorm(g.norm_out, g.D, g.norm_w, g.M, g.N, g.norm_eps, stream);
   }
   return NF_OK;
+}
+
+template <int MT, int EPI, int CG>
+int launch(const nfk_gemm_params& g, int bn, int split_k, bool stream_k, cudaStream_t stream) {
+  if constexpr (CG == 2 && EPI == 0 && MT == 1) {
+    if (bn > 256) return launch_impl<MT, EPI, CG, true>(g, bn, split_k, stream_k, stream);
+  }
+  if (bn > 256) return NF_ERR_UNSUPPORTED;
+  return launch_impl<MT, EPI, CG, false>(g, bn, split_k, stream_k, stream);
 }
 
 template <int EPI>
@@ -1291,7 +1315,9 @@ int resolve_shape(const nfk_gemm_params& gp, bool swiglu, bool rs, Shape& s) {
         static_cast<long long>(s.split_k) * g->M * g->N * 4 > g->workspace_bytes)
       return NF_ERR_BAD_ARG;
   }
-  if (s.bn < 32 || s.bn > 256 || s.bn % 32 != 0 || (s.mt != 1 && s.mt != 2 && s.mt != 4) || s.mt * s.bn > 512)
+  // Wider than one MMA instruction (256 columns): CTA pairs, one M tile, plain epilogue (the WIDE kernel).
+  const bool wide_ok = s.bn > 256 && s.bn <= 512 && s.bn % 64 == 0 && s.cg == 2 && s.mt == 1 && !swiglu && !rs;
+  if (s.bn < 32 || (s.bn > 256 && !wide_ok) || s.bn % 32 != 0 || (s.mt != 1 && s.mt != 2 && s.mt != 4) || s.mt * s.bn > 512)
     return NF_ERR_UNSUPPORTED;
   if (swiglu && (s.bn / 2) % 16 != 0) return NF_ERR_UNSUPPORTED;
   return NF_OK;

@@ -44,6 +44,13 @@ def candidates(M: int, N: int, K: int, swiglu: bool) -> List[Dict[str, int]]:
             add(1, tn, 1, 1, tail)
             if m_tiles >= 2:
                 add(1, tn, 2, 1, tail)
+    if not swiglu and m_tiles >= 2:
+        # pair tiles wider than one MMA instruction: fewer, fatter tiles (a wave of 64 tiles of 256 x 320 where
+        # 256-wide ones make 80 on 74 pairs), each weight byte fetched for 256 rows and each activation byte
+        # for 320 or more columns
+        for tn in (320, 384, 512):
+            if N >= tn:
+                add(1, tn, 2, 1, 2)
     if m_tiles <= 4:
         for tm, tn in ((2, 256), (2, 224), (2, 128), (4, 128)):
             if m_tiles > tm // 2:

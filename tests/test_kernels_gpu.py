@@ -178,6 +178,40 @@ def test_gemm_work_units_dealt_by_the_block_scheduler(M, N, K, tile_m, tile_n, c
                                                 workspace=ws, status=st))
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 320, 64), (4096, 1280, 512), (1000, 1000, 1024), (300, 2048, 192), (130, 40, 64),
+                                   (3712, 1280, 256)])
+@pytest.mark.parametrize("tile_n,split_k,num_ctas", [(320, 1, 0), (384, 1, 0), (448, 2, 0), (512, 1, 0), (320, 1, 6)])
+def test_gemm_cta_pair_tiles_wider_than_one_mma(M, N, K, tile_n, split_k, num_ctas):
+    """CTA pairs on 256 x tile_n tiles with tile_n > 256: two pair MMAs of tile_n / 2 columns per k step into one
+    accumulator, each CTA staging a quarter of the tile's weight rows per MMA (ragged edges, a tile that is mostly
+    past the last column, split-K, a restricted CTA budget)."""
+    if split_k > 1 and K // 64 < split_k:
+        pytest.skip("fewer k-blocks than splits")
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    ws = torch.zeros(max(64 << 20, split_k * M * N), device="cuda", dtype=torch.float32)
+    st = ops.new_status()
+    out = ops.gemm(a, w, residual=res, beta=0.5, bias=bias, tile_m=1, tile_n=tile_n, split_k=split_k,
+                   workspace=ws, num_ctas=num_ctas, cta_group=2, status=st)
+    ops.check_status(st, "gemm")
+    _close(out, ref.gemm(a, w, res, 0.5, bias), atol=3e-2 * math.sqrt(K / 64), rtol=2e-2)
+    # the same product through the 256-wide pair tiles, bit for bit (same k order per output element)
+    if split_k == 1:
+        assert torch.equal(out, ops.gemm(a, w, residual=res, beta=0.5, bias=bias, tile_m=1, tile_n=256, split_k=1,
+                                         workspace=ws, cta_group=2, stream_k=2, status=st))
+
+
+def test_gemm_wide_tiles_need_a_cta_pair():
+    a = torch.randn(256, 64, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(640, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        ops.gemm(a, w, tile_m=1, tile_n=320, cta_group=1)
+    with pytest.raises(RuntimeError):
+        ops.gemm_swiglu(a, w, w, tile_m=1, tile_n=320, cta_group=2)
+
+
 @pytest.mark.parametrize("M,F,K", [(256, 128, 64), (300, 3584, 1024), (1408, 1792, 2048), (129, 264, 136)])
 @pytest.mark.parametrize("tile_n", [128, 192, 224, 256])
 def test_gemm_swiglu_cta_pair(M, F, K, tile_n):
