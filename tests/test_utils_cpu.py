@@ -59,6 +59,15 @@ def test_autotune_candidates():
             assert not (x["cta_group"] == 2 and (x["tile_m"] != 1 or M <= 128))
             assert not (sw and x["split_k"] != 1)
             assert not (x["split_k"] > 1 and x["stream_k"] == 1)
+            # tiles wider than one MMA instruction: CTA pairs only, never for the SwiGLU form, and what the
+            # launcher's planner accepts
+            if x["tile_n"] > 256:
+                assert x["cta_group"] == 2 and x["tile_m"] == 1 and not sw and x["tile_n"] <= N
+                from nanoflow_b200 import ops
+                plan = ops.gemm_plan(M, N, K, tile_m=1, tile_n=x["tile_n"], cta_group=2, split_k=1, stream_k=2)
+                assert plan["tile_n"] == x["tile_n"] and plan["stages"] >= 2
+    wide = [x["tile_n"] for x in autotune.candidates(4096, 1280, 8192, False) if x["tile_n"] > 256]
+    assert 320 in wide
 
 
 def _walk(w, W, tiles, num_kb, split_k, tail_first, q):
